@@ -1,0 +1,81 @@
+/* prism_b200 - C ABI of the B200 (sm_100a) quantized linear-layer kernels.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream (as void*, a cudaStream_t), launches on that
+ * stream, never synchronizes, never allocates, and returns a status (0 = ok, see PB_* below).  The live row count
+ * `n_rows` is a device int32 read by the kernels, so one captured CUDA graph serves any live count; rows at or past it
+ * are left untouched.  Each declaration names the interface of the reference (StartLux-Prism) it stands in for.
+ */
+#ifndef PRISM_B200_H
+#define PRISM_B200_H
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define PB_OK 0
+#define PB_BAD_ARGUMENT 1      /* null / misaligned pointer, negative size, unknown enum value */
+#define PB_UNSUPPORTED_SHAPE 2 /* a size the kernels do not take (see each function) */
+#define PB_CUDA_ERROR 3        /* a CUDA call failed: pb_last_cuda_error() has the code */
+#define PB_DEVICE_TIMEOUT 4    /* a kernel gave up a bounded wait (read with pb_device_status) */
+#define PB_TOO_LARGE 5         /* beyond a stated maximum */
+
+#define PB_EPI_BF16 0 /* out bf16 [M, N] = v */
+#define PB_EPI_ADD 1  /* out fp32 [M, N] = add_rn(out, v) */
+#define PB_EPI_I32 3  /* out int32 = the raw integer sums */
+
+#define PB_MODE_PLAIN 0
+#define PB_MODE_STORE_AMAX 1
+#define PB_MODE_USE_AMAX 2
+
+int pb_version(void);
+const char* pb_status_string(int status);
+int pb_last_cuda_error(void);
+
+/* Reads (and with reset != 0 clears) the current device's status word, which a kernel sets when a bounded wait
+ * expires.  Synchronizes the device: for tests and error paths, not for the hot path. */
+int pb_device_status(int* code, unsigned* where, int reset);
+
+/* Bytes of workspace and number of int32 counters pb_w8a8_gemm needs for a split-K product whose splits are added
+ * inside the kernel (epi 0 / 1 with split > 1).  Stands in for kernels/cuda_ext.py:22-23,139-143 (_workspace). */
+long pb_w8a8_workspace_bytes(int M, int N, int split);
+int pb_w8a8_counters(int M, int N);
+
+/* W8A8 GEMM.  Replaces torch.ops.startlux_prism.w8a8_gemm / w8a8_gemm_sk / w8a8_wgmma (csrc/w8a8_gemm.cu:794-800,
+ * csrc/w8a8_wgmma.cu:709-713) and the Triton kernel behind kernels/w8a8.py:183-231 (gemm) and :234-261 (gemm_i32).
+ *   a int8 [M, K], w int8 [N, K] (both K-contiguous, 16-byte aligned, K % 16 == 0);
+ *   gk == K: a_s fp32 [M], w_s fp32 [N];  gk == 32: a_s fp32 [M, K/32], w_s fp32 [N, K/32] (K % 128 == 0);
+ *   epi PB_EPI_BF16 / PB_EPI_ADD: out [M, N] with row stride ldo elements;
+ *   epi PB_EPI_I32: out = slots int32 [split, rows, N] (ldo = N, slot_stride = rows * N elements): split z's sums.
+ *   split > 1 with epi 0 / 1 (gk == K, M <= 64): the splits are added inside the kernel through `workspace`
+ *   (pb_w8a8_workspace_bytes) and `counters` (pb_w8a8_counters, zero before the first call; left zero).
+ * The result bits do not depend on split, on the kernel chosen or on M (batch invariance). */
+int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, void* out, long ldo,
+                 const int* n_rows, int M, int N, int K, int gk, int epi, int split, long slot_stride,
+                 void* workspace, long workspace_bytes, int* counters, int n_counters, void* stream);
+
+/* Deferred residual add.  Replaces quant.fold / _fold_kernel (kernels/quant.py:128-141, :434-457):
+ * h[r, c] = add_rn(h[r, c], mul_rn(mul_rn(float(sum_p slots[p, r, c]), a_s[r]), w_s[c])).  N % 4 == 0, 16-byte aligned. */
+int pb_fold(float* h, long ldh, const int32_t* slots, long slot_stride, int S, const float* a_s, const float* w_s,
+            const int* n_rows, int rows, int N, void* stream);
+
+/* Per-token activation quantization.  Replaces quant.rows_q8 (kernels/quant.py:287-309, :481-486; gk == K, optional
+ * SmoothQuant factors inv_s [K], tensor-parallel modes 1 / 2 with amax [rows]) and w8a8.quant_rows
+ * (kernels/w8a8.py:101-112, :264-271; gk in {32, 64, 128, 256}).  x bf16 (x_fp32 = 0) or fp32 [T, K]. */
+int pb_quant_rows(const void* x, int x_fp32, const float* inv_s, int8_t* q, float* s, const int* n_rows, int T,
+                  int K, int gk, int mode, float* amax, void* stream);
+
+/* SwiGLU + per-token quantization.  Replaces quant.swiglu_q8 (kernels/quant.py:249-284, :473-478):
+ * gu bf16 [T, 2 FF] -> q int8 [T, FF], s fp32 [T].  FF % 8 == 0. */
+int pb_swiglu_q8(const void* gu, const float* inv_s, int8_t* q, float* s, const int* n_rows, int T, int FF,
+                 int mode, float* amax, void* stream);
+
+/* W4A8 activation quantization (one scale per 256 inputs + split sums of each 32).  Replaces quant.rows_g / _store_g
+ * (kernels/quant.py:314-330, :381-411): q int8 [T, K], a fp32 [K/256, Ma], xs int8 [K/256, Ma, 16].  K % 256 == 0. */
+int pb_quant_g(const void* x, int x_fp32, int8_t* q, float* a, int8_t* xs, const int* n_rows, int T, int Ma, int K,
+               void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

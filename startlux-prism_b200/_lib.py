@@ -1,0 +1,79 @@
+"""ctypes binding of libprism_b200.so (include/prism_b200.h).  Loading fails loudly when the library is missing: the
+operators have no other implementation."""
+import ctypes
+import functools
+import os
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+PATH = os.path.join(HERE, "libprism_b200.so")
+
+_vp, _i, _l = ctypes.c_void_p, ctypes.c_int, ctypes.c_long
+_SIGS = {
+    "pb_version": ([], _i),
+    "pb_status_string": ([_i], ctypes.c_char_p),
+    "pb_last_cuda_error": ([], _i),
+    "pb_device_status": ([ctypes.POINTER(_i), ctypes.POINTER(ctypes.c_uint), _i], _i),
+    "pb_w8a8_workspace_bytes": ([_i, _i, _i], _l),
+    "pb_w8a8_counters": ([_i, _i], _i),
+    "pb_w8a8_gemm": ([_vp, _vp, _vp, _vp, _vp, _l, _vp, _i, _i, _i, _i, _i, _i, _l, _vp, _l, _vp, _i, _vp], _i),
+    "pb_fold": ([_vp, _l, _vp, _l, _i, _vp, _vp, _vp, _i, _i, _vp], _i),
+    "pb_quant_rows": ([_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp], _i),
+    "pb_swiglu_q8": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp], _i),
+    "pb_quant_g": ([_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
+}
+# entry points added by later sections of the header; bound when present in the built library
+_OPTIONAL = {}
+
+
+@functools.lru_cache(None)
+def lib():
+    if not os.path.exists(PATH):
+        raise RuntimeError(f"{PATH} is not built: run `python -m prism_b200.build` (nvcc, sm_100a).  prism_b200 has no "
+                           "fallback implementation.")
+    L = ctypes.CDLL(PATH)
+    for name, (args, res) in {**_SIGS, **_OPTIONAL}.items():
+        fn = getattr(L, name)
+        fn.argtypes, fn.restype = args, res
+    return L
+
+
+def declared_symbols():
+    return sorted({**_SIGS, **_OPTIONAL})
+
+
+class PrismError(RuntimeError):
+    def __init__(self, status, what):
+        L = lib()
+        msg = L.pb_status_string(status).decode()
+        if status == 3:
+            msg += f" (CUDA error {L.pb_last_cuda_error()})"
+        super().__init__(f"{what}: {msg} [status {status}]")
+        self.status = status
+
+
+def check(status, what):
+    if status:
+        raise PrismError(status, what)
+
+
+def ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def need_cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise RuntimeError("prism_b200 operators take CUDA tensors only (there is no CPU path)")
+
+
+def device_status(reset=True):
+    """(code, where) of the current device's status word (synchronizes)."""
+    c, w = ctypes.c_int(0), ctypes.c_uint(0)
+    check(lib().pb_device_status(ctypes.byref(c), ctypes.byref(w), int(reset)), "pb_device_status")
+    return c.value, w.value

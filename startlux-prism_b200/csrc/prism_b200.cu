@@ -1,0 +1,416 @@
+// The C ABI of the library (declared in include/prism_b200.h): argument checks, tensor-map construction, kernel
+// selection and launches.  One translation unit: the kernels are header-only templates included below.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdlib.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "../../include/prism_b200.h"
+#include "common.cuh"
+#include "quant.cuh"
+#include "w8a8_gemm.cuh"
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+int cuda_fail(cudaError_t e) {
+    g_last_cuda_error = (int)e;
+    return PB_CUDA_ERROR;
+}
+#define PB_CUDA(call)                                 \
+    do {                                              \
+        cudaError_t e__ = (call);                     \
+        if (e__ != cudaSuccess) return cuda_fail(e__); \
+    } while (0)
+
+bool aligned16(const void* p) { return ((uintptr_t)p & 15) == 0; }
+
+// ------------------------------------------------------------------------------------------------- tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr;
+    uint64_t inner, outer, stride;
+    uint32_t box_inner, box_outer, kind;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && inner == o.inner && outer == o.outer && stride == o.stride && box_inner == o.box_inner &&
+               box_outer == o.box_outer && kind == o.kind;
+    }
+};
+struct MapHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = (size_t)k.ptr;
+        auto mix = [&](uint64_t v) { h ^= v + 0x9e3779b97f4a7c15ull + (h << 6) + (h >> 2); };
+        mix(k.inner); mix(k.outer); mix(k.stride); mix(k.box_inner); mix(k.box_outer); mix(k.kind);
+        return h;
+    }
+};
+
+// A 2-D row-major matrix [outer, inner] of 1-byte (kind 0, 128-byte swizzle) or 4-byte (kind 1, no swizzle) elements,
+// loaded in boxes of [box_outer, box_inner].  Maps are cached by (pointer, shape, box) and passed to kernels by value,
+// so a captured CUDA graph keeps the maps of its capture.
+int tensor_map(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t stride_bytes,
+               uint32_t box_inner, uint32_t box_outer, uint32_t kind) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
+    MapKey key{ptr, inner, outer, stride_bytes, box_inner, box_outer, kind};
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) {
+            *out = it->second;
+            return PB_OK;
+        }
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return PB_CUDA_ERROR;
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {stride_bytes};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(out, kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                    const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    kind == 0 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        g_last_cuda_error = (int)r;
+        return PB_CUDA_ERROR;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache.size() > 8192) cache.clear();
+    cache[key] = *out;
+    return PB_OK;
+}
+
+int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <typename Kernel>
+int set_smem(Kernel k, int bytes) {
+    PB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    return PB_OK;
+}
+
+// ------------------------------------------------------------------------------------------------- W8A8 launches
+template <int BN, int EPI>
+int launch_tile(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, void* out, long ldo,
+                const int* n_rows, int M, int N, int K, cudaStream_t st) {
+    using C = w8a8::TileCfg<BN>;
+    CUtensorMap ta, tw;
+    int rc;
+    if ((rc = tensor_map(&ta, a, K, M, K, w8a8::BK, w8a8::BM, 0))) return rc;
+    if ((rc = tensor_map(&tw, w, K, N, K, w8a8::BK, BN, 0))) return rc;
+    auto kern = w8a8::w8a8_tile_kernel<BN, EPI>;
+    static bool configured = false;
+    if (!configured) {
+        if ((rc = set_smem(kern, C::SMEM))) return rc;
+        configured = true;
+    }
+    const int es = EPI == w8a8::EPI_BF16 ? 2 : 4;
+    const int vec_ok = aligned16(out) && (ldo * es) % 16 == 0;
+    const int tiles = ((M + 127) / 128) * ((N + BN - 1) / BN);
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    kern<<<grid, 192, C::SMEM, st>>>(ta, tw, a_s, w_s, out, ldo, n_rows, M, N, K, vec_ok);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+template <int NB, bool GROUPED>
+int launch_swap(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, w8a8::SwapArgs p, int split,
+                cudaStream_t st) {
+    using C = w8a8::SwapCfg<NB, GROUPED>;
+    CUtensorMap tw, tx, tsw, tsa;
+    int rc;
+    if ((rc = tensor_map(&tw, w, p.K, p.N, p.K, w8a8::BK, w8a8::BM, 0))) return rc;
+    if ((rc = tensor_map(&tx, a, p.K, p.M, p.K, w8a8::BK, NB, 0))) return rc;
+    if (GROUPED) {
+        const uint64_t G = p.K / 32;
+        if ((rc = tensor_map(&tsw, w_s, G, p.N, G * 4, 4, w8a8::BM, 1))) return rc;
+        if ((rc = tensor_map(&tsa, a_s, G, p.M, G * 4, 4, NB, 1))) return rc;
+    } else {
+        tsw = tw;
+        tsa = tx;
+    }
+    auto kern = w8a8::w8a8_swap_kernel<NB, GROUPED>;
+    static bool configured = false;
+    if (!configured) {
+        if ((rc = set_smem(kern, C::SMEM))) return rc;
+        configured = true;
+    }
+    dim3 grid((p.N + 127) / 128, split, (p.M + NB - 1) / NB);
+    kern<<<grid, 192, C::SMEM, st>>>(tw, tx, tsw, tsa, p);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+template <bool GROUPED>
+int launch_swap_nb(int nb, const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, w8a8::SwapArgs p,
+                   int split, cudaStream_t st) {
+    switch (nb) {
+        case 8: return launch_swap<8, GROUPED>(a, a_s, w, w_s, p, split, st);
+        case 16: return launch_swap<16, GROUPED>(a, a_s, w, w_s, p, split, st);
+        case 32: return launch_swap<32, GROUPED>(a, a_s, w, w_s, p, split, st);
+        default: return launch_swap<64, GROUPED>(a, a_s, w, w_s, p, split, st);
+    }
+}
+
+int pick_nb(int M) { return M <= 8 ? 8 : M <= 16 ? 16 : M <= 32 ? 32 : 64; }
+
+bool div_full() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("PRISM_B200_QUANT_DIV");
+        v = (e && e[0] == 'f') ? 1 : 0;   // "full": div.full.f32 instead of the IEEE division
+    }
+    return v == 1;
+}
+
+template <int VPT>
+void launch_rows(bool bf16, bool full, int threads, const void* x, const float* inv_s, int8_t* q, float* s,
+                        const int* n_rows, int T, int K, int mode, float* amax, cudaStream_t st) {
+    if (bf16) {
+        if (full) quant::rows_q8_kernel<VPT, true, true><<<T, threads, 0, st>>>(x, inv_s, q, s, n_rows, K, mode, amax);
+        else quant::rows_q8_kernel<VPT, true, false><<<T, threads, 0, st>>>(x, inv_s, q, s, n_rows, K, mode, amax);
+    } else {
+        if (full) quant::rows_q8_kernel<VPT, false, true><<<T, threads, 0, st>>>(x, inv_s, q, s, n_rows, K, mode, amax);
+        else quant::rows_q8_kernel<VPT, false, false><<<T, threads, 0, st>>>(x, inv_s, q, s, n_rows, K, mode, amax);
+    }
+}
+
+
+}  // namespace
+
+extern "C" {
+
+int pb_version(void) { return 1; }
+
+const char* pb_status_string(int s) {
+    switch (s) {
+        case PB_OK: return "ok";
+        case PB_BAD_ARGUMENT: return "bad argument (null or misaligned pointer, negative size, unknown enum)";
+        case PB_UNSUPPORTED_SHAPE: return "unsupported shape";
+        case PB_CUDA_ERROR: return "a CUDA call failed";
+        case PB_DEVICE_TIMEOUT: return "a kernel gave up a bounded wait";
+        case PB_TOO_LARGE: return "size beyond a stated maximum";
+    }
+    return "unknown status";
+}
+
+int pb_last_cuda_error(void) { return g_last_cuda_error; }
+
+int pb_device_status(int* code, unsigned* where, int reset) {
+    int c = 0;
+    unsigned w = 0;
+    PB_CUDA(cudaDeviceSynchronize());
+    PB_CUDA(cudaMemcpyFromSymbol(&c, g_pb_device_status, sizeof(int)));
+    PB_CUDA(cudaMemcpyFromSymbol(&w, g_pb_device_status_where, sizeof(unsigned)));
+    if (code) *code = c;
+    if (where) *where = w;
+    if (reset && (c || w)) {
+        int z = 0;
+        unsigned zw = 0;
+        PB_CUDA(cudaMemcpyToSymbol(g_pb_device_status, &z, sizeof(int)));
+        PB_CUDA(cudaMemcpyToSymbol(g_pb_device_status_where, &zw, sizeof(unsigned)));
+    }
+    return PB_OK;
+}
+
+long pb_w8a8_workspace_bytes(int M, int N, int split) {
+    if (M <= 0 || N <= 0 || split <= 1) return 0;
+    const int nb = pick_nb(M);
+    const long tiles = (long)((N + 127) / 128) * ((M + nb - 1) / nb);
+    return (long)split * tiles * nb * 128 * 4;
+}
+
+int pb_w8a8_counters(int M, int N) {
+    if (M <= 0 || N <= 0) return 0;
+    const int nb = pick_nb(M);
+    return ((N + 127) / 128) * ((M + nb - 1) / nb);
+}
+
+int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, void* out, long ldo,
+                 const int* n_rows, int M, int N, int K, int gk, int epi, int split, long slot_stride,
+                 void* workspace, long workspace_bytes, int* counters, int n_counters, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!a || !w || !out || !n_rows || M <= 0 || N <= 0 || K <= 0 || split < 1) return PB_BAD_ARGUMENT;
+    if (epi != PB_EPI_BF16 && epi != PB_EPI_ADD && epi != PB_EPI_I32) return PB_BAD_ARGUMENT;
+    if (epi != PB_EPI_I32 && (!a_s || !w_s)) return PB_BAD_ARGUMENT;
+    if (!aligned16(a) || !aligned16(w)) return PB_BAD_ARGUMENT;
+    if (K % 16) return PB_UNSUPPORTED_SHAPE;
+    if (ldo < N) return PB_BAD_ARGUMENT;
+    const int KB = (K + 127) / 128;
+    if (gk == 32) {
+        // Q8_0's own scale per 32 inputs: fp32 partial sums per group, added in group order (no K split, no int32 out)
+        if (epi == PB_EPI_I32 || split != 1) return PB_UNSUPPORTED_SHAPE;
+        if (K % 128 || !aligned16(a_s) || !aligned16(w_s)) return PB_UNSUPPORTED_SHAPE;
+        w8a8::SwapArgs p{a_s, w_s, out, ldo, 0, nullptr, nullptr, n_rows, M, N, K, KB, epi, w8a8::MODE_DIRECT};
+        return launch_swap_nb<true>(pick_nb(M), a, a_s, w, w_s, p, 1, st);
+    }
+    if (gk != K) return PB_UNSUPPORTED_SHAPE;
+    if (M > 64) {
+        if (epi == PB_EPI_I32) {
+            // split z of K is a product over a K slice: run the tile kernel once per slice on offset pointers
+            if (split > 1) {
+                if (K % (split * 128)) return PB_UNSUPPORTED_SHAPE;
+                return PB_UNSUPPORTED_SHAPE;  // many rows never split K (tp.SPLIT_ROWS); callers pass split = 1
+            }
+            return N <= 128 ? launch_tile<128, w8a8::EPI_I32>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st)
+                            : launch_tile<256, w8a8::EPI_I32>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st);
+        }
+        if (split != 1) return PB_UNSUPPORTED_SHAPE;
+        if (epi == PB_EPI_BF16)
+            return N <= 128 ? launch_tile<128, w8a8::EPI_BF16>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st)
+                            : launch_tile<256, w8a8::EPI_BF16>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st);
+        return N <= 128 ? launch_tile<128, w8a8::EPI_ADD>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st)
+                        : launch_tile<256, w8a8::EPI_ADD>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st);
+    }
+    // few rows: operands swapped, K split over blockIdx.y
+    if (split > KB) split = KB;
+    int kbs = (KB + split - 1) / split;
+    split = (KB + kbs - 1) / kbs;                       // every slice non-empty
+    const int nb = pick_nb(M);
+    w8a8::SwapArgs p{a_s, w_s, out, ldo, slot_stride, (int32_t*)workspace, counters, n_rows, M, N, K, kbs, epi, 0};
+    if (epi == PB_EPI_I32) {
+        p.mode = w8a8::MODE_SLOTS;
+        if (split > 1 && slot_stride < (long)M * N) return PB_BAD_ARGUMENT;
+    } else if (split == 1) {
+        p.mode = w8a8::MODE_DIRECT;
+    } else {
+        p.mode = w8a8::MODE_WS;
+        if (!workspace || !counters) return PB_BAD_ARGUMENT;
+        if (workspace_bytes < pb_w8a8_workspace_bytes(M, N, split) || n_counters < pb_w8a8_counters(M, N))
+            return PB_TOO_LARGE;
+    }
+    return launch_swap_nb<false>(nb, a, a_s, w, w_s, p, split, st);
+}
+
+int pb_fold(float* h, long ldh, const int32_t* slots, long slot_stride, int S, const float* a_s, const float* w_s,
+            const int* n_rows, int rows, int N, void* stream) {
+    if (!h || !slots || !a_s || !w_s || !n_rows || rows <= 0 || N <= 0 || S < 1 || ldh < N) return PB_BAD_ARGUMENT;
+    if ((N % 4 == 0) && (!aligned16(h) || !aligned16(slots) || !aligned16(w_s) || (ldh % 4) || (slot_stride % 4)))
+        return PB_BAD_ARGUMENT;
+    dim3 grid(((N + 3) / 4 + 255) / 256, rows);
+    quant::fold_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(h, ldh, slots, slot_stride, S, a_s, w_s, n_rows, N);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+int pb_quant_rows(const void* x, int x_fp32, const float* inv_s, int8_t* q, float* s, const int* n_rows, int T,
+                  int K, int gk, int mode, float* amax, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!x || !q || !s || !n_rows || T <= 0 || K <= 0 || gk <= 0 || K % gk) return PB_BAD_ARGUMENT;
+    if (mode < 0 || mode > 2 || (mode != 0 && !amax)) return PB_BAD_ARGUMENT;
+    const bool bf16 = !x_fp32, full = div_full();
+    if (gk != K) {
+        if (inv_s || mode != 0) return PB_UNSUPPORTED_SHAPE;
+        if (gk != 32 && gk != 64 && gk != 128 && gk != 256) return PB_UNSUPPORTED_SHAPE;
+        if (!aligned16(x) || ((uintptr_t)q & 7)) return PB_BAD_ARGUMENT;
+        dim3 grid((K / 8 + 255) / 256, T);
+        if (bf16) {
+            if (full) quant::quant_groups_kernel<true, true><<<grid, 256, 0, st>>>(x, q, s, n_rows, K, gk);
+            else quant::quant_groups_kernel<true, false><<<grid, 256, 0, st>>>(x, q, s, n_rows, K, gk);
+        } else {
+            if (full) quant::quant_groups_kernel<false, true><<<grid, 256, 0, st>>>(x, q, s, n_rows, K, gk);
+            else quant::quant_groups_kernel<false, false><<<grid, 256, 0, st>>>(x, q, s, n_rows, K, gk);
+        }
+        PB_CUDA(cudaGetLastError());
+        return PB_OK;
+    }
+    const bool fast = K % 8 == 0 && K <= 32768 && aligned16(x) && !((uintptr_t)q & 7) && (!inv_s || aligned16(inv_s));
+    if (!fast) {
+        if (bf16) {
+            if (full) quant::rows_q8_generic_kernel<true, true><<<T, 256, 0, st>>>(x, inv_s, q, s, n_rows, K, mode, amax);
+            else quant::rows_q8_generic_kernel<true, false><<<T, 256, 0, st>>>(x, inv_s, q, s, n_rows, K, mode, amax);
+        } else {
+            if (full) quant::rows_q8_generic_kernel<false, true><<<T, 256, 0, st>>>(x, inv_s, q, s, n_rows, K, mode, amax);
+            else quant::rows_q8_generic_kernel<false, false><<<T, 256, 0, st>>>(x, inv_s, q, s, n_rows, K, mode, amax);
+        }
+        PB_CUDA(cudaGetLastError());
+        return PB_OK;
+    }
+    const int nvec = K / 8;
+    const int threads = nvec <= 1024 ? 128 : 256;
+    const int vpt = (nvec + threads - 1) / threads;
+#define PB_ROWS(V) launch_rows<V>(bf16, full, threads, x, inv_s, q, s, n_rows, T, K, mode, amax, st)
+    if (vpt <= 1) PB_ROWS(1);
+    else if (vpt <= 2) PB_ROWS(2);
+    else if (vpt <= 3) PB_ROWS(3);
+    else if (vpt <= 4) PB_ROWS(4);
+    else if (vpt <= 5) PB_ROWS(5);
+    else if (vpt <= 6) PB_ROWS(6);
+    else if (vpt <= 8) PB_ROWS(8);
+    else if (vpt <= 10) PB_ROWS(10);
+    else if (vpt <= 12) PB_ROWS(12);
+    else PB_ROWS(16);
+#undef PB_ROWS
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+int pb_swiglu_q8(const void* gu, const float* inv_s, int8_t* q, float* s, const int* n_rows, int T, int FF, int mode,
+                 float* amax, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!gu || !q || !s || !n_rows || T <= 0 || FF <= 0) return PB_BAD_ARGUMENT;
+    if (mode < 0 || mode > 2 || (mode != 0 && !amax)) return PB_BAD_ARGUMENT;
+    if (FF % 8 || FF > 32768 || !aligned16(gu) || ((uintptr_t)q & 7)) return PB_UNSUPPORTED_SHAPE;
+    const bool full = div_full();
+    const int nvec = FF / 8;
+    const int threads = nvec <= 1024 ? 128 : 256;
+    const int vpt = (nvec + threads - 1) / threads;
+    const __nv_bfloat16* g = (const __nv_bfloat16*)gu;
+#define PB_SW(V)                                                                                              \
+    do {                                                                                                      \
+        if (full) quant::swiglu_q8_kernel<V, true><<<T, threads, 0, st>>>(g, inv_s, q, s, n_rows, FF, mode, amax); \
+        else quant::swiglu_q8_kernel<V, false><<<T, threads, 0, st>>>(g, inv_s, q, s, n_rows, FF, mode, amax);     \
+    } while (0)
+    if (vpt <= 1) PB_SW(1);
+    else if (vpt <= 2) PB_SW(2);
+    else if (vpt <= 4) PB_SW(4);
+    else if (vpt <= 6) PB_SW(6);
+    else if (vpt <= 9) PB_SW(9);
+    else if (vpt <= 12) PB_SW(12);
+    else PB_SW(16);
+#undef PB_SW
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+int pb_quant_g(const void* x, int x_fp32, int8_t* q, float* a, int8_t* xs, const int* n_rows, int T, int Ma, int K,
+               void* stream) {
+    if (!x || !q || !a || !xs || !n_rows || T <= 0 || K <= 0 || Ma < T) return PB_BAD_ARGUMENT;
+    if (K % 256 || !aligned16(x) || ((uintptr_t)q & 7)) return PB_UNSUPPORTED_SHAPE;
+    dim3 grid((K / 256 + 7) / 8, T);
+    if (x_fp32) quant::quant_g_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(x, q, a, xs, n_rows, Ma, K);
+    else quant::quant_g_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(x, q, a, xs, n_rows, Ma, K);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+}  // extern "C"

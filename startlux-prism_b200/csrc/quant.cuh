@@ -1,0 +1,283 @@
+// Producers of quantized GEMM inputs and the deferred residual add.  All HBM-bound: one pass over the input with
+// 128-bit loads, the row kept in registers between the maximum and the rounding, 128-bit stores of the int8 values.
+//
+//   rows_q8    x bf16/fp32 [T, K] (* inv_s[k]) -> int8 [T, K] + one fp32 scale per row   (kernels/quant.py:287-309)
+//   quant_rows the same with one scale per group of gk inputs                             (kernels/w8a8.py:101-112)
+//   swiglu_q8  gu bf16 [T, 2 FF] -> silu(gate) * up (* inv_s) -> int8 [T, FF] + scale      (kernels/quant.py:249-284)
+//   quant_g    x -> int8 + one scale per 256 inputs + split sums of each 32 (W4A8)         (kernels/quant.py:314-330)
+//   fold       h += (float(sum of int32 slots) * a_s[row]) * w_s[col]                      (kernels/quant.py:128-141)
+//
+// Rounding contract: scale = max(amax, 1e-10) / 127 and q = rint(y / scale) with IEEE divisions (__fdiv_rn), half to
+// even.  PB_DIV_FULL selects the approximate full-range division (div.full.f32) for both instead.
+#pragma once
+#include "common.cuh"
+
+namespace quant {
+
+constexpr int MODE_PLAIN = 0;      // the row's own maximum
+constexpr int MODE_STORE_AMAX = 1; // also store the row's maximum (tensor parallel, before the max all-reduce)
+constexpr int MODE_USE_AMAX = 2;   // quantize with max(amax[t], own) (after it)
+
+template <bool FULL>
+__device__ __forceinline__ float fdiv(float a, float b) {
+    if (FULL) {
+        float r;
+        asm("div.full.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+        return r;
+    }
+    return __fdiv_rn(a, b);
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide maximum for up to 1024 threads; `red` is a 32-float shared array.
+__device__ __forceinline__ float block_max(float v, float* red) {
+    v = warp_max(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = lane < nw ? red[lane] : 0.0f;
+    r = warp_max(r);
+    __syncthreads();
+    return r;
+}
+
+__device__ __forceinline__ uint32_t pack4(int a, int b, int c, int d) {
+    return (uint32_t)(a & 0xff) | ((uint32_t)(b & 0xff) << 8) | ((uint32_t)(c & 0xff) << 16) | ((uint32_t)d << 24);
+}
+
+// Loads 8 consecutive inputs as fp32 (bf16: one 128-bit load; fp32: two).
+template <bool BF16>
+__device__ __forceinline__ void load8(const void* x, long idx, float (&v)[8]) {
+    if (BF16) {
+        const uint4 u = __ldg((const uint4*)((const __nv_bfloat16*)x + idx));
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[2 * i] = __uint_as_float(w[i] << 16);
+            v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    } else {
+        const float4 a = __ldg((const float4*)((const float*)x + idx));
+        const float4 b = __ldg((const float4*)((const float*)x + idx + 4));
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
+        v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+}
+
+template <bool FULL>
+__device__ __forceinline__ uint2 quant8(const float (&v)[8], float scale) {
+    int q[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) q[i] = __float2int_rn(fdiv<FULL>(v[i], scale));
+    return make_uint2(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]));
+}
+
+// ------------------------------------------------------------------------------------------------- rows_q8
+// One CTA per row, VPT vectors of 8 inputs per thread held in registers (K <= 8 * VPT * blockDim).
+template <int VPT, bool BF16, bool FULL>
+__global__ void __launch_bounds__(256)
+rows_q8_kernel(const void* __restrict__ x, const float* __restrict__ inv_s, int8_t* __restrict__ q,
+               float* __restrict__ s, const int* __restrict__ n_rows, int K, int mode, float* __restrict__ amax_io) {
+    __shared__ float red[32];
+    const long t = blockIdx.x;
+    if (t >= *n_rows) return;
+    const int nvec = K >> 3;
+    float v[VPT][8];
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < nvec) {
+            load8<BF16>(x, t * K + (long)c * 8, v[i]);
+            if (inv_s) {
+                const float4 a = __ldg((const float4*)(inv_s + c * 8)), b = __ldg((const float4*)(inv_s + c * 8 + 4));
+                v[i][0] = __fmul_rn(v[i][0], a.x); v[i][1] = __fmul_rn(v[i][1], a.y);
+                v[i][2] = __fmul_rn(v[i][2], a.z); v[i][3] = __fmul_rn(v[i][3], a.w);
+                v[i][4] = __fmul_rn(v[i][4], b.x); v[i][5] = __fmul_rn(v[i][5], b.y);
+                v[i][6] = __fmul_rn(v[i][6], b.z); v[i][7] = __fmul_rn(v[i][7], b.w);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[i][j]));
+        }
+    }
+    amax = block_max(amax, red);
+    if (mode == MODE_STORE_AMAX && threadIdx.x == 0) amax_io[t] = amax;
+    if (mode == MODE_USE_AMAX) amax = fmaxf(amax_io[t], amax);
+    const float scale = fdiv<FULL>(fmaxf(amax, 1e-10f), 127.0f);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < nvec) *(uint2*)(q + t * K + (long)c * 8) = quant8<FULL>(v[i], scale);
+    }
+    if (threadIdx.x == 0) s[t] = scale;
+}
+
+// Any K (no alignment assumed), two passes over the row (the second hits L2): the fallback for odd shapes.
+template <bool BF16, bool FULL>
+__global__ void __launch_bounds__(256)
+rows_q8_generic_kernel(const void* __restrict__ x, const float* __restrict__ inv_s, int8_t* __restrict__ q,
+                       float* __restrict__ s, const int* __restrict__ n_rows, int K, int mode,
+                       float* __restrict__ amax_io) {
+    __shared__ float red[32];
+    const long t = blockIdx.x;
+    if (t >= *n_rows) return;
+    auto val = [&](int k) {
+        float y = BF16 ? __bfloat162float(((const __nv_bfloat16*)x)[t * K + k]) : ((const float*)x)[t * K + k];
+        return inv_s ? __fmul_rn(y, inv_s[k]) : y;
+    };
+    float amax = 0.0f;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) amax = fmaxf(amax, fabsf(val(k)));
+    amax = block_max(amax, red);
+    if (mode == MODE_STORE_AMAX && threadIdx.x == 0) amax_io[t] = amax;
+    if (mode == MODE_USE_AMAX) amax = fmaxf(amax_io[t], amax);
+    const float scale = fdiv<FULL>(fmaxf(amax, 1e-10f), 127.0f);
+    for (int k = threadIdx.x; k < K; k += blockDim.x) q[t * K + k] = (int8_t)__float2int_rn(fdiv<FULL>(val(k), scale));
+    if (threadIdx.x == 0) s[t] = scale;
+}
+
+// ------------------------------------------------------------------------------------------------- quant_rows (groups)
+// One scale per gk inputs (gk = 32, 64, 128 or 256): a thread holds 8 inputs, gk / 8 neighbouring lanes share a group.
+template <bool BF16, bool FULL>
+__global__ void __launch_bounds__(256)
+quant_groups_kernel(const void* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ s,
+                    const int* __restrict__ n_rows, int K, int gk) {
+    const long t = blockIdx.y;
+    if (t >= *n_rows) return;
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;      // vector of 8 inputs
+    const bool in = c < (K >> 3);
+    float v[8];
+    float amax = 0.0f;
+    if (in) {
+        load8<BF16>(x, t * K + (long)c * 8, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+    }
+    for (int o = 1; o < (gk >> 3); o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = fdiv<FULL>(fmaxf(amax, 1e-10f), 127.0f);
+    if (in) {
+        *(uint2*)(q + t * K + (long)c * 8) = quant8<FULL>(v, scale);
+        if ((c & ((gk >> 3) - 1)) == 0) s[t * (K / gk) + c / (gk >> 3)] = scale;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------- swiglu_q8
+// y = g / (1 + exp(-g)) * u * inv_s[c] (the reference's expression order, kernels/quant.py:256), then rows_q8's rounding.
+__device__ __forceinline__ float swiglu(float g, float u) { return __fmul_rn(__fdiv_rn(g, 1.0f + __expf(-g)), u); }
+
+template <int VPT, bool FULL>
+__global__ void __launch_bounds__(256)
+swiglu_q8_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ inv_s, int8_t* __restrict__ q,
+                 float* __restrict__ s, const int* __restrict__ n_rows, int FF, int mode, float* __restrict__ amax_io) {
+    __shared__ float red[32];
+    const long t = blockIdx.x;
+    if (t >= *n_rows) return;
+    const int nvec = FF >> 3;
+    const __nv_bfloat16* row = gu + t * 2 * FF;
+    float v[VPT][8];
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < nvec) {
+            float g[8], u[8];
+            load8<true>(row, (long)c * 8, g);
+            load8<true>(row + FF, (long)c * 8, u);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float y = swiglu(g[j], u[j]);
+                if (inv_s) y = __fmul_rn(y, __ldg(inv_s + c * 8 + j));
+                v[i][j] = y;
+                amax = fmaxf(amax, fabsf(y));
+            }
+        }
+    }
+    amax = block_max(amax, red);
+    if (mode == MODE_STORE_AMAX && threadIdx.x == 0) amax_io[t] = amax;
+    if (mode == MODE_USE_AMAX) amax = fmaxf(amax_io[t], amax);
+    const float scale = fdiv<FULL>(fmaxf(amax, 1e-10f), 127.0f);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < nvec) *(uint2*)(q + t * FF + (long)c * 8) = quant8<FULL>(v[i], scale);
+    }
+    if (threadIdx.x == 0) s[t] = scale;
+}
+
+// ------------------------------------------------------------------------------------------------- quant_g (W4A8)
+// One warp per 256 inputs of a row: lane l holds inputs 8 l .. 8 l + 7, so 4 neighbouring lanes make a group of 32.
+// Writes q int8 [T, K], a fp32 [K/256, Ma] and xs int8 [K/256, Ma, 16] (eight S & 63 then eight S >> 6), IEEE division.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+quant_g_kernel(const void* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ a, int8_t* __restrict__ xs,
+               const int* __restrict__ n_rows, int Ma, int K) {
+    const long t = blockIdx.y;
+    if (t >= *n_rows) return;
+    const int lane = threadIdx.x & 31;
+    const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);     // super-block
+    if (b >= (K >> 8)) return;
+    float v[8];
+    load8<BF16>(x, t * K + (long)b * 256 + lane * 8, v);
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+    amax = warp_max(amax);
+    const float scale = __fdiv_rn(fmaxf(amax, 1e-10f), 127.0f);
+    int qi[8], S = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        qi[j] = __float2int_rn(__fdiv_rn(v[j], scale));
+        S += qi[j];
+    }
+    *(uint2*)(q + t * K + (long)b * 256 + lane * 8) =
+        make_uint2(pack4(qi[0], qi[1], qi[2], qi[3]), pack4(qi[4], qi[5], qi[6], qi[7]));
+    S += __shfl_xor_sync(0xffffffffu, S, 1);
+    S += __shfl_xor_sync(0xffffffffu, S, 2);
+    if (lane == 0) a[(long)b * Ma + t] = scale;
+    if ((lane & 3) == 0) {
+        int8_t* o = xs + ((long)b * Ma + t) * 16 + (lane >> 2);
+        o[0] = (int8_t)(S & 63);
+        o[8] = (int8_t)(S >> 6);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------- fold
+// h[r, c] = add_rn(h, mul_rn(mul_rn(float(sum_p slots[p, r, c]), a_s[r]), w_s[c])); 4 columns per thread.
+__global__ void __launch_bounds__(256)
+fold_kernel(float* __restrict__ h, long ldh, const int32_t* __restrict__ slots, long slot_stride, int S,
+            const float* __restrict__ a_s, const float* __restrict__ w_s, const int* __restrict__ n_rows, int N) {
+    const long r = blockIdx.y;
+    if (r >= *n_rows) return;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (c >= N) return;
+    const float sa = a_s[r];
+    if (c + 4 <= N && (N & 3) == 0 && (ldh & 3) == 0) {
+        int4 tot = __ldcs((const int4*)(slots + r * N + c));
+        for (int p = 1; p < S; ++p) {
+            const int4 v = __ldcs((const int4*)(slots + p * slot_stride + r * N + c));
+            tot.x += v.x; tot.y += v.y; tot.z += v.z; tot.w += v.w;
+        }
+        const float4 sw = __ldg((const float4*)(w_s + c));
+        float4 o = *(float4*)(h + r * ldh + c);
+        o.x = __fadd_rn(o.x, scale2(tot.x, sa, sw.x));
+        o.y = __fadd_rn(o.y, scale2(tot.y, sa, sw.y));
+        o.z = __fadd_rn(o.z, scale2(tot.z, sa, sw.z));
+        o.w = __fadd_rn(o.w, scale2(tot.w, sa, sw.w));
+        *(float4*)(h + r * ldh + c) = o;
+    } else {
+        for (int j = c; j < N && j < c + 4; ++j) {
+            int tot = 0;
+            for (int p = 0; p < S; ++p) tot += slots[p * slot_stride + r * N + j];
+            h[r * ldh + j] = __fadd_rn(h[r * ldh + j], scale2(tot, sa, w_s[j]));
+        }
+    }
+}
+
+}  // namespace quant

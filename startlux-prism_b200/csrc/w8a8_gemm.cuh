@@ -1,0 +1,578 @@
+// W8A8 GEMMs on the sm_100a tensor cores: int8 x int8 -> int32 in tensor memory (tcgen05.mma kind::i8), operand
+// tiles staged in shared memory by TMA (128-byte swizzle, K-major), warp-specialised: one TMA thread, one MMA thread,
+// four epilogue warps that read the accumulators with tcgen05.ld.
+//
+// Numerics (the reference's contract, kernels/w8a8.py:14-17,76,85; csrc/w8a8_gemm.cu:334-339,370-371): the integer
+// sum over K (or over one scale group) is exact; then v = mul_rn(mul_rn(float(acc), s_a[m]), s_w[n]); epilogue 1 adds
+// with add_rn.  No fused multiply-add anywhere in an epilogue, so every tile shape and K split gives the same bits.
+//
+// Two kernels:
+//   w8a8_tile_kernel  many rows (prefill): the activation tile is the MMA's M operand (128 rows), the weight tile its
+//                     N operand (BN rows); persistent over output tiles, two accumulator buffers in tensor memory so
+//                     a tile's epilogue overlaps the next tile's main loop.  One scale group (gk == K).
+//   w8a8_swap_kernel  few rows (decode) and per-32 scale groups: operands swapped, the weight tile (128 rows) is the
+//                     MMA's M operand so every tensor-memory lane holds an output column, the activation rows (8..64)
+//                     are its N.  Splits K over blockIdx.y: int32 partial sums go to the caller's slots (deferred
+//                     residual add), or to a workspace where the last CTA of a tile adds them (exact) and runs the
+//                     epilogue.  With GROUPED each K = 32 step writes its own accumulator columns and the epilogue
+//                     warps scale and add them in fp32 in group order (Q8_0's own per-32 scales, kernels/w8a8.py:64-76).
+#pragma once
+#include "common.cuh"
+
+namespace w8a8 {
+
+constexpr int BM = 128;        // MMA M: rows of the operand that owns the tensor-memory lanes
+constexpr int BK = 128;        // bytes (= int8 values) of K per pipeline stage: one 128-byte swizzle row
+constexpr int EPI_BF16 = 0;    // out bf16 [M, N] = v
+constexpr int EPI_ADD = 1;     // out fp32 [M, N] = add_rn(out, v)
+constexpr int EPI_I32 = 3;     // out int32 [M, N] = acc (no scales)
+
+struct Aux {                   // shared-memory control block placed after the stages
+    uint64_t full[12];
+    uint64_t empty[12];
+    uint64_t tfull[4];
+    uint64_t tempty[4];
+    uint32_t tmem_base;
+    int abort_flag;
+    int is_last;
+    int pad;
+};
+
+__device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
+    return (uint8_t*)(((uintptr_t)p + 1023) & ~(uintptr_t)1023);
+}
+
+// After an abort the producer gives every armed stage a bounded time to land before the CTA may exit (shared memory
+// must not be handed to another CTA with a bulk copy still writing into it).
+__device__ __forceinline__ void drain_armed(Aux* aux, int stages, const uint32_t* armed_parity, uint32_t armed_mask) {
+    unsigned long long t0 = global_timer_ns();
+    for (int s = 0; s < stages; ++s) {
+        if (!(armed_mask >> s & 1)) continue;
+        while (!mbar_test(smem_u32(&aux->full[s]), armed_parity[s])) {
+            if (global_timer_ns() - t0 > PB_WAIT_NS) return;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------- epilogue stores
+template <int EPI>
+__device__ __forceinline__ void store_row32(void* out, long ldo, long row, int col0, int ncols_ok, bool vec_ok,
+                                            const uint32_t (&r)[32], float sa, const float* sw) {
+    // One thread: 32 consecutive columns [col0, col0 + 32) of one output row; ncols_ok = columns inside N.
+    if (EPI == EPI_BF16) {
+        __nv_bfloat16* p = (__nv_bfloat16*)out + row * ldo + col0;
+        if (vec_ok && ncols_ok == 32) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    float x0 = scale2((int)r[v * 8 + 2 * j], sa, sw[v * 8 + 2 * j]);
+                    float x1 = scale2((int)r[v * 8 + 2 * j + 1], sa, sw[v * 8 + 2 * j + 1]);
+                    __nv_bfloat162 b = __floats2bfloat162_rn(x0, x1);
+                    w[j] = *(uint32_t*)&b;
+                }
+                *(uint4*)(p + v * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < ncols_ok) p[j] = __float2bfloat16_rn(scale2((int)r[j], sa, sw[j]));
+        }
+    } else if (EPI == EPI_ADD) {
+        float* p = (float*)out + row * ldo + col0;
+        if (vec_ok && ncols_ok == 32) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v) {
+                float4 o = *(float4*)(p + v * 4);
+                o.x = __fadd_rn(o.x, scale2((int)r[v * 4 + 0], sa, sw[v * 4 + 0]));
+                o.y = __fadd_rn(o.y, scale2((int)r[v * 4 + 1], sa, sw[v * 4 + 1]));
+                o.z = __fadd_rn(o.z, scale2((int)r[v * 4 + 2], sa, sw[v * 4 + 2]));
+                o.w = __fadd_rn(o.w, scale2((int)r[v * 4 + 3], sa, sw[v * 4 + 3]));
+                *(float4*)(p + v * 4) = o;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < ncols_ok) p[j] = __fadd_rn(p[j], scale2((int)r[j], sa, sw[j]));
+        }
+    } else {
+        int32_t* p = (int32_t*)out + row * ldo + col0;
+        if (vec_ok && ncols_ok == 32) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+                *(uint4*)(p + v * 4) = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < ncols_ok) p[j] = (int32_t)r[j];
+        }
+    }
+}
+
+// ================================================================================================= tile kernel
+template <int BN>
+struct TileCfg {
+    static constexpr int STAGES = (BN == 256) ? 4 : 6;
+    static constexpr int A_BYTES = BM * BK;
+    static constexpr int W_BYTES = BN * BK;
+    static constexpr int STAGE_BYTES = A_BYTES + W_BYTES;
+    static constexpr int ACC_COLS = 2 * BN;                            // two accumulator buffers
+    static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128
+                                   : ACC_COLS <= 256 ? 256 : 512;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + (int)sizeof(Aux) + 2 * BN * 4;
+};
+
+template <int BN, int EPI>
+__global__ void __launch_bounds__(192, 1)
+w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
+                 const float* __restrict__ a_s, const float* __restrict__ w_s, void* __restrict__ out, long ldo,
+                 const int* __restrict__ n_rows, int M, int N, int K, int vec_ok) {
+    using C = TileCfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = align1024(smem_raw);
+    Aux* aux = (Aux*)(smem + C::STAGES * C::STAGE_BYTES);
+    float* sw_stash = (float*)(aux + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    int live = *n_rows;
+    live = live < M ? live : M;
+    const int num_m = (live + BM - 1) / BM, num_n = (N + BN - 1) / BN;
+    const int num_tiles = num_m * num_n, KB = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            mbar_init(smem_u32(&aux->full[s]), 1);
+            mbar_init(smem_u32(&aux->empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&aux->tfull[b]), 1);
+            mbar_init(smem_u32(&aux->tempty[b]), 4);
+        }
+        aux->abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&aux->tmem_base), C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = aux->tmem_base;
+    volatile int* abort_flag = &aux->abort_flag;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (one thread)
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_a);
+            tma_prefetch_desc(&tm_w);
+            uint32_t armed_parity[C::STAGES];
+            uint32_t armed_mask = 0;
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int m0 = (t % num_m) * BM, n0 = (t / num_m) * BN;
+                for (int kb = 0; kb < KB; ++kb) {
+                    if (!mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1, abort_flag, 0x100 + stage)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t bar = smem_u32(&aux->full[stage]);
+                    mbar_expect_tx(bar, C::STAGE_BYTES);
+                    uint8_t* st = smem + stage * C::STAGE_BYTES;
+                    tma_load_2d(smem_u32(st), &tm_a, kb * BK, m0, bar);
+                    tma_load_2d(smem_u32(st + C::A_BYTES), &tm_w, kb * BK, n0, bar);
+                    armed_parity[stage] = phase;
+                    armed_mask |= 1u << stage;
+                    if (++stage == C::STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            if (!ok) drain_armed(aux, C::STAGES, armed_parity, armed_mask);
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (one thread)
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_i8(BM, BN);
+            int stage = 0, buf = 0;
+            uint32_t phase = 0, bphase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                if (!mbar_wait(smem_u32(&aux->tempty[buf]), bphase ^ 1, abort_flag, 0x200 + buf)) break;
+                tc_fence_after();
+                const uint32_t d = tmem_base + buf * BN;
+                for (int kb = 0; kb < KB; ++kb) {
+                    if (!mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, 0x300 + stage)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    uint8_t* st = smem + stage * C::STAGE_BYTES;
+                    const uint64_t ad = umma_desc_k128(smem_u32(st));
+                    const uint64_t bd = umma_desc_k128(smem_u32(st + C::A_BYTES));
+#pragma unroll
+                    for (int k = 0; k < BK / 32; ++k)
+                        umma_i8(d, umma_desc_advance(ad, k * 32), umma_desc_advance(bd, k * 32), idesc,
+                                (kb | k) ? 1u : 0u);
+                    tc_commit(smem_u32(&aux->empty[stage]));
+                    if (++stage == C::STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) break;
+                tc_commit(smem_u32(&aux->tfull[buf]));
+                buf ^= 1;
+                if (buf == 0) bphase ^= 1;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (4 warps, one lane quarter each)
+        const int q = warp & 3, et = threadIdx.x - 64;
+        int buf = 0;
+        uint32_t bphase = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+            const int m0 = (t % num_m) * BM, n0 = (t / num_m) * BN;
+            float* swb = sw_stash + buf * BN;
+            if (EPI != EPI_I32)
+                for (int i = et; i < BN; i += 128) swb[i] = (n0 + i < N) ? w_s[n0 + i] : 0.0f;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (!mbar_wait(smem_u32(&aux->tfull[buf]), bphase, abort_flag, 0x400 + buf)) break;
+            tc_fence_after();
+            const int row = m0 + q * 32 + lane;
+            const bool rok = row < live;
+            const float sa = (rok && EPI != EPI_I32) ? a_s[row] : 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c * 32, r);
+                tmem_ld_wait();
+                const int col0 = n0 + c * 32;
+                const int nok = N - col0 >= 32 ? 32 : (N - col0 > 0 ? N - col0 : 0);
+                if (rok && nok > 0) store_row32<EPI>(out, ldo, row, col0, nok, vec_ok != 0, r, sa, swb + c * 32);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&aux->tempty[buf]));
+            buf ^= 1;
+            if (buf == 0) bphase ^= 1;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+// ================================================================================================= swapped kernel
+// MODE_DIRECT: the CTA owns all of K (split = 1): scales + store (bf16 / fp32 add / int32).
+// MODE_SLOTS:  int32 partial sums of K slice z into slots[z] (int32 [S, rows, N]); the caller folds them later.
+// MODE_WS:     int32 partial sums into a workspace; the last CTA to finish a tile (a counter per tile) adds the
+//              slices and runs the epilogue.  Counters return to zero.
+constexpr int MODE_DIRECT = 0, MODE_SLOTS = 1, MODE_WS = 2;
+
+template <int NB, bool GROUPED>
+struct SwapCfg {
+    static constexpr int W_BYTES = BM * BK;                      // 16 KB
+    static constexpr int X_BYTES = NB * BK;
+    static constexpr int SW_BYTES = GROUPED ? BM * 16 : 0;       // 4 fp32 group scales per weight row
+    static constexpr int SA_BYTES = GROUPED ? NB * 16 : 0;       // 4 fp32 group scales per activation row
+    static constexpr int STAGE_BYTES_RAW = W_BYTES + X_BYTES + SW_BYTES + SA_BYTES;
+    static constexpr int STAGE_BYTES = (STAGE_BYTES_RAW + 1023) / 1024 * 1024;
+    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 10 ? 10 : (200 * 1024 / STAGE_BYTES);
+    static constexpr int BATCH_COLS = GROUPED ? 4 * NB : NB;     // accumulator columns written per stage
+    static constexpr int RING = GROUPED ? ((512 / BATCH_COLS) > 4 ? 4 : (512 / BATCH_COLS)) : 1;
+    static constexpr int ACC_COLS = BATCH_COLS * RING;
+    static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128
+                                   : ACC_COLS <= 256 ? 256 : 512;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + (int)sizeof(Aux);
+};
+
+struct SwapArgs {
+    const float* a_s;       // [M] (gk == K) or [M, K/32] (GROUPED; read through tm_sa)
+    const float* w_s;       // [N] (gk == K) or [N, K/32] (GROUPED; read through tm_sw)
+    void* out;              // bf16 / fp32 / int32 [M, N]; MODE_SLOTS: slots base
+    long ldo;               // row stride of out (elements)
+    long slot_stride;       // MODE_SLOTS: elements between slots
+    int32_t* ws;            // MODE_WS: split * tiles * NB * 128 int32
+    int* counters;          // MODE_WS: one per (n tile, m tile)
+    const int* n_rows;
+    int M, N, K;
+    int kb_per_split;       // 128-byte K blocks per blockIdx.y
+    int epi;                // EPI_BF16 / EPI_ADD / EPI_I32
+    int mode;
+};
+
+template <int NB>
+__device__ __forceinline__ void swap_store(const SwapArgs& p, int n, int m0, int live, const float (&v)[NB]) {
+    // thread = output column n; v[j] = value of row m0 + j.  A warp's 32 lanes write 32 consecutive columns.
+    if (n >= p.N) return;
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+        const int m = m0 + j;
+        if (m < live) {
+            if (p.epi == EPI_BF16)
+                ((__nv_bfloat16*)p.out)[(long)m * p.ldo + n] = __float2bfloat16_rn(v[j]);
+            else {
+                float* o = (float*)p.out + (long)m * p.ldo + n;
+                *o = __fadd_rn(*o, v[j]);
+            }
+        }
+    }
+}
+
+template <int NB, bool GROUPED>
+__global__ void __launch_bounds__(192, 1)
+w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                 const __grid_constant__ CUtensorMap tm_sw, const __grid_constant__ CUtensorMap tm_sa,
+                 const SwapArgs p) {
+    using C = SwapCfg<NB, GROUPED>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = align1024(smem_raw);
+    Aux* aux = (Aux*)(smem + C::STAGES * C::STAGE_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    int live = *p.n_rows;
+    live = live < p.M ? live : p.M;
+    const int n0 = blockIdx.x * BM, m0 = blockIdx.z * NB, z = blockIdx.y;
+    if (m0 >= live) return;                                    // whole CTA, before any barrier or allocation
+    const int KB = (p.K + BK - 1) / BK;
+    const int kb0 = z * p.kb_per_split;
+    int kb1 = kb0 + p.kb_per_split;
+    kb1 = kb1 < KB ? kb1 : KB;
+    const int nkb = kb1 > kb0 ? kb1 - kb0 : 0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            mbar_init(smem_u32(&aux->full[s]), 1);
+            mbar_init(smem_u32(&aux->empty[s]), GROUPED ? 5 : 1);   // MMA commit (+ 4 epilogue warps read the scales)
+        }
+        for (int b = 0; b < C::RING; ++b) {
+            mbar_init(smem_u32(&aux->tfull[b]), 1);
+            mbar_init(smem_u32(&aux->tempty[b]), 4);
+        }
+        aux->abort_flag = 0;
+        aux->is_last = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&aux->tmem_base), C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = aux->tmem_base;
+    volatile int* abort_flag = &aux->abort_flag;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_w);
+            tma_prefetch_desc(&tm_x);
+            const uint64_t pol_w = policy_evict_first();       // weights are read once
+            uint32_t armed_parity[C::STAGES];
+            uint32_t armed_mask = 0;
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int i = 0; i < nkb; ++i) {
+                if (!mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1, abort_flag, 0x500 + stage)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t bar = smem_u32(&aux->full[stage]);
+                mbar_expect_tx(bar, C::STAGE_BYTES_RAW);
+                uint8_t* st = smem + stage * C::STAGE_BYTES;
+                const int kb = kb0 + i;
+                tma_load_2d_hint(smem_u32(st), &tm_w, kb * BK, n0, bar, pol_w);
+                tma_load_2d(smem_u32(st + C::W_BYTES), &tm_x, kb * BK, m0, bar);
+                if (GROUPED) {
+                    tma_load_2d(smem_u32(st + C::W_BYTES + C::X_BYTES), &tm_sw, kb * 4, n0, bar);
+                    tma_load_2d(smem_u32(st + C::W_BYTES + C::X_BYTES + C::SW_BYTES), &tm_sa, kb * 4, m0, bar);
+                }
+                armed_parity[stage] = phase;
+                armed_mask |= 1u << stage;
+                if (++stage == C::STAGES) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+            if (!ok) drain_armed(aux, C::STAGES, armed_parity, armed_mask);
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_i8(BM, NB);
+            int stage = 0, ring = 0;
+            uint32_t phase = 0, rphase = 0;
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; ++i) {
+                if (GROUPED) {
+                    if (!mbar_wait(smem_u32(&aux->tempty[ring]), rphase ^ 1, abort_flag, 0x600 + ring)) break;
+                }
+                if (!mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, 0x700 + stage)) break;
+                tc_fence_after();
+                uint8_t* st = smem + stage * C::STAGE_BYTES;
+                const uint64_t ad = umma_desc_k128(smem_u32(st));
+                const uint64_t bd = umma_desc_k128(smem_u32(st + C::W_BYTES));
+#pragma unroll
+                for (int k = 0; k < BK / 32; ++k) {
+                    if (GROUPED)
+                        umma_i8(tmem_base + ring * C::BATCH_COLS + k * NB, umma_desc_advance(ad, k * 32),
+                                umma_desc_advance(bd, k * 32), idesc, 0u);
+                    else
+                        umma_i8(tmem_base, umma_desc_advance(ad, k * 32), umma_desc_advance(bd, k * 32), idesc,
+                                (i | k) ? 1u : 0u);
+                }
+                tc_commit(smem_u32(&aux->empty[stage]));
+                if (GROUPED) {
+                    tc_commit(smem_u32(&aux->tfull[ring]));
+                    if (++ring == C::RING) {
+                        ring = 0;
+                        rphase ^= 1;
+                    }
+                }
+                if (++stage == C::STAGES) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+            if (!GROUPED && ok) tc_commit(smem_u32(&aux->tfull[0]));
+        }
+    } else {
+        const int q = warp & 3;
+        const int nl = q * 32 + lane;                          // this thread's weight row inside the tile
+        const int n = n0 + nl;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+        if (GROUPED) {
+            float acc[NB];
+#pragma unroll
+            for (int j = 0; j < NB; ++j) acc[j] = 0.0f;
+            int stage = 0, ring = 0;
+            uint32_t phase = 0, rphase = 0;
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; ++i) {
+                if (!mbar_wait(smem_u32(&aux->tfull[ring]), rphase, abort_flag, 0x800 + ring)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                // the stage's scales landed with its operands: its full barrier has completed (the MMAs ran after
+                // it); testing it here orders this thread's reads after the bulk copies' writes
+                if (!mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, 0x880 + stage)) {
+                    ok = false;
+                    break;
+                }
+                const uint8_t* st = smem + stage * C::STAGE_BYTES + C::W_BYTES + C::X_BYTES;
+                const float4 sw4 = *(const float4*)(st + nl * 16);
+                const float4* sa4 = (const float4*)(st + C::SW_BYTES);
+#pragma unroll
+                for (int c = 0; c < NB; c += 8) {
+                    uint32_t r[4][8];
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) tmem_ld8(lane_base + ring * C::BATCH_COLS + g * NB + c, r[g]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const float4 s = sa4[c + j];
+                        float a = acc[c + j];
+                        a = __fadd_rn(a, scale2((int)r[0][j], s.x, sw4.x));      // groups in ascending order
+                        a = __fadd_rn(a, scale2((int)r[1][j], s.y, sw4.y));
+                        a = __fadd_rn(a, scale2((int)r[2][j], s.z, sw4.z));
+                        a = __fadd_rn(a, scale2((int)r[3][j], s.w, sw4.w));
+                        acc[c + j] = a;
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(smem_u32(&aux->tempty[ring]));
+                    mbar_arrive(smem_u32(&aux->empty[stage]));
+                }
+                if (++ring == C::RING) {
+                    ring = 0;
+                    rphase ^= 1;
+                }
+                if (++stage == C::STAGES) {
+                    stage = 0;
+                    phase ^= 1;
+                }
+            }
+            if (ok) swap_store<NB>(p, n, m0, live, acc);
+        } else {
+            // every epilogue thread takes the same branch: the barrier-wide AND of the wait's outcome
+            uint32_t got = (nkb > 0 && mbar_wait(smem_u32(&aux->tfull[0]), 0, abort_flag, 0x900)) ? 1u : 0u;
+            asm volatile(
+                "{\n\t.reg .pred p, q;\n\t"
+                "setp.ne.u32 p, %1, 0;\n\t"
+                "bar.red.and.pred q, 1, 128, p;\n\t"
+                "selp.u32 %0, 1, 0, q;\n\t}"
+                : "=r"(got) : "r"(got) : "memory");
+            if (got) {
+                tc_fence_after();
+                int32_t acc[NB];
+#pragma unroll
+                for (int c = 0; c < NB; c += 8) {
+                    uint32_t r[8];
+                    tmem_ld8(lane_base + c, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc[c + j] = (int32_t)r[j];
+                }
+                if (p.mode == MODE_SLOTS || (p.mode == MODE_DIRECT && p.epi == EPI_I32)) {
+                    int32_t* o = (int32_t*)p.out + (p.mode == MODE_SLOTS ? (long)z * p.slot_stride : 0);
+                    if (n < p.N) {
+#pragma unroll
+                        for (int j = 0; j < NB; ++j)
+                            if (m0 + j < live) o[(long)(m0 + j) * p.ldo + n] = acc[j];
+                    }
+                } else if (p.mode == MODE_DIRECT) {
+                    const float sw = n < p.N ? p.w_s[n] : 0.0f;
+                    float v[NB];
+#pragma unroll
+                    for (int j = 0; j < NB; ++j) {
+                        const float sa = (m0 + j < live) ? __ldg(p.a_s + m0 + j) : 0.0f;
+                        v[j] = scale2(acc[j], sa, sw);
+                    }
+                    swap_store<NB>(p, n, m0, live, v);
+                } else {
+                    // workspace: ws[z][tile][j][128]; the last CTA of the tile adds the slices in slice order
+                    const int tile = blockIdx.z * gridDim.x + blockIdx.x;
+                    const long tile_elems = (long)NB * BM;
+                    int32_t* mine = p.ws + ((long)z * gridDim.x * gridDim.z + tile) * tile_elems;
+#pragma unroll
+                    for (int j = 0; j < NB; ++j) mine[j * BM + nl] = acc[j];
+                    __threadfence();
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (threadIdx.x == 64) {
+                        const int old = atomicAdd(p.counters + tile, 1);
+                        aux->is_last = (old == (int)gridDim.y - 1);
+                    }
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    if (aux->is_last) {
+                        __threadfence();
+                        const float sw = n < p.N ? p.w_s[n] : 0.0f;
+                        float v[NB];
+#pragma unroll
+                        for (int j = 0; j < NB; ++j) {
+                            int32_t tot = 0;
+                            for (int s = 0; s < (int)gridDim.y; ++s)
+                                tot += __ldcg(p.ws + ((long)s * gridDim.x * gridDim.z + tile) * tile_elems + j * BM + nl);
+                            const float sa = (m0 + j < live) ? __ldg(p.a_s + m0 + j) : 0.0f;
+                            v[j] = scale2(tot, sa, sw);
+                        }
+                        swap_store<NB>(p, n, m0, live, v);
+                        if (threadIdx.x == 64) p.counters[tile] = 0;
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+}  // namespace w8a8

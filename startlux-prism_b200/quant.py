@@ -1,0 +1,83 @@
+"""Producers of quantized projection inputs and the deferred residual add: the operator API of the reference's
+kernels/quant.py over the sm_100a library.
+
+    rows_q8(x, inv_s, q, s, n, T, mode, amax)     x bf16 [T, K] * inv_s -> int8 + per-token scale  (quant.py:481-486)
+    swiglu_q8(gu, inv_s, q, s, n, T, mode, amax)  silu(gate) * up -> int8 + per-token scale         (quant.py:473-478)
+    rows_g(x, q, s, xs, n, T)                     W4A8: scale per 256 inputs + split group sums     (quant.py:408-411)
+    fold(h, parts, pending, n, T)                 finish a w8a8.Deferred residual add               (quant.py:448-457)
+
+Tensor-parallel modes (quant.py:14-27): 1 also stores the row's own maximum in `amax`, 2 quantizes with
+max(amax[t], own) after `amax` was max-all-reduced; a maximum is exact in any order, so every rank's int8 values and
+scales are the single-GPU kernel's.  The reference's in-kernel exchange (mode 3) is not built: `sync` must be None.
+"""
+import torch
+
+from . import _lib
+
+
+def _mode_args(mode, amax, sync, T):
+    if sync is not None or mode == 3:
+        raise NotImplementedError("in-kernel row-maximum exchange (mode 3 / sync) is not part of this build; "
+                                  "use modes 1 and 2 around a max all-reduce (tp.quantize_rows does)")
+    if mode not in (0, 1, 2):
+        raise ValueError(f"mode {mode}")
+    if mode and (amax is None or amax.dtype != torch.float32 or amax.numel() < T):
+        raise RuntimeError("modes 1 / 2 need an fp32 amax buffer of at least T elements")
+    return amax if mode else None
+
+
+def rows_q8(x, inv_s, q, s, n, T, mode=0, amax=None, sync=None):
+    """x bf16 / fp32 [>= T, K], inv_s fp32 [K] or None -> q int8 [>= T, K], s fp32 [>= T]; n: device int32 live rows."""
+    K = q.shape[1]
+    _lib.need_cuda(x, q, s, n)
+    amax = _mode_args(mode, amax, sync, T)
+    if x.dtype not in (torch.bfloat16, torch.float32) or x.shape[1] != K or not x.is_contiguous() \
+            or not q.is_contiguous():
+        raise RuntimeError("rows_q8: x must be contiguous bf16 / fp32 [T, K] matching q")
+    rc = _lib.lib().pb_quant_rows(_lib.ptr(x), int(x.dtype == torch.float32), _lib.ptr(inv_s), _lib.ptr(q),
+                                  _lib.ptr(s), _lib.ptr(n), T, K, K, mode, _lib.ptr(amax), _lib.stream())
+    _lib.check(rc, f"rows_q8 T={T} K={K} mode={mode}")
+
+
+def swiglu_q8(gu, inv_s, q, s, n, T, mode=0, amax=None, sync=None):
+    """gu bf16 [>= T, 2 FF] (gate columns then up columns) -> q int8 [>= T, FF], s fp32 [>= T]."""
+    FF = q.shape[1]
+    _lib.need_cuda(gu, q, s, n)
+    amax = _mode_args(mode, amax, sync, T)
+    if gu.dtype != torch.bfloat16 or gu.shape[1] != 2 * FF or not gu.is_contiguous() or not q.is_contiguous():
+        raise RuntimeError("swiglu_q8: gu must be contiguous bf16 [T, 2 FF]")
+    rc = _lib.lib().pb_swiglu_q8(_lib.ptr(gu), _lib.ptr(inv_s), _lib.ptr(q), _lib.ptr(s), _lib.ptr(n), T, FF, mode,
+                                 _lib.ptr(amax), _lib.stream())
+    _lib.check(rc, f"swiglu_q8 T={T} FF={FF} mode={mode}")
+
+
+def rows_g(x, q, s, xs, n, T):
+    """x bf16 / fp32 [>= T, K] -> q int8 [M, K], s fp32 [K/256, M], xs int8 [K/256, M, 16] (super-block-major)."""
+    K = q.shape[1]
+    Ma = s.shape[1]
+    _lib.need_cuda(x, q, s, xs, n)
+    if x.dtype not in (torch.bfloat16, torch.float32) or not x.is_contiguous() or x.shape[1] != K:
+        raise RuntimeError("rows_g: x must be contiguous bf16 / fp32 [T, K]")
+    if s.shape[0] != K // 256 or xs.shape != (K // 256, Ma, 16) or not s.is_contiguous() or not xs.is_contiguous():
+        raise RuntimeError("rows_g: s must be [K/256, M] and xs [K/256, M, 16], contiguous")
+    rc = _lib.lib().pb_quant_g(_lib.ptr(x), int(x.dtype == torch.float32), _lib.ptr(q), _lib.ptr(s), _lib.ptr(xs),
+                               _lib.ptr(n), T, Ma, K, _lib.stream())
+    _lib.check(rc, f"rows_g T={T} K={K}")
+
+
+def fold(h, parts, pending, n, T):
+    """Finish a deferred residual add (w8a8.Deferred) in h fp32 [>= T, N]: h += (float(sum of slots) * a_s) * w_s with
+    the unsplit epilogue's roundings.  parts: the int32 slots [S, rows, N] unless the Deferred names its own."""
+    if not pending:
+        return
+    if pending.sync is not None:
+        raise NotImplementedError("fused cross-rank reads (Deferred.sync) are not part of this build")
+    if pending.parts is not None:
+        parts = pending.parts
+    _lib.need_cuda(h, parts, n)
+    N = h.shape[1]
+    if h.dtype != torch.float32 or parts.dtype != torch.int32 or parts.shape[2] != N or h.stride(1) != 1:
+        raise RuntimeError("fold: h fp32 [T, N], parts int32 [S, rows, N]")
+    rc = _lib.lib().pb_fold(_lib.ptr(h), h.stride(0), _lib.ptr(parts), parts.stride(0), pending.n,
+                            _lib.ptr(pending.a_s), _lib.ptr(pending.w_s), _lib.ptr(n), T, N, _lib.stream())
+    _lib.check(rc, f"fold T={T} N={N} S={pending.n}")

@@ -1,0 +1,181 @@
+"""W8A8 projections: the operator API of the reference's kernels/w8a8.py over the sm_100a library.
+
+    gemm(a, a_s, w, w_s, out, n_rows, gk, epi=0, ...)   int8 x int8 GEMM with scale epilogues     (w8a8.py:183-231)
+    gemm_i32(a, a_s, w, w_s, slots, n_rows, ...)        raw int32 sums of a tensor-parallel shard (w8a8.py:234-261)
+    quant_rows(x, gk, n_rows)                           symmetric int8 per (row, group)           (w8a8.py:264-271)
+    weight_from_q8(q8, gk, smooth)                      Q8_0 -> (int8, fp32 scales)               (w8a8.py:274-286)
+    interleave_gate_up(gate, up, bn)                                                              (w8a8.py:289-294)
+    Deferred                                            a residual add left to quant.fold         (w8a8.py:171-180)
+
+gk == K (the engine's mode): one scale per token and per output channel; every kernel, K split and batch size gives an
+output element the same bits: v = (float(acc) * a_s[m]) * w_s[n], each product rounded, epi 1 adds with one more
+rounding.  gk == 32 uses Q8_0's own block scales: fp32 partial products added in group order.
+Kernel choice (this module's table replaces the reference's per-GPU JSON tables): more than 64 rows -> the persistent
+128 x 256 tile kernel; up to 64 rows -> the operand-swapped split-K kernel, the splits' int32 sums either deferred to
+the caller's `slots` (epi 1) or added inside the kernel through a workspace.
+"""
+from typing import NamedTuple
+
+import torch
+
+from . import _lib
+
+EPI_BF16, EPI_ADD, EPI_SWIGLU, EPI_I32 = 0, 1, 2, 3
+FEW_ROWS = 64                    # up to this many rows the operand-swapped kernel runs
+MAX_SPLIT = 8
+RESIDENT_CTAS = 296              # two CTAs of the few-rows kernel per SM on 148 SMs
+WS_BYTES = 96 << 20              # split-K workspace per device (allocated at the first call that needs it)
+
+_WORKSPACE = {}
+
+
+class Deferred(NamedTuple):
+    """A residual add left to the next reader of the residual (quant.fold / quant.norm_q8): `n` int32 slots of partial
+    sums and the projection's scales; `parts` names the slots when they are not the reader's own buffer; `sync` is
+    kept for signature parity with the reference's fused tensor-parallel reads (unused here)."""
+    n: int
+    a_s: torch.Tensor
+    w_s: torch.Tensor
+    parts: torch.Tensor = None
+    sync: object = None
+
+
+def _workspace(device):
+    """(workspace bytes tensor, zeroed int32 counters) of a device; allocated once, outside any graph capture."""
+    key = torch.device(device).index or 0
+    if key not in _WORKSPACE:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("the split-K workspace must exist before graph capture: run the GEMM once eagerly")
+        _WORKSPACE[key] = (torch.empty(WS_BYTES, dtype=torch.uint8, device=device),
+                           torch.zeros(65536, dtype=torch.int32, device=device))
+    return _WORKSPACE[key]
+
+
+def pick_split(M, N, K, limit=MAX_SPLIT):
+    """K splits of the few-rows kernel: as many CTAs as stay resident together, at least two 128-byte K blocks each."""
+    if M > FEW_ROWS:
+        return 1
+    tiles = -(-N // 128)
+    kb = -(-K // 128)
+    return max(1, min(limit, RESIDENT_CTAS // tiles, kb // 2))
+
+
+def _call(a, a_s, w, w_s, out, ldo, n_rows, gk, epi, split, slot_stride=0, ws=None, counters=None):
+    M, K = a.shape
+    N = w.shape[0]
+    _lib.need_cuda(a, w, out, n_rows)
+    if a.dtype != torch.int8 or w.dtype != torch.int8 or not a.is_contiguous() or not w.is_contiguous():
+        raise RuntimeError("w8a8.gemm: a and w must be contiguous int8 [rows, K]")
+    if w.shape[1] != K:
+        raise RuntimeError(f"w8a8.gemm: K mismatch ({K} vs {w.shape[1]})")
+    if n_rows.dtype != torch.int32:
+        raise RuntimeError("w8a8.gemm: n_rows must be a device int32 tensor")
+    rc = _lib.lib().pb_w8a8_gemm(_lib.ptr(a), _lib.ptr(a_s), _lib.ptr(w), _lib.ptr(w_s), _lib.ptr(out), ldo,
+                                 _lib.ptr(n_rows), M, N, K, gk, epi, split, slot_stride, _lib.ptr(ws),
+                                 0 if ws is None else ws.numel(), _lib.ptr(counters),
+                                 0 if counters is None else counters.numel(), _lib.stream())
+    _lib.check(rc, f"w8a8 gemm M={M} N={N} K={K} gk={gk} epi={epi} split={split}")
+
+
+def _scales_ok(s, rows, groups, what):
+    if s.dtype != torch.float32 or s.numel() != rows * groups or not s.is_contiguous():
+        raise RuntimeError(f"w8a8.gemm: {what} must be contiguous fp32 with {rows} x {groups} elements")
+
+
+def gemm(a, a_s, w, w_s, out, n_rows, gk, epi=0, outs=None, cfg=None, slots=None, pdl=False):
+    """a int8 [M, K], a_s fp32 [M, K/gk], w int8 [N, K], w_s fp32 [N, K/gk] -> out: bf16 [M, N] (epi 0) or added into
+    fp32 [M, N] (epi 1); out may be a column slice of a wider buffer (its row stride is honoured).  Returns a Deferred
+    when an epi 1 product split K into `slots` (int32 [S, rows, N]), else None.  cfg: None or the number of K splits.
+    pdl is accepted for signature parity (kernels start in stream order)."""
+    M, K = a.shape
+    N = w.shape[0]
+    if epi == EPI_SWIGLU:
+        raise NotImplementedError("the fused SwiGLU epilogue (epi 2) is not part of this build: use quant.swiglu_q8")
+    if epi not in (EPI_BF16, EPI_ADD):
+        raise ValueError(f"epi {epi}")
+    want = torch.bfloat16 if epi == EPI_BF16 else torch.float32
+    if out.dtype != want or out.shape[0] < M or out.shape[1] != N or out.stride(1) != 1:
+        raise RuntimeError(f"w8a8.gemm: out must be {want} [>= {M}, {N}] with unit column stride")
+    _scales_ok(a_s, M, K // gk, "a_s")
+    _scales_ok(w_s, N, K // gk, "w_s")
+    if gk != K:
+        _call(a, a_s, w, w_s, out, out.stride(0), n_rows, gk, epi, 1)
+        return None
+    split = int(cfg) if cfg is not None else pick_split(M, N, K)
+    if M > FEW_ROWS:
+        split = 1
+    if split > 1 and epi == EPI_ADD and slots is not None and slots.shape[1] >= M:
+        split = min(split, slots.shape[0])
+        if split > 1:
+            _check_slots(slots, M, N)
+            _call(a, a_s, w, w_s, slots, N, n_rows, gk, EPI_I32, split, slots.stride(0))
+            return Deferred(split, a_s, w_s)
+    ws = counters = None
+    if split > 1:
+        ws, counters = _workspace(a.device)
+        while split > 1 and _lib.lib().pb_w8a8_workspace_bytes(M, N, split) > ws.numel():
+            split -= 1
+        if split == 1:
+            ws = counters = None
+    _call(a, a_s, w, w_s, out, out.stride(0), n_rows, gk, epi, split, 0, ws, counters)
+    return None
+
+
+def _check_slots(slots, M, N):
+    if slots.dtype != torch.int32 or slots.dim() != 3 or slots.shape[1] < M or slots.shape[2] != N \
+            or slots.stride(2) != 1 or slots.stride(1) != N:
+        raise RuntimeError("slots must be int32 [S, rows >= M, N], rows contiguous")
+
+
+def gemm_i32(a, a_s, w, w_s, slots, n_rows, max_split=4, pdl=False, split=None):
+    """The int32 products a w^T without the scales into slots (int32 [S, rows, N]): a row-parallel shard's partial
+    sums, added over the ranks (exact) and scaled later (Deferred, quant.fold).  Returns the number of slots written
+    (K splits, at most max_split and slots.shape[0])."""
+    M, K = a.shape
+    N = w.shape[0]
+    _check_slots(slots, M, N)
+    S = split if split is not None else pick_split(M, N, K, min(max_split, slots.shape[0]))
+    S = max(1, min(S, max_split, slots.shape[0])) if M <= FEW_ROWS else 1
+    _call(a, a_s, w, w_s, slots, N, n_rows, K, EPI_I32, S, slots.stride(0))
+    return S
+
+
+def quant_rows(x, gk, n_rows=None):
+    """x [M, K] bf16 / fp32 -> (int8 [M, K], fp32 scales [M, K / gk]), symmetric per group of gk inputs."""
+    M, K = x.shape
+    _lib.need_cuda(x)
+    q = torch.empty(M, K, dtype=torch.int8, device=x.device)
+    s = torch.empty(M, K // gk, dtype=torch.float32, device=x.device)
+    if n_rows is None:
+        n_rows = torch.tensor([M], dtype=torch.int32, device=x.device)
+    if x.dtype not in (torch.bfloat16, torch.float32) or not x.is_contiguous():
+        raise RuntimeError("quant_rows: x must be contiguous bf16 or fp32")
+    rc = _lib.lib().pb_quant_rows(_lib.ptr(x), int(x.dtype == torch.float32), None, _lib.ptr(q), _lib.ptr(s),
+                                  _lib.ptr(n_rows), M, K, gk, 0, None, _lib.stream())
+    _lib.check(rc, f"quant_rows M={M} K={K} gk={gk}")
+    return q, s
+
+
+def weight_from_q8(q8, gk, smooth=None):
+    """Q8_0 matrix -> (int8 [N, K], fp32 scales [N, K / gk]).  gk == 32 without smoothing keeps the file's values and
+    block scales; otherwise the dequantized weights (times smooth[k], SmoothQuant) are quantized again per group:
+    s = max|g| / 127 (at least 1e-10 / 127), q = round(g / s) clamped to +-127.  Load-time, plain torch, any device."""
+    if gk == 32 and smooth is None:
+        return q8.qs.contiguous(), q8.d.float().contiguous()
+    wf = q8.dequant(torch.float32)
+    if smooth is not None:
+        wf = wf * smooth[None, :]
+    N, K = wf.shape
+    g = wf.view(N, K // gk, gk)
+    s = g.abs().amax(-1).clamp_min(1e-10) / 127.0
+    q = torch.round(g / s[..., None]).clamp(-127, 127).to(torch.int8).view(N, K)
+    return q.contiguous(), s.contiguous()
+
+
+def interleave_gate_up(gate, up, bn):
+    """Rows of gate [FF, K] and up [FF, K] -> [2 FF, K] in tiles of bn rows: bn / 2 gate rows then the same up rows."""
+    FF, K = gate.shape
+    h = bn // 2
+    if FF % h:
+        raise ValueError(f"FF {FF} is not a multiple of {h}")
+    return torch.stack([gate.view(FF // h, h, K), up.view(FF // h, h, K)], 1).reshape(2 * FF, K).contiguous()

@@ -1,0 +1,97 @@
+"""Activation quantizers and the fold on the GPU against the CPU oracle: bit for bit where the kernel does no
+transcendental arithmetic (rows_q8, quant_rows, rows_g, fold), within one int8 step for SwiGLU (exp differs in its
+last bits between a GPU and libm; tests/test_w4a8.py:91-102 sets the same bar for the reference's fused producers)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from prism_b200 import quant, synth, w8a8
+from util import first_diff, n_rows, np_bits, same
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("T,K,live", [(1, 5120, 1), (33, 5120, 30), (16, 17408, 16), (7, 2560, 7), (5, 1000, 5),
+                                      (3, 40000, 3), (9, 264, 9)])
+@pytest.mark.parametrize("smooth", [False, True])
+def test_rows_q8(dev, T, K, live, smooth):
+    x = synth.activations(T, K, seed=T + K)
+    inv = torch.exp(torch.randn(K, generator=torch.Generator().manual_seed(K)) * 0.1) if smooth else None
+    rq, rs = oracle.quant_rows(np_bits(x), inv_s=None if inv is None else inv.numpy(), live=live)
+    q = torch.full((T, K), 99, dtype=torch.int8, device=dev)
+    s = torch.full((T,), -1.0, device=dev)
+    quant.rows_q8(x.to(dev), None if inv is None else inv.to(dev), q, s, n_rows(live, dev), T)
+    assert same(q[:live], rq[:live]), first_diff(q[:live].cpu().numpy(), rq[:live])
+    assert same(s[:live], rs[:live, 0])
+    assert bool((q[live:] == 99).all()) and bool((s[live:] == -1).all())
+    # fp32 input
+    xf = x.float() * 1.001
+    rq, rs = oracle.quant_rows(xf.numpy(), inv_s=None if inv is None else inv.numpy(), live=live)
+    quant.rows_q8(xf.to(dev), None if inv is None else inv.to(dev), q, s, n_rows(live, dev), T)
+    assert same(q[:live], rq[:live]) and same(s[:live], rs[:live, 0])
+
+
+def test_rows_q8_tp_modes(dev):
+    """Modes 1 / 2 (kernels/quant.py:301-304): column halves quantized with the whole row's maximum give the whole
+    row's int8 values and scale."""
+    T, K = 9, 5120
+    x = synth.activations(T, K, seed=3)
+    rq, rs = oracle.quant_rows(np_bits(x))
+    nr = n_rows(T, dev)
+    halves = [x[:, :K // 2].contiguous().to(dev), x[:, K // 2:].contiguous().to(dev)]
+    amax = [torch.zeros(T, device=dev) for _ in halves]
+    qs = [torch.empty(T, K // 2, dtype=torch.int8, device=dev) for _ in halves]
+    ss = [torch.empty(T, device=dev) for _ in halves]
+    for h, am, q, s in zip(halves, amax, qs, ss):
+        quant.rows_q8(h, None, q, s, nr, T, mode=1, amax=am)
+    tot = torch.maximum(amax[0], amax[1])
+    for h, q, s in zip(halves, qs, ss):
+        quant.rows_q8(h, None, q, s, nr, T, mode=2, amax=tot.clone())
+    assert same(torch.cat(qs, 1), rq) and same(ss[0], rs[:, 0]) and same(ss[1], rs[:, 0])
+
+
+@pytest.mark.parametrize("T,K,gk", [(4, 5120, 32), (3, 1024, 128), (17, 512, 256), (2, 17408, 32)])
+def test_quant_rows_groups(dev, T, K, gk):
+    x = synth.activations(T, K, seed=gk)
+    rq, rs = oracle.quant_rows(np_bits(x), gk)
+    q, s = w8a8.quant_rows(x.to(dev), gk)
+    assert same(q, rq) and same(s, rs)
+
+
+@pytest.mark.parametrize("T,K,live", [(33, 2560, 33), (5, 5120, 4), (2, 17408, 2)])
+def test_rows_g(dev, T, K, live):
+    """rows_g against the oracle's quantize_ref restatement (tests/test_w4a8.py:80-90)."""
+    x = synth.activations(T, K, seed=K, outliers=K // 64)
+    rq, ra, rxs = oracle.quant_g(np_bits(x), live)
+    q = torch.zeros(T, K, dtype=torch.int8, device=dev)
+    a = torch.zeros(K // 256, T, device=dev)
+    xs = torch.zeros(K // 256, T, 16, dtype=torch.int8, device=dev)
+    quant.rows_g(x.to(dev), q, a, xs, n_rows(live, dev), T)
+    assert same(q, rq) and same(a, ra) and same(xs, rxs)
+
+
+@pytest.mark.parametrize("T,FF,live", [(5, 17408, 5), (3, 1024, 2), (2, 4352, 2)])
+def test_swiglu_q8(dev, T, FF, live):
+    g = torch.Generator().manual_seed(FF)
+    gu = (torch.randn(T, 2 * FF, generator=g) * 2).to(torch.bfloat16)
+    rq, rs = oracle.swiglu_q8(np_bits(gu), live=live)
+    q = torch.zeros(T, FF, dtype=torch.int8, device=dev)
+    s = torch.zeros(T, device=dev)
+    quant.swiglu_q8(gu.to(dev), None, q, s, n_rows(live, dev), T)
+    assert np.abs(q.cpu().numpy().astype(int) - rq.astype(int)).max() <= 1
+    assert np.allclose(s.cpu().numpy()[:live], rs[:live], rtol=1e-5)
+    assert not bool(q[live:].any())
+
+
+def test_fold_odd(dev):
+    """fold with N not a multiple of 4 and a strided residual."""
+    T, N, S = 5, 30, 3
+    g = torch.Generator().manual_seed(0)
+    slots = torch.randint(-10 ** 6, 10 ** 6, (S, T, N), generator=g, dtype=torch.int32)
+    sa, sw = torch.rand(T, generator=g) * 1e-2, torch.rand(N, generator=g) * 1e-3
+    h = torch.randn(T, N, generator=g)
+    ref = oracle.fold(h.numpy(), slots.numpy(), sa.numpy(), sw.numpy(), live=4)
+    hd = h.to(dev)
+    quant.fold(hd, slots.to(dev), w8a8.Deferred(S, sa.to(dev), sw.to(dev)), n_rows(4, dev), T)
+    assert same(hd, ref)

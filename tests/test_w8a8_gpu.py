@@ -1,0 +1,150 @@
+"""W8A8 GEMM on the GPU against the CPU oracle, bit for bit: the tile kernel (many rows), the operand-swapped kernel
+(few rows) with every K-split mode, per-32 scale groups, padded buckets (live < M), odd N, strided outputs.  The cases
+follow the reference's tests/test_cuda_gemm.py (shapes :24-29, poison-filled slots :82, rows >= live untouched :67)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from prism_b200 import quant, w8a8
+from util import bf16_from_bits, first_diff, n_rows, np_bits, rand_w8a8, same
+
+pytestmark = pytest.mark.gpu
+
+# (M, N, K, live)
+SHAPES = [(8, 128, 256, 3), (1, 8192, 2560, 1), (16, 5120, 5120, 16), (64, 12352, 2560, 64), (64, 5120, 5120, 50),
+          (33, 1000, 1024, 33), (100, 2560, 9216, 77), (256, 5120, 6144, 256), (384, 4608, 2560, 361),
+          (130, 328, 400, 129)]
+
+
+def run(dev, a, w, sa, sw, out, live, gk, epi, **kw):
+    return w8a8.gemm(a.to(dev), sa.to(dev), w.to(dev), sw.to(dev), out, n_rows(live, dev), gk, epi=epi, **kw)
+
+
+@pytest.mark.parametrize("M,N,K,live", SHAPES)
+def test_gemm_one_group(dev, M, N, K, live):
+    a, w, sa, sw = rand_w8a8(M, N, K, seed=M * 7 + N)
+    an, wn, san, swn = a.numpy(), w.numpy(), sa.numpy(), sw.numpy()
+    ref0 = oracle.w8a8_gemm(an, san, wn, swn, K, 0, live)
+    base = torch.randn(M, N, generator=torch.Generator().manual_seed(1))
+    ref1 = oracle.w8a8_gemm(an, san, wn, swn, K, 1, live, out=base.numpy())
+    splits = [None, 1] + ([2, 3, 8] if M <= 64 else [])
+    for split in splits:
+        out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+        run(dev, a, w, sa, sw, out, live, K, 0, cfg=split)
+        assert same(out, bf16_from_bits(ref0)), ("bf16", split, first_diff(np_bits(out), ref0))
+        res = base.to(dev)
+        run(dev, a, w, sa, sw, res, live, K, 1, cfg=split)
+        assert same(res, ref1), ("add", split, first_diff(res.cpu().numpy(), ref1))
+
+
+@pytest.mark.parametrize("M,N,K,live", [(8, 128, 256, 3), (64, 5120, 6144, 64), (50, 5120, 17408, 47),
+                                        (100, 5120, 17408, 77), (384, 2560, 2048, 361)])
+def test_int32_slots_and_fold(dev, M, N, K, live):
+    """gemm_i32 / deferred split-K: the slots' sum is the exact integer product, rows >= live keep the poison, and
+    folding gives the unsplit residual add's bits (tests/test_cuda_gemm.py:175-225)."""
+    a, w, sa, sw = rand_w8a8(M, N, K, seed=N + K)
+    an, wn = a.numpy(), w.numpy()
+    exact = oracle.w8a8_gemm(an, sa.numpy(), wn, sw.numpy(), K, 3, live)
+    base = torch.randn(M, N, generator=torch.Generator().manual_seed(2))
+    ref1 = oracle.w8a8_gemm(an, sa.numpy(), wn, sw.numpy(), K, 1, live, out=base.numpy())
+    nr = n_rows(live, dev)
+    ad, wd, sad, swd = a.to(dev), w.to(dev), sa.to(dev).view(-1), sw.to(dev).view(-1)
+    for split in ([1, 2, 4] if M <= 64 else [1]):
+        slots = torch.full((4, M, N), -(1 << 30), dtype=torch.int32, device=dev)
+        S = w8a8.gemm_i32(ad, sad, wd, swd, slots, nr, max_split=4, split=split)
+        assert S == split
+        tot = slots[:S, :live].sum(0, dtype=torch.int32)
+        assert same(tot, exact[:live]), (split, first_diff(tot.cpu().numpy(), exact[:live]))
+        assert bool((slots[:S, live:] == -(1 << 30)).all()) and bool((slots[S:] == -(1 << 30)).all())
+        res = base.to(dev)
+        quant.fold(res, slots, w8a8.Deferred(S, sad, swd), nr, M)
+        assert same(res, ref1), (split, first_diff(res.cpu().numpy(), ref1))
+    if M <= 64:
+        # gemm() itself defers when given slots
+        slots = torch.full((4, M, N), -(1 << 30), dtype=torch.int32, device=dev)
+        res = base.to(dev)
+        d = w8a8.gemm(ad, sad, wd, swd, res, nr, K, epi=1, slots=slots, cfg=4)
+        assert isinstance(d, w8a8.Deferred) and d.n == 4
+        quant.fold(res, slots, d, nr, M)
+        assert same(res, ref1)
+
+
+@pytest.mark.parametrize("M,N,K,live", [(16, 5120, 5120, 16), (5, 256, 384, 4), (64, 1000, 1024, 61),
+                                        (150, 512, 2560, 140)])
+def test_gemm_q8_0_groups(dev, M, N, K, live):
+    """gk = 32: Q8_0's own block scales, fp32 partial sums added in group order (kernels/w8a8.py:64-76)."""
+    a, w, sa, sw = rand_w8a8(M, N, K, seed=K + M, groups=K // 32)
+    ref0 = oracle.w8a8_gemm(a.numpy(), sa.numpy(), w.numpy(), sw.numpy(), 32, 0, live)
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+    run(dev, a, w, sa, sw, out, live, 32, 0)
+    assert same(out, bf16_from_bits(ref0)), first_diff(np_bits(out), ref0)
+    base = torch.randn(M, N, generator=torch.Generator().manual_seed(3))
+    ref1 = oracle.w8a8_gemm(a.numpy(), sa.numpy(), w.numpy(), sw.numpy(), 32, 1, live, out=base.numpy())
+    res = base.to(dev)
+    run(dev, a, w, sa, sw, res, live, 32, 1)
+    assert same(res, ref1), first_diff(res.cpu().numpy(), ref1)
+
+
+def test_strided_output_and_determinism(dev):
+    """out as a column slice of a wider buffer (engine/model.py:848), twice: same bits, neighbours untouched."""
+    M, N, K = 48, 640, 1024
+    a, w, sa, sw = rand_w8a8(M, N, K, seed=5)
+    ref0 = oracle.w8a8_gemm(a.numpy(), sa.numpy(), w.numpy(), sw.numpy(), K, 0, M)
+    for M2 in (M, 200):
+        a2 = a if M2 == M else torch.cat([a, a, a, a, a[:8]])
+        sa2 = sa if M2 == M else torch.cat([sa, sa, sa, sa, sa[:8]])
+        wide = torch.full((M2, N + 200), 7.0, dtype=torch.bfloat16, device=dev)
+        for _ in range(2):
+            run(dev, a2, w, sa2, sw, wide[:, 100:100 + N], M2, K, 0)
+            assert same(wide[:M, 100:100 + N].contiguous(), bf16_from_bits(ref0))
+            assert bool((wide[:, :100] == 7).all()) and bool((wide[:, 100 + N:] == 7).all())
+
+
+def test_graph_replay_live_rows(dev):
+    """One captured graph serves every live count: n_rows is read on the device (tests/test_cuda_gemm.py:149-169)."""
+    M, N, K = 384, 1536, 2560
+    a, w, sa, sw = rand_w8a8(M, N, K, seed=11)
+    full = oracle.w8a8_gemm(a.numpy(), sa.numpy(), w.numpy(), sw.numpy(), K, 0, M)
+    ad, wd, sad, swd = a.to(dev), w.to(dev), sa.to(dev), sw.to(dev)
+    nr = n_rows(M, dev)
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+    w8a8.gemm(ad, sad, wd, swd, out, nr, K)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        w8a8.gemm(ad, sad, wd, swd, out, nr, K)
+    for live in (1, 97, 128, 129, 300, 384):
+        nr.fill_(live)
+        out.zero_()
+        g.replay()
+        torch.cuda.synchronize()
+        assert same(out[:live].contiguous(), bf16_from_bits(full[:live])), live
+        assert live == M or not bool(out[live:].any())
+
+
+def test_config0_synthetic(dev):
+    """BASELINE config 0: Q8_0 weights [5120, 5120] ~ N(0, 0.02^2), bf16 activations [16, 5120] with 8 outlier
+    channels, per-token int8, per-32 block scales, bf16 out."""
+    from prism_b200 import synth
+    q8 = synth.q8_0(synth.weights(5120, 5120, synth.seed_w(0, 1)))
+    x = synth.activations(16, 5120, synth.seed_x(0, 1, 16))
+    wq, ws = w8a8.weight_from_q8(q8, 32)
+    xq, xs = oracle.quant_rows(np_bits(x), 32)
+    ref = oracle.w8a8_gemm(xq, xs, wq.numpy(), ws.numpy(), 32, 0)
+    q, s = w8a8.quant_rows(x.to(dev), 32)
+    assert same(q, xq) and same(s, xs)
+    out = torch.zeros(16, 5120, dtype=torch.bfloat16, device=dev)
+    w8a8.gemm(q, s, wq.to(dev), ws.to(dev), out, n_rows(16, dev), 32)
+    assert same(out, bf16_from_bits(ref)), first_diff(np_bits(out), ref)
+    # the engine's mode: one scale per output channel (requantized), one per token
+    wq1, ws1 = w8a8.weight_from_q8(q8, 5120)
+    xq1, xs1 = oracle.quant_rows(np_bits(x))
+    ref1 = oracle.w8a8_gemm(xq1, xs1, wq1.numpy(), ws1.numpy(), 5120, 0)
+    q1 = torch.empty(16, 5120, dtype=torch.int8, device=dev)
+    s1 = torch.empty(16, dtype=torch.float32, device=dev)
+    quant.rows_q8(x.to(dev), None, q1, s1, n_rows(16, dev), 16)
+    assert same(q1, xq1) and same(s1, xs1.reshape(-1))
+    out1 = torch.zeros(16, 5120, dtype=torch.bfloat16, device=dev)
+    w8a8.gemm(q1, s1, wq1.to(dev), ws1.to(dev).view(-1), out1, n_rows(16, dev), 5120)
+    assert same(out1, bf16_from_bits(ref1)), first_diff(np_bits(out1), ref1)
