@@ -1,0 +1,419 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized linear-layer hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W]            this build (prism_b200)
+    python bench.py --impl reference [--gpus N] ...                 the reference's CPU arithmetic on the host cores
+    python bench.py --detail                                        per-shape table (GEMM TOPS / decode GB/s), no JSON line
+
+Workload (config "w8a8-27b-layer-set"): 4 decoder layers of the 27B-class linear set (q|k|v 7168x5120, o 5120x5120,
+gate|up 34816x5120, down 5120x17408; W8A8 with one scale per token and per output row, the engine's mode) over M = 8192
+rows, every GEMM fed by its activation quantizer (prism_b200.linear_stack).  A step is one pass.  The metric is int8
+GEMM throughput in TOPS = 2 * M * sum(N * K) * layers / time (the quantizers' work is not counted as ops).
+With --gpus N the same pass runs tensor-parallel over N ranks (column- / row-parallel, int32 all-reduce): total work
+is fixed, so scaling is "strong".  Weights (1.3 GB) and activations exceed the 126 MB L2, so nothing is served from a
+warm cache between steps.  Synthetic data: seeded N(0, 0.02^2) weights through Q8_0, N(0, 1) residual rows.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LAYERS = 4
+M_DEFAULT = 8192
+METRIC = "w8a8_int8_gemm_throughput"
+UNIT = "TOPS"
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm=p["hbm_gbs"], bf16=p["bf16_tflops_sustained"], bf16_burst=p["bf16_tflops"], src="measured")
+    return dict(hbm=6650.0, bf16=1400.0, bf16_burst=1590.0, src="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows, self.proc, self.index = [], None, index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = sorted(float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 9 and r[5 + i].lower().startswith("active")
+                                                         for r in self.rows)]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------------ CPU arm
+_CPU = {}
+
+
+def cpu_layer_pass(rows):
+    """One layer of the same linear set through the reference's CPU emulation (oracle/emulation.py: fake-quantized
+    operands multiplied in fp32 by torch on every host core) for `rows` of the workload's rows.  Returns
+    (seconds, ops, threads)."""
+    import torch
+
+    from oracle import emulation
+    if "set" not in _CPU:
+        _CPU["set"] = emulation.LayerSet()
+    ls = _CPU["set"]
+    h = torch.randn(rows, 5120, generator=torch.Generator().manual_seed(rows))
+    dt, ops, _ = ls.run(h)
+    return dt, ops, ls.threads
+
+
+CPU_SAMPLE_ROWS = 256
+
+
+def run_reference(args):
+    """The reference arm: the reference's CPU emulation of the path (restated in oracle/emulation.py; the reference's own
+    is Python that needs its model files) on every host core, a bounded sample of the workload per step."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    rows = CPU_SAMPLE_ROWS                              # sample: 256 of the 8192 rows through one of the 4 layers
+    for _ in range(args.warmup):
+        cpu_layer_pass(rows)
+    t = []
+    for _ in range(args.steps):
+        dt, ops, cores = cpu_layer_pass(rows)
+        t.append(dt)
+    sec = sum(t) / len(t)
+    val = ops / sec / 1e12
+    line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "s8", "data": "synthetic",
+            "config": {"workload": "w8a8-27b-layer-set", "rows": M_DEFAULT, "layers": LAYERS,
+                       "l2": "inputs larger than L2"},
+            "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
+                             "sample": f"{rows} of {M_DEFAULT} rows through 1 of {LAYERS} layers per step"},
+            "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------------ GPU arm
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    from prism_b200 import _lib, linear_stack as LS, tp
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    _lib.lib()
+    group = None
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        group = tp.Group(rank, world, backend="nccl", local_rank=local)
+    M = args.rows
+    layers = []
+    for i in range(LAYERS):
+        whole = LS.make_layer_weights(i, dev)
+        layers.append(LS.shard_layer(whole, world, rank))
+        del whole
+    torch.cuda.empty_cache()
+    stack = LS.LinearStack(layers, M, dev, group)
+    gen = torch.Generator(device=dev).manual_seed(5)
+    h0 = torch.randn(M, LS.HIDDEN, generator=gen, device=dev)
+    ops = LS.OPS_PER_ROW_LAYER * M * LAYERS
+
+    def sync():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        stack(h0)
+    sync()
+    code, where = _lib.device_status()
+    if code:
+        raise SystemExit(f"device status {code} at {where:#x}")
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    # ---- device-resident timing
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    e0.record()
+    for _ in range(args.steps):
+        stack(h0)
+    e1.record()
+    sync()
+    ms = e0.elapsed_time(e1) / args.steps
+    # ---- per-GEMM durations for the roofline (events around each launch, same stream)
+    gemm_ms = time_gemms(stack, h0, args.steps) if world == 1 else None
+    # ---- end to end: host buffers, copies inside the timed region, pipelined over three streams
+    e2e_ms, h2d, d2h = time_e2e(stack, h0, args.steps, sync)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = t.tolist()
+    if rank == 0:
+        pk = peaks()
+        value = ops / (ms * 1e-3) / 1e12
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+                "vs_baseline": None, "dtype": "s8", "data": "synthetic",
+                "config": {"workload": "w8a8-27b-layer-set", "rows": M, "layers": LAYERS,
+                           "parallelism": f"tp{world}", "l2": "inputs larger than L2 (1.3 GB of weights per pass)"},
+                "e2e": {"value": ops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                        "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
+                "gpu_launches": launches_per_step(world) * args.steps, "clocks": clocks}
+        if gemm_ms is not None:
+            achieved = ops / (gemm_ms * 1e-3) / 1e12
+            peak = 2.0 * pk["bf16"]
+            line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                                "frac": achieved / peak, "traffic": None,
+                                "kernel": "w8a8_tile_kernel<256>", "gemm_ms_per_step": gemm_ms,
+                                "peak_note": f"2 x {pk['src']} sustained bf16 ({pk['bf16']}): the int8 tcgen05 rate is "
+                                             "twice the bf16 rate; nominal dense int8 is 4500"}
+        if world == 1 and not args.no_cpu:
+            rows = CPU_SAMPLE_ROWS
+            cpu_layer_pass(rows)
+            dt, cops, cores = min(cpu_layer_pass(rows) for _ in range(3))
+            line["cpu_baseline"] = {"value": cops / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
+                                    "sample": f"{rows} of {M} rows through 1 of {LAYERS} layers"}
+        print(json.dumps(line), flush=True)
+    if group is not None:
+        sync()
+        group.close()
+
+
+def launches_per_step(world):
+    # per layer: 2 rows_q8 + rows_q8(attn) + swiglu + 4 GEMMs (+ fold per row-parallel projection and second quantizer
+    # passes when tensor parallel)
+    per_layer = 8 + (4 if world > 1 else 0)
+    return per_layer * LAYERS
+
+
+def time_gemms(stack, h0, steps):
+    """Sum of the GEMM kernels' durations per step: CUDA events around each w8a8.gemm call of a pass."""
+    import torch
+
+    from prism_b200 import w8a8
+    events = []
+    orig = w8a8.gemm
+
+    def timed(*a, **k):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        r = orig(*a, **k)
+        e.record()
+        events.append((s, e))
+        return r
+    w8a8.gemm = timed
+    try:
+        for _ in range(steps):
+            stack(h0)
+        torch.cuda.synchronize()
+    finally:
+        w8a8.gemm = orig
+    return sum(s.elapsed_time(e) for s, e in events) / steps
+
+
+def time_e2e(stack, h0, steps, sync):
+    """Host -> device copy of every step's input rows from pinned memory and device -> host copy of its result, inside
+    the timed region; copies of neighbouring steps overlap the compute on their own streams (two device buffers)."""
+    import torch
+    dev = h0.device
+    host_in = h0.cpu().pin_memory()
+    host_out = torch.empty_like(host_in).pin_memory()
+    d_in = [torch.empty_like(h0) for _ in range(2)]
+    d_out = [torch.empty_like(h0) for _ in range(2)]
+    s_in, s_out, s_c = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.current_stream(dev)
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_c = [torch.cuda.Event() for _ in range(2)]
+    ev_free_in = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+    sync()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record(s_c)
+    s_in.wait_stream(s_c)
+    s_out.wait_stream(s_c)
+    for i in range(steps):
+        b = i & 1
+        with torch.cuda.stream(s_in):
+            if i >= 2:
+                s_in.wait_event(ev_free_in[b])
+            d_in[b].copy_(host_in, non_blocking=True)
+            ev_in[b].record(s_in)
+        s_c.wait_event(ev_in[b])
+        if i >= 2:
+            s_c.wait_event(ev_out[b])
+        out = stack(d_in[b])
+        ev_free_in[b].record(s_c)
+        d_out[b].copy_(out, non_blocking=True)
+        ev_c[b].record(s_c)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_c[b])
+            host_out.copy_(d_out[b], non_blocking=True)
+            ev_out[b].record(s_out)
+    s_c.wait_stream(s_out)
+    s_c.wait_stream(s_in)
+    t1.record(s_c)
+    sync()
+    nbytes = h0.numel() * h0.element_size()
+    return t0.elapsed_time(t1) / steps, nbytes, nbytes
+
+
+
+# ------------------------------------------------------------------------------------------------------ detail table
+SHAPES = {"qkv": (7168, 5120, 0), "o": (5120, 5120, 1), "gate_up": (34816, 5120, 0), "down": (5120, 17408, 1)}
+
+
+def graph_time(fn_of_copy, copies, iters=None, reps=5):
+    """Microseconds per call: a CUDA graph of back-to-back calls cycling over `copies` operand sets (so weights
+    stream from HBM, not from L2), best of `reps` replays, CUDA events around each replay."""
+    import torch
+    iters = iters or max(copies, 8)
+    for c in range(copies):
+        fn_of_copy(c)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(iters):
+            fn_of_copy(i % copies)
+    best = 1e30
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) * 1e3 / iters)
+    return best
+
+
+def run_detail(args):
+    """Per projection shape and row count: time, TOPS, algorithmic GB/s (weights at GGUF Q8_0 density for gk = 32, int8
+    + one fp32 scale per row for gk = K) and the fractions of the measured peaks.  One JSON object per line."""
+    import torch
+
+    from prism_b200 import _lib, quant, w8a8
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    pk = peaks()
+    L2 = 126 << 20
+    rows_list = [int(x) for x in (args.detail_rows or "1,8,16,64,256,2048,8192").split(",")]
+    only = args.detail_shapes.split(",") if args.detail_shapes else list(SHAPES)
+    gks = [int(x) for x in (args.detail_gk or "0").split(",")]            # 0 = one group (gk == K)
+    gen = torch.Generator(device=dev).manual_seed(1)
+    for name in only:
+        N, K, epi = SHAPES[name]
+        copies = max(4, -(-3 * L2 // (N * K)))
+        ws = [torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev, generator=gen) for _ in range(copies)]
+        for gk in gks:
+            G = 1 if gk == 0 else K // gk
+            sw = torch.rand(N, G, device=dev, generator=gen) * 1e-3
+            for M in rows_list:
+                if gk and M > 256:
+                    continue
+                a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev, generator=gen)
+                sa = torch.rand(M, G, device=dev, generator=gen) * 1e-2
+                nr = torch.tensor([M], dtype=torch.int32, device=dev)
+                out = torch.zeros(M, N, dtype=torch.bfloat16 if epi == 0 else torch.float32, device=dev)
+                slots = torch.zeros(4, M, N, dtype=torch.int32, device=dev) if (epi == 1 and M <= 64 and not gk) else None
+                pend = {}
+
+                def call(c):
+                    pend[0] = w8a8.gemm(a, sa, ws[c], sw, out, nr, gk or K, epi=epi, slots=slots,
+                                        cfg=args.detail_split)
+                call(0)
+                us = graph_time(call, copies)
+                fold_us = 0.0
+                if pend[0] is not None:
+                    fold_us = graph_time(lambda c: quant.fold(out, slots, pend[0], nr, M), 1, iters=8)
+                ops = 2.0 * M * N * K
+                wbytes = N * K * 34 / 32 if gk == 32 else N * K + 4 * N
+                obytes = (2 if epi == 0 else 8) * M * N if pend[0] is None else 4 * pend[0].n * M * N
+                abytes = M * K + 4 * M * G
+                gbs = (wbytes + abytes + obytes) / us / 1e3
+                print(json.dumps({"shape": name, "N": N, "K": K, "M": M, "gk": gk or K, "epi": epi,
+                                  "split": None if pend[0] is None else pend[0].n, "us": round(us, 2),
+                                  "fold_us": round(fold_us, 2), "tops": round(ops / us / 1e6, 1),
+                                  "gbs": round(gbs, 1), "frac_hbm_measured": round(gbs / pk["hbm"], 3),
+                                  "frac_int8_2x_bf16_sustained": round(ops / us / 1e6 / (2 * pk["bf16"]), 3)}),
+                      flush=True)
+        del ws
+        torch.cuda.empty_cache()
+    # activation quantizers
+    for T, K in ((8192, 5120), (8192, 17408), (64, 5120)):
+        x = torch.randn(T, K, device=dev, generator=gen).to(torch.bfloat16)
+        q = torch.empty(T, K, dtype=torch.int8, device=dev)
+        s = torch.empty(T, device=dev)
+        nr = torch.tensor([T], dtype=torch.int32, device=dev)
+        us = graph_time(lambda c: quant.rows_q8(x, None, q, s, nr, T), 1, iters=8)
+        b = 3.0 * T * K + 4 * T
+        print(json.dumps({"kernel": "rows_q8", "T": T, "K": K, "us": round(us, 2), "gbs": round(b / us / 1e3, 1),
+                          "frac_hbm_measured": round(b / us / 1e3 / pk["hbm"], 3)}), flush=True)
+    code, where = _lib.device_status()
+    print(json.dumps({"device_status": code, "where": where}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="prism_b200", choices=["prism_b200", "reference"])
+    ap.add_argument("--rows", type=int, default=M_DEFAULT)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--detail", action="store_true", help="per-shape GEMM table instead of the JSON line")
+    ap.add_argument("--detail-rows", default=None)
+    ap.add_argument("--detail-shapes", default=None)
+    ap.add_argument("--detail-gk", default=None, help="comma list; 0 = one group per row (gk == K), 32 = Q8_0 blocks")
+    ap.add_argument("--detail-split", type=int, default=None)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    elif args.detail:
+        run_detail(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

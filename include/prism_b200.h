@@ -61,9 +61,10 @@ int pb_fold(float* h, long ldh, const int32_t* slots, long slot_stride, int S, c
 
 /* Per-token activation quantization.  Replaces quant.rows_q8 (kernels/quant.py:287-309, :481-486; gk == K, optional
  * SmoothQuant factors inv_s [K], tensor-parallel modes 1 / 2 with amax [rows]) and w8a8.quant_rows
- * (kernels/w8a8.py:101-112, :264-271; gk in {32, 64, 128, 256}).  x bf16 (x_fp32 = 0) or fp32 [T, K]. */
-int pb_quant_rows(const void* x, int x_fp32, const float* inv_s, int8_t* q, float* s, const int* n_rows, int T,
-                  int K, int gk, int mode, float* amax, void* stream);
+ * (kernels/w8a8.py:101-112, :264-271; gk in {32, 64, 128, 256}).  x bf16 (x_fp32 = 0) or fp32 [T, K] with row
+ * stride ldx elements (a column slice of a wider buffer when ldx > K; gk == K only). */
+int pb_quant_rows(const void* x, int x_fp32, long ldx, const float* inv_s, int8_t* q, float* s, const int* n_rows,
+                  int T, int K, int gk, int mode, float* amax, void* stream);
 
 /* SwiGLU + per-token quantization.  Replaces quant.swiglu_q8 (kernels/quant.py:249-284, :473-478):
  * gu bf16 [T, 2 FF] -> q int8 [T, FF], s fp32 [T].  FF % 8 == 0. */

@@ -193,14 +193,14 @@ bool div_full() {
 }
 
 template <int VPT>
-void launch_rows(bool bf16, bool full, int threads, const void* x, const float* inv_s, int8_t* q, float* s,
+void launch_rows(bool bf16, bool full, int threads, const void* x, long ldx, const float* inv_s, int8_t* q, float* s,
                         const int* n_rows, int T, int K, int mode, float* amax, cudaStream_t st) {
     if (bf16) {
-        if (full) quant::rows_q8_kernel<VPT, true, true><<<T, threads, 0, st>>>(x, inv_s, q, s, n_rows, K, mode, amax);
-        else quant::rows_q8_kernel<VPT, true, false><<<T, threads, 0, st>>>(x, inv_s, q, s, n_rows, K, mode, amax);
+        if (full) quant::rows_q8_kernel<VPT, true, true><<<T, threads, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax);
+        else quant::rows_q8_kernel<VPT, true, false><<<T, threads, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax);
     } else {
-        if (full) quant::rows_q8_kernel<VPT, false, true><<<T, threads, 0, st>>>(x, inv_s, q, s, n_rows, K, mode, amax);
-        else quant::rows_q8_kernel<VPT, false, false><<<T, threads, 0, st>>>(x, inv_s, q, s, n_rows, K, mode, amax);
+        if (full) quant::rows_q8_kernel<VPT, false, true><<<T, threads, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax);
+        else quant::rows_q8_kernel<VPT, false, false><<<T, threads, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax);
     }
 }
 
@@ -322,14 +322,14 @@ int pb_fold(float* h, long ldh, const int32_t* slots, long slot_stride, int S, c
     return PB_OK;
 }
 
-int pb_quant_rows(const void* x, int x_fp32, const float* inv_s, int8_t* q, float* s, const int* n_rows, int T,
-                  int K, int gk, int mode, float* amax, void* stream) {
+int pb_quant_rows(const void* x, int x_fp32, long ldx, const float* inv_s, int8_t* q, float* s, const int* n_rows,
+                  int T, int K, int gk, int mode, float* amax, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     if (!x || !q || !s || !n_rows || T <= 0 || K <= 0 || gk <= 0 || K % gk) return PB_BAD_ARGUMENT;
-    if (mode < 0 || mode > 2 || (mode != 0 && !amax)) return PB_BAD_ARGUMENT;
+    if (mode < 0 || mode > 2 || (mode != 0 && !amax) || ldx < K) return PB_BAD_ARGUMENT;
     const bool bf16 = !x_fp32, full = div_full();
     if (gk != K) {
-        if (inv_s || mode != 0) return PB_UNSUPPORTED_SHAPE;
+        if (inv_s || mode != 0 || ldx != K) return PB_UNSUPPORTED_SHAPE;
         if (gk != 32 && gk != 64 && gk != 128 && gk != 256) return PB_UNSUPPORTED_SHAPE;
         if (!aligned16(x) || ((uintptr_t)q & 7)) return PB_BAD_ARGUMENT;
         dim3 grid((K / 8 + 255) / 256, T);
@@ -343,14 +343,14 @@ int pb_quant_rows(const void* x, int x_fp32, const float* inv_s, int8_t* q, floa
         PB_CUDA(cudaGetLastError());
         return PB_OK;
     }
-    const bool fast = K % 8 == 0 && K <= 32768 && aligned16(x) && !((uintptr_t)q & 7) && (!inv_s || aligned16(inv_s));
+    const bool fast = K % 8 == 0 && K <= 32768 && aligned16(x) && (ldx * (bf16 ? 2 : 4)) % 16 == 0 && !((uintptr_t)q & 7) && (!inv_s || aligned16(inv_s));
     if (!fast) {
         if (bf16) {
-            if (full) quant::rows_q8_generic_kernel<true, true><<<T, 256, 0, st>>>(x, inv_s, q, s, n_rows, K, mode, amax);
-            else quant::rows_q8_generic_kernel<true, false><<<T, 256, 0, st>>>(x, inv_s, q, s, n_rows, K, mode, amax);
+            if (full) quant::rows_q8_generic_kernel<true, true><<<T, 256, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax);
+            else quant::rows_q8_generic_kernel<true, false><<<T, 256, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax);
         } else {
-            if (full) quant::rows_q8_generic_kernel<false, true><<<T, 256, 0, st>>>(x, inv_s, q, s, n_rows, K, mode, amax);
-            else quant::rows_q8_generic_kernel<false, false><<<T, 256, 0, st>>>(x, inv_s, q, s, n_rows, K, mode, amax);
+            if (full) quant::rows_q8_generic_kernel<false, true><<<T, 256, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax);
+            else quant::rows_q8_generic_kernel<false, false><<<T, 256, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax);
         }
         PB_CUDA(cudaGetLastError());
         return PB_OK;
@@ -358,7 +358,7 @@ int pb_quant_rows(const void* x, int x_fp32, const float* inv_s, int8_t* q, floa
     const int nvec = K / 8;
     const int threads = nvec <= 1024 ? 128 : 256;
     const int vpt = (nvec + threads - 1) / threads;
-#define PB_ROWS(V) launch_rows<V>(bf16, full, threads, x, inv_s, q, s, n_rows, T, K, mode, amax, st)
+#define PB_ROWS(V) launch_rows<V>(bf16, full, threads, x, ldx, inv_s, q, s, n_rows, T, K, mode, amax, st)
     if (vpt <= 1) PB_ROWS(1);
     else if (vpt <= 2) PB_ROWS(2);
     else if (vpt <= 3) PB_ROWS(3);

@@ -81,7 +81,7 @@ __device__ __forceinline__ uint2 quant8(const float (&v)[8], float scale) {
 // One CTA per row, VPT vectors of 8 inputs per thread held in registers (K <= 8 * VPT * blockDim).
 template <int VPT, bool BF16, bool FULL>
 __global__ void __launch_bounds__(256)
-rows_q8_kernel(const void* __restrict__ x, const float* __restrict__ inv_s, int8_t* __restrict__ q,
+rows_q8_kernel(const void* __restrict__ x, long ldx, const float* __restrict__ inv_s, int8_t* __restrict__ q,
                float* __restrict__ s, const int* __restrict__ n_rows, int K, int mode, float* __restrict__ amax_io) {
     __shared__ float red[32];
     const long t = blockIdx.x;
@@ -93,7 +93,7 @@ rows_q8_kernel(const void* __restrict__ x, const float* __restrict__ inv_s, int8
     for (int i = 0; i < VPT; ++i) {
         const int c = threadIdx.x + i * blockDim.x;
         if (c < nvec) {
-            load8<BF16>(x, t * K + (long)c * 8, v[i]);
+            load8<BF16>(x, t * ldx + (long)c * 8, v[i]);
             if (inv_s) {
                 const float4 a = __ldg((const float4*)(inv_s + c * 8)), b = __ldg((const float4*)(inv_s + c * 8 + 4));
                 v[i][0] = __fmul_rn(v[i][0], a.x); v[i][1] = __fmul_rn(v[i][1], a.y);
@@ -120,14 +120,14 @@ rows_q8_kernel(const void* __restrict__ x, const float* __restrict__ inv_s, int8
 // Any K (no alignment assumed), two passes over the row (the second hits L2): the fallback for odd shapes.
 template <bool BF16, bool FULL>
 __global__ void __launch_bounds__(256)
-rows_q8_generic_kernel(const void* __restrict__ x, const float* __restrict__ inv_s, int8_t* __restrict__ q,
-                       float* __restrict__ s, const int* __restrict__ n_rows, int K, int mode,
+rows_q8_generic_kernel(const void* __restrict__ x, long ldx, const float* __restrict__ inv_s,
+                       int8_t* __restrict__ q, float* __restrict__ s, const int* __restrict__ n_rows, int K, int mode,
                        float* __restrict__ amax_io) {
     __shared__ float red[32];
     const long t = blockIdx.x;
     if (t >= *n_rows) return;
     auto val = [&](int k) {
-        float y = BF16 ? __bfloat162float(((const __nv_bfloat16*)x)[t * K + k]) : ((const float*)x)[t * K + k];
+        float y = BF16 ? __bfloat162float(((const __nv_bfloat16*)x)[t * ldx + k]) : ((const float*)x)[t * ldx + k];
         return inv_s ? __fmul_rn(y, inv_s[k]) : y;
     };
     float amax = 0.0f;

@@ -410,9 +410,15 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             bool ok = true;
             for (int i = 0; i < nkb && ok; ++i) {
                 if (GROUPED) {
-                    if (!mbar_wait(smem_u32(&aux->tempty[ring]), rphase ^ 1, abort_flag, 0x600 + ring)) break;
+                    if (!mbar_wait(smem_u32(&aux->tempty[ring]), rphase ^ 1, abort_flag, 0x600 + ring)) {
+                        ok = false;
+                        break;
+                    }
                 }
-                if (!mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, 0x700 + stage)) break;
+                if (!mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, 0x700 + stage)) {
+                    ok = false;
+                    break;
+                }
                 tc_fence_after();
                 uint8_t* st = smem + stage * C::STAGE_BYTES;
                 const uint64_t ad = umma_desc_k128(smem_u32(st));

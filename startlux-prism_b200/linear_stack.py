@@ -1,0 +1,106 @@
+"""The decoder-layer linear set of the 27B-class model as one callable pass: the workload of the benchmark and of the
+tensor-parallel identity tests.  Per layer, on an fp32 residual stream h [M, hidden]:
+
+    rows_q8(h)                        -> int8 input of q|k|v                (stand-in for norm_q8: no RMSNorm weight)
+    q|k|v  GEMM, column-parallel      -> bf16 [M, 7168 / n]
+    mixer stand-in                    -> this rank's q columns of that output (attention itself is not on the path)
+    quantize_rows(rows_q8)            -> int8, scale from the row maximum over all ranks
+    o      GEMM, row-parallel         -> h += ...   (one rank: fused residual epilogue; more: int32 sums, all-reduce, fold)
+    rows_q8(h)                        -> int8 input of gate|up
+    gate|up GEMM, column-parallel     -> bf16 [M, 34816 / n]
+    quantize_rows(swiglu_q8)          -> int8 [M, 17408 / n]
+    down   GEMM, row-parallel         -> h += ...
+
+Weights are quantized whole (Q8_0 -> one scale per output row) and sliced afterwards, so every rank count computes the
+single-GPU bits.  All buffers are allocated at construction; a pass allocates nothing and can be graph-captured.
+"""
+import torch
+
+from . import quant, synth, tp, w8a8
+
+HIDDEN, Q_COLS, KV_COLS, FFN = 5120, 5120, 1024, 17408
+OPS_PER_ROW_LAYER = 2 * (HIDDEN * (Q_COLS + 2 * KV_COLS) + Q_COLS * HIDDEN + HIDDEN * 2 * FFN + FFN * HIDDEN)
+
+
+def make_layer_weights(layer, device, hidden=HIDDEN, q_cols=Q_COLS, kv_cols=KV_COLS, ffn=FFN, seed_cfg=1):
+    """Whole-matrix W8A8 weights of one layer: dict name -> (int8 [N, K], fp32 [N]).  N(0, 0.02^2) values drawn on
+    `device` from a seeded generator, quantized to Q8_0 (ggml's rule) and requantized to one scale per output row
+    (w8a8.weight_from_q8 with gk == K, the engine's mode)."""
+    shapes = {"qkv": (q_cols + 2 * kv_cols, hidden), "o": (hidden, q_cols), "gate_up": (2 * ffn, hidden),
+              "down": (hidden, ffn)}
+    out = {}
+    for i, (name, (n, k)) in enumerate(shapes.items()):
+        g = torch.Generator(device=device).manual_seed(synth.seed_w(seed_cfg, i) + 97 * layer)
+        wq = torch.empty(n, k, dtype=torch.int8, device=device)
+        ws = torch.empty(n, dtype=torch.float32, device=device)
+        for r0 in range(0, n, 4096):                                   # in row chunks: bounded temporary memory
+            w = torch.randn(min(4096, n - r0), k, generator=g, device=device) * 0.02
+            q, s = w8a8.weight_from_q8(synth.q8_0(w), k)
+            wq[r0:r0 + w.shape[0]], ws[r0:r0 + w.shape[0]] = q, s.view(-1)
+        out[name] = (wq, ws)
+    return out
+
+
+def shard_layer(whole, n, r, hidden=HIDDEN, q_cols=Q_COLS, kv_cols=KV_COLS, ffn=FFN):
+    """Rank r's slices of a layer's whole weights (rows of the column-parallel ones, input columns of the others)."""
+    if n == 1:
+        return whole
+    idx = tp.linear_shards(q_cols, kv_cols, ffn, n, r)
+    dev = whole["qkv"][0].device
+    ix = {k: v.to(dev) for k, v in idx.items()}
+    return {"qkv": (whole["qkv"][0][ix["qkv"]].contiguous(), whole["qkv"][1][ix["qkv"]].contiguous()),
+            "o": (whole["o"][0][:, ix["o"]].contiguous(), whole["o"][1]),
+            "gate_up": (whole["gate_up"][0][ix["gu"]].contiguous(), whole["gate_up"][1][ix["gu"]].contiguous()),
+            "down": (whole["down"][0][:, ix["down"]].contiguous(), whole["down"][1])}
+
+
+class LinearStack:
+    def __init__(self, layers, M, device, group=None, hidden=HIDDEN, q_cols=Q_COLS, kv_cols=KV_COLS, ffn=FFN):
+        """layers: list of per-rank weight dicts (shard_layer).  group: tp.Group or None."""
+        self.layers, self.M, self.g = layers, M, group
+        n = group.world if group is not None else 1
+        self.n, self.hidden = n, hidden
+        self.ql, self.kvl, self.fl = q_cols // n, kv_cols // n, ffn // n
+        i8, f32, bf = torch.int8, torch.float32, torch.bfloat16
+        e = lambda *s, dtype: torch.empty(*s, dtype=dtype, device=device)             # noqa: E731
+        self.h = e(M, hidden, dtype=f32)
+        self.xq, self.xs = e(M, hidden, dtype=i8), e(M, dtype=f32)
+        self.qkv = e(M, self.ql + 2 * self.kvl, dtype=bf)
+        self.aq, self.as_ = e(M, self.ql, dtype=i8), e(M, dtype=f32)
+        self.gu = e(M, 2 * self.fl, dtype=bf)
+        self.dq, self.ds = e(M, self.fl, dtype=i8), e(M, dtype=f32)
+        self.amax = e(M, dtype=f32)
+        self.parts = torch.zeros(tp.parts_elems(M, hidden), dtype=torch.int32, device=device)
+        self.n_rows = torch.tensor([M], dtype=torch.int32, device=device)
+
+    def __call__(self, h_in):
+        """One pass: h_in fp32 [M, hidden] is copied into the working residual, which is returned (a view of an
+        internal buffer, overwritten by the next pass)."""
+        M, nr, g = self.M, self.n_rows, self.g
+        self.h.copy_(h_in, non_blocking=True)
+        pend = None
+        for lw in self.layers:
+            quant.fold(self.h, self.parts, pend, nr, M)
+            quant.rows_q8(self.h, None, self.xq, self.xs, nr, M)
+            w8a8.gemm(self.xq, self.xs, *lw["qkv"], self.qkv, nr, self.hidden)
+            tp.quantize_rows(g if self.n > 1 else None, quant.rows_q8, M, self.amax, self.qkv[:, :self.ql], None,
+                             self.aq, self.as_, nr, M)
+            pend = self._out(self.aq, self.as_, lw["o"])
+            quant.fold(self.h, self.parts, pend, nr, M)
+            quant.rows_q8(self.h, None, self.xq, self.xs, nr, M)
+            w8a8.gemm(self.xq, self.xs, *lw["gate_up"], self.gu, nr, self.hidden)
+            tp.quantize_rows(g if self.n > 1 else None, quant.swiglu_q8, M, self.amax, self.gu, None, self.dq,
+                             self.ds, nr, M)
+            pend = self._out(self.dq, self.ds, lw["down"])
+        quant.fold(self.h, self.parts, pend, nr, M)
+        return self.h
+
+    def _out(self, a, a_s, wt):
+        """A row-parallel projection into the residual: one rank adds in the GEMM's epilogue (or defers a K split to
+        the fold); several ranks all-reduce int32 sums and fold."""
+        w, w_s = wt
+        if self.n > 1:
+            return tp.out_proj(self.g, a, a_s, w, w_s, self.parts, self.M, self.n_rows)
+        S_max = tp.MAX_SPLIT if self.M <= tp.SPLIT_ROWS else 1
+        slots = self.parts[:S_max * self.M * self.hidden].view(S_max, self.M, self.hidden)
+        return w8a8.gemm(a, a_s, w, w_s, self.h, self.n_rows, a.shape[1], epi=1, slots=slots)

@@ -27,14 +27,14 @@ def _mode_args(mode, amax, sync, T):
 
 
 def rows_q8(x, inv_s, q, s, n, T, mode=0, amax=None, sync=None):
-    """x bf16 / fp32 [>= T, K], inv_s fp32 [K] or None -> q int8 [>= T, K], s fp32 [>= T]; n: device int32 live rows."""
+    """x bf16 / fp32 [>= T, K] (rows may be strided: a column slice of a wider buffer), inv_s fp32 [K] or None ->
+    q int8 [>= T, K], s fp32 [>= T]; n: device int32 live rows."""
     K = q.shape[1]
     _lib.need_cuda(x, q, s, n)
     amax = _mode_args(mode, amax, sync, T)
-    if x.dtype not in (torch.bfloat16, torch.float32) or x.shape[1] != K or not x.is_contiguous() \
-            or not q.is_contiguous():
-        raise RuntimeError("rows_q8: x must be contiguous bf16 / fp32 [T, K] matching q")
-    rc = _lib.lib().pb_quant_rows(_lib.ptr(x), int(x.dtype == torch.float32), _lib.ptr(inv_s), _lib.ptr(q),
+    if x.dtype not in (torch.bfloat16, torch.float32) or x.shape[1] != K or x.stride(1) != 1 or not q.is_contiguous():
+        raise RuntimeError("rows_q8: x must be bf16 / fp32 [T, K] with unit column stride, matching q")
+    rc = _lib.lib().pb_quant_rows(_lib.ptr(x), int(x.dtype == torch.float32), x.stride(0), _lib.ptr(inv_s), _lib.ptr(q),
                                   _lib.ptr(s), _lib.ptr(n), T, K, K, mode, _lib.ptr(amax), _lib.stream())
     _lib.check(rc, f"rows_q8 T={T} K={K} mode={mode}")
 

@@ -1,0 +1,156 @@
+"""Tensor-parallel sharded linears: the reference's tp.py sharding rules and the two exchange steps of a row-parallel
+projection, one process per GPU over torch.distributed (NCCL over NVLink; gloo on CPU for tests of the host logic).
+
+    shard_config(cfg, n), shard_index(cfg, n, r)     which rows / columns a rank holds          (tp.py:83-125)
+    Group(rank, world, ...)                          process group: sum_, max_                   (tp.py:333-357, :435-439)
+    quantize_rows(g, fn, rows, amax, *args)          global row maximum before quantizing        (tp.py:143-156)
+    out_proj(g, a, a_s, w, w_s, flat, rows, n_rows)  int32 partial sums -> all-reduce -> Deferred (tp.py:159-180)
+
+Exactness (tp.py:24-31): weights are quantized whole and then sliced; a column-parallel output is a whole-K dot
+product; a row-parallel projection all-reduces int32 partial sums (exact in any order, so NCCL's algorithm choice
+cannot change a bit) and the residual's next reader scales the total once; a row-parallel input's per-token scale is
+the max over all ranks (exact).  Outputs are therefore bit-identical at every GPU count, 8 included: unlike the
+reference's in-kernel protocols (4 ranks at most) nothing here depends on the group size.
+
+Not built (engine orchestration, outside the linear-layer path): the shared-memory channel to follower processes, the
+mirrored-object RPC, the fused in-kernel exchanges over symmetric memory (quant.Sync).
+"""
+from __future__ import annotations
+
+import dataclasses
+import os
+
+import torch
+import torch.distributed as dist
+
+SPLIT_ROWS = 512      # output projections split K into several int32 slots only up to this many rows
+MAX_SPLIT = 4
+
+
+def shard_config(cfg, n):
+    """The config of one rank's shard: its heads and FFN columns; v_heads_full keeps the whole model's value heads."""
+    for what, v in (("attention heads", cfg.n_head), ("kv heads", cfg.n_kv_head),
+                    ("linear-attention key heads", cfg.k_heads), ("FFN width", cfg.ffn)):
+        if v % n:
+            raise ValueError(f"--tp {n} does not divide the model's {v} {what}")
+    if cfg.v_heads % cfg.k_heads:
+        raise ValueError("value heads must be a multiple of key heads")
+    c = dataclasses.replace(cfg, n_head=cfg.n_head // n, n_kv_head=cfg.n_kv_head // n, k_heads=cfg.k_heads // n,
+                            v_heads=cfg.v_heads // n, ffn=cfg.ffn // n)
+    c.v_heads_full = cfg.v_heads
+    c.tp = n
+    return c
+
+
+def shard_index(cfg, n, r):
+    """Rank r's rows of the column-parallel projections and columns of the row-parallel ones, as int64 indices over the
+    whole model's tensors, in the order the rank's kernels read them:
+      qkv   attention: the q|gate rows of its heads (2 * head_dim rows per head), then its kv heads' k rows, then v rows
+      o     its heads' input columns
+      inp   linear attention: q and k channels of its key heads, the v channels of the value heads that read them (value
+            head m * k_heads + k reads key head k), their z rows, then their beta and alpha rows
+      conv  its conv channels;  vh its value heads;  out their input columns
+      gu    its gate columns then its up columns;  down their input columns."""
+    H, KV, HD = cfg.n_head, cfg.n_kv_head, cfg.head_dim
+    HK, HV, D, FF = cfg.k_heads, cfg.v_heads, cfg.gdn_dim, cfg.ffn
+    Hl, KVl, HKl, FFl = H // n, KV // n, HK // n, FF // n
+    span = lambda a, b: torch.arange(a, b, dtype=torch.int64)                        # noqa: E731
+    channels = lambda heads: (heads[:, None] * D + span(0, D)[None, :]).reshape(-1)  # noqa: E731
+    kh = span(r * HKl, (r + 1) * HKl)
+    vh = torch.cat([m * HK + kh for m in range(HV // HK)])
+    q_rows, conv_dim = H * 2 * HD, 2 * HK * D + HV * D
+    conv = torch.cat([channels(kh), HK * D + channels(kh), 2 * HK * D + channels(vh)])
+    return dict(
+        qkv=torch.cat([span(r * Hl * 2 * HD, (r + 1) * Hl * 2 * HD), q_rows + span(r * KVl * HD, (r + 1) * KVl * HD),
+                       q_rows + KV * HD + span(r * KVl * HD, (r + 1) * KVl * HD)]),
+        o=span(r * Hl * HD, (r + 1) * Hl * HD),
+        inp=torch.cat([conv, conv_dim + channels(vh), conv_dim + HV * D + vh, conv_dim + HV * D + HV + vh]),
+        conv=conv, vh=vh, out=channels(vh),
+        gu=torch.cat([span(r * FFl, (r + 1) * FFl), FF + span(r * FFl, (r + 1) * FFl)]),
+        down=span(r * FFl, (r + 1) * FFl))
+
+
+def linear_shards(q_cols, kv_cols, ffn, n, r):
+    """Index sets of the plain decoder-layer linear set (q | k | v fused, o, gate | up fused, down) for rank r of n:
+    qkv rows (its q columns, then its k, then its v columns; a rank holds 1 / n of each, so with n above the kv head
+    count a kv head's rows are split, which is exact: output rows are independent), o input columns (its q columns),
+    gu rows, down input columns."""
+    span = lambda a, b: torch.arange(a, b, dtype=torch.int64)                        # noqa: E731
+    for what, v in (("q columns", q_cols), ("kv columns", kv_cols), ("FFN width", ffn)):
+        if v % n:
+            raise ValueError(f"{n} ranks do not divide the {v} {what}")
+    ql, kl, fl = q_cols // n, kv_cols // n, ffn // n
+    return dict(qkv=torch.cat([span(r * ql, (r + 1) * ql), q_cols + span(r * kl, (r + 1) * kl),
+                               q_cols + kv_cols + span(r * kl, (r + 1) * kl)]),
+                o=span(r * ql, (r + 1) * ql),
+                gu=torch.cat([span(r * fl, (r + 1) * fl), ffn + span(r * fl, (r + 1) * fl)]),
+                down=span(r * fl, (r + 1) * fl))
+
+
+class Group:
+    """One rank of a tensor-parallel group.  backend "nccl": its GPU is cuda:local_rank, collectives run on the current
+    CUDA stream (capturable); backend "gloo": CPU tensors (tests).  Joins an already initialised default process group
+    (torchrun) or initialises one at 127.0.0.1:port."""
+
+    def __init__(self, rank, world, port=None, backend="nccl", local_rank=None, timeout_s=600):
+        self.rank, self.world, self.backend = rank, world, backend
+        if backend == "nccl":
+            self.device = torch.device("cuda", rank if local_rank is None else local_rank)
+            torch.cuda.set_device(self.device)
+        else:
+            self.device = torch.device("cpu")
+        if not dist.is_initialized():
+            import datetime
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            if port is not None:
+                os.environ["MASTER_PORT"] = str(port)
+            kw = dict(device_id=self.device) if backend == "nccl" else {}
+            dist.init_process_group(backend, rank=rank, world_size=world,
+                                    timeout=datetime.timedelta(seconds=timeout_s), **kw)
+        self.pg = dist.group.WORLD
+
+    def sum_(self, x):
+        if self.world > 1:
+            dist.all_reduce(x, op=dist.ReduceOp.SUM, group=self.pg)
+
+    def max_(self, x):
+        if self.world > 1:
+            dist.all_reduce(x, op=dist.ReduceOp.MAX, group=self.pg)
+
+    def barrier(self):
+        if self.world > 1:
+            dist.barrier(group=self.pg)
+
+    def close(self):
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def quantize_rows(g, fn, rows, amax, *args):
+    """The input of a row-parallel projection, quantized by fn (quant.rows_q8 / swiglu_q8) with the row's maximum over
+    all ranks: this rank's maxima stored (mode 1), max-all-reduced in `amax`, then the rows quantized (mode 2).  One
+    rank: the plain kernel."""
+    if g is None or g.world == 1:
+        fn(*args)
+        return
+    fn(*args, mode=1, amax=amax)
+    g.max_(amax[:rows])
+    fn(*args, mode=2, amax=amax)
+
+
+def out_proj(g, a, a_s, w, w_s, flat, rows, n_rows, pdl=0):
+    """A row-parallel output projection: this rank's int32 partial sums (w8a8.gemm_i32) into `flat` (int32 room for
+    parts_elems(rows, N) values), summed over the ranks, returned as the residual add the next quant.fold finishes."""
+    from . import w8a8 as KW
+    N = w.shape[0]
+    S_max = MAX_SPLIT if rows <= SPLIT_ROWS else 1
+    slots = flat[:S_max * rows * N].view(S_max, rows, N)
+    S = KW.gemm_i32(a, a_s, w, w_s, slots, n_rows, max_split=S_max, pdl=pdl)
+    if g is not None:
+        g.sum_(slots[:S])
+    return KW.Deferred(S, a_s, w_s, slots[:S])
+
+
+def parts_elems(rows, hidden):
+    """int32 elements out_proj needs for passes of up to `rows` rows."""
+    return max(MAX_SPLIT * min(rows, SPLIT_ROWS), rows) * hidden

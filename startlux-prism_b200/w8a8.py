@@ -60,6 +60,15 @@ def pick_split(M, N, K, limit=MAX_SPLIT):
     return max(1, min(limit, RESIDENT_CTAS // tiles, kb // 2))
 
 
+def effective_split(K, split):
+    """The K splits the few-rows kernel really runs for a request of `split`: whole 128-byte K blocks per slice, no
+    empty slice (the library applies the same rule)."""
+    kb = -(-K // 128)
+    split = max(1, min(split, kb))
+    per = -(-kb // split)
+    return -(-kb // per)
+
+
 def _call(a, a_s, w, w_s, out, ldo, n_rows, gk, epi, split, slot_stride=0, ws=None, counters=None):
     M, K = a.shape
     N = w.shape[0]
@@ -102,10 +111,9 @@ def gemm(a, a_s, w, w_s, out, n_rows, gk, epi=0, outs=None, cfg=None, slots=None
         _call(a, a_s, w, w_s, out, out.stride(0), n_rows, gk, epi, 1)
         return None
     split = int(cfg) if cfg is not None else pick_split(M, N, K)
-    if M > FEW_ROWS:
-        split = 1
+    split = effective_split(K, split) if M <= FEW_ROWS else 1
     if split > 1 and epi == EPI_ADD and slots is not None and slots.shape[1] >= M:
-        split = min(split, slots.shape[0])
+        split = effective_split(K, min(split, slots.shape[0]))
         if split > 1:
             _check_slots(slots, M, N)
             _call(a, a_s, w, w_s, slots, N, n_rows, gk, EPI_I32, split, slots.stride(0))
@@ -135,7 +143,7 @@ def gemm_i32(a, a_s, w, w_s, slots, n_rows, max_split=4, pdl=False, split=None):
     N = w.shape[0]
     _check_slots(slots, M, N)
     S = split if split is not None else pick_split(M, N, K, min(max_split, slots.shape[0]))
-    S = max(1, min(S, max_split, slots.shape[0])) if M <= FEW_ROWS else 1
+    S = effective_split(K, max(1, min(S, max_split, slots.shape[0]))) if M <= FEW_ROWS else 1
     _call(a, a_s, w, w_s, slots, N, n_rows, K, EPI_I32, S, slots.stride(0))
     return S
 
@@ -150,7 +158,7 @@ def quant_rows(x, gk, n_rows=None):
         n_rows = torch.tensor([M], dtype=torch.int32, device=x.device)
     if x.dtype not in (torch.bfloat16, torch.float32) or not x.is_contiguous():
         raise RuntimeError("quant_rows: x must be contiguous bf16 or fp32")
-    rc = _lib.lib().pb_quant_rows(_lib.ptr(x), int(x.dtype == torch.float32), None, _lib.ptr(q), _lib.ptr(s),
+    rc = _lib.lib().pb_quant_rows(_lib.ptr(x), int(x.dtype == torch.float32), K, None, _lib.ptr(q), _lib.ptr(s),
                                   _lib.ptr(n_rows), M, K, gk, 0, None, _lib.stream())
     _lib.check(rc, f"quant_rows M={M} K={K} gk={gk}")
     return q, s

@@ -53,7 +53,7 @@ def test_int32_slots_and_fold(dev, M, N, K, live):
     for split in ([1, 2, 4] if M <= 64 else [1]):
         slots = torch.full((4, M, N), -(1 << 30), dtype=torch.int32, device=dev)
         S = w8a8.gemm_i32(ad, sad, wd, swd, slots, nr, max_split=4, split=split)
-        assert S == split
+        assert S == w8a8.effective_split(K, split)
         tot = slots[:S, :live].sum(0, dtype=torch.int32)
         assert same(tot, exact[:live]), (split, first_diff(tot.cpu().numpy(), exact[:live]))
         assert bool((slots[:S, live:] == -(1 << 30)).all()) and bool((slots[S:] == -(1 << 30)).all())
@@ -65,7 +65,7 @@ def test_int32_slots_and_fold(dev, M, N, K, live):
         slots = torch.full((4, M, N), -(1 << 30), dtype=torch.int32, device=dev)
         res = base.to(dev)
         d = w8a8.gemm(ad, sad, wd, swd, res, nr, K, epi=1, slots=slots, cfg=4)
-        assert isinstance(d, w8a8.Deferred) and d.n == 4
+        assert isinstance(d, w8a8.Deferred) and d.n == w8a8.effective_split(K, 4)
         quant.fold(res, slots, d, nr, M)
         assert same(res, ref1)
 
