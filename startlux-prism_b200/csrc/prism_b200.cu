@@ -133,11 +133,11 @@ int launch_tile(const int8_t* a, const float* a_s, const int8_t* w, const float*
         if ((rc = set_smem(kern, C::SMEM))) return rc;
         configured = true;
     }
-    const int es = EPI == w8a8::EPI_BF16 ? 2 : 4;
-    const int vec_ok = aligned16(out) && (ldo * es) % 16 == 0;
+    // the coalesced epilogue moves 32-bit words: bf16 outputs need an even row stride and a 4-byte aligned base
+    const int word_ok = EPI == w8a8::EPI_BF16 ? (((uintptr_t)out & 3) == 0 && ldo % 2 == 0) : 1;
     const int tiles = ((M + 127) / 128) * ((N + BN - 1) / BN);
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    kern<<<grid, 192, C::SMEM, st>>>(ta, tw, a_s, w_s, out, ldo, n_rows, M, N, K, vec_ok);
+    kern<<<grid, 192, C::SMEM, st>>>(ta, tw, a_s, w_s, out, ldo, n_rows, M, N, K, word_ok);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }
@@ -343,7 +343,7 @@ int pb_quant_rows(const void* x, int x_fp32, long ldx, const float* inv_s, int8_
         PB_CUDA(cudaGetLastError());
         return PB_OK;
     }
-    const bool fast = K % 8 == 0 && K <= 32768 && aligned16(x) && (ldx * (bf16 ? 2 : 4)) % 16 == 0 && !((uintptr_t)q & 7) && (!inv_s || aligned16(inv_s));
+    const bool fast = K % 8 == 0 && K <= 65536 && aligned16(x) && (ldx * (bf16 ? 2 : 4)) % 16 == 0 && !((uintptr_t)q & 7) && (!inv_s || aligned16(inv_s));
     if (!fast) {
         if (bf16) {
             if (full) quant::rows_q8_generic_kernel<true, true><<<T, 256, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax);
@@ -355,21 +355,12 @@ int pb_quant_rows(const void* x, int x_fp32, long ldx, const float* inv_s, int8_
         PB_CUDA(cudaGetLastError());
         return PB_OK;
     }
+    // 4 vectors of 8 inputs per thread (8 beyond 32768 / 2 inputs), as many threads as the row needs
     const int nvec = K / 8;
-    const int threads = nvec <= 1024 ? 128 : 256;
-    const int vpt = (nvec + threads - 1) / threads;
-#define PB_ROWS(V) launch_rows<V>(bf16, full, threads, x, ldx, inv_s, q, s, n_rows, T, K, mode, amax, st)
-    if (vpt <= 1) PB_ROWS(1);
-    else if (vpt <= 2) PB_ROWS(2);
-    else if (vpt <= 3) PB_ROWS(3);
-    else if (vpt <= 4) PB_ROWS(4);
-    else if (vpt <= 5) PB_ROWS(5);
-    else if (vpt <= 6) PB_ROWS(6);
-    else if (vpt <= 8) PB_ROWS(8);
-    else if (vpt <= 10) PB_ROWS(10);
-    else if (vpt <= 12) PB_ROWS(12);
-    else PB_ROWS(16);
-#undef PB_ROWS
+    const int vpt = nvec <= 4096 ? 4 : 8;
+    const int threads = ((nvec + vpt - 1) / vpt + 31) / 32 * 32;
+    if (vpt == 4) launch_rows<4>(bf16, full, threads, x, ldx, inv_s, q, s, n_rows, T, K, mode, amax, st);
+    else launch_rows<8>(bf16, full, threads, x, ldx, inv_s, q, s, n_rows, T, K, mode, amax, st);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }
@@ -382,22 +373,10 @@ int pb_swiglu_q8(const void* gu, const float* inv_s, int8_t* q, float* s, const 
     if (FF % 8 || FF > 32768 || !aligned16(gu) || ((uintptr_t)q & 7)) return PB_UNSUPPORTED_SHAPE;
     const bool full = div_full();
     const int nvec = FF / 8;
-    const int threads = nvec <= 1024 ? 128 : 256;
-    const int vpt = (nvec + threads - 1) / threads;
+    const int threads = ((nvec + 3) / 4 + 31) / 32 * 32;          // 4 vectors of 8 outputs per thread
     const __nv_bfloat16* g = (const __nv_bfloat16*)gu;
-#define PB_SW(V)                                                                                              \
-    do {                                                                                                      \
-        if (full) quant::swiglu_q8_kernel<V, true><<<T, threads, 0, st>>>(g, inv_s, q, s, n_rows, FF, mode, amax); \
-        else quant::swiglu_q8_kernel<V, false><<<T, threads, 0, st>>>(g, inv_s, q, s, n_rows, FF, mode, amax);     \
-    } while (0)
-    if (vpt <= 1) PB_SW(1);
-    else if (vpt <= 2) PB_SW(2);
-    else if (vpt <= 4) PB_SW(4);
-    else if (vpt <= 6) PB_SW(6);
-    else if (vpt <= 9) PB_SW(9);
-    else if (vpt <= 12) PB_SW(12);
-    else PB_SW(16);
-#undef PB_SW
+    if (full) quant::swiglu_q8_kernel<4, true><<<T, threads, 0, st>>>(g, inv_s, q, s, n_rows, FF, mode, amax);
+    else quant::swiglu_q8_kernel<4, false><<<T, threads, 0, st>>>(g, inv_s, q, s, n_rows, FF, mode, amax);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }

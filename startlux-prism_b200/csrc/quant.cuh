@@ -69,18 +69,36 @@ __device__ __forceinline__ void load8(const void* x, long idx, float (&v)[8]) {
     }
 }
 
+// q = rint(v / scale) for 8 values, bit-identical to the IEEE division but cheaper: y' = v * (1 / scale) is within
+// 3e-5 of the true quotient for |quotient| <= 128, so rint(y') can differ from rint(v / scale) only when y' lies
+// within that distance of a rounding boundary k + 0.5; those (rare) values take the exact division.
 template <bool FULL>
-__device__ __forceinline__ uint2 quant8(const float (&v)[8], float scale) {
+__device__ __forceinline__ uint2 quant8(const float (&v)[8], float scale, float rcp) {
     int q[8];
+    if (FULL) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) q[i] = __float2int_rn(fdiv<FULL>(v[i], scale));
+        for (int i = 0; i < 8; ++i) q[i] = __float2int_rn(fdiv<true>(v[i], scale));
+    } else {
+        bool near = false;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float y = __fmul_rn(v[i], rcp);
+            const float r = rintf(y);
+            q[i] = (int)r;
+            near |= fabsf(fabsf(y - r) - 0.5f) < 1e-3f;
+        }
+        if (near) {                                             // rare: one branch per 8 values
+#pragma unroll
+            for (int i = 0; i < 8; ++i) q[i] = __float2int_rn(__fdiv_rn(v[i], scale));
+        }
+    }
     return make_uint2(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]));
 }
 
 // ------------------------------------------------------------------------------------------------- rows_q8
 // One CTA per row, VPT vectors of 8 inputs per thread held in registers (K <= 8 * VPT * blockDim).
 template <int VPT, bool BF16, bool FULL>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 rows_q8_kernel(const void* __restrict__ x, long ldx, const float* __restrict__ inv_s, int8_t* __restrict__ q,
                float* __restrict__ s, const int* __restrict__ n_rows, int K, int mode, float* __restrict__ amax_io) {
     __shared__ float red[32];
@@ -109,10 +127,11 @@ rows_q8_kernel(const void* __restrict__ x, long ldx, const float* __restrict__ i
     if (mode == MODE_STORE_AMAX && threadIdx.x == 0) amax_io[t] = amax;
     if (mode == MODE_USE_AMAX) amax = fmaxf(amax_io[t], amax);
     const float scale = fdiv<FULL>(fmaxf(amax, 1e-10f), 127.0f);
+    const float rcp = __fdiv_rn(1.0f, scale);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int c = threadIdx.x + i * blockDim.x;
-        if (c < nvec) *(uint2*)(q + t * K + (long)c * 8) = quant8<FULL>(v[i], scale);
+        if (c < nvec) *(uint2*)(q + t * K + (long)c * 8) = quant8<FULL>(v[i], scale, rcp);
     }
     if (threadIdx.x == 0) s[t] = scale;
 }
@@ -163,7 +182,7 @@ quant_groups_kernel(const void* __restrict__ x, int8_t* __restrict__ q, float* _
     for (int o = 1; o < (gk >> 3); o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     const float scale = fdiv<FULL>(fmaxf(amax, 1e-10f), 127.0f);
     if (in) {
-        *(uint2*)(q + t * K + (long)c * 8) = quant8<FULL>(v, scale);
+        *(uint2*)(q + t * K + (long)c * 8) = quant8<FULL>(v, scale, __fdiv_rn(1.0f, scale));
         if ((c & ((gk >> 3) - 1)) == 0) s[t * (K / gk) + c / (gk >> 3)] = scale;
     }
 }
@@ -173,7 +192,7 @@ quant_groups_kernel(const void* __restrict__ x, int8_t* __restrict__ q, float* _
 __device__ __forceinline__ float swiglu(float g, float u) { return __fmul_rn(__fdiv_rn(g, 1.0f + __expf(-g)), u); }
 
 template <int VPT, bool FULL>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 swiglu_q8_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ inv_s, int8_t* __restrict__ q,
                  float* __restrict__ s, const int* __restrict__ n_rows, int FF, int mode, float* __restrict__ amax_io) {
     __shared__ float red[32];
@@ -203,10 +222,11 @@ swiglu_q8_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__
     if (mode == MODE_STORE_AMAX && threadIdx.x == 0) amax_io[t] = amax;
     if (mode == MODE_USE_AMAX) amax = fmaxf(amax_io[t], amax);
     const float scale = fdiv<FULL>(fmaxf(amax, 1e-10f), 127.0f);
+    const float rcp = __fdiv_rn(1.0f, scale);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int c = threadIdx.x + i * blockDim.x;
-        if (c < nvec) *(uint2*)(q + t * FF + (long)c * 8) = quant8<FULL>(v[i], scale);
+        if (c < nvec) *(uint2*)(q + t * FF + (long)c * 8) = quant8<FULL>(v[i], scale, rcp);
     }
     if (threadIdx.x == 0) s[t] = scale;
 }

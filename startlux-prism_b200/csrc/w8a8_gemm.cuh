@@ -120,19 +120,20 @@ struct TileCfg {
     static constexpr int ACC_COLS = 2 * BN;                            // two accumulator buffers
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128
                                    : ACC_COLS <= 256 ? 256 : 512;
-    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + (int)sizeof(Aux) + 2 * BN * 4;
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + (int)sizeof(Aux) + 2 * BN * 4 + 4 * 32 * 33 * 4;
 };
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(192, 1)
 w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                  const float* __restrict__ a_s, const float* __restrict__ w_s, void* __restrict__ out, long ldo,
-                 const int* __restrict__ n_rows, int M, int N, int K, int vec_ok) {
+                 const int* __restrict__ n_rows, int M, int N, int K, int word_ok) {
     using C = TileCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align1024(smem_raw);
     Aux* aux = (Aux*)(smem + C::STAGES * C::STAGE_BYTES);
     float* sw_stash = (float*)(aux + 1);
+    uint32_t* stage_buf = (uint32_t*)(sw_stash + 2 * BN);          // 4 warps x 32 rows x 33 words
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     int live = *n_rows;
@@ -240,20 +241,109 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             float* swb = sw_stash + buf * BN;
             if (EPI != EPI_I32)
                 for (int i = et; i < BN; i += 128) swb[i] = (n0 + i < N) ? w_s[n0 + i] : 0.0f;
+            if (EPI == EPI_ADD) {
+                // the residual rows this CTA adds into one tile from now: pulled into L2 while that tile's main loop
+                // runs (the first tile's are requested as its main loop starts)
+                const int tn = (t == (int)blockIdx.x) ? t : t + (int)gridDim.x;
+                for (int pass = 0; pass < 2; ++pass) {
+                    const int tt = pass == 0 ? tn : tn + (int)gridDim.x;
+                    if (pass == 1 && t != (int)blockIdx.x) break;
+                    if (tt >= num_tiles) break;
+                    const int pm0 = (tt % num_m) * BM, pn0 = (tt / num_m) * BN;
+                    for (int line = et; line < BM * (BN / 32); line += 128) {
+                        const int pr = pm0 + line / (BN / 32), pc = pn0 + (line % (BN / 32)) * 32;
+                        if (pr < live && pc < N)
+                            asm volatile("prefetch.global.L2 [%0];" ::"l"((const float*)out + (long)pr * ldo + pc));
+                    }
+                }
+            }
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (!mbar_wait(smem_u32(&aux->tfull[buf]), bphase, abort_flag, 0x400 + buf)) break;
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
             const bool rok = row < live;
             const float sa = (rok && EPI != EPI_I32) ? a_s[row] : 0.0f;
+            uint32_t* stg = stage_buf + q * (32 * 33);
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+            if (word_ok) {
+                // coalesced path: every thread scales its row's values and parks them in shared memory (row-major,
+                // 33-word pitch: conflict-free both ways); then each warp instruction moves one row's 32 consecutive
+                // words (128 bytes) to or from global memory.
+                constexpr int CPW = (EPI == EPI_BF16) ? 2 : 1;            // output columns per 32-bit word
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN + c * 32, r);
-                tmem_ld_wait();
-                const int col0 = n0 + c * 32;
-                const int nok = N - col0 >= 32 ? 32 : (N - col0 > 0 ? N - col0 : 0);
-                if (rok && nok > 0) store_row32<EPI>(out, ldo, row, col0, nok, vec_ok != 0, r, sa, swb + c * 32);
+                for (int c0 = 0; c0 < BN; c0 += 32 * CPW) {
+                    if (n0 + c0 >= N) break;
+                    uint32_t r[32];
+                    tmem_ld32(lane_addr + c0, r);
+                    tmem_ld_wait();
+                    if (EPI == EPI_BF16) {
+                        uint32_t r2[32];
+                        tmem_ld32(lane_addr + c0 + 32, r2);
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            __nv_bfloat162 b2 = __floats2bfloat162_rn(scale2((int)r[2 * j], sa, swb[c0 + 2 * j]),
+                                                                      scale2((int)r[2 * j + 1], sa, swb[c0 + 2 * j + 1]));
+                            stg[lane * 33 + j] = *(uint32_t*)&b2;
+                        }
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            __nv_bfloat162 b2 = __floats2bfloat162_rn(
+                                scale2((int)r2[2 * j], sa, swb[c0 + 32 + 2 * j]),
+                                scale2((int)r2[2 * j + 1], sa, swb[c0 + 32 + 2 * j + 1]));
+                            stg[lane * 33 + 16 + j] = *(uint32_t*)&b2;
+                        }
+                    } else if (EPI == EPI_ADD) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) stg[lane * 33 + j] = __float_as_uint(scale2((int)r[j], sa, swb[c0 + j]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) stg[lane * 33 + j] = r[j];
+                    }
+                    __syncwarp();
+                    const int col = n0 + c0 + lane * CPW;                 // first column of this lane's word
+                    const int rows_here = live - (m0 + q * 32);           // live rows among this warp's 32
+                    if (col + CPW <= N) {
+                        if (EPI == EPI_ADD) {
+                            // all 32 rows' loads are issued before the first add: one round trip per chunk, not 32
+                            float* base = (float*)out + (long)(m0 + q * 32) * ldo + col;
+                            float o[32];
+#pragma unroll
+                            for (int rr = 0; rr < 32; ++rr)
+                                if (rr < rows_here) o[rr] = __ldcg(base + (long)rr * ldo);
+#pragma unroll
+                            for (int rr = 0; rr < 32; ++rr)
+                                if (rr < rows_here)
+                                    base[(long)rr * ldo] = __fadd_rn(o[rr], __uint_as_float(stg[rr * 33 + lane]));
+                        } else {
+#pragma unroll 8
+                            for (int rr = 0; rr < 32; ++rr) {
+                                if (rr < rows_here) {
+                                    const long off = (long)(m0 + q * 32 + rr) * ldo + col;
+                                    const uint32_t v = stg[rr * 33 + lane];
+                                    if (EPI == EPI_BF16)
+                                        *(uint32_t*)((__nv_bfloat16*)out + off) = v;
+                                    else
+                                        ((uint32_t*)out)[off] = v;
+                                }
+                            }
+                        }
+                    } else if (EPI == EPI_BF16 && col < N) {              // odd N: the word's first column only
+                        for (int rr = 0; rr < 32 && rr < rows_here; ++rr)
+                            ((uint16_t*)out)[(long)(m0 + q * 32 + rr) * ldo + col] = (uint16_t)(stg[rr * 33 + lane] & 0xffff);
+                    }
+                    __syncwarp();
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(lane_addr + c * 32, r);
+                    tmem_ld_wait();
+                    const int col0 = n0 + c * 32;
+                    const int nok = N - col0 >= 32 ? 32 : (N - col0 > 0 ? N - col0 : 0);
+                    if (rok && nok > 0) store_row32<EPI>(out, ldo, row, col0, nok, false, r, sa, swb + c * 32);
+                }
             }
             tc_fence_before();
             __syncwarp();
@@ -282,9 +372,10 @@ struct SwapCfg {
     static constexpr int SA_BYTES = GROUPED ? NB * 16 : 0;       // 4 fp32 group scales per activation row
     static constexpr int STAGE_BYTES_RAW = W_BYTES + X_BYTES + SW_BYTES + SA_BYTES;
     static constexpr int STAGE_BYTES = (STAGE_BYTES_RAW + 1023) / 1024 * 1024;
-    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 10 ? 10 : (200 * 1024 / STAGE_BYTES);
+    // about 110 KB per CTA: two CTAs share an SM, so twice the CTAs stream weights at once
+    static constexpr int STAGES = (108 * 1024 / STAGE_BYTES) > 8 ? 8 : (108 * 1024 / STAGE_BYTES);
     static constexpr int BATCH_COLS = GROUPED ? 4 * NB : NB;     // accumulator columns written per stage
-    static constexpr int RING = GROUPED ? ((512 / BATCH_COLS) > 4 ? 4 : (512 / BATCH_COLS)) : 1;
+    static constexpr int RING = GROUPED ? ((256 / BATCH_COLS) > 4 ? 4 : (256 / BATCH_COLS)) : 1;
     static constexpr int ACC_COLS = BATCH_COLS * RING;
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128
                                    : ACC_COLS <= 256 ? 256 : 512;
@@ -560,14 +651,19 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                     if (aux->is_last) {
                         __threadfence();
                         const float sw = n < p.N ? p.w_s[n] : 0.0f;
+                        int32_t tot[NB];
+#pragma unroll
+                        for (int j = 0; j < NB; ++j) tot[j] = 0;
+                        for (int s = 0; s < (int)gridDim.y; ++s) {
+                            const int32_t* src = p.ws + ((long)s * gridDim.x * gridDim.z + tile) * tile_elems + nl;
+#pragma unroll
+                            for (int j = 0; j < NB; ++j) tot[j] += __ldcg(src + j * BM);
+                        }
                         float v[NB];
 #pragma unroll
                         for (int j = 0; j < NB; ++j) {
-                            int32_t tot = 0;
-                            for (int s = 0; s < (int)gridDim.y; ++s)
-                                tot += __ldcg(p.ws + ((long)s * gridDim.x * gridDim.z + tile) * tile_elems + j * BM + nl);
                             const float sa = (m0 + j < live) ? __ldg(p.a_s + m0 + j) : 0.0f;
-                            v[j] = scale2(tot, sa, sw);
+                            v[j] = scale2(tot[j], sa, sw);
                         }
                         swap_store<NB>(p, n, m0, live, v);
                         if (threadIdx.x == 64) p.counters[tile] = 0;

@@ -1,0 +1,144 @@
+"""The CPU oracle against the golden vectors produced by the reference's own CPU-runnable code
+(tests/golden/make_golden.py) and against its literal known-answer vectors.  CPU only."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from oracle import emulation
+
+G = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def load(name):
+    return np.load(os.path.join(G, name))
+
+
+def test_w4a8_quantize_ref():
+    g = load("w4a8.npz")
+    q, a, xs = oracle.quant_g(g["x"])
+    assert np.array_equal(q, g["xq"]) and np.array_equal(a, g["a"]) and np.array_equal(xs, g["xs"])
+    sums = xs.transpose(1, 0, 2).reshape(5, -1, 2, 8).astype(np.int32)
+    assert np.array_equal((sums[:, :, 0] + 64 * sums[:, :, 1]).reshape(5, -1), g["sums"])
+
+
+@pytest.mark.parametrize("kind,tag", [("q4k", "4"), ("q6k", "6")])
+def test_w4a8_gemm_ref(kind, tag):
+    """orc_w4a8_gemm (hardware fmaf) == the reference's gemm_ref (its float64 emulation of a fused multiply-add)."""
+    g = load("w4a8.npz")
+    mn = g["mn4"] if kind == "q4k" else None
+    dm = g["dm4"] if kind == "q4k" else None
+    base = np.zeros((5, 24), np.float32)
+    y = oracle.w4a8_gemm(g["xq"], g["a"], g["xs"], kind, g[f"q{tag}"], g[f"sc{tag}"], mn, g[f"d{tag}"], dm, epi=1,
+                         out=base)
+    assert np.array_equal(y.view(np.uint32), g[f"y{tag}"].view(np.uint32))
+    yb = oracle.w4a8_gemm(g["xq"], g["a"], g["xs"], kind, g[f"q{tag}"], g[f"sc{tag}"], mn, g[f"d{tag}"], dm, epi=0)
+    assert np.array_equal(yb, oracle.bf16_bits(g[f"y{tag}"]))
+
+
+def test_fma_emulation_is_fmaf():
+    """The reference's fma32 (w4a8.py:164-174) equals a hardware single-rounding fma on its own samples."""
+    g = load("w4a8.npz")
+    got = np.array([np.float32(np.float64(a) * np.float64(b) + np.float64(c)) for a, b, c in
+                    zip(g["fa"][:64], g["fb"][:64], g["fc"][:64])])          # double rounding differs rarely: only a hint
+    import ctypes
+    libm = ctypes.CDLL("libm.so.6")
+    libm.fmaf.restype = ctypes.c_float
+    libm.fmaf.argtypes = [ctypes.c_float] * 3
+    hw = np.array([libm.fmaf(float(a), float(b), float(c)) for a, b, c in zip(g["fa"], g["fb"], g["fc"])], np.float32)
+    assert np.array_equal(hw.view(np.uint32), g["fma"].view(np.uint32))
+    assert np.mean(got == g["fma"][:64]) > 0.9
+
+
+def test_mxfp4_activation_quant():
+    g = load("mxfp4.npz")
+    for tag in ("bf16", "f32"):
+        q, s = oracle.mxfp4_quant(g[f"act_{tag}"])
+        assert np.array_equal(s, g[f"act_s_{tag}"]), tag
+        assert np.array_equal(q, g[f"act_q_{tag}"]), tag
+    q, s = oracle.mxfp4_quant(g["act_bf16"], inv=g["act_inv"])
+    assert np.array_equal(s, g["act_s_scaled"]) and np.array_equal(q, g["act_q_scaled"])
+
+
+def test_mxfp4_weight_rule_and_grid():
+    """The exact exponent rule equals numpy's ceil(log2(amax / 6)) on the reference's packed weights, and the
+    known-answer grid of tests/test_mxfp4.py:34-38 survives quantize -> dequantize."""
+    g = load("mxfp4.npz")
+    q, s = oracle.mxfp4_quant(g["w"], neg_zero=False)
+    assert np.array_equal(s, g["s_max"]) and np.array_equal(q, g["q_max"])
+    q, s = oracle.mxfp4_quant(g["grid"], neg_zero=False)
+    assert np.array_equal(q, g["grid_q"]) and np.array_equal(s, g["grid_s"])
+    lut = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, 0, -.5, -1, -1.5, -2, -3, -4, -6], np.float32)
+    deq = np.empty((1, 32), np.float32)
+    deq[:, 0::2], deq[:, 1::2] = lut[q & 15], lut[q >> 4]
+    deq *= np.exp2(s.astype(np.int32) - 127).astype(np.float32)
+    assert np.abs(deq - g["grid"]).max() < 1e-6
+    assert np.array_equal(deq, g["grid_deq"])
+
+
+def test_mxfp4_gemm_is_dequantized_product():
+    g = load("mxfp4.npz")
+    aq, a_s = g["act_q_bf16"][:, :128], g["act_s_bf16"][:, :8]
+    _, acc = oracle.mxfp4_gemm(aq, a_s, g["q_max"], g["s_max"])
+    lut = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, 0, -.5, -1, -1.5, -2, -3, -4, -6], np.float64)
+
+    def deq(q, s):
+        o = np.empty((q.shape[0], q.shape[1] * 2))
+        o[:, 0::2], o[:, 1::2] = lut[q & 15], lut[q >> 4]
+        return (o.reshape(q.shape[0], -1, 32) * np.exp2(s.astype(np.float64) - 127)[..., None]).reshape(q.shape[0], -1)
+    assert np.array_equal(deq(g["q_max"], g["s_max"]).astype(np.float32), g["deq_max"])
+    ref = deq(aq, a_s) @ deq(g["q_max"], g["s_max"]).T
+    assert np.allclose(acc, ref, rtol=1e-12, atol=0)
+
+
+def test_w8a8_gemm_against_float64():
+    """The bound the reference's own test uses (tests/test_cuda_gemm.py:50,66-67,95): bf16 store within 8e-3 and the
+    fp32 residual add within 1e-4 of the float64 product; int32 sums exact; per-32 groups likewise."""
+    rng = np.random.default_rng(0)
+    M, N, K = 9, 40, 512
+    a = rng.integers(-127, 128, (M, K), dtype=np.int8)
+    w = rng.integers(-127, 128, (N, K), dtype=np.int8)
+    for G in (1, K // 32):
+        sa = (rng.random((M, G)) * 1e-2).astype(np.float32)
+        sw = (rng.random((N, G)) * 1e-3).astype(np.float32)
+        ref = np.zeros((M, N))
+        for g in range(G):
+            ks = slice(g * K // G, (g + 1) * K // G)
+            ref += (a[:, ks].astype(np.float64) @ w[:, ks].astype(np.float64).T) * sa[:, g:g + 1] * sw[:, g][None]
+        o0 = oracle.bf16_to_f32(oracle.w8a8_gemm(a, sa, w, sw, K // G, 0, live=7))
+        rel = np.abs(o0[:7] - ref[:7]) / np.maximum(np.abs(ref[:7]), 1e-2)
+        assert rel.max() < 8e-3 and not o0[7:].any()
+        o1 = oracle.w8a8_gemm(a, sa, w, sw, K // G, 1, out=np.ones((M, N), np.float32))
+        assert (np.abs(o1 - 1 - ref) / np.maximum(np.abs(ref), 1e-2)).max() < 1e-4
+    exact = oracle.w8a8_gemm(a, sa, w, sw, K, 3)
+    assert np.array_equal(exact, a.astype(np.int64) @ w.astype(np.int64).T)
+    # fold of K-split int32 slots == the unsplit residual add
+    sa1, sw1 = sa[:, :1].copy(), sw[:, :1].copy()
+    halves = np.stack([a[:, :256].astype(np.int32) @ w[:, :256].astype(np.int32).T,
+                       a[:, 256:].astype(np.int32) @ w[:, 256:].astype(np.int32).T])
+    h = rng.standard_normal((M, N)).astype(np.float32)
+    assert np.array_equal(oracle.fold(h, halves, sa1[:, 0], sw1[:, 0]),
+                          oracle.w8a8_gemm(a, sa1, w, sw1, K, 1, out=h))
+
+
+def test_quant_rows_matches_torch_division():
+    """IEEE contract: the oracle's per-token quantizer equals torch's true division / round-half-even."""
+    x = torch.randn(7, 640, generator=torch.Generator().manual_seed(0)).to(torch.bfloat16)
+    bits = x.view(torch.int16).numpy().view(np.uint16)
+    q, s = oracle.quant_rows(bits)
+    xf = x.float()
+    sc = xf.abs().amax(1).clamp_min(1e-10) / torch.full((7,), 127.0)
+    assert np.array_equal(s[:, 0], sc.numpy())
+    assert np.array_equal(q, torch.round(xf / sc[:, None]).to(torch.int8).numpy())
+    q32, s32 = oracle.quant_rows(bits, 32)
+    sg = xf.view(7, 20, 32).abs().amax(-1).clamp_min(1e-10) / torch.full((7, 20), 127.0)
+    assert np.array_equal(s32, sg.numpy())
+
+
+def test_cpu_emulation_fake_quantizers():
+    g = load("sims.npz")
+    x = torch.from_numpy(g["x"])
+    assert np.array_equal(emulation.int8_rows(x).numpy(), g["int8_rows"])
+    assert np.array_equal(emulation.int8_groups(32)(x).numpy(), g["int8_g32"])
