@@ -76,6 +76,17 @@ int pb_swiglu_q8(const void* gu, const float* inv_s, int8_t* q, float* s, const 
 int pb_quant_g(const void* x, int x_fp32, int8_t* q, float* a, int8_t* xs, const int* n_rows, int T, int Ma, int K,
                void* stream);
 
+/* W4A8 GEMM on k-quant weights.  Replaces torch.ops.startlux_prism.w4a8_gemm / w4a8_wgmma (csrc/w4a8_gemm.cu:963-969,
+ * csrc/w4a8_wgmma.cu:744-748) behind kernels/w4a8.py:353-366 (gemm).  Operands in the repacked layout of
+ * kernels/w4a8.py:44-94: kind 0 (Q4_K): wq uint8 [N, K/2], wsc / wmn uint8 [K/256, N, 8], wd / wdm fp32 [K/256, N];
+ * kind 1 (Q6_K): wq int8 [N, K], wsc int8 [K/256, N, 16], wd fp32 [K/256, N] (wmn, wdm, xs unused).  Activations as
+ * pb_quant_g writes them: xq int8 [M, K], a fp32 [K/256, Ma], xs int8 [K/256, Ma, 16].  out bf16 (epi 0) or fp32 +=
+ * (epi 1), row stride ldo.  K % 256 == 0, N % 4 == 0, 16-byte aligned operands.  Bit-identical to the reference's
+ * gemm_ref (kernels/w4a8.py:177-199) for every M (batch invariance). */
+int pb_w4a8_gemm(const int8_t* xq, const float* a, const int8_t* xs, int Ma, int kind, const void* wq,
+                 const void* wsc, const void* wmn, const float* wd, const float* wdm, void* out, long ldo,
+                 const int* n_rows, int M, int N, int K, int epi, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -12,6 +12,7 @@
 #include "common.cuh"
 #include "quant.cuh"
 #include "w8a8_gemm.cuh"
+#include "w4a8_gemm.cuh"
 
 namespace {
 
@@ -65,7 +66,8 @@ struct MapHash {
     }
 };
 
-// A 2-D row-major matrix [outer, inner] of 1-byte (kind 0, 128-byte swizzle) or 4-byte (kind 1, no swizzle) elements,
+// A 2-D row-major matrix [outer, inner] of 1-byte (kind 0, 128-byte swizzle) or 4-byte (kind 1 fp32 / kind 3 uint32,
+// no swizzle) elements,
 // loaded in boxes of [box_outer, box_inner].  Maps are cached by (pointer, shape, box) and passed to kernels by value,
 // so a captured CUDA graph keeps the maps of its capture.
 int tensor_map(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer, uint64_t stride_bytes,
@@ -87,7 +89,9 @@ int tensor_map(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer
     cuuint64_t strides[1] = {stride_bytes};
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = fn(out, kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+    const CUtensorMapDataType dt = kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                   : kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
+    CUresult r = fn(out, dt, 2,
                     const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     kind == 0 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -179,6 +183,43 @@ int launch_swap_nb(int nb, const int8_t* a, const float* a_s, const int8_t* w, c
         case 32: return launch_swap<32, GROUPED>(a, a_s, w, w_s, p, split, st);
         default: return launch_swap<64, GROUPED>(a, a_s, w, w_s, p, split, st);
     }
+}
+
+
+template <int KIND>
+int launch_w4a8(const int8_t* xq, const float* a, const int8_t* xs, int Ma, const void* wq, const void* wsc,
+                const void* wmn, const float* wd, const float* wdm, void* out, long ldo, const int* n_rows, int M,
+                int N, int K, int epi, cudaStream_t st) {
+    using C = w4a8::Cfg<KIND>;
+    w4a8::Maps m;
+    int rc;
+    const uint64_t NSB = K / 256;
+    if ((rc = tensor_map(&m.x, xq, K, M, K, 128, 128, 0))) return rc;
+    if (KIND == w4a8::KIND_Q4K) {
+        if ((rc = tensor_map(&m.wq, wq, K / 2, N, K / 2, 128, 64, 0))) return rc;
+        if ((rc = tensor_map(&m.xs, xs, (uint64_t)Ma * 4, NSB, (uint64_t)Ma * 16, 256, 1, 3))) return rc;
+        if ((rc = tensor_map(&m.sc, wsc, (uint64_t)N * 2, NSB, (uint64_t)N * 8, 128, 1, 3))) return rc;
+        if ((rc = tensor_map(&m.mn, wmn, (uint64_t)N * 2, NSB, (uint64_t)N * 8, 128, 1, 3))) return rc;
+        if ((rc = tensor_map(&m.dm, wdm, N, NSB, (uint64_t)N * 4, 64, 1, 1))) return rc;
+    } else {
+        if ((rc = tensor_map(&m.wq, wq, K, N, K, 128, 64, 0))) return rc;
+        if ((rc = tensor_map(&m.sc, wsc, (uint64_t)N * 4, NSB, (uint64_t)N * 16, 256, 1, 3))) return rc;
+        m.xs = m.x;
+        m.mn = m.x;
+        m.dm = m.x;
+    }
+    if ((rc = tensor_map(&m.d, wd, N, NSB, (uint64_t)N * 4, 64, 1, 1))) return rc;
+    auto kern = w4a8::w4a8_kernel<KIND>;
+    static bool configured = false;
+    if (!configured) {
+        if ((rc = set_smem(kern, C::SMEM))) return rc;
+        configured = true;
+    }
+    w4a8::Args p{a, out, ldo, n_rows, M, N, K, Ma, epi};
+    const int grid = ((M + 127) / 128) * ((N + 63) / 64);
+    kern<<<grid, w4a8::THREADS, C::SMEM, st>>>(m, p);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
 }
 
 int pick_nb(int M) { return M <= 8 ? 8 : M <= 16 ? 16 : M <= 32 ? 32 : 64; }
@@ -390,6 +431,22 @@ int pb_quant_g(const void* x, int x_fp32, int8_t* q, float* a, int8_t* xs, const
     else quant::quant_g_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(x, q, a, xs, n_rows, Ma, K);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
+}
+
+int pb_w4a8_gemm(const int8_t* xq, const float* a, const int8_t* xs, int Ma, int kind, const void* wq,
+                 const void* wsc, const void* wmn, const float* wd, const float* wdm, void* out, long ldo,
+                 const int* n_rows, int M, int N, int K, int epi, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!xq || !a || !wq || !wsc || !wd || !out || !n_rows || M <= 0 || N <= 0 || K <= 0 || Ma < M) return PB_BAD_ARGUMENT;
+    if (kind != 0 && kind != 1) return PB_BAD_ARGUMENT;
+    if (kind == 0 && (!xs || !wmn || !wdm)) return PB_BAD_ARGUMENT;
+    if (epi != PB_EPI_BF16 && epi != PB_EPI_ADD) return PB_BAD_ARGUMENT;
+    if (K % 256 || N % 4 || ldo < N) return PB_UNSUPPORTED_SHAPE;
+    if (!aligned16(xq) || !aligned16(wq) || !aligned16(wsc) || !aligned16(wd) || (kind == 0 && (!aligned16(xs) ||
+        !aligned16(wmn) || !aligned16(wdm)))) return PB_BAD_ARGUMENT;
+    if (kind == 0)
+        return launch_w4a8<w4a8::KIND_Q4K>(xq, a, xs, Ma, wq, wsc, wmn, wd, wdm, out, ldo, n_rows, M, N, K, epi, st);
+    return launch_w4a8<w4a8::KIND_Q6K>(xq, a, xs, Ma, wq, wsc, wmn, wd, wdm, out, ldo, n_rows, M, N, K, epi, st);
 }
 
 }  // extern "C"

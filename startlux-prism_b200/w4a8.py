@@ -1,0 +1,146 @@
+"""W4A8 projections on a Q4_K_M file's own weights: the operator API of the reference's kernels/w4a8.py over the
+sm_100a library.
+
+    W4                         a repacked k-quant matrix                                   (w4a8.py:44-67)
+    repack(kq)                 KQuant (Q4_K / Q6_K raw super-blocks) -> W4                 (w4a8.py:70-94)
+    concat, segments, seg_rows, seg_width, gemm_segs   fused projections of mixed kinds    (w4a8.py:97-140)
+    gemm(xq, a, xs, w, out, n_rows, epi)               the GEMM                            (w4a8.py:353-366)
+
+Layouts (the GEMM kernel reads exactly these):
+  Q4_K  q uint8 [n, k/2]: per 32 inputs 16 bytes, byte t = q[t] | q[t + 16] << 4; sc, mn uint8 [k/256, n, 8] (the 6-bit
+        sub-block scales and mins, super-block-major); d, dm fp32 [k/256, n].
+  Q6_K  q int8 [n, k] (value - 32); sc int8 [k/256, n, 16]; d fp32 [k/256, n].
+Activations come from quant.rows_g: xq int8 [M, k], a fp32 [k/256, M], xs int8 [k/256, M, 16].
+The arithmetic is the reference's (w4a8.py:14-24): integer inside a 256-input super-block, one fp32 step per
+super-block, the same bits for every kernel shape and batch.
+"""
+from __future__ import annotations
+
+from typing import NamedTuple
+
+import torch
+
+from . import _lib
+from . import gguf_weights as GW
+
+QK_K = 256
+
+
+class W4(NamedTuple):
+    kind: str               # "q4k" or "q6k"
+    q: torch.Tensor
+    sc: torch.Tensor
+    mn: torch.Tensor        # q6k: None
+    d: torch.Tensor
+    dm: torch.Tensor        # q6k: None
+    n: int
+    k: int
+
+    @property
+    def shape(self):
+        return (self.n, self.k)
+
+    def rows(self, r0, r1):
+        """Rows r0:r1: the values a view, the super-block-major scales copied (the GEMM reads them contiguous)."""
+        cut = lambda t: None if t is None else t[:, r0:r1].contiguous()     # noqa: E731
+        return W4(self.kind, self.q[r0:r1], cut(self.sc), cut(self.mn), cut(self.d), cut(self.dm), r1 - r0, self.k)
+
+    def to(self, device):
+        mv = lambda t: None if t is None else t.to(device)                   # noqa: E731
+        return W4(self.kind, mv(self.q), mv(self.sc), mv(self.mn), mv(self.d), mv(self.dm), self.n, self.k)
+
+    def nbytes(self):
+        return sum(t.numel() * t.element_size() for t in (self.q, self.sc, self.mn, self.d, self.dm) if t is not None)
+
+
+def repack(kq: GW.KQuant) -> W4:
+    """A KQuant matrix (any device) -> W4."""
+    raw = kq.raw
+    n, nb = raw.shape[0], raw.shape[1]
+    blocks = raw.reshape(n * nb, raw.shape[2])
+    major = lambda t: t.reshape(n, nb, -1).transpose(0, 1).contiguous()     # noqa: E731  [n, nb, x] -> [nb, n, x]
+    if kq.type == GW.GGML_Q4_K:
+        d = blocks[:, 0:2].contiguous().view(torch.float16).float().reshape(n, nb)
+        dm = blocks[:, 2:4].contiguous().view(torch.float16).float().reshape(n, nb)
+        sc, mn = GW.scale_min_k4(blocks[:, 4:16])
+        # ggml keeps two sub-blocks per 32 bytes (low nibbles, high nibbles); regroup per sub-block of 32 inputs and
+        # pair input t with input t + 16 in one byte
+        v = blocks[:, 16:144].to(torch.int32).reshape(-1, 4, 32)
+        v = torch.stack([v & 15, v >> 4], 2).reshape(n, nb * 8, 32)
+        q = (v[..., :16] | (v[..., 16:] << 4)).to(torch.uint8).reshape(n, kq.k // 2)
+        return W4("q4k", q.contiguous(), major(sc.to(torch.uint8)), major(mn.to(torch.uint8)), d.t().contiguous(),
+                  dm.t().contiguous(), n, kq.k)
+    if kq.type == GW.GGML_Q6_K:
+        q = (GW.q6k_values(blocks) - 32).to(torch.int8).reshape(n, kq.k)
+        sc = blocks[:, 192:208].contiguous().view(torch.int8)
+        d = blocks[:, 208:210].contiguous().view(torch.float16).float().reshape(n, nb)
+        return W4("q6k", q.contiguous(), major(sc), None, d.t().contiguous(), None, n, kq.k)
+    raise ValueError(f"k-quant type {kq.type}: Q4_K and Q6_K are supported")
+
+
+def concat(ws):
+    """Row-concatenation of W4 matrices of one kind (a fused projection)."""
+    kinds = {w.kind for w in ws}
+    if len(kinds) != 1:
+        raise ValueError(f"cannot fuse k-quant kinds {kinds}")
+    cat = lambda f: None if getattr(ws[0], f) is None else torch.cat(      # noqa: E731
+        [getattr(w, f) for w in ws], 0 if f == "q" else 1)
+    return W4(ws[0].kind, cat("q"), cat("sc"), cat("mn"), cat("d"), cat("dm"), sum(w.n for w in ws), ws[0].k)
+
+
+def segments(kqs, device):
+    """The KQuant matrices of a fused projection -> [(W4, first output column)]: neighbours of one kind fused (a
+    Q4_K_M file puts a Q6_K v under Q4_K q and k)."""
+    out, off = [], 0
+    for kq in kqs:
+        if not isinstance(kq, GW.KQuant):
+            raise ValueError(f"the W4A8 path needs k-quant projections, not {type(kq).__name__}")
+        w = repack(kq.to(device))
+        if out and out[-1][0].kind == w.kind:
+            out[-1] = (concat([out[-1][0], w]), out[-1][1])
+        else:
+            out.append((w, off))
+        off += w.n
+    return out
+
+
+def seg_rows(segs, r0, r1):
+    """Output columns r0:r1 of a fused projection, as segments with first columns counted from r0."""
+    out = []
+    for w, off in segs:
+        a, b = max(r0, off), min(r1, off + w.n)
+        if a < b:
+            out.append((w.rows(a - off, b - off), a - r0))
+    return out
+
+
+def seg_width(segs):
+    return max(off + w.n for w, off in segs)
+
+
+def gemm_segs(xq, a, xs, segs, out, n_rows, epi=0, pdl=0):
+    """A fused projection: one GEMM per segment, each into its columns of out."""
+    for w, off in segs:
+        gemm(xq, a, xs, w, out[:, off:off + w.n], n_rows, epi, pdl=pdl)
+
+
+def gemm(xq, a, xs, w: W4, out, n_rows, epi=0, cfg=None, pdl=0):
+    """xq int8 [M, K], a fp32 [K/256, M], xs int8 [K/256, M, 16], w W4 [N, K] -> out [M, N]: bf16 (epi 0) or added
+    into fp32 (epi 1); out may be a column slice.  cfg and pdl are accepted for signature parity (one kernel shape)."""
+    M, K = xq.shape
+    _lib.need_cuda(xq, a, w.q, out, n_rows)
+    if K != w.k or a.shape[0] != K // QK_K or not xq.is_contiguous() or not a.is_contiguous():
+        raise RuntimeError("w4a8.gemm: xq [M, K] int8 contiguous, a [K/256, M] fp32 contiguous")
+    want = torch.bfloat16 if epi == 0 else torch.float32
+    if out.dtype != want or out.shape[1] != w.n or out.stride(1) != 1 or out.shape[0] < M:
+        raise RuntimeError(f"w4a8.gemm: out must be {want} [>= {M}, {w.n}] with unit column stride")
+    q4 = w.kind == "q4k"
+    if q4 and (xs is None or xs.shape[1] != a.shape[1] or not xs.is_contiguous()):
+        raise RuntimeError("w4a8.gemm: Q4_K needs the activation group sums xs [K/256, M, 16]")
+    for t in (w.q, w.sc, w.mn, w.d, w.dm):
+        if t is not None and not t.is_contiguous():
+            raise RuntimeError("w4a8.gemm: W4 tensors must be contiguous (W4.rows copies the scales)")
+    rc = _lib.lib().pb_w4a8_gemm(_lib.ptr(xq), _lib.ptr(a), _lib.ptr(xs) if q4 else None, a.shape[1], 0 if q4 else 1,
+                                 _lib.ptr(w.q), _lib.ptr(w.sc), _lib.ptr(w.mn), _lib.ptr(w.d), _lib.ptr(w.dm),
+                                 _lib.ptr(out), out.stride(0), _lib.ptr(n_rows), M, w.n, K, epi, _lib.stream())
+    _lib.check(rc, f"w4a8 gemm {w.kind} M={M} N={w.n} K={K} epi={epi}")

@@ -130,3 +130,22 @@ def test_linear_shards_partition():
     with pytest.raises(ValueError):
         tp.linear_shards(5120, 1024, 17408, 3, 0)
     assert tp.parts_elems(64, 5120) == 4 * 64 * 5120 and tp.parts_elems(8192, 5120) == 8192 * 5120
+
+
+def test_w4a8_repack_matches_reference():
+    from prism_b200 import w4a8
+    g, k = load("w4a8.npz"), load("kquant.npz")
+    w = w4a8.repack(GW.KQuant(torch.from_numpy(k["raw4"]), GW.GGML_Q4_K, 512))
+    assert w.kind == "q4k" and (w.n, w.k) == (24, 512)
+    for f in ("q", "sc", "mn", "d", "dm"):
+        assert np.array_equal(getattr(w, f).numpy(), g[f + "4"]), f
+    w6 = w4a8.repack(GW.KQuant(torch.from_numpy(k["raw6"]), GW.GGML_Q6_K, 512))
+    for f in ("q", "sc", "d"):
+        assert np.array_equal(getattr(w6, f).numpy(), g[f + "6"]), f
+    assert w6.mn is None and w6.dm is None
+    both = w4a8.concat([w, w])
+    assert both.n == 48 and both.sc.shape == (2, 48, 8) and both.q.shape == (48, 256)
+    part = both.rows(10, 30)
+    assert part.n == 20 and np.array_equal(part.d.numpy(), np.concatenate([g["d4"], g["d4"]], 1)[:, 10:30])
+    with pytest.raises(ValueError):
+        w4a8.concat([w, w6])
