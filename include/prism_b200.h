@@ -87,6 +87,24 @@ int pb_w4a8_gemm(const int8_t* xq, const float* a, const int8_t* xs, int Ma, int
                  const void* wsc, const void* wmn, const float* wd, const float* wdm, void* out, long ldo,
                  const int* n_rows, int M, int N, int K, int epi, void* stream);
 
+/* pb_w8a8_gemm for callers that cannot allocate device memory.  No counterpart in the reference (its stream-K
+ * workspace is always a torch allocation, kernels/cuda_ext.py:139-143).
+ * Some hosts of this library have no allocator to offer: a plugin loaded into a process whose memory pool is owned by
+ * another runtime, a replay thread that may only launch, a code path that runs while a stream is being captured (where
+ * cudaMalloc is illegal).  For them the few-rows split-K GEMM (M <= 64, gk == K, epi 0 / 1) keeps its scratch - the
+ * int32 partial sums of the K splits and the per-tile arrival counters - in a fixed array inside the library's device
+ * image: pb_w8a8_static_scratch_bytes() = 16 MiB of partial sums plus 4,096 counters, resident on every GPU that loads
+ * the library until the process exits.  Same arguments and result bits as pb_w8a8_gemm; a product whose scratch
+ * (pb_w8a8_workspace_bytes / pb_w8a8_counters) exceeds the array returns PB_TOO_LARGE and launches nothing.
+ * The call makes no cudaMalloc / cudaFree and calls no allocating library routine.  The first call on each device
+ * looks up the array's device address (cudaGetSymbolAddress, with that device current) and should therefore come
+ * before any stream capture on that device.  All calls on a device share the one array: the counters are cleared on
+ * the stream before each launch, but two calls that overlap on the GPU (different streams) race on it - serialize
+ * them. */
+long pb_w8a8_static_scratch_bytes(void);
+int pb_w8a8_gemm_static(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, void* out, long ldo,
+                        const int* n_rows, int M, int N, int K, int epi, int split, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -25,7 +25,10 @@ _SIGS = {
     "pb_w4a8_gemm": ([_vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _l, _vp, _i, _i, _i, _i, _vp], _i),
 }
 # entry points added by later sections of the header; bound when present in the built library
-_OPTIONAL = {}
+_OPTIONAL = {
+    "pb_w8a8_static_scratch_bytes": ([], _l),
+    "pb_w8a8_gemm_static": ([_vp, _vp, _vp, _vp, _vp, _l, _vp, _i, _i, _i, _i, _i, _vp], _i),
+}
 
 
 @functools.lru_cache(None)

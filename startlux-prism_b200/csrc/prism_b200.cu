@@ -248,6 +248,37 @@ void launch_rows(bool bf16, bool full, int threads, const void* x, long ldx, con
 
 }  // namespace
 
+// ------------------------------------------------------------------------------------------------- static scratch
+// Scratch of pb_w8a8_gemm_static: the split-K workspace and its per-tile counters live in the library's own device
+// image instead of in memory the caller allocates.  Every GPU that loads the library holds these bytes until the
+// process exits.  In host code the array's name is only a handle for the runtime: the device address is looked up
+// with cudaGetSymbolAddress, once per device, and that address is what the kernel receives.
+#define PB_STATIC_WS_BYTES (16l << 20)
+#define PB_STATIC_COUNTERS 4096
+static __device__ __align__(256) unsigned char g_static_scratch[PB_STATIC_WS_BYTES + PB_STATIC_COUNTERS * 4];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {};
+std::mutex g_static_scratch_mu;
+
+// The device address of g_static_scratch on the current device (set-up on the first call per device).
+int static_scratch(void** out) {
+    int dev = -1;
+    PB_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return PB_TOO_LARGE;
+    std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+    if (!g_static_scratch_addr[dev]) {
+        void* ptr = nullptr;
+        PB_CUDA(cudaGetSymbolAddress((void**)&ptr, g_static_scratch));
+        if (!ptr) return PB_CUDA_ERROR;
+        g_static_scratch_addr[dev] = ptr;
+    }
+    *out = g_static_scratch_addr[dev];
+    return PB_OK;
+}
+}  // namespace
+
 extern "C" {
 
 int pb_version(void) { return 1; }
@@ -447,6 +478,36 @@ int pb_w4a8_gemm(const int8_t* xq, const float* a, const int8_t* xs, int Ma, int
     if (kind == 0)
         return launch_w4a8<w4a8::KIND_Q4K>(xq, a, xs, Ma, wq, wsc, wmn, wd, wdm, out, ldo, n_rows, M, N, K, epi, st);
     return launch_w4a8<w4a8::KIND_Q6K>(xq, a, xs, Ma, wq, wsc, wmn, wd, wdm, out, ldo, n_rows, M, N, K, epi, st);
+}
+
+long pb_w8a8_static_scratch_bytes(void) { return PB_STATIC_WS_BYTES; }
+
+int pb_w8a8_gemm_static(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, void* out, long ldo,
+                        const int* n_rows, int M, int N, int K, int epi, int split, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!a || !w || !out || !n_rows || !a_s || !w_s || M <= 0 || N <= 0 || K <= 0 || split < 1) return PB_BAD_ARGUMENT;
+    if (epi != PB_EPI_BF16 && epi != PB_EPI_ADD) return PB_BAD_ARGUMENT;
+    if (!aligned16(a) || !aligned16(w) || ldo < N) return PB_BAD_ARGUMENT;
+    if (K % 16 || M > 64) return PB_UNSUPPORTED_SHAPE;
+    const int KB = (K + 127) / 128;
+    if (split > KB) split = KB;
+    const int kbs = (KB + split - 1) / split;
+    split = (KB + kbs - 1) / kbs;
+    // sizes beyond the static array are refused, never truncated
+    if (split > 1 && (pb_w8a8_workspace_bytes(M, N, split) > PB_STATIC_WS_BYTES || pb_w8a8_counters(M, N) > PB_STATIC_COUNTERS))
+        return PB_TOO_LARGE;
+    void* scratch = nullptr;
+    int rc = static_scratch(&scratch);
+    if (rc) return rc;
+    int32_t* ws = (int32_t*)scratch;
+    int* counters = (int*)((unsigned char*)scratch + PB_STATIC_WS_BYTES);
+    w8a8::SwapArgs p{a_s, w_s, out, ldo, 0, ws, counters, n_rows, M, N, K, kbs, epi,
+                     split == 1 ? w8a8::MODE_DIRECT : w8a8::MODE_WS};
+    if (split > 1) {
+        // the counters must start at zero; the array keeps whatever an earlier call (or an aborted one) left
+        PB_CUDA(cudaMemsetAsync(counters, 0, (size_t)pb_w8a8_counters(M, N) * sizeof(int), st));
+    }
+    return launch_swap_nb<false>(pick_nb(M), a, a_s, w, w_s, p, split, st);
 }
 
 }  // extern "C"
