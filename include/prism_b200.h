@@ -87,6 +87,21 @@ int pb_w4a8_gemm(const int8_t* xq, const float* a, const int8_t* xs, int Ma, int
                  const void* wsc, const void* wmn, const float* wd, const float* wdm, void* out, long ldo,
                  const int* n_rows, int M, int N, int K, int epi, void* stream);
 
+/* MXFP4.  Replace the reference's ctypes ABI (csrc/mxfp4_gemm.cu:121-168: mxfp4_sfa_bytes / mxfp4_sfb_bytes,
+ * mxfp4_prepare_sfa / mxfp4_prepare_sfb, mxfp4_gemm) and its Triton kernels (kernels/mxfp4.py:119-185 quantize_act,
+ * :260-317 gemm).  Formats (kernels/mxfp4.py:3-5): codes uint8 [rows, K/2] (two e2m1 per byte, low nibble first),
+ * scales uint8 [rows, K/32] (UE8M0: 2^(s - 127)).
+ *   pb_mxfp4_quant       x bf16 / fp32 [n, K] (times inv [K] when given) -> q, s.  K % 32 == 0.
+ *   pb_mxfp4_sf_bytes    bytes of the tensor core's tiled scale layout for a [rows, K] operand (K % 128 == 0)
+ *   pb_mxfp4_prepare_sf  s [rows, K/32] -> that layout (weights: once at load; activations: per call, as the reference)
+ *   pb_mxfp4_gemm        out [M, N] = deq(A) deq(B)^T, fp32 accumulation: bf16 store (epi 0) or fp32 out += (epi 1);
+ *                        a_sf / b_sf are the tiled scales.  K % 256 == 0.  M is a host integer (the reference's n_rows). */
+long pb_mxfp4_sf_bytes(int rows, int K);
+int pb_mxfp4_prepare_sf(const void* s, void* dst, int rows, int K, void* stream);
+int pb_mxfp4_quant(const void* x, int x_fp32, const float* inv, void* q, void* s, int n, int K, void* stream);
+int pb_mxfp4_gemm(const void* aq, const void* a_sf, const void* bq, const void* b_sf, void* out, long ldo, int M,
+                  int N, int K, int epi, void* stream);
+
 /* pb_w8a8_gemm for callers that cannot allocate device memory.  No counterpart in the reference (its stream-K
  * workspace is always a torch allocation, kernels/cuda_ext.py:139-143).
  * Some hosts of this library have no allocator to offer: a plugin loaded into a process whose memory pool is owned by

@@ -13,6 +13,7 @@
 #include "quant.cuh"
 #include "w8a8_gemm.cuh"
 #include "w4a8_gemm.cuh"
+#include "mxfp4_gemm.cuh"
 
 namespace {
 
@@ -508,6 +509,54 @@ int pb_w8a8_gemm_static(const int8_t* a, const float* a_s, const int8_t* w, cons
         PB_CUDA(cudaMemsetAsync(counters, 0, (size_t)pb_w8a8_counters(M, N) * sizeof(int), st));
     }
     return launch_swap_nb<false>(pick_nb(M), a, a_s, w, w_s, p, split, st);
+}
+
+long pb_mxfp4_sf_bytes(int rows, int K) {
+    if (rows <= 0 || K <= 0 || K % 128) return 0;
+    return (long)((rows + 127) / 128) * (K / 128) * 512;
+}
+
+int pb_mxfp4_prepare_sf(const void* s, void* dst, int rows, int K, void* stream) {
+    if (!s || !dst || rows <= 0 || K <= 0) return PB_BAD_ARGUMENT;
+    if (K % 128 || ((uintptr_t)dst & 15)) return PB_UNSUPPORTED_SHAPE;
+    const long threads = (long)((rows + 127) / 128) * (K / 128) * 128;
+    mxfp4::sf_tile_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+        (const uint8_t*)s, (uint8_t*)dst, rows, K);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+int pb_mxfp4_quant(const void* x, int x_fp32, const float* inv, void* q, void* s, int n, int K, void* stream) {
+    if (!x || !q || !s || n <= 0 || K <= 0) return PB_BAD_ARGUMENT;
+    if (K % 32 || !aligned16(x) || ((uintptr_t)q & 3)) return PB_UNSUPPORTED_SHAPE;
+    dim3 grid((K / 8 + 255) / 256, n);
+    if (x_fp32) mxfp4::mxfp4_quant_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(x, inv, (uint8_t*)q, (uint8_t*)s, n, K);
+    else mxfp4::mxfp4_quant_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(x, inv, (uint8_t*)q, (uint8_t*)s, n, K);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+int pb_mxfp4_gemm(const void* aq, const void* a_sf, const void* bq, const void* b_sf, void* out, long ldo, int M,
+                  int N, int K, int epi, void* stream) {
+    if (!aq || !a_sf || !bq || !b_sf || !out || M <= 0 || N <= 0 || K <= 0 || ldo < N) return PB_BAD_ARGUMENT;
+    if (epi != 0 && epi != 1) return PB_BAD_ARGUMENT;
+    if (K % 256) return PB_UNSUPPORTED_SHAPE;
+    if (!aligned16(aq) || !aligned16(bq) || !aligned16(a_sf) || !aligned16(b_sf)) return PB_BAD_ARGUMENT;
+    CUtensorMap ta, tb;
+    int rc;
+    if ((rc = tensor_map(&ta, aq, K / 2, M, K / 2, 128, 128, 0))) return rc;
+    if ((rc = tensor_map(&tb, bq, K / 2, N, K / 2, 128, 128, 0))) return rc;
+    static bool configured = false;
+    if (!configured) {
+        if ((rc = set_smem(mxfp4::mxfp4_gemm_kernel, mxfp4::SMEM))) return rc;
+        configured = true;
+    }
+    mxfp4::GemmArgs p{(const uint8_t*)a_sf, (const uint8_t*)b_sf, out, ldo, M, N, K, epi};
+    const int tiles = ((M + 127) / 128) * ((N + 127) / 128);
+    const int grid = tiles < sm_count() ? tiles : sm_count();
+    mxfp4::mxfp4_gemm_kernel<<<grid, 192, mxfp4::SMEM, (cudaStream_t)stream>>>(ta, tb, p);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
 }
 
 }  // extern "C"

@@ -149,3 +149,17 @@ def test_w4a8_repack_matches_reference():
     assert part.n == 20 and np.array_equal(part.d.numpy(), np.concatenate([g["d4"], g["d4"]], 1)[:, 10:30])
     with pytest.raises(ValueError):
         w4a8.concat([w, w6])
+
+
+def test_mxfp4_pack_matches_reference():
+    from prism_b200 import mxfp4
+    g = load("mxfp4.npz")
+    w = torch.from_numpy(g["w"])
+    for mode in ("max", "mse"):
+        m = mxfp4.pack(w, mode)
+        assert np.array_equal(m.q.numpy(), g[f"q_{mode}"]) and np.array_equal(m.s.numpy(), g[f"s_{mode}"]), mode
+        assert np.array_equal(mxfp4.dequant_packed(m.q, m.s).numpy(), g[f"deq_{mode}"])
+    m = mxfp4.pack(torch.from_numpy(g["grid"]))                   # tests/test_mxfp4.py:34-38: exact-grid values survive
+    assert np.array_equal(m.q.numpy(), g["grid_q"]) and np.array_equal(m.s.numpy(), g["grid_s"])
+    assert float((mxfp4.dequant_packed(m.q, m.s) - torch.from_numpy(g["grid"])).abs().max()) < 1e-6
+    assert mxfp4.MX4(m.q, m.s, 1, 32).rows(0, 1).shape == (1, 32)
