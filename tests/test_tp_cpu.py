@@ -1,0 +1,87 @@
+"""The tensor-parallel host logic on CPU ranks (gloo, world size 2): the process group's exact int32 SUM / fp32 MAX,
+tp.out_proj and tp.quantize_rows plumbing.  The GPU kernels are replaced by the CPU oracle inside this test only
+(monkeypatched in the child processes): what is checked is that the two exchange steps compose to the one-rank bits."""
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _rank(rank, world, port):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle
+    from prism_b200 import tp, w8a8
+    g = tp.Group(rank, world, port=port, backend="gloo")
+    try:
+        gen = torch.Generator().manual_seed(0)
+        M, N, K = 6, 32, 256
+        a = torch.randint(-127, 128, (M, K), generator=gen, dtype=torch.int8)
+        w = torch.randint(-127, 128, (N, K), generator=gen, dtype=torch.int8)
+        x = torch.randn(M, K, generator=gen)
+        sw = torch.rand(N, generator=gen) * 1e-3
+        k = K // world
+        # --- quantize_rows: modes 1 / 2 around the MAX all-reduce
+        def rows_q8(xs, q, s, mode=0, amax=None):
+            qq, ss, am = oracle.quant_rows(xs.numpy(), amax_in=None if mode != 2 else amax.numpy()[:, None].copy(),
+                                           want_amax=True)
+            q.copy_(torch.from_numpy(qq))
+            s.copy_(torch.from_numpy(ss[:, 0]))
+            if mode == 1:
+                amax.copy_(torch.from_numpy(am[:, 0]))
+        shard = x[:, rank * k:(rank + 1) * k].contiguous()
+        q = torch.zeros(M, k, dtype=torch.int8)
+        s = torch.zeros(M)
+        amax = torch.zeros(M)
+        tp.quantize_rows(g, rows_q8, M, amax, shard, q, s)
+        wq, ws = oracle.quant_rows(x.numpy())
+        ok_quant = np.array_equal(q.numpy(), wq[:, rank * k:(rank + 1) * k]) and np.array_equal(s.numpy(), ws[:, 0])
+        # --- out_proj: int32 partial sums -> SUM all-reduce -> Deferred
+        def gemm_i32(aa, a_s, ww, w_s, slots, n_rows, max_split=4, pdl=False):
+            slots[0].copy_(torch.from_numpy(oracle.w8a8_gemm(aa.numpy(), np.ones((M, 1), np.float32), ww.numpy(),
+                                                              np.ones((N, 1), np.float32), aa.shape[1], 3)))
+            return 1
+        w8a8.gemm_i32 = gemm_i32
+        flat = torch.zeros(tp.parts_elems(M, N), dtype=torch.int32)
+        sa = torch.from_numpy(ws[:, 0].copy())
+        d = tp.out_proj(g, torch.from_numpy(wq[:, rank * k:(rank + 1) * k].copy()), sa,
+                        w[:, rank * k:(rank + 1) * k].contiguous(), sw, flat, M, None)
+        exact = oracle.w8a8_gemm(wq, ws, w.numpy(), sw.numpy()[:, None], K, 3)
+        ok_sum = d.n == 1 and np.array_equal(d.parts[0].numpy(), exact)
+        h = torch.randn(M, N, generator=torch.Generator().manual_seed(1))
+        folded = oracle.fold(h.numpy(), d.parts.numpy(), sa.numpy(), sw.numpy())
+        ok_fold = np.array_equal(folded, oracle.w8a8_gemm(wq, ws, w.numpy(), sw.numpy()[:, None], K, 1, out=h.numpy()))
+        res = (rank, bool(ok_quant), bool(ok_sum), bool(ok_fold))
+    finally:
+        g.barrier()
+        g.close()
+    return res
+
+
+def _entry(rank, world, port, ret):
+    ret[rank] = _rank(rank, world, port)
+
+
+def test_two_cpu_ranks_compose_to_one_rank_bits():
+    import oracle
+    oracle.build()
+    world, port = 2, 29731
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_entry, args=(world, port, ret), nprocs=world, join=True)
+    assert len(ret) == world
+    for r in range(world):
+        assert ret[r] == (r, True, True, True), ret[r]
+
+
+def test_group_single_rank_is_a_no_op():
+    sys.path.insert(0, ROOT)
+    from prism_b200 import tp
+    calls = []
+    tp.quantize_rows(None, lambda *a, **k: calls.append((a, k)), 4, None, 1, 2)
+    assert calls == [((1, 2), {})]
