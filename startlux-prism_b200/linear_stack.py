@@ -71,6 +71,8 @@ class LinearStack:
         self.dq, self.ds = e(M, self.fl, dtype=i8), e(M, dtype=f32)
         self.amax = e(M, dtype=f32)
         self.parts = torch.zeros(tp.parts_elems(M, hidden), dtype=torch.int32, device=device)
+        self.s_max = tp.MAX_SPLIT if M <= tp.SPLIT_ROWS else 1
+        self.slots = self.parts[:self.s_max * M * hidden].view(self.s_max, M, hidden)
         self.n_rows = torch.tensor([M], dtype=torch.int32, device=device)
 
     def __call__(self, h_in):
@@ -80,19 +82,19 @@ class LinearStack:
         self.h.copy_(h_in, non_blocking=True)
         pend = None
         for lw in self.layers:
-            quant.fold(self.h, self.parts, pend, nr, M)
+            quant.fold(self.h, self.slots, pend, nr, M)
             quant.rows_q8(self.h, None, self.xq, self.xs, nr, M)
             w8a8.gemm(self.xq, self.xs, *lw["qkv"], self.qkv, nr, self.hidden)
             tp.quantize_rows(g if self.n > 1 else None, quant.rows_q8, M, self.amax, self.qkv[:, :self.ql], None,
                              self.aq, self.as_, nr, M)
             pend = self._out(self.aq, self.as_, lw["o"])
-            quant.fold(self.h, self.parts, pend, nr, M)
+            quant.fold(self.h, self.slots, pend, nr, M)
             quant.rows_q8(self.h, None, self.xq, self.xs, nr, M)
             w8a8.gemm(self.xq, self.xs, *lw["gate_up"], self.gu, nr, self.hidden)
             tp.quantize_rows(g if self.n > 1 else None, quant.swiglu_q8, M, self.amax, self.gu, None, self.dq,
                              self.ds, nr, M)
             pend = self._out(self.dq, self.ds, lw["down"])
-        quant.fold(self.h, self.parts, pend, nr, M)
+        quant.fold(self.h, self.slots, pend, nr, M)
         return self.h
 
     def _out(self, a, a_s, wt):
@@ -101,6 +103,4 @@ class LinearStack:
         w, w_s = wt
         if self.n > 1:
             return tp.out_proj(self.g, a, a_s, w, w_s, self.parts, self.M, self.n_rows)
-        S_max = tp.MAX_SPLIT if self.M <= tp.SPLIT_ROWS else 1
-        slots = self.parts[:S_max * self.M * self.hidden].view(S_max, self.M, self.hidden)
-        return w8a8.gemm(a, a_s, w, w_s, self.h, self.n_rows, a.shape[1], epi=1, slots=slots)
+        return w8a8.gemm(a, a_s, w, w_s, self.h, self.n_rows, a.shape[1], epi=1, slots=self.slots)
