@@ -393,6 +393,87 @@ def run_detail(args):
     print(json.dumps({"device_status": code, "where": where}))
 
 
+# ------------------------------------------------------------------------------------------------------ probes
+def run_probe(args):
+    """A few eager launches of one kernel on a case larger than L2 but small in memory: the command ncu captures
+    (`ncu -k regex:<kernel> -c 3 python bench.py --probe <case>`); also prints the CUDA-event time per launch."""
+    import torch
+
+    from prism_b200 import _lib, mxfp4, quant, synth, w4a8, w8a8
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    gen = torch.Generator(device=dev).manual_seed(2)
+    case = args.probe
+    ri = lambda *s: torch.randint(-127, 128, s, dtype=torch.int8, device=dev, generator=gen)     # noqa: E731
+    if case in ("tile", "tile_add", "decode", "decode32"):
+        M = 2048 if case.startswith("tile") else 16
+        N, K = (34816, 5120) if case in ("tile", "decode32") else (5120, 17408)
+        if case == "tile_add":
+            N, K = 5120, 17408
+        gk = 32 if case == "decode32" else K
+        a, w = ri(M, K), ri(N, K)
+        sa = torch.rand(M, K // gk, device=dev, generator=gen) * 1e-2
+        sw = torch.rand(N, K // gk, device=dev, generator=gen) * 1e-3
+        epi = 1 if case in ("tile_add", "decode") else 0
+        out = torch.zeros(M, N, dtype=torch.float32 if epi else torch.bfloat16, device=dev)
+        slots = torch.zeros(4, M, N, dtype=torch.int32, device=dev) if case == "decode" else None
+        nr = torch.tensor([M], dtype=torch.int32, device=dev)
+        fn = lambda: w8a8.gemm(a, sa, w, sw, out, nr, gk, epi=epi, slots=slots)                   # noqa: E731
+        ops, nbytes = 2.0 * M * N * K, N * K + M * K
+    elif case in ("w4a8_q4k", "w4a8_q6k"):
+        M, N, K = 2048, 8192, 5120
+        wcpu = synth.weights(N, K, 3)
+        w = w4a8.repack((synth.q4_k if case.endswith("q4k") else synth.q6_k)(wcpu)).to(dev)
+        x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
+        q = torch.empty(M, K, dtype=torch.int8, device=dev)
+        s = torch.empty(K // 256, M, device=dev)
+        xs = torch.empty(K // 256, M, 16, dtype=torch.int8, device=dev)
+        nr = torch.tensor([M], dtype=torch.int32, device=dev)
+        quant.rows_g(x, q, s, xs, nr, M)
+        out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+        fn = lambda: w4a8.gemm(q, s, xs, w, out, nr)                                              # noqa: E731
+        ops, nbytes = 2.0 * M * N * K, w.nbytes() + M * K
+    elif case == "mxfp4":
+        M, N, K = 2048, 34816, 5120
+        wq = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev, generator=gen)
+        ws = torch.randint(118, 126, (N, K // 32), dtype=torch.uint8, device=dev, generator=gen)
+        w = mxfp4.prepare(mxfp4.MX4(wq, ws, N, K))
+        x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
+        q = torch.empty(M, K // 2, dtype=torch.uint8, device=dev)
+        s = torch.empty(M, K // 32, dtype=torch.uint8, device=dev)
+        mxfp4.quantize_act(x, q, s)
+        out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+        fn = lambda: mxfp4.gemm(q, s, w, out, M)                                                  # noqa: E731
+        ops, nbytes = 2.0 * M * N * K, N * K * 17 // 32 + M * K * 17 // 32
+    elif case in ("rows_q8", "swiglu_q8"):
+        T, K = 8192, 17408
+        nr = torch.tensor([T], dtype=torch.int32, device=dev)
+        q = torch.empty(T, K, dtype=torch.int8, device=dev)
+        s = torch.empty(T, device=dev)
+        if case == "rows_q8":
+            x = torch.randn(T, K, device=dev, generator=gen).to(torch.bfloat16)
+            fn = lambda: quant.rows_q8(x, None, q, s, nr, T)                                      # noqa: E731
+            ops, nbytes = 0.0, 3 * T * K
+        else:
+            x = torch.randn(T, 2 * K, device=dev, generator=gen).to(torch.bfloat16)
+            fn = lambda: quant.swiglu_q8(x, None, q, s, nr, T)                                    # noqa: E731
+            ops, nbytes = 0.0, 5 * T * K
+    else:
+        raise SystemExit(f"unknown probe {case}")
+    fn()
+    torch.cuda.synchronize()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(5)]
+    for a0, a1 in ev:
+        a0.record()
+        fn()
+        a1.record()
+    torch.cuda.synchronize()
+    us = min(a0.elapsed_time(a1) for a0, a1 in ev) * 1e3
+    code, where = _lib.device_status()
+    print(json.dumps({"probe": case, "us": round(us, 2), "tops": round(ops / us / 1e6, 1),
+                      "gbs": round(nbytes / us / 1e3, 1), "device_status": code}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -402,6 +483,7 @@ def main():
     ap.add_argument("--rows", type=int, default=M_DEFAULT)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--detail", action="store_true", help="per-shape GEMM table instead of the JSON line")
+    ap.add_argument("--probe", default=None, help="one kernel case, a few eager launches (for ncu)")
     ap.add_argument("--detail-rows", default=None)
     ap.add_argument("--detail-shapes", default=None)
     ap.add_argument("--detail-gk", default=None, help="comma list; 0 = one group per row (gk == K), 32 = Q8_0 blocks")
@@ -409,6 +491,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.probe:
+        run_probe(args)
     elif args.detail:
         run_detail(args)
     else:

@@ -11,6 +11,7 @@
 #include "../../include/prism_b200.h"
 #include "common.cuh"
 #include "quant.cuh"
+#include "quant_pipe.cuh"
 #include "w8a8_gemm.cuh"
 #include "w4a8_gemm.cuh"
 #include "mxfp4_gemm.cuh"
@@ -223,6 +224,54 @@ int launch_w4a8(const int8_t* xq, const float* a, const int8_t* xs, int Ma, cons
     return PB_OK;
 }
 
+// Row-pipelined quantizers (quant_pipe.cuh): persistent CTAs, rows staged in shared memory by bulk copies.
+template <int KIND, int VPT, bool BF16>
+int launch_pipe_v(bool full, const quant::PipeArgs& p, int grid, int smem, cudaStream_t st) {
+    int rc;
+    if (full) {
+        auto k = quant::row_pipe_kernel<KIND, VPT, BF16, true>;
+        static bool c = false;
+        if (!c) { if ((rc = set_smem(k, 200 * 1024))) return rc; c = true; }
+        k<<<grid, quant::PIPE_THREADS, smem, st>>>(p);
+    } else {
+        auto k = quant::row_pipe_kernel<KIND, VPT, BF16, false>;
+        static bool c = false;
+        if (!c) { if ((rc = set_smem(k, 200 * 1024))) return rc; c = true; }
+        k<<<grid, quant::PIPE_THREADS, smem, st>>>(p);
+    }
+    return PB_OK;
+}
+
+template <int KIND, bool BF16>
+int launch_pipe(bool full, quant::PipeArgs p, cudaStream_t st) {
+    const int nvec = p.K / 8;
+    const int vpt = (nvec + quant::PIPE_THREADS - 1) / quant::PIPE_THREADS;
+    int stages = (96 * 1024) / p.row_bytes;                       // about 96 KB per CTA: two CTAs per SM
+    int per_sm = 2;
+    if (stages < 3) {                                             // long rows: one CTA per SM, up to 200 KB
+        stages = (199 * 1024) / p.row_bytes;
+        per_sm = 1;
+    }
+    if (stages < 2) return PB_UNSUPPORTED_SHAPE;
+    if (stages > 8) stages = 8;
+    p.stages = stages;
+    const int smem = stages * p.row_bytes + 128;
+    int grid = sm_count() * per_sm;
+    if (grid > p.T) grid = p.T;
+    int rc;
+    if (vpt <= 2) rc = launch_pipe_v<KIND, 2, BF16>(full, p, grid, smem, st);
+    else if (vpt <= 3) rc = launch_pipe_v<KIND, 3, BF16>(full, p, grid, smem, st);
+    else if (vpt <= 5) rc = launch_pipe_v<KIND, 5, BF16>(full, p, grid, smem, st);
+    else if (vpt <= 9) rc = launch_pipe_v<KIND, 9, BF16>(full, p, grid, smem, st);
+    else if (vpt <= 16) rc = launch_pipe_v<KIND, 16, BF16>(full, p, grid, smem, st);
+    else return PB_UNSUPPORTED_SHAPE;
+    if (rc) return rc;
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+constexpr int kPipeMinRows = 256;      // below this one CTA per row is as good (too few rows to pipeline)
+
 int pick_nb(int M) { return M <= 8 ? 8 : M <= 16 ? 16 : M <= 32 ? 32 : 64; }
 
 bool div_full() {
@@ -428,6 +477,12 @@ int pb_quant_rows(const void* x, int x_fp32, long ldx, const float* inv_s, int8_
         PB_CUDA(cudaGetLastError());
         return PB_OK;
     }
+    if (T >= kPipeMinRows && K <= 32768) {
+        quant::PipeArgs pa{x, ldx, inv_s, q, s, n_rows, amax, T, K, mode, K * (bf16 ? 2 : 4), 0};
+        const int rc = bf16 ? launch_pipe<quant::PIPE_ROWS, true>(full, pa, st)
+                            : launch_pipe<quant::PIPE_ROWS, false>(full, pa, st);
+        if (rc != PB_UNSUPPORTED_SHAPE) return rc;
+    }
     // 4 vectors of 8 inputs per thread (8 beyond 32768 / 2 inputs), as many threads as the row needs
     const int nvec = K / 8;
     const int vpt = nvec <= 4096 ? 4 : 8;
@@ -445,6 +500,11 @@ int pb_swiglu_q8(const void* gu, const float* inv_s, int8_t* q, float* s, const 
     if (mode < 0 || mode > 2 || (mode != 0 && !amax)) return PB_BAD_ARGUMENT;
     if (FF % 8 || FF > 32768 || !aligned16(gu) || ((uintptr_t)q & 7)) return PB_UNSUPPORTED_SHAPE;
     const bool full = div_full();
+    if (T >= kPipeMinRows) {
+        quant::PipeArgs pa{gu, 2l * FF, inv_s, q, s, n_rows, amax, T, FF, mode, 4 * FF, 0};
+        const int rc = launch_pipe<quant::PIPE_SWIGLU, true>(full, pa, st);
+        if (rc != PB_UNSUPPORTED_SHAPE) return rc;
+    }
     const int nvec = FF / 8;
     const int threads = ((nvec + 3) / 4 + 31) / 32 * 32;          // 4 vectors of 8 outputs per thread
     const __nv_bfloat16* g = (const __nv_bfloat16*)gu;

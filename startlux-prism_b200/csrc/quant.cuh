@@ -188,8 +188,10 @@ quant_groups_kernel(const void* __restrict__ x, int8_t* __restrict__ q, float* _
 }
 
 // ------------------------------------------------------------------------------------------------- swiglu_q8
-// y = g / (1 + exp(-g)) * u * inv_s[c] (the reference's expression order, kernels/quant.py:256), then rows_q8's rounding.
-__device__ __forceinline__ float swiglu(float g, float u) { return __fmul_rn(__fdiv_rn(g, 1.0f + __expf(-g)), u); }
+// y = g / (1 + exp(-g)) * u * inv_s[c] (the reference's expression order, kernels/quant.py:256; the division is the
+// approximate full-range one a Triton `/` lowers to), then rows_q8's rounding.  The same expression as the
+// row-pipelined kernel (quant_pipe.cuh): a row's bits do not depend on which kernel quantizes it.
+__device__ __forceinline__ float swiglu(float g, float u) { return __fmul_rn(fdiv<true>(g, 1.0f + __expf(-g)), u); }
 
 template <int VPT, bool FULL>
 __global__ void __launch_bounds__(1024)

@@ -95,3 +95,52 @@ def test_fold_odd(dev):
     hd = h.to(dev)
     quant.fold(hd, slots.to(dev), w8a8.Deferred(S, sa.to(dev), sw.to(dev)), n_rows(4, dev), T)
     assert same(hd, ref)
+
+
+@pytest.mark.parametrize("T,K,live", [(300, 5120, 290), (1000, 2560, 1000), (260, 17408, 257), (512, 264, 512)])
+def test_rows_q8_many_rows(dev, T, K, live):
+    """From 256 rows the row-pipelined kernel runs (persistent CTAs, rows staged in shared memory): the same bits as
+    the oracle, for bf16, fp32, smoothed and strided inputs; rows >= live untouched."""
+    x = synth.activations(T, K, seed=T)
+    inv = torch.exp(torch.randn(K, generator=torch.Generator().manual_seed(1)) * 0.1)
+    nr = n_rows(live, dev)
+    for xin, iv in ((x, None), (x, inv), (x.float() * 0.731, None)):
+        ref_in = np_bits(xin) if xin.dtype == torch.bfloat16 else xin.numpy()
+        rq, rs = oracle.quant_rows(ref_in, inv_s=None if iv is None else iv.numpy(), live=live)
+        q = torch.full((T, K), 99, dtype=torch.int8, device=dev)
+        s = torch.full((T,), -1.0, device=dev)
+        quant.rows_q8(xin.to(dev), None if iv is None else iv.to(dev), q, s, nr, T)
+        assert same(q[:live], rq[:live]), first_diff(q[:live].cpu().numpy(), rq[:live])
+        assert same(s[:live], rs[:live, 0])
+        assert bool((q[live:] == 99).all()) and bool((s[live:] == -1).all())
+    wide = torch.zeros(T, K + 64, dtype=torch.bfloat16)
+    wide[:, 32:32 + K] = x
+    rq, rs = oracle.quant_rows(np_bits(x), live=live)
+    q = torch.zeros(T, K, dtype=torch.int8, device=dev)
+    s = torch.zeros(T, device=dev)
+    quant.rows_q8(wide.to(dev)[:, 32:32 + K], None, q, s, nr, T)
+    assert same(q[:live], rq[:live]) and same(s[:live], rs[:live, 0])
+    # tensor-parallel modes on the pipelined kernel
+    amax = torch.zeros(T, device=dev)
+    quant.rows_q8(x.to(dev), None, q, s, nr, T, mode=1, amax=amax)
+    big = amax * 2
+    quant.rows_q8(x.to(dev), None, q, s, nr, T, mode=2, amax=big)
+    assert np.allclose(s[:live].cpu().numpy(), 2 * rs[:live, 0], rtol=1e-6)
+
+
+@pytest.mark.parametrize("T,FF", [(300, 17408), (256, 1024)])
+def test_swiglu_q8_many_rows(dev, T, FF):
+    """The pipelined SwiGLU quantizer against the oracle within one int8 step, and bit-identical to the per-row
+    kernel (the first 200 rows quantized alone)."""
+    g = torch.Generator().manual_seed(FF + 1)
+    gu = (torch.randn(T, 2 * FF, generator=g) * 2).to(torch.bfloat16)
+    rq, rs = oracle.swiglu_q8(np_bits(gu))
+    q = torch.zeros(T, FF, dtype=torch.int8, device=dev)
+    s = torch.zeros(T, device=dev)
+    quant.swiglu_q8(gu.to(dev), None, q, s, n_rows(T, dev), T)
+    assert np.abs(q.cpu().numpy().astype(int) - rq.astype(int)).max() <= 1
+    assert np.allclose(s.cpu().numpy(), rs, rtol=1e-5)
+    q2 = torch.zeros(200, FF, dtype=torch.int8, device=dev)
+    s2 = torch.zeros(200, device=dev)
+    quant.swiglu_q8(gu[:200].contiguous().to(dev), None, q2, s2, n_rows(200, dev), 200)
+    assert same(q2, q[:200].contiguous()) and same(s2, s[:200].contiguous())
