@@ -71,7 +71,9 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
 // runs to its normal end (tensor memory freed, no trap).  Also returns false at once when another role aborted.
 #define PB_WAIT_NS 4000000000ull
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned where) {
-    if (mbar_test(bar, parity)) return true;
+#pragma unroll 1
+    for (int i = 0; i < 4096; ++i)                       // the common case: no clock read, no flag read
+        if (mbar_test(bar, parity)) return true;
     unsigned long long t0 = global_timer_ns();
     for (unsigned it = 1;; ++it) {
         if (mbar_test(bar, parity)) return true;

@@ -225,19 +225,19 @@ int launch_w4a8(const int8_t* xq, const float* a, const int8_t* xs, int Ma, cons
 }
 
 // Row-pipelined quantizers (quant_pipe.cuh): persistent CTAs, rows staged in shared memory by bulk copies.
-template <int KIND, int VPT, bool BF16>
+template <int KIND, int VPT, bool BF16, int THREADS>
 int launch_pipe_v(bool full, const quant::PipeArgs& p, int grid, int smem, cudaStream_t st) {
     int rc;
     if (full) {
-        auto k = quant::row_pipe_kernel<KIND, VPT, BF16, true>;
+        auto k = quant::row_pipe_kernel<KIND, VPT, BF16, true, THREADS>;
         static bool c = false;
         if (!c) { if ((rc = set_smem(k, 200 * 1024))) return rc; c = true; }
-        k<<<grid, quant::PIPE_THREADS, smem, st>>>(p);
+        k<<<grid, THREADS, smem, st>>>(p);
     } else {
-        auto k = quant::row_pipe_kernel<KIND, VPT, BF16, false>;
+        auto k = quant::row_pipe_kernel<KIND, VPT, BF16, false, THREADS>;
         static bool c = false;
         if (!c) { if ((rc = set_smem(k, 200 * 1024))) return rc; c = true; }
-        k<<<grid, quant::PIPE_THREADS, smem, st>>>(p);
+        k<<<grid, THREADS, smem, st>>>(p);
     }
     return PB_OK;
 }
@@ -245,10 +245,10 @@ int launch_pipe_v(bool full, const quant::PipeArgs& p, int grid, int smem, cudaS
 template <int KIND, bool BF16>
 int launch_pipe(bool full, quant::PipeArgs p, cudaStream_t st) {
     const int nvec = p.K / 8;
-    const int vpt = (nvec + quant::PIPE_THREADS - 1) / quant::PIPE_THREADS;
-    int stages = (96 * 1024) / p.row_bytes;                       // about 96 KB per CTA: two CTAs per SM
+    // two CTAs per SM: about 100 KB of row ring each
+    int stages = (100 * 1024) / p.row_bytes;
     int per_sm = 2;
-    if (stages < 3) {                                             // long rows: one CTA per SM, up to 200 KB
+    if (stages < 2) {                                             // very long rows: one CTA per SM
         stages = (199 * 1024) / p.row_bytes;
         per_sm = 1;
     }
@@ -259,11 +259,10 @@ int launch_pipe(bool full, quant::PipeArgs p, cudaStream_t st) {
     int grid = sm_count() * per_sm;
     if (grid > p.T) grid = p.T;
     int rc;
-    if (vpt <= 2) rc = launch_pipe_v<KIND, 2, BF16>(full, p, grid, smem, st);
-    else if (vpt <= 3) rc = launch_pipe_v<KIND, 3, BF16>(full, p, grid, smem, st);
-    else if (vpt <= 5) rc = launch_pipe_v<KIND, 5, BF16>(full, p, grid, smem, st);
-    else if (vpt <= 9) rc = launch_pipe_v<KIND, 9, BF16>(full, p, grid, smem, st);
-    else if (vpt <= 16) rc = launch_pipe_v<KIND, 16, BF16>(full, p, grid, smem, st);
+    if (nvec <= 256 * 3) rc = launch_pipe_v<KIND, 3, BF16, 256>(full, p, grid, smem, st);
+    else if (nvec <= 512 * 3) rc = launch_pipe_v<KIND, 3, BF16, 512>(full, p, grid, smem, st);
+    else if (nvec <= 512 * 5) rc = launch_pipe_v<KIND, 5, BF16, 512>(full, p, grid, smem, st);
+    else if (nvec <= 512 * 8) rc = launch_pipe_v<KIND, 8, BF16, 512>(full, p, grid, smem, st);
     else return PB_UNSUPPORTED_SHAPE;
     if (rc) return rc;
     PB_CUDA(cudaGetLastError());

@@ -69,30 +69,37 @@ __device__ __forceinline__ void load8(const void* x, long idx, float (&v)[8]) {
     }
 }
 
-// q = rint(v / scale) for 8 values, bit-identical to the IEEE division but cheaper: y' = v * (1 / scale) is within
-// 3e-5 of the true quotient for |quotient| <= 128, so rint(y') can differ from rint(v / scale) only when y' lies
-// within that distance of a rounding boundary k + 0.5; those (rare) values take the exact division.
+// q = rint(v / scale) for 8 values, bit-identical to the IEEE division but far cheaper.  t = fma(v, 1 / scale, 1.5 * 2^23)
+// holds rint(v / scale) (computed from the exact product, half to even) in its low mantissa bits, so the int8 value is
+// the low byte of t: no conversion instruction.  y' = v * (1 / scale) is within 3e-5 of the true quotient for
+// |quotient| <= 128, so this can differ from rint(v / scale) only when y' lies that close to a rounding boundary
+// k + 0.5: d = y' - rint(y') is then near +-0.5, and those (rare) vectors take the exact division instead.
 template <bool FULL>
 __device__ __forceinline__ uint2 quant8(const float (&v)[8], float scale, float rcp) {
-    int q[8];
     if (FULL) {
+        int q[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) q[i] = __float2int_rn(fdiv<true>(v[i], scale));
-    } else {
-        bool near = false;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float y = __fmul_rn(v[i], rcp);
-            const float r = rintf(y);
-            q[i] = (int)r;
-            near |= fabsf(fabsf(y - r) - 0.5f) < 1e-3f;
-        }
-        if (near) {                                             // rare: one branch per 8 values
-#pragma unroll
-            for (int i = 0; i < 8; ++i) q[i] = __float2int_rn(__fdiv_rn(v[i], scale));
-        }
+        return make_uint2(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]));
     }
-    return make_uint2(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]));
+    const float magic = 12582912.0f;
+    uint32_t t[8];
+    bool near = false;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float tf = __fmaf_rn(v[i], rcp, magic);
+        const float d = __fmaf_rn(v[i], rcp, -__fadd_rn(tf, -magic));
+        near |= fabsf(d) > 0.499f;
+        t[i] = __float_as_uint(tf);
+    }
+    if (near) {                                                 // rare: one branch per 8 values
+        int q[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q[i] = __float2int_rn(__fdiv_rn(v[i], scale));
+        return make_uint2(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]));
+    }
+    return make_uint2(__byte_perm(__byte_perm(t[0], t[1], 0x0040), __byte_perm(t[2], t[3], 0x0040), 0x5410),
+                      __byte_perm(__byte_perm(t[4], t[5], 0x0040), __byte_perm(t[6], t[7], 0x0040), 0x5410));
 }
 
 // ------------------------------------------------------------------------------------------------- rows_q8
