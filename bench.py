@@ -404,6 +404,8 @@ def run_probe(args):
     torch.cuda.set_device(dev)
     gen = torch.Generator(device=dev).manual_seed(2)
     case = args.probe
+    if case == "peak":
+        return run_peak(dev)
     ri = lambda *s: torch.randint(-127, 128, s, dtype=torch.int8, device=dev, generator=gen)     # noqa: E731
     if case in ("tile", "tile_add", "decode", "decode32"):
         M = 2048 if case.startswith("tile") else 16
@@ -472,6 +474,60 @@ def run_probe(args):
     code, where = _lib.device_status()
     print(json.dumps({"probe": case, "us": round(us, 2), "tops": round(ops / us / 1e6, 1),
                       "gbs": round(nbytes / us / 1e3, 1), "device_status": code}), flush=True)
+
+
+def run_peak(dev):
+    """The int8 tensor-core ceiling: pb_int8_peak_probe for ~2 s per operand pattern with the SM clock and power sampled,
+    next to the same loop over a real GEMM (gate|up, M = 8192)."""
+    import torch
+
+    from prism_b200 import _lib, w8a8
+    L = _lib.lib()
+    iters = 20000
+    ops = 2.0 * 128 * 256 * 128 * iters * 148
+    st = lambda: torch.cuda.current_stream().cuda_stream                  # noqa: E731
+    for pattern in (0, 1):
+        L.pb_int8_peak_probe(200, pattern, None, st())
+        torch.cuda.synchronize()
+        sampler = ClockSampler(0)
+        sampler.start()
+        best, t_end = 0.0, time.time() + 2.0
+        rates = []
+        while time.time() < t_end:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _lib.check(L.pb_int8_peak_probe(iters, pattern, None, st()), "peak probe")
+            e1.record()
+            torch.cuda.synchronize()
+            rates.append(ops / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+        clocks = sampler.stop()
+        print(json.dumps({"probe": "int8_peak", "pattern": "random" if pattern else "zeros", "tops_first": round(rates[0], 1),
+                          "tops_last": round(rates[-1], 1), "tops_max": round(max(rates), 1), "launches": len(rates),
+                          "clocks": clocks}), flush=True)
+    gen = torch.Generator(device=dev).manual_seed(2)
+    M, N, K = 8192, 34816, 5120
+    a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev, generator=gen)
+    w = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev, generator=gen)
+    g = (torch.randn(M, K, device=dev, generator=gen) * 25).round().clamp(-127, 127).to(torch.int8)
+    sa, sw = torch.rand(M, device=dev) * 1e-2, torch.rand(N, device=dev) * 1e-3
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+    nr = torch.tensor([M], dtype=torch.int32, device=dev)
+    for name, act in (("uniform int8 activations", a), ("gaussian int8 activations (sigma 25)", g)):
+        w8a8.gemm(act, sa, w, sw, out, nr, K)
+        torch.cuda.synchronize()
+        sampler = ClockSampler(0)
+        sampler.start()
+        rates, t_end = [], time.time() + 2.0
+        while time.time() < t_end:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                w8a8.gemm(act, sa, w, sw, out, nr, K)
+            e1.record()
+            torch.cuda.synchronize()
+            rates.append(10 * 2.0 * M * N * K / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+        print(json.dumps({"probe": "gemm_sustained", "case": name, "tops_first": round(rates[0], 1),
+                          "tops_last": round(rates[-1], 1), "clocks": sampler.stop()}), flush=True)
 
 
 def main():

@@ -102,6 +102,11 @@ int pb_mxfp4_quant(const void* x, int x_fp32, const float* inv, void* q, void* s
 int pb_mxfp4_gemm(const void* aq, const void* a_sf, const void* bq, const void* b_sf, void* out, long ldo, int M,
                   int N, int K, int epi, void* stream);
 
+/* Measurement aid: the int8 tensor-core rate with shared-memory-resident operands and no loads (one CTA per SM, `iters`
+ * batches of four 128 x 256 x 32 MMAs each; pattern 0 = zero operands, 1 = pseudo-random bytes).  ops = 2 * 128 * 256 *
+ * 128 * iters per SM.  Counterpart of the reference's bench/csrc/mma_peak.cu.  cycles (device, one per SM) may be NULL. */
+int pb_int8_peak_probe(int iters, int pattern, unsigned long long* cycles, void* stream);
+
 /* pb_w8a8_gemm for callers that cannot allocate device memory.  No counterpart in the reference (its stream-K
  * workspace is always a torch allocation, kernels/cuda_ext.py:139-143).
  * Some hosts of this library have no allocator to offer: a plugin loaded into a process whose memory pool is owned by

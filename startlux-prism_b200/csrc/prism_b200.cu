@@ -148,6 +148,40 @@ int launch_tile(const int8_t* a, const float* a_s, const int8_t* w, const float*
     return PB_OK;
 }
 
+// The CTA-pair kernel (clusters of two): 256 x 256 tiles.  Opt-in with PRISM_B200_PAIR=1: under the 1 kW power cap it
+// sustains the same rate as the single-CTA tile kernel and is a little slower in short bursts.
+bool pair_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("PRISM_B200_PAIR");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
+
+template <int EPI>
+int launch_pair(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, void* out, long ldo,
+                const int* n_rows, int M, int N, int K, cudaStream_t st) {
+    CUtensorMap ta, tw;
+    int rc;
+    if ((rc = tensor_map(&ta, a, K, M, K, w8a8::BK, w8a8::BM, 0))) return rc;
+    if ((rc = tensor_map(&tw, w, K, N, K, w8a8::BK, w8a8::BM, 0))) return rc;
+    auto kern = w8a8::w8a8_pair_kernel<EPI>;
+    static bool configured = false;
+    if (!configured) {
+        if ((rc = set_smem(kern, w8a8::PAIR_SMEM))) return rc;
+        configured = true;
+    }
+    const int word_ok = EPI == w8a8::EPI_BF16 ? (((uintptr_t)out & 3) == 0 && ldo % 2 == 0) : 1;
+    const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    int pairs = sm_count() / 2;
+    if (pairs > tiles) pairs = tiles;
+    // the kernel carries its cluster shape (2 x 1 x 1) at compile time: an even grid is all a launch needs
+    kern<<<2 * pairs, 192, w8a8::PAIR_SMEM, st>>>(ta, tw, a_s, w_s, out, ldo, n_rows, M, N, K, word_ok);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
 template <int NB, bool GROUPED>
 int launch_swap(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, w8a8::SwapArgs p, int split,
                 cudaStream_t st) {
@@ -395,6 +429,11 @@ int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float
         return launch_swap_nb<true>(pick_nb(M), a, a_s, w, w_s, p, 1, st);
     }
     if (gk != K) return PB_UNSUPPORTED_SHAPE;
+    if (M >= 512 && N >= 256 && pair_enabled() && split == 1) {
+        if (epi == PB_EPI_I32) return launch_pair<w8a8::EPI_I32>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st);
+        if (epi == PB_EPI_BF16) return launch_pair<w8a8::EPI_BF16>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st);
+        return launch_pair<w8a8::EPI_ADD>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st);
+    }
     if (M > 64) {
         if (epi == PB_EPI_I32) {
             // split z of K is a product over a K slice: run the tile kernel once per slice on offset pointers
@@ -614,6 +653,20 @@ int pb_mxfp4_gemm(const void* aq, const void* a_sf, const void* bq, const void* 
     const int tiles = ((M + 127) / 128) * ((N + 127) / 128);
     const int grid = tiles < sm_count() ? tiles : sm_count();
     mxfp4::mxfp4_gemm_kernel<<<grid, 192, mxfp4::SMEM, (cudaStream_t)stream>>>(ta, tb, p);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+int pb_int8_peak_probe(int iters, int pattern, unsigned long long* cycles, void* stream) {
+    if (iters <= 0) return PB_BAD_ARGUMENT;
+    const int smem = (128 + 256) * 128 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        int rc = set_smem(w8a8::int8_peak_kernel, smem);
+        if (rc) return rc;
+        configured = true;
+    }
+    w8a8::int8_peak_kernel<<<sm_count(), 128, smem, (cudaStream_t)stream>>>(iters, pattern, cycles);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }

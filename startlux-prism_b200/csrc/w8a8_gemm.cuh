@@ -111,6 +111,95 @@ __device__ __forceinline__ void store_row32(void* out, long ldo, long row, int c
 }
 
 // ================================================================================================= tile kernel
+// The epilogue of one 128 x BN accumulator (one lane quarter per warp, thread = row): scale, then store.
+template <int BN, int EPI>
+__device__ __forceinline__ void drain_accumulator(void* __restrict__ out, long ldo, int N, int live, int m0, int n0,
+                                                  int q, int lane, uint32_t lane_addr, uint32_t* stg,
+                                                  const float* swb, float sa, bool word_ok) {
+    const int row = m0 + q * 32 + lane;
+    const bool rok = row < live;
+    if (word_ok) {
+        // coalesced path: every thread scales its row's values and parks them in shared memory (row-major,
+        // 33-word pitch: conflict-free both ways); then each warp instruction moves one row's 32 consecutive
+        // words (128 bytes) to or from global memory.
+        constexpr int CPW = (EPI == EPI_BF16) ? 2 : 1;            // output columns per 32-bit word
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 32 * CPW) {
+            if (n0 + c0 >= N) break;
+            uint32_t r[32];
+            tmem_ld32(lane_addr + c0, r);
+            tmem_ld_wait();
+            if (EPI == EPI_BF16) {
+                uint32_t r2[32];
+                tmem_ld32(lane_addr + c0 + 32, r2);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(scale2((int)r[2 * j], sa, swb[c0 + 2 * j]),
+                                                              scale2((int)r[2 * j + 1], sa, swb[c0 + 2 * j + 1]));
+                    stg[lane * 33 + j] = *(uint32_t*)&b2;
+                }
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(
+                        scale2((int)r2[2 * j], sa, swb[c0 + 32 + 2 * j]),
+                        scale2((int)r2[2 * j + 1], sa, swb[c0 + 32 + 2 * j + 1]));
+                    stg[lane * 33 + 16 + j] = *(uint32_t*)&b2;
+                }
+            } else if (EPI == EPI_ADD) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) stg[lane * 33 + j] = __float_as_uint(scale2((int)r[j], sa, swb[c0 + j]));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) stg[lane * 33 + j] = r[j];
+            }
+            __syncwarp();
+            const int col = n0 + c0 + lane * CPW;                 // first column of this lane's word
+            const int rows_here = live - (m0 + q * 32);           // live rows among this warp's 32
+            if (col + CPW <= N) {
+                if (EPI == EPI_ADD) {
+                    // all 32 rows' loads are issued before the first add: one round trip per chunk, not 32
+                    float* base = (float*)out + (long)(m0 + q * 32) * ldo + col;
+                    float o[32];
+#pragma unroll
+                    for (int rr = 0; rr < 32; ++rr)
+                        if (rr < rows_here) o[rr] = __ldcg(base + (long)rr * ldo);
+#pragma unroll
+                    for (int rr = 0; rr < 32; ++rr)
+                        if (rr < rows_here)
+                            base[(long)rr * ldo] = __fadd_rn(o[rr], __uint_as_float(stg[rr * 33 + lane]));
+                } else {
+#pragma unroll 8
+                    for (int rr = 0; rr < 32; ++rr) {
+                        if (rr < rows_here) {
+                            const long off = (long)(m0 + q * 32 + rr) * ldo + col;
+                            const uint32_t v = stg[rr * 33 + lane];
+                            if (EPI == EPI_BF16)
+                                *(uint32_t*)((__nv_bfloat16*)out + off) = v;
+                            else
+                                ((uint32_t*)out)[off] = v;
+                        }
+                    }
+                }
+            } else if (EPI == EPI_BF16 && col < N) {              // odd N: the word's first column only
+                for (int rr = 0; rr < 32 && rr < rows_here; ++rr)
+                    ((uint16_t*)out)[(long)(m0 + q * 32 + rr) * ldo + col] = (uint16_t)(stg[rr * 33 + lane] & 0xffff);
+            }
+            __syncwarp();
+        }
+    } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(lane_addr + c * 32, r);
+            tmem_ld_wait();
+            const int col0 = n0 + c * 32;
+            const int nok = N - col0 >= 32 ? 32 : (N - col0 > 0 ? N - col0 : 0);
+            if (rok && nok > 0) store_row32<EPI>(out, ldo, row, col0, nok, false, r, sa, swb + c * 32);
+        }
+    }
+}
+
 template <int BN>
 struct TileCfg {
     static constexpr int STAGES = (BN == 256) ? 4 : 6;
@@ -265,86 +354,7 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             const float sa = (rok && EPI != EPI_I32) ? a_s[row] : 0.0f;
             uint32_t* stg = stage_buf + q * (32 * 33);
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
-            if (word_ok) {
-                // coalesced path: every thread scales its row's values and parks them in shared memory (row-major,
-                // 33-word pitch: conflict-free both ways); then each warp instruction moves one row's 32 consecutive
-                // words (128 bytes) to or from global memory.
-                constexpr int CPW = (EPI == EPI_BF16) ? 2 : 1;            // output columns per 32-bit word
-#pragma unroll 1
-                for (int c0 = 0; c0 < BN; c0 += 32 * CPW) {
-                    if (n0 + c0 >= N) break;
-                    uint32_t r[32];
-                    tmem_ld32(lane_addr + c0, r);
-                    tmem_ld_wait();
-                    if (EPI == EPI_BF16) {
-                        uint32_t r2[32];
-                        tmem_ld32(lane_addr + c0 + 32, r2);
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            __nv_bfloat162 b2 = __floats2bfloat162_rn(scale2((int)r[2 * j], sa, swb[c0 + 2 * j]),
-                                                                      scale2((int)r[2 * j + 1], sa, swb[c0 + 2 * j + 1]));
-                            stg[lane * 33 + j] = *(uint32_t*)&b2;
-                        }
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int j = 0; j < 16; ++j) {
-                            __nv_bfloat162 b2 = __floats2bfloat162_rn(
-                                scale2((int)r2[2 * j], sa, swb[c0 + 32 + 2 * j]),
-                                scale2((int)r2[2 * j + 1], sa, swb[c0 + 32 + 2 * j + 1]));
-                            stg[lane * 33 + 16 + j] = *(uint32_t*)&b2;
-                        }
-                    } else if (EPI == EPI_ADD) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) stg[lane * 33 + j] = __float_as_uint(scale2((int)r[j], sa, swb[c0 + j]));
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) stg[lane * 33 + j] = r[j];
-                    }
-                    __syncwarp();
-                    const int col = n0 + c0 + lane * CPW;                 // first column of this lane's word
-                    const int rows_here = live - (m0 + q * 32);           // live rows among this warp's 32
-                    if (col + CPW <= N) {
-                        if (EPI == EPI_ADD) {
-                            // all 32 rows' loads are issued before the first add: one round trip per chunk, not 32
-                            float* base = (float*)out + (long)(m0 + q * 32) * ldo + col;
-                            float o[32];
-#pragma unroll
-                            for (int rr = 0; rr < 32; ++rr)
-                                if (rr < rows_here) o[rr] = __ldcg(base + (long)rr * ldo);
-#pragma unroll
-                            for (int rr = 0; rr < 32; ++rr)
-                                if (rr < rows_here)
-                                    base[(long)rr * ldo] = __fadd_rn(o[rr], __uint_as_float(stg[rr * 33 + lane]));
-                        } else {
-#pragma unroll 8
-                            for (int rr = 0; rr < 32; ++rr) {
-                                if (rr < rows_here) {
-                                    const long off = (long)(m0 + q * 32 + rr) * ldo + col;
-                                    const uint32_t v = stg[rr * 33 + lane];
-                                    if (EPI == EPI_BF16)
-                                        *(uint32_t*)((__nv_bfloat16*)out + off) = v;
-                                    else
-                                        ((uint32_t*)out)[off] = v;
-                                }
-                            }
-                        }
-                    } else if (EPI == EPI_BF16 && col < N) {              // odd N: the word's first column only
-                        for (int rr = 0; rr < 32 && rr < rows_here; ++rr)
-                            ((uint16_t*)out)[(long)(m0 + q * 32 + rr) * ldo + col] = (uint16_t)(stg[rr * 33 + lane] & 0xffff);
-                    }
-                    __syncwarp();
-                }
-            } else {
-#pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
-                    uint32_t r[32];
-                    tmem_ld32(lane_addr + c * 32, r);
-                    tmem_ld_wait();
-                    const int col0 = n0 + c * 32;
-                    const int nok = N - col0 >= 32 ? 32 : (N - col0 > 0 ? N - col0 : 0);
-                    if (rok && nok > 0) store_row32<EPI>(out, ldo, row, col0, nok, false, r, sa, swb + c * 32);
-                }
-            }
+            drain_accumulator<BN, EPI>(out, ldo, N, live, m0, n0, q, lane, lane_addr, stg, swb, sa, word_ok != 0);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&aux->tempty[buf]));
@@ -355,6 +365,181 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+
+// ================================================================================================= pair kernel
+// The tile kernel on CTA pairs (clusters of two, tcgen05 cta_group::2): a pair owns a 256 x 256 output tile; each CTA
+// loads its own 128 activation rows and its own 128 of the 256 weight rows per K block (32 KB instead of the single-CTA
+// kernel's 48 KB for the same tensor work, and half the weight tile's shared-memory reads), the leader (cluster rank
+// 0) issues 256 x 256 x 32 MMAs that write 128 accumulator lanes in each CTA, and each CTA's epilogue warps drain their
+// own lanes.  Barriers: `full` lives in the leader and counts both CTAs' bytes; `empty` and `tfull` exist in both CTAs
+// and are each committed to by the leader; `tempty` lives in the leader and takes one arrival per epilogue warp of
+// both CTAs.  No multicast anywhere.
+constexpr int PAIR_BN = 256;
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_STAGE_BYTES = 2 * BM * BK;                     // 16 KB of A + 16 KB of B per CTA
+constexpr int PAIR_SMEM = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + (int)sizeof(Aux) + 2 * PAIR_BN * 4 + 4 * 32 * 33 * 4;
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+w8a8_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
+                 const float* __restrict__ a_s, const float* __restrict__ w_s, void* __restrict__ out, long ldo,
+                 const int* __restrict__ n_rows, int M, int N, int K, int word_ok) {
+    constexpr int BN = PAIR_BN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = align1024(smem_raw);
+    Aux* aux = (Aux*)(smem + PAIR_STAGES * PAIR_STAGE_BYTES);
+    float* sw_stash = (float*)(aux + 1);
+    uint32_t* stage_buf = (uint32_t*)(sw_stash + 2 * BN);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const bool leader = rank == 0;
+
+    int live = *n_rows;
+    live = live < M ? live : M;
+    const int num_m = (live + 2 * BM - 1) / (2 * BM), num_n = (N + BN - 1) / BN;
+    const int num_tiles = num_m * num_n, KB = (K + BK - 1) / BK;
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PAIR_STAGES; ++s) {
+            mbar_init(smem_u32(&aux->full[s]), 1);                // used in the leader only
+            mbar_init(smem_u32(&aux->empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&aux->tfull[b]), 1);
+            mbar_init(smem_u32(&aux->tempty[b]), 8);              // used in the leader only: 4 warps of each CTA
+        }
+        aux->abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(&aux->tmem_base), 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                            // both CTAs' barriers exist before any remote use
+    tc_fence_after();
+    const uint32_t tmem_base = aux->tmem_base;
+    volatile int* abort_flag = &aux->abort_flag;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (one thread per CTA)
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_a);
+            tma_prefetch_desc(&tm_w);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = pair; t < num_tiles && ok; t += npairs) {
+                const int m0 = (t % num_m) * 2 * BM + (int)rank * BM, n0 = (t / num_m) * BN + (int)rank * (BN / 2);
+                for (int kb = 0; kb < KB; ++kb) {
+                    if (!mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1, abort_flag, 0x1100 + stage)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t bar = map_to_cta(smem_u32(&aux->full[stage]), 0);
+                    if (leader) mbar_expect_tx(smem_u32(&aux->full[stage]), 2 * PAIR_STAGE_BYTES);
+                    uint8_t* st = smem + stage * PAIR_STAGE_BYTES;
+                    tma_load_2d_pair(smem_u32(st), &tm_a, kb * BK, m0, bar);
+                    tma_load_2d_pair(smem_u32(st + BM * BK), &tm_w, kb * BK, n0, bar);
+                    if (++stage == PAIR_STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            if (!ok) {
+                unsigned long long t0 = global_timer_ns();
+                while (global_timer_ns() - t0 < 2000000ull) {
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (the leader's one thread)
+        if (leader && lane == 0) {
+            const uint32_t idesc = umma_idesc_i8(2 * BM, BN);
+            int stage = 0, buf = 0;
+            uint32_t phase = 0, bphase = 0;
+            bool ok = true;
+            for (int t = pair; t < num_tiles && ok; t += npairs) {
+                if (!mbar_wait(smem_u32(&aux->tempty[buf]), bphase ^ 1, abort_flag, 0x1200 + buf)) break;
+                tc_fence_after();
+                const uint32_t d = tmem_base + buf * BN;
+                for (int kb = 0; kb < KB; ++kb) {
+                    if (!mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, 0x1300 + stage)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    uint8_t* st = smem + stage * PAIR_STAGE_BYTES;
+                    const uint64_t ad = umma_desc_k128(smem_u32(st));
+                    const uint64_t bd = umma_desc_k128(smem_u32(st + BM * BK));
+#pragma unroll
+                    for (int k = 0; k < BK / 32; ++k)
+                        umma_i8_pair(d, umma_desc_advance(ad, k * 32), umma_desc_advance(bd, k * 32), idesc,
+                                     (kb | k) ? 1u : 0u);
+                    const uint32_t eb = smem_u32(&aux->empty[stage]);
+                    tc_commit_pair(eb);                           // this CTA's producer may refill the stage ...
+                    tc_commit_pair(map_to_cta(eb, 1));            // ... and the peer's
+                    if (++stage == PAIR_STAGES) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) break;
+                const uint32_t fb = smem_u32(&aux->tfull[buf]);
+                tc_commit_pair(fb);
+                tc_commit_pair(map_to_cta(fb, 1));
+                buf ^= 1;
+                if (buf == 0) bphase ^= 1;
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (4 warps per CTA, own lanes)
+        const int q = warp & 3, et = threadIdx.x - 64;
+        int buf = 0;
+        uint32_t bphase = 0;
+        for (int t = pair; t < num_tiles; t += npairs) {
+            const int m0 = (t % num_m) * 2 * BM + (int)rank * BM, n0 = (t / num_m) * BN;
+            float* swb = sw_stash + buf * BN;
+            if (EPI != EPI_I32)
+                for (int i = et; i < BN; i += 128) swb[i] = (n0 + i < N) ? w_s[n0 + i] : 0.0f;
+            if (EPI == EPI_ADD) {
+                const int tn = (t == pair) ? t : t + npairs;
+                for (int pass = 0; pass < 2; ++pass) {
+                    const int tt = pass == 0 ? tn : tn + npairs;
+                    if (pass == 1 && t != pair) break;
+                    if (tt >= num_tiles) break;
+                    const int pm0 = (tt % num_m) * 2 * BM + (int)rank * BM, pn0 = (tt / num_m) * BN;
+                    for (int line = et; line < BM * (BN / 32); line += 128) {
+                        const int pr = pm0 + line / (BN / 32), pc = pn0 + (line % (BN / 32)) * 32;
+                        if (pr < live && pc < N)
+                            asm volatile("prefetch.global.L2 [%0];" ::"l"((const float*)out + (long)pr * ldo + pc));
+                    }
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (!mbar_wait(smem_u32(&aux->tfull[buf]), bphase, abort_flag, 0x1400 + buf)) break;
+            tc_fence_after();
+            const int row = m0 + q * 32 + lane;
+            const float sa = (row < live && EPI != EPI_I32) ? a_s[row] : 0.0f;
+            uint32_t* stg = stage_buf + q * (32 * 33);
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+            drain_accumulator<BN, EPI>(out, ldo, N, live, m0, n0, q, lane, lane_addr, stg, swb, sa, word_ok != 0);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&aux->tempty[buf]), 0));
+            buf ^= 1;
+            if (buf == 0) bphase ^= 1;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                            // no CTA leaves while its peer may still signal it
+    if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
 }
 
 // ================================================================================================= swapped kernel
@@ -675,6 +860,56 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+// ================================================================================================= peak probe
+// The tensor core's int8 rate with no operand traffic at all: every CTA fills one stage of shared memory once
+// (pattern 0: zeros, 1: pseudo-random bytes) and its MMA thread issues `iters` batches of four 128 x 256 x 32 MMAs
+// on it.  What a GEMM kernel can reach at most on this GPU at the clock the power cap allows: the roofline's measured
+// denominator (the method of the reference's bench/csrc/mma_peak.cu, on tcgen05).
+__global__ void __launch_bounds__(128, 1) int8_peak_kernel(int iters, int pattern, unsigned long long* cycles) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = align1024(smem_raw);
+    __shared__ uint64_t done;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    const int warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < (128 + 256) * 128 / 4; i += blockDim.x) {
+        uint32_t v = (uint32_t)i * 2654435761u + blockIdx.x * 40503u;
+        v ^= v >> 13;
+        v *= 0x9E3779B1u;
+        ((uint32_t*)smem)[i] = pattern ? (v ^ (v >> 15)) : 0u;
+    }
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&done), 1);
+        abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(&tmem_slot), 256);
+        tmem_relinquish();
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    if (threadIdx.x == 0) {
+        const uint32_t idesc = umma_idesc_i8(128, 256);
+        const uint64_t ad = umma_desc_k128(smem_u32(smem)), bd = umma_desc_k128(smem_u32(smem + 128 * 128));
+        const long long c0 = clock64();
+        for (int it = 0; it < iters; ++it) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                umma_i8(tmem_base, umma_desc_advance(ad, k * 32), umma_desc_advance(bd, k * 32), idesc, (it | k) ? 1u : 0u);
+        }
+        tc_commit(smem_u32(&done));
+        mbar_wait(smem_u32(&done), 0, &abort_flag, 0x1500);
+        if (cycles) cycles[blockIdx.x] = (unsigned long long)(clock64() - c0);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, 256);
 }
 
 }  // namespace w8a8

@@ -148,3 +148,35 @@ def test_config0_synthetic(dev):
     out1 = torch.zeros(16, 5120, dtype=torch.bfloat16, device=dev)
     w8a8.gemm(q1, s1, wq1.to(dev), ws1.to(dev).view(-1), out1, n_rows(16, dev), 5120)
     assert same(out1, bf16_from_bits(ref1)), first_diff(np_bits(out1), ref1)
+
+
+@pytest.mark.parametrize("M,N,K,live", [(512, 512, 1024, 512), (700, 1000, 2560, 650), (2048, 5120, 5120, 2048),
+                                        (1300, 4608, 640, 1290)])
+def test_gemm_cta_pairs(dev, M, N, K, live, monkeypatch):
+    """The CTA-pair kernel (clusters of two, 256 x 256 tiles; PRISM_B200_PAIR=1 before the library's first GEMM): all
+    three epilogues against the oracle bit for bit, partial tiles in M and N, rows >= live untouched.  Run in a child
+    process so the switch is read afresh."""
+    import os
+    import subprocess
+    import sys
+    if os.environ.get("PRISM_B200_PAIR") != "1":
+        env = dict(os.environ, PRISM_B200_PAIR="1")
+        r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", __file__, "-k",
+                            f"test_gemm_cta_pairs and {M}-{N}-{K}-{live}"], env=env, capture_output=True, text=True)
+        assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+        return
+    a, w, sa, sw = rand_w8a8(M, N, K, seed=M + K)
+    an, wn, san, swn = a.numpy(), w.numpy(), sa.numpy(), sw.numpy()
+    ref0 = oracle.w8a8_gemm(an, san, wn, swn, K, 0, live)
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+    run(dev, a, w, sa, sw, out, live, K, 0)
+    assert same(out, bf16_from_bits(ref0)), first_diff(np_bits(out), ref0)
+    base = torch.randn(M, N, generator=torch.Generator().manual_seed(1))
+    ref1 = oracle.w8a8_gemm(an, san, wn, swn, K, 1, live, out=base.numpy())
+    res = base.to(dev)
+    run(dev, a, w, sa, sw, res, live, K, 1)
+    assert same(res, ref1), first_diff(res.cpu().numpy(), ref1)
+    exact = oracle.w8a8_gemm(an, san, wn, swn, K, 3, live)
+    slots = torch.full((1, M, N), -(1 << 30), dtype=torch.int32, device=dev)
+    assert w8a8.gemm_i32(a.to(dev), sa.to(dev).view(-1), w.to(dev), sw.to(dev).view(-1), slots, n_rows(live, dev)) == 1
+    assert same(slots[0, :live], exact[:live]) and bool((slots[0, live:] == -(1 << 30)).all())
