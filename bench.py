@@ -360,7 +360,7 @@ def run_detail(args):
 
                 def call(c):
                     pend[0] = w8a8.gemm(a, sa, ws[c], sw, out, nr, gk or K, epi=epi, slots=slots,
-                                        cfg=args.detail_split)
+                                        cfg=args.detail_split, pdl=args.detail_pdl)
                 call(0)
                 us = graph_time(call, copies)
                 fold_us = 0.0
@@ -544,6 +544,7 @@ def main():
     ap.add_argument("--detail-shapes", default=None)
     ap.add_argument("--detail-gk", default=None, help="comma list; 0 = one group per row (gk == K), 32 = Q8_0 blocks")
     ap.add_argument("--detail-split", type=int, default=None)
+    ap.add_argument("--detail-pdl", action="store_true", help="few-rows GEMMs as programmatic dependent launches")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -49,10 +49,13 @@ int pb_w8a8_counters(int M, int N);
  *   epi PB_EPI_I32: out = slots int32 [split, rows, N] (ldo = N, slot_stride = rows * N elements): split z's sums.
  *   split > 1 with epi 0 / 1 (gk == K, M <= 64): the splits are added inside the kernel through `workspace`
  *   (pb_w8a8_workspace_bytes) and `counters` (pb_w8a8_counters, zero before the first call; left zero).
+ *   pdl != 0 (few rows only; ignored otherwise): launch as a programmatic dependent of the kernel before it on the
+ *   stream (csrc/w8a8_gemm.cu:273-296): the weights start streaming while that kernel still runs; activations,
+ *   scales and every output are touched only after it has completed.  n_rows must not be written by that kernel.
  * The result bits do not depend on split, on the kernel chosen or on M (batch invariance). */
 int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, void* out, long ldo,
                  const int* n_rows, int M, int N, int K, int gk, int epi, int split, long slot_stride,
-                 void* workspace, long workspace_bytes, int* counters, int n_counters, void* stream);
+                 void* workspace, long workspace_bytes, int* counters, int n_counters, int pdl, void* stream);
 
 /* Deferred residual add.  Replaces quant.fold / _fold_kernel (kernels/quant.py:128-141, :434-457):
  * h[r, c] = add_rn(h[r, c], mul_rn(mul_rn(float(sum_p slots[p, r, c]), a_s[r]), w_s[c])).  N % 4 == 0, 16-byte aligned. */

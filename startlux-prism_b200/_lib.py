@@ -17,7 +17,7 @@ _SIGS = {
     "pb_device_status": ([ctypes.POINTER(_i), ctypes.POINTER(ctypes.c_uint), _i], _i),
     "pb_w8a8_workspace_bytes": ([_i, _i, _i], _l),
     "pb_w8a8_counters": ([_i, _i], _i),
-    "pb_w8a8_gemm": ([_vp, _vp, _vp, _vp, _vp, _l, _vp, _i, _i, _i, _i, _i, _i, _l, _vp, _l, _vp, _i, _vp], _i),
+    "pb_w8a8_gemm": ([_vp, _vp, _vp, _vp, _vp, _l, _vp, _i, _i, _i, _i, _i, _i, _l, _vp, _l, _vp, _i, _i, _vp], _i),
     "pb_fold": ([_vp, _l, _vp, _l, _i, _vp, _vp, _vp, _i, _i, _vp], _i),
     "pb_quant_rows": ([_vp, _i, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp], _i),
     "pb_swiglu_q8": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp], _i),

@@ -134,16 +134,18 @@ int launch_tile(const int8_t* a, const float* a_s, const int8_t* w, const float*
     if ((rc = tensor_map(&ta, a, K, M, K, w8a8::BK, w8a8::BM, 0))) return rc;
     if ((rc = tensor_map(&tw, w, K, N, K, w8a8::BK, BN, 0))) return rc;
     auto kern = w8a8::w8a8_tile_kernel<BN, EPI>;
+    constexpr int smem = EPI == w8a8::EPI_ADD ? C::SMEM_ADD : C::SMEM;
+    static_assert(smem <= 232448, "tile kernel shared memory");
     static bool configured = false;
     if (!configured) {
-        if ((rc = set_smem(kern, C::SMEM))) return rc;
+        if ((rc = set_smem(kern, smem))) return rc;
         configured = true;
     }
     // the coalesced epilogue moves 32-bit words: bf16 outputs need an even row stride and a 4-byte aligned base
     const int word_ok = EPI == w8a8::EPI_BF16 ? (((uintptr_t)out & 3) == 0 && ldo % 2 == 0) : 1;
     const int tiles = ((M + 127) / 128) * ((N + BN - 1) / BN);
     const int grid = tiles < sm_count() ? tiles : sm_count();
-    kern<<<grid, 192, C::SMEM, st>>>(ta, tw, a_s, w_s, out, ldo, n_rows, M, N, K, word_ok);
+    kern<<<grid, w8a8::TileWarps<EPI>::THREADS, smem, st>>>(ta, tw, a_s, w_s, out, ldo, n_rows, M, N, K, word_ok);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }
@@ -205,6 +207,20 @@ int launch_swap(const int8_t* a, const float* a_s, const int8_t* w, const float*
         configured = true;
     }
     dim3 grid((p.N + 127) / 128, split, (p.M + NB - 1) / NB);
+    if (p.pdl) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(192);
+        cfg.dynamicSmemBytes = C::SMEM;
+        cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        PB_CUDA(cudaLaunchKernelEx(&cfg, kern, tw, tx, tsw, tsa, p));
+        return PB_OK;
+    }
     kern<<<grid, 192, C::SMEM, st>>>(tw, tx, tsw, tsa, p);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
@@ -412,7 +428,7 @@ int pb_w8a8_counters(int M, int N) {
 
 int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, void* out, long ldo,
                  const int* n_rows, int M, int N, int K, int gk, int epi, int split, long slot_stride,
-                 void* workspace, long workspace_bytes, int* counters, int n_counters, void* stream) {
+                 void* workspace, long workspace_bytes, int* counters, int n_counters, int pdl, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     if (!a || !w || !out || !n_rows || M <= 0 || N <= 0 || K <= 0 || split < 1) return PB_BAD_ARGUMENT;
     if (epi != PB_EPI_BF16 && epi != PB_EPI_ADD && epi != PB_EPI_I32) return PB_BAD_ARGUMENT;
@@ -425,7 +441,7 @@ int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float
         // Q8_0's own scale per 32 inputs: fp32 partial sums per group, added in group order (no K split, no int32 out)
         if (epi == PB_EPI_I32 || split != 1) return PB_UNSUPPORTED_SHAPE;
         if (K % 128 || !aligned16(a_s) || !aligned16(w_s)) return PB_UNSUPPORTED_SHAPE;
-        w8a8::SwapArgs p{a_s, w_s, out, ldo, 0, nullptr, nullptr, n_rows, M, N, K, KB, epi, w8a8::MODE_DIRECT};
+        w8a8::SwapArgs p{a_s, w_s, out, ldo, 0, nullptr, nullptr, n_rows, M, N, K, KB, epi, w8a8::MODE_DIRECT, pdl != 0};
         return launch_swap_nb<true>(pick_nb(M), a, a_s, w, w_s, p, 1, st);
     }
     if (gk != K) return PB_UNSUPPORTED_SHAPE;
@@ -456,7 +472,7 @@ int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float
     int kbs = (KB + split - 1) / split;
     split = (KB + kbs - 1) / kbs;                       // every slice non-empty
     const int nb = pick_nb(M);
-    w8a8::SwapArgs p{a_s, w_s, out, ldo, slot_stride, (int32_t*)workspace, counters, n_rows, M, N, K, kbs, epi, 0};
+    w8a8::SwapArgs p{a_s, w_s, out, ldo, slot_stride, (int32_t*)workspace, counters, n_rows, M, N, K, kbs, epi, 0, pdl != 0};
     if (epi == PB_EPI_I32) {
         p.mode = w8a8::MODE_SLOTS;
         if (split > 1 && slot_stride < (long)M * N) return PB_BAD_ARGUMENT;
@@ -601,7 +617,7 @@ int pb_w8a8_gemm_static(const int8_t* a, const float* a_s, const int8_t* w, cons
     int32_t* ws = (int32_t*)scratch;
     int* counters = (int*)((unsigned char*)scratch + PB_STATIC_WS_BYTES);
     w8a8::SwapArgs p{a_s, w_s, out, ldo, 0, ws, counters, n_rows, M, N, K, kbs, epi,
-                     split == 1 ? w8a8::MODE_DIRECT : w8a8::MODE_WS};
+                     split == 1 ? w8a8::MODE_DIRECT : w8a8::MODE_WS, 0};
     if (split > 1) {
         // the counters must start at zero; the array keeps whatever an earlier call (or an aborted one) left
         PB_CUDA(cudaMemsetAsync(counters, 0, (size_t)pb_w8a8_counters(M, N) * sizeof(int), st));

@@ -200,6 +200,46 @@ __device__ __forceinline__ void drain_accumulator(void* __restrict__ out, long l
     }
 }
 
+// The residual-add epilogue of columns [c_begin, c_end) of one accumulator, for one warp: out += v with every
+// global access a full 128-byte row segment.  The loads of the next 32-column chunk are in flight while the current
+// one is scaled, transposed through shared memory (32 x 32 words, XOR-swizzled: conflict-free both ways) and stored.
+__device__ __forceinline__ void drain_add(float* __restrict__ out, long ldo, int N, int live, int m0, int n0, int q,
+                                          int lane, uint32_t lane_addr, uint32_t* stg, const float* swb, float sa,
+                                          int c_begin, int c_end) {
+    const int rows_here = live - (m0 + q * 32);
+    float* base = out + (long)(m0 + q * 32) * ldo + n0 + lane;
+    float o_next[32];
+    auto load_chunk = [&](int c0) {
+        if (n0 + c0 + lane < N) {
+#pragma unroll
+            for (int rr = 0; rr < 32; ++rr)
+                if (rr < rows_here) o_next[rr] = __ldcg(base + (long)rr * ldo + c0);
+        }
+    };
+    if (n0 + c_begin < N) load_chunk(c_begin);
+#pragma unroll 1
+    for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+        if (n0 + c0 >= N) break;
+        float o[32];
+#pragma unroll
+        for (int rr = 0; rr < 32; ++rr) o[rr] = o_next[rr];
+        if (c0 + 32 < c_end && n0 + c0 + 32 < N) load_chunk(c0 + 32);
+        uint32_t r[32];
+        tmem_ld32(lane_addr + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) stg[lane * 32 + (j ^ lane)] = __float_as_uint(scale2((int)r[j], sa, swb[c0 + j]));
+        __syncwarp();
+        if (n0 + c0 + lane < N) {
+#pragma unroll
+            for (int rr = 0; rr < 32; ++rr)
+                if (rr < rows_here)
+                    base[(long)rr * ldo + c0] = __fadd_rn(o[rr], __uint_as_float(stg[rr * 32 + (lane ^ rr)]));
+        }
+        __syncwarp();
+    }
+}
+
 template <int BN>
 struct TileCfg {
     static constexpr int STAGES = (BN == 256) ? 4 : 6;
@@ -209,20 +249,32 @@ struct TileCfg {
     static constexpr int ACC_COLS = 2 * BN;                            // two accumulator buffers
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128
                                    : ACC_COLS <= 256 ? 256 : 512;
+    // + control block + scale stash + per-warp staging: (2 stashes, 4 x 33-word-pitch buffers) or, for the residual
+    // add, (1 stash, 8 x 32-word-pitch buffers)
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + (int)sizeof(Aux) + 2 * BN * 4 + 4 * 32 * 33 * 4;
+    static constexpr int SMEM_ADD = STAGES * STAGE_BYTES + 1024 + (int)sizeof(Aux) + BN * 4 + 8 * 32 * 32 * 4;
+};
+
+// Epilogue warps: four (one per tensor-memory lane quarter), eight for the residual add (two per quarter, half the
+// columns each: its global round trips are what the main loop must hide).
+template <int EPI>
+struct TileWarps {
+    static constexpr int EPI_WARPS = EPI == EPI_ADD ? 8 : 4;
+    static constexpr int THREADS = 64 + 32 * EPI_WARPS;
 };
 
 template <int BN, int EPI>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(TileWarps<EPI>::THREADS, 1)
 w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                  const float* __restrict__ a_s, const float* __restrict__ w_s, void* __restrict__ out, long ldo,
                  const int* __restrict__ n_rows, int M, int N, int K, int word_ok) {
     using C = TileCfg<BN>;
+    using W = TileWarps<EPI>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align1024(smem_raw);
     Aux* aux = (Aux*)(smem + C::STAGES * C::STAGE_BYTES);
     float* sw_stash = (float*)(aux + 1);
-    uint32_t* stage_buf = (uint32_t*)(sw_stash + 2 * BN);          // 4 warps x 32 rows x 33 words
+    uint32_t* stage_buf = (uint32_t*)(sw_stash + (EPI == EPI_ADD ? 1 : 2) * BN);   // per-warp transpose staging
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     int live = *n_rows;
@@ -237,7 +289,7 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&aux->tfull[b]), 1);
-            mbar_init(smem_u32(&aux->tempty[b]), 4);
+            mbar_init(smem_u32(&aux->tempty[b]), W::EPI_WARPS);
         }
         aux->abort_flag = 0;
         mbar_fence_init();
@@ -321,15 +373,21 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             }
         }
     } else {
-        // ------------------------------------------------------------------ epilogue (4 warps, one lane quarter each)
+        // ------------------------------------------------------------------ epilogue (one lane quarter per warp)
+        constexpr int ET = 32 * W::EPI_WARPS;                    // epilogue threads
         const int q = warp & 3, et = threadIdx.x - 64;
+        const int half = (warp - 2) >> 2;                        // EPI_ADD: which half of the columns
         int buf = 0;
         uint32_t bphase = 0;
         for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
             const int m0 = (t % num_m) * BM, n0 = (t / num_m) * BN;
-            float* swb = sw_stash + buf * BN;
+            float* swb = sw_stash + (EPI == EPI_ADD ? 0 : buf * BN);
+            if (EPI == EPI_ADD) {
+                // one scale stash: everyone must be done with the previous tile's before it is rewritten
+                asm volatile("bar.sync 1, %0;" ::"n"(ET) : "memory");
+            }
             if (EPI != EPI_I32)
-                for (int i = et; i < BN; i += 128) swb[i] = (n0 + i < N) ? w_s[n0 + i] : 0.0f;
+                for (int i = et; i < BN; i += ET) swb[i] = (n0 + i < N) ? w_s[n0 + i] : 0.0f;
             if (EPI == EPI_ADD) {
                 // the residual rows this CTA adds into one tile from now: pulled into L2 while that tile's main loop
                 // runs (the first tile's are requested as its main loop starts)
@@ -339,22 +397,28 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     if (pass == 1 && t != (int)blockIdx.x) break;
                     if (tt >= num_tiles) break;
                     const int pm0 = (tt % num_m) * BM, pn0 = (tt / num_m) * BN;
-                    for (int line = et; line < BM * (BN / 32); line += 128) {
+                    for (int line = et; line < BM * (BN / 32); line += ET) {
                         const int pr = pm0 + line / (BN / 32), pc = pn0 + (line % (BN / 32)) * 32;
                         if (pr < live && pc < N)
                             asm volatile("prefetch.global.L2 [%0];" ::"l"((const float*)out + (long)pr * ldo + pc));
                     }
                 }
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(ET) : "memory");
             if (!mbar_wait(smem_u32(&aux->tfull[buf]), bphase, abort_flag, 0x400 + buf)) break;
             tc_fence_after();
             const int row = m0 + q * 32 + lane;
             const bool rok = row < live;
             const float sa = (rok && EPI != EPI_I32) ? a_s[row] : 0.0f;
-            uint32_t* stg = stage_buf + q * (32 * 33);
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
-            drain_accumulator<BN, EPI>(out, ldo, N, live, m0, n0, q, lane, lane_addr, stg, swb, sa, word_ok != 0);
+            if (EPI == EPI_ADD) {
+                uint32_t* stg = stage_buf + (warp - 2) * (32 * 32);
+                drain_add((float*)out, ldo, N, live, m0, n0, q, lane, lane_addr, stg, swb, sa, half * (BN / 2),
+                          (half + 1) * (BN / 2));
+            } else {
+                uint32_t* stg = stage_buf + q * (32 * 33);
+                drain_accumulator<BN, EPI>(out, ldo, N, live, m0, n0, q, lane, lane_addr, stg, swb, sa, word_ok != 0);
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&aux->tempty[buf]));
@@ -580,6 +644,7 @@ struct SwapArgs {
     int kb_per_split;       // 128-byte K blocks per blockIdx.y
     int epi;                // EPI_BF16 / EPI_ADD / EPI_I32
     int mode;
+    int pdl;                // launched as a programmatic dependent: weights may stream before the wait
 };
 
 template <int NB>
@@ -643,6 +708,7 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     tc_fence_after();
     const uint32_t tmem_base = aux->tmem_base;
     volatile int* abort_flag = &aux->abort_flag;
+    if (p.pdl) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the next kernel may begin its set-up
 
     if (warp == 0) {
         if (lane == 0) {
@@ -654,7 +720,30 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int i = 0; i < nkb; ++i) {
+            // Programmatic dependent launch: this grid may start while the kernel before it (the producer of the
+            // activations) still runs.  The weights do not depend on it: the first stages' weight tiles are requested
+            // at once, the activation tiles after the wait.
+            const int pre = p.pdl ? (nkb < C::STAGES ? nkb : C::STAGES) : 0;
+            for (int i = 0; i < pre; ++i) {
+                const uint32_t bar = smem_u32(&aux->full[i]);
+                mbar_expect_tx(bar, C::STAGE_BYTES_RAW);
+                uint8_t* st = smem + i * C::STAGE_BYTES;
+                tma_load_2d_hint(smem_u32(st), &tm_w, (kb0 + i) * BK, n0, bar, pol_w);
+                if (GROUPED) tma_load_2d(smem_u32(st + C::W_BYTES + C::X_BYTES), &tm_sw, (kb0 + i) * 4, n0, bar);
+                armed_parity[i] = 0;
+                armed_mask |= 1u << i;
+            }
+            if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
+            for (int i = 0; i < pre; ++i) {
+                const uint32_t bar = smem_u32(&aux->full[i]);
+                uint8_t* st = smem + i * C::STAGE_BYTES;
+                tma_load_2d(smem_u32(st + C::W_BYTES), &tm_x, (kb0 + i) * BK, m0, bar);
+                if (GROUPED)
+                    tma_load_2d(smem_u32(st + C::W_BYTES + C::X_BYTES + C::SW_BYTES), &tm_sa, (kb0 + i) * 4, m0, bar);
+            }
+            if (pre == C::STAGES) phase = 1;
+            else stage = pre;
+            for (int i = pre; i < nkb; ++i) {
                 if (!mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1, abort_flag, 0x500 + stage)) {
                     ok = false;
                     break;
@@ -726,6 +815,7 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     } else {
         const int q = warp & 3;
         const int nl = q * 32 + lane;                          // this thread's weight row inside the tile
+        if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");   // before any global read or write of this warp
         const int n = n0 + nl;
         const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
         if (GROUPED) {

@@ -69,7 +69,7 @@ def effective_split(K, split):
     return -(-kb // per)
 
 
-def _call(a, a_s, w, w_s, out, ldo, n_rows, gk, epi, split, slot_stride=0, ws=None, counters=None):
+def _call(a, a_s, w, w_s, out, ldo, n_rows, gk, epi, split, slot_stride=0, ws=None, counters=None, pdl=False):
     M, K = a.shape
     N = w.shape[0]
     _lib.need_cuda(a, w, out, n_rows)
@@ -82,7 +82,7 @@ def _call(a, a_s, w, w_s, out, ldo, n_rows, gk, epi, split, slot_stride=0, ws=No
     rc = _lib.lib().pb_w8a8_gemm(_lib.ptr(a), _lib.ptr(a_s), _lib.ptr(w), _lib.ptr(w_s), _lib.ptr(out), ldo,
                                  _lib.ptr(n_rows), M, N, K, gk, epi, split, slot_stride, _lib.ptr(ws),
                                  0 if ws is None else ws.numel(), _lib.ptr(counters),
-                                 0 if counters is None else counters.numel(), _lib.stream())
+                                 0 if counters is None else counters.numel(), int(bool(pdl)), _lib.stream())
     _lib.check(rc, f"w8a8 gemm M={M} N={N} K={K} gk={gk} epi={epi} split={split}")
 
 
@@ -95,7 +95,8 @@ def gemm(a, a_s, w, w_s, out, n_rows, gk, epi=0, outs=None, cfg=None, slots=None
     """a int8 [M, K], a_s fp32 [M, K/gk], w int8 [N, K], w_s fp32 [N, K/gk] -> out: bf16 [M, N] (epi 0) or added into
     fp32 [M, N] (epi 1); out may be a column slice of a wider buffer (its row stride is honoured).  Returns a Deferred
     when an epi 1 product split K into `slots` (int32 [S, rows, N]), else None.  cfg: None or the number of K splits.
-    pdl is accepted for signature parity (kernels start in stream order)."""
+    pdl: the few-rows kernel is launched as a programmatic dependent of the kernel before it on the stream: its
+    weights stream while that kernel (the producer of a and a_s) still runs; everything else waits for it."""
     M, K = a.shape
     N = w.shape[0]
     if epi == EPI_SWIGLU:
@@ -108,7 +109,7 @@ def gemm(a, a_s, w, w_s, out, n_rows, gk, epi=0, outs=None, cfg=None, slots=None
     _scales_ok(a_s, M, K // gk, "a_s")
     _scales_ok(w_s, N, K // gk, "w_s")
     if gk != K:
-        _call(a, a_s, w, w_s, out, out.stride(0), n_rows, gk, epi, 1)
+        _call(a, a_s, w, w_s, out, out.stride(0), n_rows, gk, epi, 1, pdl=pdl)
         return None
     split = int(cfg) if cfg is not None else pick_split(M, N, K)
     split = effective_split(K, split) if M <= FEW_ROWS else 1
@@ -116,7 +117,7 @@ def gemm(a, a_s, w, w_s, out, n_rows, gk, epi=0, outs=None, cfg=None, slots=None
         split = effective_split(K, min(split, slots.shape[0]))
         if split > 1:
             _check_slots(slots, M, N)
-            _call(a, a_s, w, w_s, slots, N, n_rows, gk, EPI_I32, split, slots.stride(0))
+            _call(a, a_s, w, w_s, slots, N, n_rows, gk, EPI_I32, split, slots.stride(0), pdl=pdl)
             return Deferred(split, a_s, w_s)
     ws = counters = None
     if split > 1:
@@ -125,7 +126,7 @@ def gemm(a, a_s, w, w_s, out, n_rows, gk, epi=0, outs=None, cfg=None, slots=None
             split -= 1
         if split == 1:
             ws = counters = None
-    _call(a, a_s, w, w_s, out, out.stride(0), n_rows, gk, epi, split, 0, ws, counters)
+    _call(a, a_s, w, w_s, out, out.stride(0), n_rows, gk, epi, split, 0, ws, counters, pdl=pdl)
     return None
 
 
@@ -144,7 +145,7 @@ def gemm_i32(a, a_s, w, w_s, slots, n_rows, max_split=4, pdl=False, split=None):
     _check_slots(slots, M, N)
     S = split if split is not None else pick_split(M, N, K, min(max_split, slots.shape[0]))
     S = effective_split(K, max(1, min(S, max_split, slots.shape[0]))) if M <= FEW_ROWS else 1
-    _call(a, a_s, w, w_s, slots, N, n_rows, K, EPI_I32, S, slots.stride(0))
+    _call(a, a_s, w, w_s, slots, N, n_rows, K, EPI_I32, S, slots.stride(0), pdl=pdl)
     return S
 
 

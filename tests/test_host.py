@@ -39,12 +39,12 @@ def test_operators_refuse_cpu_tensors(lib):
 
 def test_argument_checks_without_gpu(lib):
     """Bad arguments are refused before any CUDA call."""
-    assert lib.pb_w8a8_gemm(None, None, None, None, None, 0, None, 1, 1, 16, 16, 0, 1, 0, None, 0, None, 0, None) == 1
+    assert lib.pb_w8a8_gemm(None, None, None, None, None, 0, None, 1, 1, 16, 16, 0, 1, 0, None, 0, None, 0, 0, None) == 1
     buf = (ctypes.c_char * 4096)()
     p = ctypes.addressof(buf)
     p16 = (p + 15) & ~15
-    assert lib.pb_w8a8_gemm(p16, p16, p16, p16, p16, 8, p16, 4, 8, 24, 24, 0, 1, 0, None, 0, None, 0, None) == 2  # K % 16
-    assert lib.pb_w8a8_gemm(p16 + 1, p16, p16, p16, p16, 8, p16, 4, 8, 32, 32, 0, 1, 0, None, 0, None, 0, None) == 1
+    assert lib.pb_w8a8_gemm(p16, p16, p16, p16, p16, 8, p16, 4, 8, 24, 24, 0, 1, 0, None, 0, None, 0, 0, None) == 2  # K % 16
+    assert lib.pb_w8a8_gemm(p16 + 1, p16, p16, p16, p16, 8, p16, 4, 8, 32, 32, 0, 1, 0, None, 0, None, 0, 0, None) == 1
     assert lib.pb_quant_rows(p16, 0, 32, None, p16, p16, p16, 4, 64, 64, 1, None, None) == 1   # mode 1 without amax
     assert lib.pb_w8a8_workspace_bytes(16, 5120, 4) == 4 * 40 * 16 * 128 * 4
     assert lib.pb_w8a8_counters(64, 7168) == 56

@@ -180,3 +180,47 @@ def test_gemm_cta_pairs(dev, M, N, K, live, monkeypatch):
     slots = torch.full((1, M, N), -(1 << 30), dtype=torch.int32, device=dev)
     assert w8a8.gemm_i32(a.to(dev), sa.to(dev).view(-1), w.to(dev), sw.to(dev).view(-1), slots, n_rows(live, dev)) == 1
     assert same(slots[0, :live], exact[:live]) and bool((slots[0, live:] == -(1 << 30)).all())
+
+
+@pytest.mark.parametrize("gk", [0, 32])
+def test_programmatic_dependent_launch(dev, gk):
+    """pdl=True: the GEMM may start while its producer (the quantizer of its input) still runs; the weights stream
+    early, the activations are read after the producer completed.  Same bits, eagerly and in a replayed graph."""
+    from prism_b200 import synth
+    M, N, K = 16, 5120, 5120
+    gkk = gk or K
+    x = synth.activations(M, K, seed=77)
+    w = torch.randint(-127, 128, (N, K), generator=torch.Generator().manual_seed(5), dtype=torch.int8)
+    sw = torch.rand(N, K // gkk, generator=torch.Generator().manual_seed(6)) * 1e-3
+    rq, rs = oracle.quant_rows(np_bits(x), gkk)
+    ref = oracle.w8a8_gemm(rq, rs, w.numpy(), sw.numpy(), gkk, 0)
+    xd, wd, swd = x.to(dev), w.to(dev), sw.to(dev)
+    nr = n_rows(M, dev)
+    q = torch.empty(M, K, dtype=torch.int8, device=dev)
+    s = torch.empty(M, K // gkk, device=dev)
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+
+    def step():
+        q.zero_()                                         # the producer really has to run before the GEMM reads q
+        if gk:
+            qq, ss = w8a8.quant_rows(xd, gk, nr)
+            q.copy_(qq)
+            s.copy_(ss)
+        else:
+            quant.rows_q8(xd, None, q, s.view(-1), nr, M)
+        w8a8.gemm(q, s if gk else s.view(-1), wd, swd if gk else swd.view(-1), out, nr, gkk, pdl=True)
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    assert same(out, bf16_from_bits(ref))
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            step()
+            step()
+    out.zero_()
+    g.replay()
+    torch.cuda.synchronize()
+    assert same(out, bf16_from_bits(ref))

@@ -25,7 +25,7 @@ def call_plain(L, a, sa, w, sw, out, nr, epi, split, ws, counters):
     M, K = a.shape
     return L.pb_w8a8_gemm(a.data_ptr(), sa.data_ptr(), w.data_ptr(), sw.data_ptr(), out.data_ptr(), out.stride(0),
                           nr.data_ptr(), M, w.shape[0], K, K, epi, split, 0, ws.data_ptr(), ws.numel(),
-                          counters.data_ptr(), counters.numel(), torch.cuda.current_stream().cuda_stream)
+                          counters.data_ptr(), counters.numel(), 0, torch.cuda.current_stream().cuda_stream)
 
 
 @pytest.mark.parametrize("M,N,K,live,split", [(16, 5120, 5120, 16, 4), (64, 1000, 2560, 50, 5), (8, 7168, 5120, 8, 5)])
