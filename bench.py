@@ -205,11 +205,19 @@ def run_gpu(args):
         if gemm_ms is not None:
             achieved = ops / (gemm_ms * 1e-3) / 1e12
             peak = 2.0 * pk["bf16"]
+            # DRAM traffic per launch of the dominant kernel (the gate|up GEMM): ncu measured 1.00 x the algorithmic
+            # read bytes on the M = 2048 capture (profiles/w8a8_tile_kernel_gate_up_M2048.md); scaled to this M by the
+            # units processed: weights once + activations + bf16 output
+            n_gu, k_gu = 34816, 5120
+            traffic = n_gu * k_gu + M * k_gu + 2 * M * n_gu
             line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                                "frac": achieved / peak, "traffic": None,
+                                "frac": achieved / peak, "traffic": traffic,
                                 "kernel": "w8a8_tile_kernel<256>", "gemm_ms_per_step": gemm_ms,
                                 "peak_note": f"2 x {pk['src']} sustained bf16 ({pk['bf16']}): the int8 tcgen05 rate is "
-                                             "twice the bf16 rate; nominal dense int8 is 4500"}
+                                             "twice the bf16 rate; nominal dense int8 4500; measured with "
+                                             "bench.py --probe peak: 4590 with zero operands at 1965 MHz, 3727 "
+                                             "sustained with random operands under the 1 kW cap (no memory traffic)",
+                                "traffic_note": "scaled from the ncu capture at M = 2048 (reads = 1.00 x algorithmic)"}
         if world == 1 and not args.no_cpu:
             rows = CPU_SAMPLE_ROWS
             cpu_layer_pass(rows)
@@ -341,7 +349,7 @@ def run_detail(args):
     only = args.detail_shapes.split(",") if args.detail_shapes else list(SHAPES)
     gks = [int(x) for x in (args.detail_gk or "0").split(",")]            # 0 = one group (gk == K)
     gen = torch.Generator(device=dev).manual_seed(1)
-    for name in only:
+    for name in ([] if args.detail_formats and "w8a8" not in args.detail_formats else only):
         N, K, epi = SHAPES[name]
         copies = max(4, -(-3 * L2 // (N * K)))
         ws = [torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev, generator=gen) for _ in range(copies)]
@@ -379,6 +387,65 @@ def run_detail(args):
                       flush=True)
         del ws
         torch.cuda.empty_cache()
+    # W4A8 (Q4_K_M assignment: q|k Q4_K + v Q6_K, o and gate|up Q4_K, down Q6_K) and MXFP4, same shapes and row counts
+    from prism_b200 import mxfp4, w4a8
+    if args.detail_formats:
+        fmts = args.detail_formats.split(",")
+        kinds = {"qkv": [("q4k", 6144), ("q6k", 1024)], "o": [("q4k", 5120)], "gate_up": [("q4k", 34816)],
+                 "down": [("q6k", 5120)]}
+
+        def rand_w4(kind, n, k):
+            u8 = lambda *sh, hi=256: torch.randint(0, hi, sh, dtype=torch.uint8, device=dev, generator=gen)   # noqa: E731
+            f = lambda *sh: torch.rand(*sh, device=dev, generator=gen) * 1e-3                                # noqa: E731
+            if kind == "q4k":
+                return w4a8.W4("q4k", u8(n, k // 2), u8(k // 256, n, 8, hi=64), u8(k // 256, n, 8, hi=64),
+                               f(k // 256, n), f(k // 256, n), n, k)
+            return w4a8.W4("q6k", torch.randint(-32, 32, (n, k), dtype=torch.int8, device=dev, generator=gen),
+                           torch.randint(-128, 128, (k // 256, n, 16), dtype=torch.int8, device=dev, generator=gen),
+                           None, f(k // 256, n), None, n, k)
+        for name in only:
+            N, K, epi = SHAPES[name]
+            if "w4a8" in fmts:
+                segs, off = [], 0
+                for kind, n in kinds[name]:
+                    segs.append((rand_w4(kind, n, K), off))
+                    off += n
+                wbytes = sum(n * K * (144 if kind == "q4k" else 210) // 256 for kind, n in kinds[name])
+                for M in rows_list:
+                    x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
+                    q = torch.empty(M, K, dtype=torch.int8, device=dev)
+                    sa = torch.empty(K // 256, M, device=dev)
+                    xs = torch.empty(K // 256, M, 16, dtype=torch.int8, device=dev)
+                    nr = torch.tensor([M], dtype=torch.int32, device=dev)
+                    quant.rows_g(x, q, sa, xs, nr, M)
+                    out = torch.zeros(M, N, dtype=torch.bfloat16 if epi == 0 else torch.float32, device=dev)
+                    us = graph_time(lambda c: w4a8.gemm_segs(q, sa, xs, segs, out, nr, epi), 1, iters=4)
+                    ops = 2.0 * M * N * K
+                    nbytes = wbytes + M * K * (1 + 20 / 256) + (2 if epi == 0 else 8) * M * N
+                    print(json.dumps({"format": "w4a8", "shape": name, "kinds": [k for k, _ in kinds[name]], "M": M,
+                                      "us": round(us, 2), "tops": round(ops / us / 1e6, 1),
+                                      "gbs_gguf_density": round(nbytes / us / 1e3, 1),
+                                      "frac_hbm_measured": round(nbytes / us / 1e3 / pk["hbm"], 3)}), flush=True)
+            if "mxfp4" in fmts:
+                wq = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev, generator=gen)
+                wsc = torch.randint(118, 126, (N, K // 32), dtype=torch.uint8, device=dev, generator=gen)
+                wm = mxfp4.prepare(mxfp4.MX4(wq, wsc, N, K))
+                for M in rows_list:
+                    x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
+                    q = torch.empty(M, K // 2, dtype=torch.uint8, device=dev)
+                    sc = torch.empty(M, K // 32, dtype=torch.uint8, device=dev)
+                    mxfp4.quantize_act(x, q, sc)
+                    out = torch.zeros(M, N, dtype=torch.bfloat16 if epi == 0 else torch.float32, device=dev)
+                    mxfp4.gemm(q, sc, wm, out, M, epi=epi)
+                    us = graph_time(lambda c: mxfp4.gemm(q, sc, wm, out, M, epi=epi), 1, iters=4)
+                    ops = 2.0 * M * N * K
+                    nbytes = (N + M) * K * 17 / 32 + (2 if epi == 0 else 8) * M * N
+                    print(json.dumps({"format": "mxfp4", "shape": name, "M": M, "us": round(us, 2),
+                                      "tflops": round(ops / us / 1e6, 1), "gbs": round(nbytes / us / 1e3, 1),
+                                      "frac_hbm_measured": round(nbytes / us / 1e3 / pk["hbm"], 3),
+                                      "frac_fp4_4x_bf16_sustained": round(ops / us / 1e6 / (4 * pk["bf16"]), 3)}),
+                          flush=True)
+            torch.cuda.empty_cache()
     # activation quantizers
     for T, K in ((8192, 5120), (8192, 17408), (64, 5120)):
         x = torch.randn(T, K, device=dev, generator=gen).to(torch.bfloat16)
@@ -544,6 +611,7 @@ def main():
     ap.add_argument("--detail-shapes", default=None)
     ap.add_argument("--detail-gk", default=None, help="comma list; 0 = one group per row (gk == K), 32 = Q8_0 blocks")
     ap.add_argument("--detail-split", type=int, default=None)
+    ap.add_argument("--detail-formats", default=None, help="comma list of extra formats: w4a8,mxfp4")
     ap.add_argument("--detail-pdl", action="store_true", help="few-rows GEMMs as programmatic dependent launches")
     args = ap.parse_args()
     if args.impl == "reference":
