@@ -554,7 +554,7 @@ def run_peak(dev):
     ops = 2.0 * 128 * 256 * 128 * iters * 148
     st = lambda: torch.cuda.current_stream().cuda_stream                  # noqa: E731
     for pattern in (0, 1):
-        L.pb_int8_peak_probe(200, pattern, None, st())
+        L.pb_int8_peak_probe(200, pattern, 256, None, st())
         torch.cuda.synchronize()
         sampler = ClockSampler(0)
         sampler.start()
@@ -563,7 +563,7 @@ def run_peak(dev):
         while time.time() < t_end:
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            _lib.check(L.pb_int8_peak_probe(iters, pattern, None, st()), "peak probe")
+            _lib.check(L.pb_int8_peak_probe(iters, pattern, 256, None, st()), "peak probe")
             e1.record()
             torch.cuda.synchronize()
             rates.append(ops / (e0.elapsed_time(e1) * 1e-3) / 1e12)
@@ -571,6 +571,13 @@ def run_peak(dev):
         print(json.dumps({"probe": "int8_peak", "pattern": "random" if pattern else "zeros", "tops_first": round(rates[0], 1),
                           "tops_last": round(rates[-1], 1), "tops_max": round(max(rates), 1), "launches": len(rates),
                           "clocks": clocks}), flush=True)
+    # issue cost of one MMA against its N: small-N instructions have a floor (what bounds the few-rows kernels)
+    cyc = torch.zeros(148, dtype=torch.int64, device=dev)
+    for n in (16, 32, 64, 128, 256):
+        _lib.check(L.pb_int8_peak_probe(2000, 0, n, cyc.data_ptr(), st()), "peak probe")
+        torch.cuda.synchronize()
+        print(json.dumps({"probe": "mma_issue", "mma": f"128x{n}x32", "cycles_per_mma": round(float(cyc.float().mean()) / 8000, 1)}),
+              flush=True)
     gen = torch.Generator(device=dev).manual_seed(2)
     M, N, K = 8192, 34816, 5120
     a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev, generator=gen)

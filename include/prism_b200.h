@@ -49,6 +49,8 @@ int pb_w8a8_counters(int M, int N);
  *   epi PB_EPI_I32: out = slots int32 [split, rows, N] (ldo = N, slot_stride = rows * N elements): split z's sums.
  *   split > 1 with epi 0 / 1 (gk == K, M <= 64): the splits are added inside the kernel through `workspace`
  *   (pb_w8a8_workspace_bytes) and `counters` (pb_w8a8_counters, zero before the first call; left zero).
+ *   split > 1 with gk == 32 (M <= 64, epi 0 / 1, same workspace): each K slice adds its groups in order, the slices'
+ *   fp32 sums are added in slice order: deterministic, within one bf16 step of the unsplit (reference) order.
  *   pdl != 0 (few rows only; ignored otherwise): launch as a programmatic dependent of the kernel before it on the
  *   stream (csrc/w8a8_gemm.cu:273-296): the weights start streaming while that kernel still runs; activations,
  *   scales and every output are touched only after it has completed.  n_rows must not be written by that kernel.
@@ -106,9 +108,9 @@ int pb_mxfp4_gemm(const void* aq, const void* a_sf, const void* bq, const void* 
                   int N, int K, int epi, void* stream);
 
 /* Measurement aid: the int8 tensor-core rate with shared-memory-resident operands and no loads (one CTA per SM, `iters`
- * batches of four 128 x 256 x 32 MMAs each; pattern 0 = zero operands, 1 = pseudo-random bytes).  ops = 2 * 128 * 256 *
- * 128 * iters per SM.  Counterpart of the reference's bench/csrc/mma_peak.cu.  cycles (device, one per SM) may be NULL. */
-int pb_int8_peak_probe(int iters, int pattern, unsigned long long* cycles, void* stream);
+ * batches of four 128 x mma_n x 32 MMAs each, mma_n a multiple of 16 up to 256; pattern 0 = zero operands, 1 =
+ * pseudo-random bytes).  ops = 2 * 128 * mma_n * 128 * iters per SM.  Counterpart of the reference's bench/csrc/mma_peak.cu.  cycles (device, one per SM) may be NULL. */
+int pb_int8_peak_probe(int iters, int pattern, int mma_n, unsigned long long* cycles, void* stream);
 
 /* pb_w8a8_gemm for callers that cannot allocate device memory.  No counterpart in the reference (its stream-K
  * workspace is always a torch allocation, kernels/cuda_ext.py:139-143).

@@ -30,7 +30,7 @@ _SIGS = {
 }
 # entry points added by later sections of the header; bound when present in the built library
 _OPTIONAL = {
-    "pb_int8_peak_probe": ([_i, _i, _vp, _vp], _i),
+    "pb_int8_peak_probe": ([_i, _i, _i, _vp, _vp], _i),
     "pb_w8a8_static_scratch_bytes": ([], _l),
     "pb_w8a8_gemm_static": ([_vp, _vp, _vp, _vp, _vp, _l, _vp, _i, _i, _i, _i, _i, _vp], _i),
 }

@@ -203,15 +203,18 @@ int launch_swap(const int8_t* a, const float* a_s, const int8_t* w, const float*
     auto kern = w8a8::w8a8_swap_kernel<NB, GROUPED>;
     static bool configured = false;
     if (!configured) {
-        if ((rc = set_smem(kern, C::SMEM))) return rc;
+        if ((rc = set_smem(kern, C::smem_bytes(C::STAGES_DEEP)))) return rc;
         configured = true;
     }
     dim3 grid((p.N + 127) / 128, split, (p.M + NB - 1) / NB);
+    // a grid no larger than the SM count gets one CTA per SM and the deepest pipeline; a larger one two CTAs per SM
+    p.stages = (long)grid.x * grid.y * grid.z <= sm_count() ? C::STAGES_DEEP : C::STAGES;
+    const int smem = C::smem_bytes(p.stages);
     if (p.pdl) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
-        cfg.blockDim = dim3(192);
-        cfg.dynamicSmemBytes = C::SMEM;
+        cfg.blockDim = dim3(C::THREADS);
+        cfg.dynamicSmemBytes = smem;
         cfg.stream = st;
         cudaLaunchAttribute attr[1];
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -221,7 +224,7 @@ int launch_swap(const int8_t* a, const float* a_s, const int8_t* w, const float*
         PB_CUDA(cudaLaunchKernelEx(&cfg, kern, tw, tx, tsw, tsa, p));
         return PB_OK;
     }
-    kern<<<grid, 192, C::SMEM, st>>>(tw, tx, tsw, tsa, p);
+    kern<<<grid, C::THREADS, smem, st>>>(tw, tx, tsw, tsa, p);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }
@@ -230,7 +233,6 @@ template <bool GROUPED>
 int launch_swap_nb(int nb, const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, w8a8::SwapArgs p,
                    int split, cudaStream_t st) {
     switch (nb) {
-        case 8: return launch_swap<8, GROUPED>(a, a_s, w, w_s, p, split, st);
         case 16: return launch_swap<16, GROUPED>(a, a_s, w, w_s, p, split, st);
         case 32: return launch_swap<32, GROUPED>(a, a_s, w, w_s, p, split, st);
         default: return launch_swap<64, GROUPED>(a, a_s, w, w_s, p, split, st);
@@ -321,7 +323,8 @@ int launch_pipe(bool full, quant::PipeArgs p, cudaStream_t st) {
 
 constexpr int kPipeMinRows = 256;      // below this one CTA per row is as good (too few rows to pipeline)
 
-int pick_nb(int M) { return M <= 8 ? 8 : M <= 16 ? 16 : M <= 32 ? 32 : 64; }
+// activation rows per CTA = the MMA's N: tcgen05.mma with M = 128 takes N = 16, 32, ... 256 (N = 8 needs M = 64)
+int pick_nb(int M) { return M <= 16 ? 16 : M <= 32 ? 32 : 64; }
 
 bool div_full() {
     static int v = -1;
@@ -439,10 +442,22 @@ int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float
     const int KB = (K + 127) / 128;
     if (gk == 32) {
         // Q8_0's own scale per 32 inputs: fp32 partial sums per group, added in group order (no K split, no int32 out)
-        if (epi == PB_EPI_I32 || split != 1) return PB_UNSUPPORTED_SHAPE;
+        if (epi == PB_EPI_I32) return PB_UNSUPPORTED_SHAPE;
         if (K % 128 || !aligned16(a_s) || !aligned16(w_s)) return PB_UNSUPPORTED_SHAPE;
-        w8a8::SwapArgs p{a_s, w_s, out, ldo, 0, nullptr, nullptr, n_rows, M, N, K, KB, epi, w8a8::MODE_DIRECT, pdl != 0};
-        return launch_swap_nb<true>(pick_nb(M), a, a_s, w, w_s, p, 1, st);
+        if (split > 1 && M > 64) return PB_UNSUPPORTED_SHAPE;
+        if (split > KB) split = KB;
+        const int kbs = (KB + split - 1) / split;
+        split = (KB + kbs - 1) / kbs;
+        w8a8::SwapArgs p{a_s, w_s, out, ldo, 0, (int32_t*)workspace, counters, n_rows, M, N, K, kbs, epi,
+                         split == 1 ? w8a8::MODE_DIRECT : w8a8::MODE_WS, pdl != 0, 0};
+        if (split > 1) {
+            // fp32 slice sums are added in slice order by the tile's last CTA: deterministic, within fp32 rounding of
+            // the unsplit group order (one bf16 step at most after the store)
+            if (!workspace || !counters) return PB_BAD_ARGUMENT;
+            if (workspace_bytes < pb_w8a8_workspace_bytes(M, N, split) || n_counters < pb_w8a8_counters(M, N))
+                return PB_TOO_LARGE;
+        }
+        return launch_swap_nb<true>(pick_nb(M), a, a_s, w, w_s, p, split, st);
     }
     if (gk != K) return PB_UNSUPPORTED_SHAPE;
     if (M >= 512 && N >= 256 && pair_enabled() && split == 1) {
@@ -472,7 +487,7 @@ int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float
     int kbs = (KB + split - 1) / split;
     split = (KB + kbs - 1) / kbs;                       // every slice non-empty
     const int nb = pick_nb(M);
-    w8a8::SwapArgs p{a_s, w_s, out, ldo, slot_stride, (int32_t*)workspace, counters, n_rows, M, N, K, kbs, epi, 0, pdl != 0};
+    w8a8::SwapArgs p{a_s, w_s, out, ldo, slot_stride, (int32_t*)workspace, counters, n_rows, M, N, K, kbs, epi, 0, pdl != 0, 0};
     if (epi == PB_EPI_I32) {
         p.mode = w8a8::MODE_SLOTS;
         if (split > 1 && slot_stride < (long)M * N) return PB_BAD_ARGUMENT;
@@ -617,7 +632,7 @@ int pb_w8a8_gemm_static(const int8_t* a, const float* a_s, const int8_t* w, cons
     int32_t* ws = (int32_t*)scratch;
     int* counters = (int*)((unsigned char*)scratch + PB_STATIC_WS_BYTES);
     w8a8::SwapArgs p{a_s, w_s, out, ldo, 0, ws, counters, n_rows, M, N, K, kbs, epi,
-                     split == 1 ? w8a8::MODE_DIRECT : w8a8::MODE_WS, 0};
+                     split == 1 ? w8a8::MODE_DIRECT : w8a8::MODE_WS, 0, 0};
     if (split > 1) {
         // the counters must start at zero; the array keeps whatever an earlier call (or an aborted one) left
         PB_CUDA(cudaMemsetAsync(counters, 0, (size_t)pb_w8a8_counters(M, N) * sizeof(int), st));
@@ -673,8 +688,8 @@ int pb_mxfp4_gemm(const void* aq, const void* a_sf, const void* bq, const void* 
     return PB_OK;
 }
 
-int pb_int8_peak_probe(int iters, int pattern, unsigned long long* cycles, void* stream) {
-    if (iters <= 0) return PB_BAD_ARGUMENT;
+int pb_int8_peak_probe(int iters, int pattern, int mma_n, unsigned long long* cycles, void* stream) {
+    if (iters <= 0 || mma_n < 16 || mma_n > 256 || mma_n % 16) return PB_BAD_ARGUMENT;
     const int smem = (128 + 256) * 128 + 1024;
     static bool configured = false;
     if (!configured) {
@@ -682,7 +697,7 @@ int pb_int8_peak_probe(int iters, int pattern, unsigned long long* cycles, void*
         if (rc) return rc;
         configured = true;
     }
-    w8a8::int8_peak_kernel<<<sm_count(), 128, smem, (cudaStream_t)stream>>>(iters, pattern, cycles);
+    w8a8::int8_peak_kernel<<<sm_count(), 128, smem, (cudaStream_t)stream>>>(iters, pattern, mma_n, cycles);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }

@@ -37,17 +37,18 @@ struct Cfg {
     static constexpr int OFF_XS = OFF_WQ + WQ_BYTES;
     static constexpr int OFF_SC = OFF_XS + XS_BYTES;
     static constexpr int OFF_MN = OFF_SC + SC_BYTES;
-    static constexpr int OFF_D = OFF_MN + MN_BYTES;                      // fp32 d[64]
-    static constexpr int OFF_DM = OFF_D + BN * 4;                        // fp32 dmin[64]
-    static constexpr int TX_BYTES = OFF_DM + (KIND == KIND_Q4K ? BN * 4 : 0);
-    static constexpr int STAGE_BYTES = (OFF_DM + BN * 4 + 1023) / 1024 * 1024;
+    static constexpr int TX_BYTES = OFF_MN + MN_BYTES;
+    static constexpr int STAGE_BYTES = (TX_BYTES + 1023) / 1024 * 1024;
     static constexpr int STAGES = 3;
     static constexpr int BX_BYTES = 2 * 128 * 128;                       // expanded planes: two K blocks x 128 rows
     static constexpr int BM_BYTES = KIND == KIND_Q4K ? 128 * 16 : 0;     // mins operand (one 16-byte K chunk per row)
     static constexpr int EXP_BYTES = BX_BYTES + 2048;
     static constexpr int OFF_EXP = STAGES * STAGE_BYTES;
     static constexpr int OFF_ZERO = OFF_EXP + 2 * EXP_BYTES;             // 2 KB of zeros: the second K chunk of the
-    static constexpr int OFF_AUX = OFF_ZERO + 2048;                      //   K = 32 mins operands
+    static constexpr int OFF_SCL = OFF_ZERO + 2048;                      //   K = 32 mins operands
+    static constexpr int SCL_SLOTS = 8;                                  // ring of per-super-block weight scales
+    static constexpr int SCL_BYTES = 512;                                //   (fp32 d[64], then dmin[64])
+    static constexpr int OFF_AUX = OFF_SCL + SCL_SLOTS * SCL_BYTES;
     static constexpr int SET_COLS = KIND == KIND_Q4K ? 256 : 128;        // P0 | P1 (| MLO | MHI), 64 columns each
     static constexpr int TMEM_COLS = 2 * SET_COLS;
     static constexpr int SMEM = OFF_AUX + 1024 + 512;
@@ -57,6 +58,7 @@ struct Aux4 {
     uint64_t full[4], empty[4];
     uint64_t exp_full[2], exp_empty[2];
     uint64_t acc_full[2], acc_empty[2];
+    uint64_t sfull[8], sempty[8];
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -132,7 +134,11 @@ w4a8_kernel(const __grid_constant__ Maps maps, const Args p) {
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
             mbar_init(smem_u32(&aux->full[s]), 1);
-            mbar_init(smem_u32(&aux->empty[s]), 1 + 4 + 8);              // MMA commit, expander warps, epilogue warps
+            mbar_init(smem_u32(&aux->empty[s]), 1 + 4);                  // MMA commit, expander warps
+        }
+        for (int i = 0; i < C::SCL_SLOTS; ++i) {
+            mbar_init(smem_u32(&aux->sfull[i]), 1);
+            mbar_init(smem_u32(&aux->sempty[i]), 8);                     // the 8 epilogue warps
         }
         for (int e = 0; e < 2; ++e) {
             mbar_init(smem_u32(&aux->exp_full[e]), 4);
@@ -177,13 +183,23 @@ w4a8_kernel(const __grid_constant__ Maps maps, const Args p) {
                     tma_load_2d(st + C::OFF_XS + 1024, &maps.xs, m0 * 4 + 256, b, bar);
                     tma_load_2d(st + C::OFF_SC, &maps.sc, n0 * 2, b, bar);
                     tma_load_2d(st + C::OFF_MN, &maps.mn, n0 * 2, b, bar);
-                    tma_load_2d(st + C::OFF_DM, &maps.dm, n0, b, bar);
                 } else {
                     tma_load_2d(st + C::OFF_WQ, &maps.wq, b * 256, n0, bar);
                     tma_load_2d(st + C::OFF_WQ + BN * 128, &maps.wq, b * 256 + 128, n0, bar);
                     tma_load_2d(st + C::OFF_SC, &maps.sc, n0 * 4, b, bar);
                 }
-                tma_load_2d(st + C::OFF_D, &maps.d, n0, b, bar);
+                // the super-block's weight scales go to their own, deeper ring: the epilogue reads them long after
+                // the operand stage has been handed back
+                const int slot = b & (C::SCL_SLOTS - 1);
+                if (!mbar_wait(smem_u32(&aux->sempty[slot]), ((b / C::SCL_SLOTS) & 1) ^ 1, abort_flag, 0xA40 + slot)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t sbar = smem_u32(&aux->sfull[slot]);
+                mbar_expect_tx(sbar, KIND == KIND_Q4K ? 512 : 256);
+                const uint32_t sdst = smem_u32(smem + C::OFF_SCL + slot * C::SCL_BYTES);
+                tma_load_2d(sdst, &maps.d, n0, b, sbar);
+                if (KIND == KIND_Q4K) tma_load_2d(sdst + 256, &maps.dm, n0, b, sbar);
                 if (++stage == C::STAGES) {
                     stage = 0;
                     phase ^= 1;
@@ -297,22 +313,20 @@ w4a8_kernel(const __grid_constant__ Maps maps, const Args p) {
         float y[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) y[j] = 0.0f;
-        int stage = 0;
-        uint32_t phase = 0;
         bool ok = true;
         for (int b = 0; b < NSB; ++b) {
             const int e = b & 1;
             const uint32_t eph = (b >> 1) & 1;
+            const int slot = b & (C::SCL_SLOTS - 1);
+            const float* dv = (const float*)(smem + C::OFF_SCL + slot * C::SCL_BYTES) + ch * 32;
+            const float* dmv = dv + 64;
+            const float am = (m0 + ml < p.Ma) ? __ldg(p.a + (long)b * p.Ma + m0 + ml) : 0.0f;
             if (!mbar_wait(smem_u32(&aux->acc_full[e]), eph, abort_flag, 0xD00 + e) ||
-                !mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, 0xD10 + stage)) {
+                !mbar_wait(smem_u32(&aux->sfull[slot]), (b / C::SCL_SLOTS) & 1, abort_flag, 0xD20 + slot)) {
                 ok = false;
                 break;
             }
             tc_fence_after();
-            const uint8_t* st = smem + stage * C::STAGE_BYTES;
-            const float am = (m0 + ml < p.Ma) ? __ldg(p.a + (long)b * p.Ma + m0 + ml) : 0.0f;
-            const float* dv = (const float*)(st + C::OFF_D) + ch * 32;
-            const float* dmv = (const float*)(st + C::OFF_DM) + ch * 32;
             const uint32_t set = lane_base + e * C::SET_COLS;
 #pragma unroll
             for (int c = 0; c < 32; c += 16) {
@@ -345,11 +359,7 @@ w4a8_kernel(const __grid_constant__ Maps maps, const Args p) {
             __syncwarp();
             if (lane == 0) {
                 mbar_arrive(smem_u32(&aux->acc_empty[e]));
-                mbar_arrive(smem_u32(&aux->empty[stage]));
-            }
-            if (++stage == C::STAGES) {
-                stage = 0;
-                phase ^= 1;
+                mbar_arrive(smem_u32(&aux->sempty[slot]));
             }
         }
         if (ok) {

@@ -30,8 +30,8 @@ constexpr int EPI_I32 = 3;     // out int32 [M, N] = acc (no scales)
 struct Aux {                   // shared-memory control block placed after the stages
     uint64_t full[12];
     uint64_t empty[12];
-    uint64_t tfull[4];
-    uint64_t tempty[4];
+    uint64_t tfull[8];
+    uint64_t tempty[8];
     uint32_t tmem_base;
     int abort_flag;
     int is_last;
@@ -343,15 +343,22 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             int stage = 0, buf = 0;
             uint32_t phase = 0, bphase = 0;
             bool ok = true;
+            // An mbarrier test costs this thread about 200 cycles before its answer can be used, as much as issuing
+            // two MMAs.  So the test of the NEXT stage's barrier is issued before the current stage's MMAs and its
+            // answer read after them: the thread stays ahead of the tensor core (512 cycles per stage).
+            bool ready = mbar_test(smem_u32(&aux->full[0]), 0);
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
                 if (!mbar_wait(smem_u32(&aux->tempty[buf]), bphase ^ 1, abort_flag, 0x200 + buf)) break;
                 tc_fence_after();
                 const uint32_t d = tmem_base + buf * BN;
                 for (int kb = 0; kb < KB; ++kb) {
-                    if (!mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, 0x300 + stage)) {
+                    if (!ready && !mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, 0x300 + stage)) {
                         ok = false;
                         break;
                     }
+                    const int nstage = stage + 1 == C::STAGES ? 0 : stage + 1;
+                    const uint32_t nphase = nstage == 0 ? phase ^ 1 : phase;
+                    const bool ready_next = mbar_test(smem_u32(&aux->full[nstage]), nphase);
                     tc_fence_after();
                     uint8_t* st = smem + stage * C::STAGE_BYTES;
                     const uint64_t ad = umma_desc_k128(smem_u32(st));
@@ -361,10 +368,9 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                         umma_i8(d, umma_desc_advance(ad, k * 32), umma_desc_advance(bd, k * 32), idesc,
                                 (kb | k) ? 1u : 0u);
                     tc_commit(smem_u32(&aux->empty[stage]));
-                    if (++stage == C::STAGES) {
-                        stage = 0;
-                        phase ^= 1;
-                    }
+                    stage = nstage;
+                    phase = nphase;
+                    ready = ready_next;
                 }
                 if (!ok) break;
                 tc_commit(smem_u32(&aux->tfull[buf]));
@@ -617,23 +623,28 @@ template <int NB, bool GROUPED>
 struct SwapCfg {
     static constexpr int W_BYTES = BM * BK;                      // 16 KB
     static constexpr int X_BYTES = NB * BK;
-    static constexpr int SW_BYTES = GROUPED ? BM * 16 : 0;       // 4 fp32 group scales per weight row
+    static constexpr int SW_BYTES = 0;                           // weight group scales: read by their thread, not staged
     static constexpr int SA_BYTES = GROUPED ? NB * 16 : 0;       // 4 fp32 group scales per activation row
     static constexpr int STAGE_BYTES_RAW = W_BYTES + X_BYTES + SW_BYTES + SA_BYTES;
     static constexpr int STAGE_BYTES = (STAGE_BYTES_RAW + 1023) / 1024 * 1024;
-    // about 110 KB per CTA: two CTAs share an SM, so twice the CTAs stream weights at once
+    // about 110 KB per CTA, so that two CTAs share an SM, when the grid has more CTAs than SMs; otherwise one CTA per
+    // SM with all the shared memory (bytes in flight per SM are what hides the DRAM latency)
     static constexpr int STAGES = (108 * 1024 / STAGE_BYTES) > 8 ? 8 : (108 * 1024 / STAGE_BYTES);
+    static constexpr int STAGES_DEEP = (212 * 1024 / STAGE_BYTES) > 12 ? 12 : (212 * 1024 / STAGE_BYTES);
     static constexpr int BATCH_COLS = GROUPED ? 4 * NB : NB;     // accumulator columns written per stage
     static constexpr int RING = GROUPED ? ((256 / BATCH_COLS) > 4 ? 4 : (256 / BATCH_COLS)) : 1;
     static constexpr int ACC_COLS = BATCH_COLS * RING;
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128
                                    : ACC_COLS <= 256 ? 256 : 512;
-    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + (int)sizeof(Aux);
+    static constexpr int smem_bytes(int stages) { return stages * STAGE_BYTES + 1024 + (int)sizeof(Aux); }
+    // per-32 groups keep the epilogue warps busy after every stage: two warps per lane quarter from 16 rows up
+    static constexpr int EPI_WARPS = (GROUPED && NB >= 16) ? 8 : 4;
+    static constexpr int THREADS = 64 + 32 * EPI_WARPS;
 };
 
 struct SwapArgs {
     const float* a_s;       // [M] (gk == K) or [M, K/32] (GROUPED; read through tm_sa)
-    const float* w_s;       // [N] (gk == K) or [N, K/32] (GROUPED; read through tm_sw)
+    const float* w_s;       // [N] (gk == K) or [N, K/32] (GROUPED: each thread reads its row)
     void* out;              // bf16 / fp32 / int32 [M, N]; MODE_SLOTS: slots base
     long ldo;               // row stride of out (elements)
     long slot_stride;       // MODE_SLOTS: elements between slots
@@ -645,6 +656,7 @@ struct SwapArgs {
     int epi;                // EPI_BF16 / EPI_ADD / EPI_I32
     int mode;
     int pdl;                // launched as a programmatic dependent: weights may stream before the wait
+    int stages;             // pipeline depth (shared-memory stages per CTA)
 };
 
 template <int NB>
@@ -666,14 +678,15 @@ __device__ __forceinline__ void swap_store(const SwapArgs& p, int n, int m0, int
 }
 
 template <int NB, bool GROUPED>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(SwapCfg<NB, GROUPED>::THREADS, 1)
 w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                  const __grid_constant__ CUtensorMap tm_sw, const __grid_constant__ CUtensorMap tm_sa,
                  const SwapArgs p) {
     using C = SwapCfg<NB, GROUPED>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align1024(smem_raw);
-    Aux* aux = (Aux*)(smem + C::STAGES * C::STAGE_BYTES);
+    const int NST = p.stages;                                  // pipeline depth chosen by the host (2 .. 12)
+    Aux* aux = (Aux*)(smem + NST * C::STAGE_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     int live = *p.n_rows;
@@ -687,13 +700,13 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     const int nkb = kb1 > kb0 ? kb1 - kb0 : 0;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < C::STAGES; ++s) {
+        for (int s = 0; s < NST; ++s) {
             mbar_init(smem_u32(&aux->full[s]), 1);
-            mbar_init(smem_u32(&aux->empty[s]), GROUPED ? 5 : 1);   // MMA commit (+ 4 epilogue warps read the scales)
+            mbar_init(smem_u32(&aux->empty[s]), GROUPED ? C::EPI_WARPS : 1);   // the MMA's commit, or (per-32 groups) the epilogue warps
         }
         for (int b = 0; b < C::RING; ++b) {
             mbar_init(smem_u32(&aux->tfull[b]), 1);
-            mbar_init(smem_u32(&aux->tempty[b]), 4);
+            mbar_init(smem_u32(&aux->tempty[b]), C::EPI_WARPS);
         }
         aux->abort_flag = 0;
         aux->is_last = 0;
@@ -715,7 +728,7 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             tma_prefetch_desc(&tm_w);
             tma_prefetch_desc(&tm_x);
             const uint64_t pol_w = policy_evict_first();       // weights are read once
-            uint32_t armed_parity[C::STAGES];
+            uint32_t armed_parity[12];
             uint32_t armed_mask = 0;
             int stage = 0;
             uint32_t phase = 0;
@@ -723,13 +736,12 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             // Programmatic dependent launch: this grid may start while the kernel before it (the producer of the
             // activations) still runs.  The weights do not depend on it: the first stages' weight tiles are requested
             // at once, the activation tiles after the wait.
-            const int pre = p.pdl ? (nkb < C::STAGES ? nkb : C::STAGES) : 0;
+            const int pre = p.pdl ? (nkb < NST ? nkb : NST) : 0;
             for (int i = 0; i < pre; ++i) {
                 const uint32_t bar = smem_u32(&aux->full[i]);
                 mbar_expect_tx(bar, C::STAGE_BYTES_RAW);
                 uint8_t* st = smem + i * C::STAGE_BYTES;
                 tma_load_2d_hint(smem_u32(st), &tm_w, (kb0 + i) * BK, n0, bar, pol_w);
-                if (GROUPED) tma_load_2d(smem_u32(st + C::W_BYTES + C::X_BYTES), &tm_sw, (kb0 + i) * 4, n0, bar);
                 armed_parity[i] = 0;
                 armed_mask |= 1u << i;
             }
@@ -739,9 +751,9 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                 uint8_t* st = smem + i * C::STAGE_BYTES;
                 tma_load_2d(smem_u32(st + C::W_BYTES), &tm_x, (kb0 + i) * BK, m0, bar);
                 if (GROUPED)
-                    tma_load_2d(smem_u32(st + C::W_BYTES + C::X_BYTES + C::SW_BYTES), &tm_sa, (kb0 + i) * 4, m0, bar);
+                    tma_load_2d(smem_u32(st + C::W_BYTES + C::X_BYTES), &tm_sa, (kb0 + i) * 4, m0, bar);
             }
-            if (pre == C::STAGES) phase = 1;
+            if (pre == NST) phase = 1;
             else stage = pre;
             for (int i = pre; i < nkb; ++i) {
                 if (!mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1, abort_flag, 0x500 + stage)) {
@@ -754,18 +766,15 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                 const int kb = kb0 + i;
                 tma_load_2d_hint(smem_u32(st), &tm_w, kb * BK, n0, bar, pol_w);
                 tma_load_2d(smem_u32(st + C::W_BYTES), &tm_x, kb * BK, m0, bar);
-                if (GROUPED) {
-                    tma_load_2d(smem_u32(st + C::W_BYTES + C::X_BYTES), &tm_sw, kb * 4, n0, bar);
-                    tma_load_2d(smem_u32(st + C::W_BYTES + C::X_BYTES + C::SW_BYTES), &tm_sa, kb * 4, m0, bar);
-                }
+                if (GROUPED) tma_load_2d(smem_u32(st + C::W_BYTES + C::X_BYTES), &tm_sa, kb * 4, m0, bar);
                 armed_parity[stage] = phase;
                 armed_mask |= 1u << stage;
-                if (++stage == C::STAGES) {
+                if (++stage == NST) {
                     stage = 0;
                     phase ^= 1;
                 }
             }
-            if (!ok) drain_armed(aux, C::STAGES, armed_parity, armed_mask);
+            if (!ok) drain_armed(aux, NST, armed_parity, armed_mask);
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -773,17 +782,26 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             int stage = 0, ring = 0;
             uint32_t phase = 0, rphase = 0;
             bool ok = true;
+            // An mbarrier test keeps this thread waiting about 200 cycles for its answer: the tests of the NEXT stage's
+            // barriers are issued before the current stage's MMAs, their answers read after them.
+            bool ready = nkb > 0 && mbar_test(smem_u32(&aux->full[0]), 0);
+            bool ring_free = true;                                   // a fresh ring slot is free
             for (int i = 0; i < nkb && ok; ++i) {
-                if (GROUPED) {
-                    if (!mbar_wait(smem_u32(&aux->tempty[ring]), rphase ^ 1, abort_flag, 0x600 + ring)) {
-                        ok = false;
-                        break;
-                    }
-                }
-                if (!mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, 0x700 + stage)) {
+                if (GROUPED && !ring_free &&
+                    !mbar_wait(smem_u32(&aux->tempty[ring]), rphase ^ 1, abort_flag, 0x600 + ring)) {
                     ok = false;
                     break;
                 }
+                if (!ready && !mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, 0x700 + stage)) {
+                    ok = false;
+                    break;
+                }
+                const int nstage = stage + 1 == NST ? 0 : stage + 1;
+                const uint32_t nphase = nstage == 0 ? phase ^ 1 : phase;
+                const int nring = ring + 1 == C::RING ? 0 : ring + 1;
+                const uint32_t nrphase = nring == 0 ? rphase ^ 1 : rphase;
+                const bool ready_next = mbar_test(smem_u32(&aux->full[nstage]), nphase);
+                const bool ring_free_next = GROUPED ? mbar_test(smem_u32(&aux->tempty[nring]), nrphase ^ 1) : true;
                 tc_fence_after();
                 uint8_t* st = smem + stage * C::STAGE_BYTES;
                 const uint64_t ad = umma_desc_k128(smem_u32(st));
@@ -797,18 +815,16 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                         umma_i8(tmem_base, umma_desc_advance(ad, k * 32), umma_desc_advance(bd, k * 32), idesc,
                                 (i | k) ? 1u : 0u);
                 }
-                tc_commit(smem_u32(&aux->empty[stage]));
-                if (GROUPED) {
-                    tc_commit(smem_u32(&aux->tfull[ring]));
-                    if (++ring == C::RING) {
-                        ring = 0;
-                        rphase ^= 1;
-                    }
-                }
-                if (++stage == C::STAGES) {
-                    stage = 0;
-                    phase ^= 1;
-                }
+                // per-32 groups: the epilogue warps hand the stage back themselves (they read its scales after these
+                // MMAs have completed), so one commit per stage is enough
+                if (GROUPED) tc_commit(smem_u32(&aux->tfull[ring]));
+                else tc_commit(smem_u32(&aux->empty[stage]));
+                stage = nstage;
+                phase = nphase;
+                ring = nring;
+                rphase = nrphase;
+                ready = ready_next;
+                ring_free = ring_free_next;
             }
             if (!GROUPED && ok) tc_commit(smem_u32(&aux->tfull[0]));
         }
@@ -819,13 +835,22 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         const int n = n0 + nl;
         const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
         if (GROUPED) {
-            float acc[NB];
+            // NH activation rows per warp: all NB with four epilogue warps, half of them with eight (two per lane quarter)
+            constexpr int NH = C::EPI_WARPS == 8 ? NB / 2 : NB;
+            const int j0 = C::EPI_WARPS == 8 ? ((warp - 2) >> 2) * NH : 0;
+            float2 acc[NH / 2];                                     // rows (j0 + 2i, j0 + 2i + 1)
 #pragma unroll
-            for (int j = 0; j < NB; ++j) acc[j] = 0.0f;
+            for (int j = 0; j < NH / 2; ++j) acc[j] = make_float2(0.0f, 0.0f);
             int stage = 0, ring = 0;
             uint32_t phase = 0, rphase = 0;
             bool ok = true;
+            // this thread's weight row: four group scales (16 bytes) per stage, read straight from global memory one
+            // stage ahead (a tensor-map box of 128 rows x 16 bytes costs the TMA unit a request per row)
+            const float4* swp = (const float4*)(p.w_s + (long)(n < p.N ? n : 0) * (p.K >> 5)) + kb0;
+            float4 sw_next = nkb > 0 ? __ldg(swp) : make_float4(0.f, 0.f, 0.f, 0.f);
             for (int i = 0; i < nkb && ok; ++i) {
+                const float4 sw4 = sw_next;
+                if (i + 1 < nkb) sw_next = __ldg(swp + i + 1);
                 if (!mbar_wait(smem_u32(&aux->tfull[ring]), rphase, abort_flag, 0x800 + ring)) {
                     ok = false;
                     break;
@@ -838,23 +863,39 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                     break;
                 }
                 const uint8_t* st = smem + stage * C::STAGE_BYTES + C::W_BYTES + C::X_BYTES;
-                const float4 sw4 = *(const float4*)(st + nl * 16);
-                const float4* sa4 = (const float4*)(st + C::SW_BYTES);
+                const float4* sa4 = (const float4*)st + j0;
+                const float2 w0 = make_float2(sw4.x, sw4.x), w1 = make_float2(sw4.y, sw4.y),
+                             w2 = make_float2(sw4.z, sw4.z), w3 = make_float2(sw4.w, sw4.w);
 #pragma unroll
-                for (int c = 0; c < NB; c += 8) {
+                for (int c = 0; c < NH; c += 8) {
+                    if (m0 + j0 + c >= live) break;                // these eight rows are not live: nothing to add
                     uint32_t r[4][8];
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) tmem_ld8(lane_base + ring * C::BATCH_COLS + g * NB + c, r[g]);
+                    for (int g = 0; g < 4; ++g) tmem_ld8(lane_base + ring * C::BATCH_COLS + g * NB + j0 + c, r[g]);
                     tmem_ld_wait();
+                    // (float(sum_g) * sa[m, g]) * sw[n, g] for two rows per instruction (packed fp32 multiplies, each
+                    // lane rounded to nearest like mul_rn), then scalar add_rn in ascending group order.  The adds stay
+                    // scalar on purpose: the assembler contracts a packed multiply followed by a packed add into one
+                    // fused multiply-add (measured: 15 % of results change), which would break the reference's
+                    // two-rounding contract.
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const float4 s = sa4[c + j];
-                        float a = acc[c + j];
-                        a = __fadd_rn(a, scale2((int)r[0][j], s.x, sw4.x));      // groups in ascending order
-                        a = __fadd_rn(a, scale2((int)r[1][j], s.y, sw4.y));
-                        a = __fadd_rn(a, scale2((int)r[2][j], s.z, sw4.z));
-                        a = __fadd_rn(a, scale2((int)r[3][j], s.w, sw4.w));
-                        acc[c + j] = a;
+                    for (int j = 0; j < 8; j += 2) {
+                        const float4 s0 = sa4[c + j], s1 = sa4[c + j + 1];
+                        float2 a = acc[(c + j) >> 1];
+                        float2 t;
+                        t = __fmul2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[0][j]), __int2float_rn((int)r[0][j + 1])),
+                                                  make_float2(s0.x, s1.x)), w0);
+                        a.x = __fadd_rn(a.x, t.x); a.y = __fadd_rn(a.y, t.y);
+                        t = __fmul2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[1][j]), __int2float_rn((int)r[1][j + 1])),
+                                                  make_float2(s0.y, s1.y)), w1);
+                        a.x = __fadd_rn(a.x, t.x); a.y = __fadd_rn(a.y, t.y);
+                        t = __fmul2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[2][j]), __int2float_rn((int)r[2][j + 1])),
+                                                  make_float2(s0.z, s1.z)), w2);
+                        a.x = __fadd_rn(a.x, t.x); a.y = __fadd_rn(a.y, t.y);
+                        t = __fmul2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[3][j]), __int2float_rn((int)r[3][j + 1])),
+                                                  make_float2(s0.w, s1.w)), w3);
+                        a.x = __fadd_rn(a.x, t.x); a.y = __fadd_rn(a.y, t.y);
+                        acc[(c + j) >> 1] = a;
                     }
                 }
                 tc_fence_before();
@@ -867,12 +908,62 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                     ring = 0;
                     rphase ^= 1;
                 }
-                if (++stage == C::STAGES) {
+                if (++stage == NST) {
                     stage = 0;
                     phase ^= 1;
                 }
             }
-            if (ok) swap_store<NB>(p, n, m0, live, acc);
+            float v[NH];
+#pragma unroll
+            for (int j = 0; j < NH / 2; ++j) {
+                v[2 * j] = acc[j].x;
+                v[2 * j + 1] = acc[j].y;
+            }
+            if (p.mode == MODE_WS) {
+                // K split over blockIdx.y: every slice has added its own groups in order from zero; the last CTA of
+                // the tile adds the slices' fp32 sums in slice order (deterministic, but not the unsplit order: results
+                // agree with it to fp32 rounding, i.e. within one bf16 step after the store)
+                constexpr int ET = 32 * C::EPI_WARPS;
+                uint32_t got = ok ? 1u : 0u;
+                asm volatile(
+                    "{\n\t.reg .pred p, q;\n\t"
+                    "setp.ne.u32 p, %1, 0;\n\t"
+                    "bar.red.and.pred q, 1, %2, p;\n\t"
+                    "selp.u32 %0, 1, 0, q;\n\t}"
+                    : "=r"(got) : "r"(got), "n"(ET) : "memory");
+                if (got) {
+                    const int tile = blockIdx.z * gridDim.x + blockIdx.x;
+                    const long tile_elems = (long)NB * BM;
+                    float* ws = (float*)p.ws;
+                    float* mine = ws + ((long)z * gridDim.x * gridDim.z + tile) * tile_elems;
+#pragma unroll
+                    for (int j = 0; j < NH; ++j) mine[(j0 + j) * BM + nl] = v[j];
+                    __threadfence();
+                    asm volatile("bar.sync 1, %0;" ::"n"(ET) : "memory");
+                    if (threadIdx.x == 64) {
+                        const int old = atomicAdd(p.counters + tile, 1);
+                        aux->is_last = (old == (int)gridDim.y - 1);
+                    }
+                    asm volatile("bar.sync 1, %0;" ::"n"(ET) : "memory");
+                    if (aux->is_last) {
+                        __threadfence();
+#pragma unroll
+                        for (int j = 0; j < NH; ++j) v[j] = 0.0f;
+                        for (int sl = 0; sl < (int)gridDim.y; ++sl) {
+                            const float* src = ws + ((long)sl * gridDim.x * gridDim.z + tile) * tile_elems + nl;
+#pragma unroll
+                            for (int j = 0; j < NH; ++j) {
+                                const float part = __ldcg(src + (j0 + j) * BM);
+                                v[j] = sl == 0 ? part : __fadd_rn(v[j], part);
+                            }
+                        }
+                        swap_store<NH>(p, n, m0 + j0, live, v);
+                        if (threadIdx.x == 64) p.counters[tile] = 0;
+                    }
+                }
+            } else if (ok) {
+                swap_store<NH>(p, n, m0 + j0, live, v);
+            }
         } else {
             // every epilogue thread takes the same branch: the barrier-wide AND of the wait's outcome
             uint32_t got = (nkb > 0 && mbar_wait(smem_u32(&aux->tfull[0]), 0, abort_flag, 0x900)) ? 1u : 0u;
@@ -957,7 +1048,7 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 // (pattern 0: zeros, 1: pseudo-random bytes) and its MMA thread issues `iters` batches of four 128 x 256 x 32 MMAs
 // on it.  What a GEMM kernel can reach at most on this GPU at the clock the power cap allows: the roofline's measured
 // denominator (the method of the reference's bench/csrc/mma_peak.cu, on tcgen05).
-__global__ void __launch_bounds__(128, 1) int8_peak_kernel(int iters, int pattern, unsigned long long* cycles) {
+__global__ void __launch_bounds__(128, 1) int8_peak_kernel(int iters, int pattern, int mma_n, unsigned long long* cycles) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align1024(smem_raw);
     __shared__ uint64_t done;
@@ -985,7 +1076,7 @@ __global__ void __launch_bounds__(128, 1) int8_peak_kernel(int iters, int patter
     tc_fence_after();
     const uint32_t tmem_base = tmem_slot;
     if (threadIdx.x == 0) {
-        const uint32_t idesc = umma_idesc_i8(128, 256);
+        const uint32_t idesc = umma_idesc_i8(128, mma_n);
         const uint64_t ad = umma_desc_k128(smem_u32(smem)), bd = umma_desc_k128(smem_u32(smem + 128 * 128));
         const long long c0 = clock64();
         for (int it = 0; it < iters; ++it) {

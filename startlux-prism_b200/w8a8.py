@@ -109,7 +109,13 @@ def gemm(a, a_s, w, w_s, out, n_rows, gk, epi=0, outs=None, cfg=None, slots=None
     _scales_ok(a_s, M, K // gk, "a_s")
     _scales_ok(w_s, N, K // gk, "w_s")
     if gk != K:
-        _call(a, a_s, w, w_s, out, out.stride(0), n_rows, gk, epi, 1, pdl=pdl)
+        # Q8_0's own scales: one K slice keeps the reference's group order (bit-exact); cfg = K splits (few rows only)
+        # trades that for parallelism: slices added in slice order, within one bf16 step of the unsplit result
+        split = effective_split(K, int(cfg)) if cfg is not None and M <= FEW_ROWS else 1
+        ws = counters = None
+        if split > 1:
+            ws, counters = _workspace(a.device)
+        _call(a, a_s, w, w_s, out, out.stride(0), n_rows, gk, epi, split, 0, ws, counters, pdl=pdl)
         return None
     split = int(cfg) if cfg is not None else pick_split(M, N, K)
     split = effective_split(K, split) if M <= FEW_ROWS else 1

@@ -71,9 +71,10 @@ def test_int32_slots_and_fold(dev, M, N, K, live):
 
 
 @pytest.mark.parametrize("M,N,K,live", [(16, 5120, 5120, 16), (5, 256, 384, 4), (64, 1000, 1024, 61),
-                                        (150, 512, 2560, 140)])
+                                        (150, 512, 2560, 140), (3, 35840, 2048, 3)])
 def test_gemm_q8_0_groups(dev, M, N, K, live):
-    """gk = 32: Q8_0's own block scales, fp32 partial sums added in group order (kernels/w8a8.py:64-76)."""
+    """gk = 32: Q8_0's own block scales, fp32 partial sums added in group order (kernels/w8a8.py:64-76).  The last
+    case has more CTAs than SMs: two CTAs share an SM and its tensor memory."""
     a, w, sa, sw = rand_w8a8(M, N, K, seed=K + M, groups=K // 32)
     ref0 = oracle.w8a8_gemm(a.numpy(), sa.numpy(), w.numpy(), sw.numpy(), 32, 0, live)
     out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
@@ -224,3 +225,29 @@ def test_programmatic_dependent_launch(dev, gk):
     g.replay()
     torch.cuda.synchronize()
     assert same(out, bf16_from_bits(ref))
+
+
+@pytest.mark.parametrize("M,N,K,split", [(16, 5120, 5120, 4), (1, 7168, 5120, 5), (64, 1000, 1024, 3), (8, 7168, 5120, 5)])
+def test_q8_0_groups_split_k(dev, M, N, K, split):
+    """gk = 32 with K splits (opt-in): slice sums are added in slice order - deterministic (two runs agree bit for
+    bit) and within one bf16 step of the reference's unsplit group order; the fp32 residual add agrees to 1e-6."""
+    a, w, sa, sw = rand_w8a8(M, N, K, seed=split, groups=K // 32)
+    ref0 = oracle.w8a8_gemm(a.numpy(), sa.numpy(), w.numpy(), sw.numpy(), 32, 0)
+    outs = []
+    for _ in range(2):
+        out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+        run(dev, a, w, sa, sw, out, M, 32, 0, cfg=split)
+        outs.append(out)
+    assert same(outs[0], outs[1])
+    # the slices' fp32 sums differ from the unsplit order by fp32 rounding of the partial sums (about 1e-5 absolute
+    # here), which the bf16 store turns into at most one step except where the value itself is that small
+    got = bf16_from_bits(np_bits(outs[0])).float().numpy()
+    want = bf16_from_bits(ref0).float().numpy()
+    assert (np.abs(got - want) <= np.abs(want) * 2.0 ** -7 + 5e-5).all()
+    assert (got != want).mean() < 0.01
+    base = torch.randn(M, N, generator=torch.Generator().manual_seed(3))
+    ref1 = oracle.w8a8_gemm(a.numpy(), sa.numpy(), w.numpy(), sw.numpy(), 32, 1, out=base.numpy())
+    res = base.to(dev)
+    w8a8._workspace(dev)[0].fill_(0xFF)          # a slice read before it was written would give NaN
+    run(dev, a, w, sa, sw, res, M, 32, 1, cfg=split)
+    assert np.allclose(res.cpu().numpy(), ref1, rtol=1e-5, atol=5e-5)
