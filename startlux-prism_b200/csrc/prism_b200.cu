@@ -14,6 +14,7 @@
 #include "quant_pipe.cuh"
 #include "w8a8_gemm.cuh"
 #include "w4a8_gemm.cuh"
+#include "w4a8_few.cuh"
 #include "mxfp4_gemm.cuh"
 
 namespace {
@@ -161,6 +162,16 @@ bool pair_enabled() {
     return v == 1;
 }
 
+// PRISM_B200_W4A8_TILE=1 keeps the many-rows W4A8 kernel for every batch (comparison runs).
+bool w4a8_tile_only() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("PRISM_B200_W4A8_TILE");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
+
 template <int EPI>
 int launch_pair(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, void* out, long ldo,
                 const int* n_rows, int M, int N, int K, cudaStream_t st) {
@@ -272,6 +283,44 @@ int launch_w4a8(const int8_t* xq, const float* a, const int8_t* xs, int Ma, cons
     w4a8::Args p{a, out, ldo, n_rows, M, N, K, Ma, epi};
     const int grid = ((M + 127) / 128) * ((N + 63) / 64);
     kern<<<grid, w4a8::THREADS, C::SMEM, st>>>(m, p);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+// Few activation rows (w4a8_few.cuh): weight tiles of 128 (Q4_K) or 64 (Q6_K) rows against 16 activation rows.
+template <int KIND>
+int launch_w4a8_few(const int8_t* xq, const float* a, const int8_t* xs, int Ma, const void* wq, const void* wsc,
+                    const void* wmn, const float* wd, const float* wdm, void* out, long ldo, const int* n_rows, int M,
+                    int N, int K, int epi, cudaStream_t st) {
+    using C = w4a8::FewCfg<KIND>;
+    w4a8::FewMaps m;
+    int rc;
+    const uint64_t NSB = K / 256;
+    if ((rc = tensor_map(&m.x, xq, K, M, K, 128, w4a8::FEW_NB, 0))) return rc;
+    if (KIND == w4a8::KIND_Q4K) {
+        if ((rc = tensor_map(&m.wq, wq, K / 2, N, K / 2, 128, 128, 0))) return rc;
+        if ((rc = tensor_map(&m.xs, xs, (uint64_t)Ma * 4, NSB, (uint64_t)Ma * 16, w4a8::FEW_NB * 4, 1, 3))) return rc;
+        if ((rc = tensor_map(&m.sc, wsc, (uint64_t)N * 2, NSB, (uint64_t)N * 8, 256, 1, 3))) return rc;
+        if ((rc = tensor_map(&m.mn, wmn, (uint64_t)N * 2, NSB, (uint64_t)N * 8, 256, 1, 3))) return rc;
+        if ((rc = tensor_map(&m.dm, wdm, N, NSB, (uint64_t)N * 4, 128, 1, 1))) return rc;
+    } else {
+        if ((rc = tensor_map(&m.wq, wq, K, N, K, 128, 64, 0))) return rc;
+        if ((rc = tensor_map(&m.sc, wsc, (uint64_t)N * 4, NSB, (uint64_t)N * 16, 256, 1, 3))) return rc;
+        m.xs = m.x;
+        m.mn = m.x;
+        m.dm = m.x;
+    }
+    if ((rc = tensor_map(&m.d, wd, N, NSB, (uint64_t)N * 4, C::TILE_N, 1, 1))) return rc;
+    auto kern = w4a8::w4a8_few_kernel<KIND>;
+    static bool configured = false;
+    if (!configured) {
+        if ((rc = set_smem(kern, C::SMEM))) return rc;
+        configured = true;
+    }
+    w4a8::Args p{a, out, ldo, n_rows, M, N, K, Ma, epi};
+    // the row tiles of one weight tile are neighbours in launch order: the weights of all but the first come from L2
+    dim3 grid((M + w4a8::FEW_NB - 1) / w4a8::FEW_NB, (N + C::TILE_N - 1) / C::TILE_N);
+    kern<<<grid, w4a8::FEW_THREADS, C::SMEM, st>>>(m, p);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }
@@ -605,6 +654,11 @@ int pb_w4a8_gemm(const int8_t* xq, const float* a, const int8_t* xs, int Ma, int
     if (K % 256 || N % 4 || ldo < N) return PB_UNSUPPORTED_SHAPE;
     if (!aligned16(xq) || !aligned16(wq) || !aligned16(wsc) || !aligned16(wd) || (kind == 0 && (!aligned16(xs) ||
         !aligned16(wmn) || !aligned16(wdm)))) return PB_BAD_ARGUMENT;
+    if (M <= 32 && !w4a8_tile_only()) {                            // measured: the many-rows kernel is faster from 64 rows
+        if (kind == 0)
+            return launch_w4a8_few<w4a8::KIND_Q4K>(xq, a, xs, Ma, wq, wsc, wmn, wd, wdm, out, ldo, n_rows, M, N, K, epi, st);
+        return launch_w4a8_few<w4a8::KIND_Q6K>(xq, a, xs, Ma, wq, wsc, wmn, wd, wdm, out, ldo, n_rows, M, N, K, epi, st);
+    }
     if (kind == 0)
         return launch_w4a8<w4a8::KIND_Q4K>(xq, a, xs, Ma, wq, wsc, wmn, wd, wdm, out, ldo, n_rows, M, N, K, epi, st);
     return launch_w4a8<w4a8::KIND_Q6K>(xq, a, xs, Ma, wq, wsc, wmn, wd, wdm, out, ldo, n_rows, M, N, K, epi, st);
