@@ -172,6 +172,16 @@ bool w4a8_tile_only() {
     return v == 1;
 }
 
+// PRISM_B200_W4A8_STAGED=1: the few-rows Q4_K kernel that stages the expanded operand in shared memory (comparison runs).
+bool w4a8_few_staged() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("PRISM_B200_W4A8_STAGED");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
+
 template <int EPI>
 int launch_pair(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, void* out, long ldo,
                 const int* n_rows, int M, int N, int K, cudaStream_t st) {
@@ -280,7 +290,7 @@ int launch_w4a8(const int8_t* xq, const float* a, const int8_t* xs, int Ma, cons
         if ((rc = set_smem(kern, C::SMEM))) return rc;
         configured = true;
     }
-    w4a8::Args p{a, out, ldo, n_rows, M, N, K, Ma, epi};
+    w4a8::Args p{a, out, ldo, n_rows, M, N, K, Ma, epi, nullptr, nullptr, nullptr, nullptr};
     const int grid = ((M + 127) / 128) * ((N + 63) / 64);
     kern<<<grid, w4a8::THREADS, C::SMEM, st>>>(m, p);
     PB_CUDA(cudaGetLastError());
@@ -311,15 +321,26 @@ int launch_w4a8_few(const int8_t* xq, const float* a, const int8_t* xs, int Ma, 
         m.dm = m.x;
     }
     if ((rc = tensor_map(&m.d, wd, N, NSB, (uint64_t)N * 4, C::TILE_N, 1, 1))) return rc;
+    w4a8::Args p{a, out, ldo, n_rows, M, N, K, Ma, epi, (const uint8_t*)wsc, (const uint8_t*)wmn, wd, wdm};
+    // the row tiles of one weight tile are neighbours in launch order: the weights of all but the first come from L2
+    dim3 grid((M + w4a8::FEW_NB - 1) / w4a8::FEW_NB, (N + C::TILE_N - 1) / C::TILE_N);
+    if (KIND == w4a8::KIND_Q4K && !w4a8_few_staged()) {
+        // Q4_K: the expanded operand goes through tensor memory
+        static bool configured_tm = false;
+        if (!configured_tm) {
+            if ((rc = set_smem(w4a8::w4a8_few_q4k_tm_kernel, w4a8::TmCfg::SMEM))) return rc;
+            configured_tm = true;
+        }
+        w4a8::w4a8_few_q4k_tm_kernel<<<grid, w4a8::FEW_THREADS, w4a8::TmCfg::SMEM, st>>>(m, p);
+        PB_CUDA(cudaGetLastError());
+        return PB_OK;
+    }
     auto kern = w4a8::w4a8_few_kernel<KIND>;
     static bool configured = false;
     if (!configured) {
         if ((rc = set_smem(kern, C::SMEM))) return rc;
         configured = true;
     }
-    w4a8::Args p{a, out, ldo, n_rows, M, N, K, Ma, epi};
-    // the row tiles of one weight tile are neighbours in launch order: the weights of all but the first come from L2
-    dim3 grid((M + w4a8::FEW_NB - 1) / w4a8::FEW_NB, (N + C::TILE_N - 1) / C::TILE_N);
     kern<<<grid, w4a8::FEW_THREADS, C::SMEM, st>>>(m, p);
     PB_CUDA(cudaGetLastError());
     return PB_OK;

@@ -439,4 +439,283 @@ w4a8_few_kernel(const __grid_constant__ FewMaps maps, const Args p) {
     if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
+// ================================================================================================ Q4_K, operand in tensor memory
+// The same Q4_K arithmetic with the expanded weights handed to the tensor core through TENSOR memory instead of shared
+// memory (tcgen05.mma with its A operand in tensor memory): an expander thread owns a weight row (= lane), splits its
+// nibbles in registers and stores them with tcgen05.st.  Shared memory then only carries the packed bytes (written once
+// by the bulk copy, read once by the expanders) - a third of the traffic of the staged version, which was what bounded
+// it - and the 32 KB operand buffers become eight more stages of packed weights in flight.
+//   tensor memory: 3 accumulator sets x 128 columns | 2 operand buffers x 64 columns (256 inputs x 8 bit per lane)
+//   shared memory: 8 stages x 16 KB packed weights | 8 slots x 5 KB (activations 4 KB, their group sums)
+// One thread issues every bulk copy, and each copy costs it about 150 cycles: the per-row scales (sc, mn, d, dmin)
+// are therefore not copied into shared memory at all - the epilogue thread of a weight row reads its own 24 bytes per
+// super-block straight from global memory, one super-block ahead (a warp's reads are contiguous).
+struct TmCfg {
+    static constexpr int W_BYTES = 128 * 128;
+    static constexpr int W_STAGES = 8;
+    static constexpr int SOFF_XS = 2 * FEW_NB * 128;                     // after the two activation K blocks
+    static constexpr int SCL_TX = SOFF_XS + FEW_NB * 16;
+    static constexpr int SCL_BYTES = 5120;
+    static constexpr int SCL_SLOTS = 8;
+    static constexpr int OFF_SCL = W_STAGES * W_BYTES;
+    static constexpr int OFF_AUX = OFF_SCL + SCL_SLOTS * SCL_BYTES;
+    static constexpr int SMEM = OFF_AUX + 512 + 1024;
+    static constexpr int D_SETS = 3, SET_COLS = 8 * FEW_NB;
+    static constexpr int A_BUFS = 2, A_COLS = 64, A_COL0 = D_SETS * SET_COLS;
+    static constexpr int TMEM_COLS = 512;
+};
+static_assert(TmCfg::SCL_TX <= TmCfg::SCL_BYTES, "scale slot");
+static_assert(TmCfg::A_COL0 + TmCfg::A_BUFS * TmCfg::A_COLS <= 512, "tensor memory");
+
+struct AuxTm {
+    uint64_t wfull[8], wempty[8];
+    uint64_t sfull[8], sempty[8];
+    uint64_t afull[2];
+    uint64_t acc_full[3], acc_empty[3];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__global__ void __launch_bounds__(FEW_THREADS, 1)
+w4a8_few_q4k_tm_kernel(const __grid_constant__ FewMaps maps, const Args p) {
+    using C = TmCfg;
+    constexpr int NB = FEW_NB;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    AuxTm* aux = (AuxTm*)(smem + C::OFF_AUX);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    int live = *p.n_rows;
+    live = live < p.M ? live : p.M;
+    const int m0 = blockIdx.x * NB, n0 = blockIdx.y * 128;
+    if (m0 >= live) return;                                              // whole CTA, before any barrier or allocation
+    const int NSB = p.K / 256;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::W_STAGES; ++s) {
+            mbar_init(smem_u32(&aux->wfull[s]), 1);
+            mbar_init(smem_u32(&aux->wempty[s]), 8);                     // the expander warps
+        }
+        for (int i = 0; i < C::SCL_SLOTS; ++i) {
+            mbar_init(smem_u32(&aux->sfull[i]), 1);
+            mbar_init(smem_u32(&aux->sempty[i]), 8);                     // the epilogue warps (the MMAs that read the
+        }                                                                //   slot's activations have completed by then)
+        for (int e = 0; e < C::A_BUFS; ++e) mbar_init(smem_u32(&aux->afull[e]), 8);
+        for (int a = 0; a < C::D_SETS; ++a) {
+            mbar_init(smem_u32(&aux->acc_full[a]), 1);
+            mbar_init(smem_u32(&aux->acc_empty[a]), 8);
+        }
+        aux->abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&aux->tmem_base), C::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = aux->tmem_base;
+    volatile int* abort_flag = &aux->abort_flag;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            const uint64_t pol_w = gridDim.x == 1 ? policy_evict_first() : policy_evict_last();
+            bool ok = true;
+            for (int b = 0; b < NSB && ok; ++b) {
+                const int ws = b & (C::W_STAGES - 1), slot = b & (C::SCL_SLOTS - 1);
+                const uint32_t ph = (b >> 3) & 1;
+                if (!mbar_wait(smem_u32(&aux->wempty[ws]), ph ^ 1, abort_flag, 0x1300 + ws)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t wbar = smem_u32(&aux->wfull[ws]);
+                mbar_expect_tx(wbar, C::W_BYTES);
+                tma_load_2d_hint(smem_u32(smem + ws * C::W_BYTES), &maps.wq, b * 128, n0, wbar, pol_w);
+                if (!mbar_wait(smem_u32(&aux->sempty[slot]), ph ^ 1, abort_flag, 0x1340 + slot)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t sbar = smem_u32(&aux->sfull[slot]);
+                mbar_expect_tx(sbar, C::SCL_TX);
+                const uint32_t sdst = smem_u32(smem + C::OFF_SCL + slot * C::SCL_BYTES);
+                tma_load_2d(sdst, &maps.x, b * 256, m0, sbar);
+                tma_load_2d(sdst + NB * 128, &maps.x, b * 256 + 128, m0, sbar);
+                tma_load_2d(sdst + C::SOFF_XS, &maps.xs, m0 * 4, b, sbar);
+            }
+            if (!ok) {                                       // let armed copies land before the CTA can exit
+                unsigned long long t0 = global_timer_ns();
+                while (global_timer_ns() - t0 < 2000000ull) {
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_i8(128, NB);
+            int a = 0;
+            uint32_t aph = 0;
+            bool r_acc = true;                                           // fresh accumulator sets are free
+            bool r_a = NSB > 0 && mbar_test(smem_u32(&aux->afull[0]), 0);
+            bool r_s = NSB > 0 && mbar_test(smem_u32(&aux->sfull[0]), 0);
+            for (int b = 0; b < NSB; ++b) {
+                const int e = b & 1, slot = b & (C::SCL_SLOTS - 1);
+                const uint32_t eph = (b >> 1) & 1, sph = (b >> 3) & 1;
+                if (!r_acc && !mbar_wait(smem_u32(&aux->acc_empty[a]), aph ^ 1, abort_flag, 0x1420 + a)) break;
+                if (!r_s && !mbar_wait(smem_u32(&aux->sfull[slot]), sph, abort_flag, 0x1400 + slot)) break;
+                if (!r_a && !mbar_wait(smem_u32(&aux->afull[e]), eph, abort_flag, 0x1410 + e)) break;
+                // the next super-block's barriers are tested before this one's MMAs are issued (the answers take time)
+                const int na = a + 1 == C::D_SETS ? 0 : a + 1;
+                const uint32_t naph = na == 0 ? aph ^ 1 : aph;
+                r_acc = mbar_test(smem_u32(&aux->acc_empty[na]), naph ^ 1);
+                r_s = mbar_test(smem_u32(&aux->sfull[(b + 1) & (C::SCL_SLOTS - 1)]), ((b + 1) >> 3) & 1);
+                r_a = mbar_test(smem_u32(&aux->afull[e ^ 1]), ((b + 1) >> 1) & 1);
+                tc_fence_after();
+                const uint32_t xs = smem_u32(smem + C::OFF_SCL + slot * C::SCL_BYTES);
+                const uint32_t d = tmem_base + a * C::SET_COLS;
+                const uint32_t at = tmem_base + C::A_COL0 + e * C::A_COLS;
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {                            // sub-block g: 8 operand columns -> its own 16 columns
+                    const uint64_t bd = umma_desc_advance(umma_desc_k128(xs + (g >> 2) * NB * 128), (g & 3) * 32);
+                    umma_i8_ts(d + g * NB, at + g * 8, bd, idesc, 0u);
+                }
+                tc_commit(smem_u32(&aux->acc_full[a]));
+                a = na;
+                aph = naph;
+            }
+        }
+    } else if (warp < 10) {
+        // ------------------------------------------------------------------ expanders: packed weights -> tensor memory
+        const int q = warp & 3, kh = (warp - 2) >> 2;                    // lane quarter, K half of the super-block
+        const int n = q * 32 + lane;                                     // weight row in the tile = tensor-memory lane
+        const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16) + C::A_COL0 + kh * 32;
+        for (int b = 0; b < NSB; ++b) {
+            const int ws = b & (C::W_STAGES - 1), e = b & 1;
+            if (!mbar_wait(smem_u32(&aux->wfull[ws]), (b >> 3) & 1, abort_flag, 0x1500 + ws)) break;
+            // operand buffer e was last read by the MMAs of super-block b - 2: their commit completed that set's barrier
+            if (b >= 2 && !mbar_wait(smem_u32(&aux->acc_full[(b - 2) % C::D_SETS]), ((b - 2) / C::D_SETS) & 1, abort_flag,
+                                     0x1510 + e)) break;
+            tc_fence_after();
+            const uint8_t* st = smem + ws * C::W_BYTES;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint4 w = *(const uint4*)(st + swz(n, kh * 4 + j));
+                // inputs 0..15 are the low nibbles, 16..31 the high nibbles: four values per 32-bit column
+                const uint32_t r[8] = {w.x & 0x0F0F0F0Fu, w.y & 0x0F0F0F0Fu, w.z & 0x0F0F0F0Fu, w.w & 0x0F0F0F0Fu,
+                                       (w.x >> 4) & 0x0F0F0F0Fu, (w.y >> 4) & 0x0F0F0F0Fu, (w.z >> 4) & 0x0F0F0F0Fu,
+                                       (w.w >> 4) & 0x0F0F0F0Fu};
+                tmem_st8(lane_base + e * C::A_COLS + j * 8, r);
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&aux->afull[e]));
+                mbar_arrive(smem_u32(&aux->wempty[ws]));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue: one weight row, eight rows of x per thread
+        const int q = warp & 3, hsel = (warp - 10) >> 2;
+        const int c0 = hsel * 8;
+        const int nl = q * 32 + lane;
+        const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
+        const bool rows_live = m0 + c0 < live;                           // warp-uniform
+        float y[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) y[j] = 0.0f;
+        bool ok = true;
+        const int ml = m0 + (lane & 15);                                 // lane l carries the scale of activation row m0 + (l & 15)
+        float am_next = (NSB > 0 && ml < p.Ma) ? __ldg(p.a + ml) : 0.0f;
+        const int n = n0 + nl;
+        // this weight row's scales, one super-block ahead: sc, mn uint8 [K/256, N, 8]; d, dmin fp32 [K/256, N]
+        const long nn = n < p.N ? n : 0;
+        const uint2* scp = (const uint2*)p.sc + nn;
+        const uint2* mnp = (const uint2*)p.mn + nn;
+        const float* dp = p.d + nn;
+        const float* dmp = p.dm + nn;
+        uint2 sc_next = make_uint2(0, 0), mn_next = make_uint2(0, 0);
+        float d_next = 0.0f, dm_next = 0.0f;
+        if (NSB > 0) {
+            sc_next = __ldg(scp);
+            mn_next = __ldg(mnp);
+            d_next = __ldg(dp);
+            dm_next = __ldg(dmp);
+        }
+        int a = 0;
+        uint32_t aph = 0;
+        for (int b = 0; b < NSB; ++b) {
+            const int slot = b & (C::SCL_SLOTS - 1);
+            const float am_l = am_next;
+            const uint2 sc8 = sc_next, mn8 = mn_next;
+            const float dv = d_next, ndm = -dm_next;
+            if (b + 1 < NSB) {
+                if (ml < p.Ma) am_next = __ldg(p.a + (long)(b + 1) * p.Ma + ml);
+                sc_next = __ldg(scp + (long)(b + 1) * p.N);
+                mn_next = __ldg(mnp + (long)(b + 1) * p.N);
+                d_next = __ldg(dp + (long)(b + 1) * p.N);
+                dm_next = __ldg(dmp + (long)(b + 1) * p.N);
+            }
+            if (!mbar_wait(smem_u32(&aux->sfull[slot]), (b >> 3) & 1, abort_flag, 0x1620 + slot) ||
+                !mbar_wait(smem_u32(&aux->acc_full[a]), aph, abort_flag, 0x1600 + a)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            if (rows_live) {
+                const uint8_t* sl = smem + C::OFF_SCL + slot * C::SCL_BYTES;
+                int scg[8];
+#pragma unroll
+                for (int g = 0; g < 8; ++g) scg[g] = (int)(((g < 4 ? sc8.x : sc8.y) >> (8 * (g & 3))) & 0xff);
+                const uint32_t set = lane_base + a * C::SET_COLS;
+                uint32_t r[8][8];
+#pragma unroll
+                for (int g = 0; g < 8; ++g) tmem_ld8(set + g * NB + c0, r[g]);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    int acc = scg[0] * (int)r[0][j];
+#pragma unroll
+                    for (int g = 1; g < 8; ++g) acc += scg[g] * (int)r[g][j];
+                    const uint4 s16 = *(const uint4*)(sl + C::SOFF_XS + (c0 + j) * 16);       // eight S & 63, eight S >> 6
+                    const int mlo = __dp4a((int)mn8.x, (int)s16.x, __dp4a((int)mn8.y, (int)s16.y, 0));
+                    const int mhi = __dp4a((int)mn8.x, (int)s16.z, __dp4a((int)mn8.y, (int)s16.w, 0));
+                    const int mins = mlo + 64 * mhi;
+                    const float am = __shfl_sync(0xffffffffu, am_l, c0 + j);
+                    float t = __fmul_rn(dv, __int2float_rn(acc));
+                    t = __fmaf_rn(ndm, __int2float_rn(mins), t);
+                    y[j] = __fmaf_rn(am, t, y[j]);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(smem_u32(&aux->acc_empty[a]));
+                mbar_arrive(smem_u32(&aux->sempty[slot]));
+            }
+            if (++a == C::D_SETS) {
+                a = 0;
+                aph ^= 1;
+            }
+        }
+        if (ok && n < p.N) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int m = m0 + c0 + j;
+                if (m < live) {
+                    if (p.epi == 0) ((__nv_bfloat16*)p.out)[(long)m * p.ldo + n] = __float2bfloat16_rn(y[j]);
+                    else {
+                        float* o = (float*)p.out + (long)m * p.ldo + n;
+                        *o = __fadd_rn(*o, y[j]);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
 }  // namespace w4a8

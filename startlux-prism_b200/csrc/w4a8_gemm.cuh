@@ -73,6 +73,10 @@ struct Args {
     long ldo;
     const int* n_rows;
     int M, N, K, Ma, epi;
+    const uint8_t* sc;       // few-rows Q4_K kernel: the per-row scales read straight from global memory
+    const uint8_t* mn;
+    const float* d;
+    const float* dm;
 };
 
 // K-major operand without swizzle: 8-row x 16-byte core matrices, `sbo` bytes between 8-row groups, `lbo` bytes
