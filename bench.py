@@ -489,10 +489,10 @@ def run_probe(args):
         nr = torch.tensor([M], dtype=torch.int32, device=dev)
         fn = lambda: w8a8.gemm(a, sa, w, sw, out, nr, gk, epi=epi, slots=slots)                   # noqa: E731
         ops, nbytes = 2.0 * M * N * K, N * K + M * K
-    elif case in ("w4a8_q4k", "w4a8_q6k"):
-        M, N, K = 2048, 8192, 5120
+    elif case in ("w4a8_q4k", "w4a8_q6k", "w4a8_q4k_decode", "w4a8_q6k_decode"):
+        M, N, K = (16, 34816, 5120) if case.endswith("decode") else (2048, 8192, 5120)
         wcpu = synth.weights(N, K, 3)
-        w = w4a8.repack((synth.q4_k if case.endswith("q4k") else synth.q6_k)(wcpu)).to(dev)
+        w = w4a8.repack((synth.q4_k if "q4k" in case else synth.q6_k)(wcpu)).to(dev)
         x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
         q = torch.empty(M, K, dtype=torch.int8, device=dev)
         s = torch.empty(K // 256, M, device=dev)

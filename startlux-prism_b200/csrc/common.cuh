@@ -65,15 +65,29 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+// The same test, but the thread may stay suspended up to `ns` nanoseconds while the phase is incomplete (it is woken
+// when the phase completes): a waiting warp then issues next to nothing instead of spinning against the working ones.
+__device__ __forceinline__ bool mbar_test_sleep(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity), "r"(ns) : "memory");
+    return ok != 0;
+}
 
 // A wait with a wall-clock bound (about 4 s).  On expiry it records PB_DEVICE_TIMEOUT with `where`, raises the CTA's
 // abort flag (a shared-memory word every role polls) and returns false; the caller leaves its loop and the kernel
 // runs to its normal end (tensor memory freed, no trap).  Also returns false at once when another role aborted.
 #define PB_WAIT_NS 4000000000ull
+#ifndef PB_SLEEP_NS
+#define PB_SLEEP_NS 2000u
+#endif
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned where) {
 #pragma unroll 1
     for (int i = 0; i < 4096; ++i)                       // the common case: no clock read, no flag read
-        if (mbar_test(bar, parity)) return true;
+        if (mbar_test_sleep(bar, parity, PB_SLEEP_NS)) return true;
     unsigned long long t0 = global_timer_ns();
     for (unsigned it = 1;; ++it) {
         if (mbar_test(bar, parity)) return true;
@@ -218,6 +232,19 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8])
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
                  : : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
                  : "memory");
+}
+// 32 consecutive columns per lane in one instruction (tensor-memory instructions cost the pipe per instruction, not
+// per byte: few wide ones beat many narrow ones).
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        : : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+            "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+            "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+            "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 

@@ -598,15 +598,21 @@ w4a8_few_q4k_tm_kernel(const __grid_constant__ FewMaps maps, const Args p) {
                                      0x1510 + e)) break;
             tc_fence_after();
             const uint8_t* st = smem + ws * C::W_BYTES;
+            uint32_t r[32];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const uint4 w = *(const uint4*)(st + swz(n, kh * 4 + j));
                 // inputs 0..15 are the low nibbles, 16..31 the high nibbles: four values per 32-bit column
-                const uint32_t r[8] = {w.x & 0x0F0F0F0Fu, w.y & 0x0F0F0F0Fu, w.z & 0x0F0F0F0Fu, w.w & 0x0F0F0F0Fu,
-                                       (w.x >> 4) & 0x0F0F0F0Fu, (w.y >> 4) & 0x0F0F0F0Fu, (w.z >> 4) & 0x0F0F0F0Fu,
-                                       (w.w >> 4) & 0x0F0F0F0Fu};
-                tmem_st8(lane_base + e * C::A_COLS + j * 8, r);
+                r[8 * j + 0] = w.x & 0x0F0F0F0Fu;
+                r[8 * j + 1] = w.y & 0x0F0F0F0Fu;
+                r[8 * j + 2] = w.z & 0x0F0F0F0Fu;
+                r[8 * j + 3] = w.w & 0x0F0F0F0Fu;
+                r[8 * j + 4] = (w.x >> 4) & 0x0F0F0F0Fu;
+                r[8 * j + 5] = (w.y >> 4) & 0x0F0F0F0Fu;
+                r[8 * j + 6] = (w.z >> 4) & 0x0F0F0F0Fu;
+                r[8 * j + 7] = (w.w >> 4) & 0x0F0F0F0Fu;
             }
+            tmem_st32(lane_base + e * C::A_COLS, r);                     // this K half: 128 inputs = 32 columns
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
