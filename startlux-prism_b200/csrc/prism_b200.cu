@@ -128,7 +128,8 @@ int set_smem(Kernel k, int bytes) {
 // ------------------------------------------------------------------------------------------------- W8A8 launches
 template <int BN, int EPI>
 int launch_tile(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, void* out, long ldo,
-                const int* n_rows, int M, int N, int K, cudaStream_t st) {
+                const int* n_rows, int M, int N, int K, cudaStream_t st, int split = 1, void* workspace = nullptr,
+                int* counters = nullptr) {
     using C = w8a8::TileCfg<BN>;
     CUtensorMap ta, tw;
     int rc;
@@ -144,9 +145,12 @@ int launch_tile(const int8_t* a, const float* a_s, const int8_t* w, const float*
     }
     // the coalesced epilogue moves 32-bit words: bf16 outputs need an even row stride and a 4-byte aligned base
     const int word_ok = EPI == w8a8::EPI_BF16 ? (((uintptr_t)out & 3) == 0 && ldo % 2 == 0) : 1;
-    const int tiles = ((M + 127) / 128) * ((N + BN - 1) / BN);
-    const int grid = tiles < sm_count() ? tiles : sm_count();
-    kern<<<grid, w8a8::TileWarps<EPI>::THREADS, smem, st>>>(ta, tw, a_s, w_s, out, ldo, n_rows, M, N, K, word_ok);
+    const int KB = (K + 127) / 128;
+    const int kbs = (KB + split - 1) / split;
+    const int units = ((M + 127) / 128) * ((N + BN - 1) / BN) * split;
+    const int grid = units < sm_count() ? units : sm_count();
+    kern<<<grid, w8a8::TileWarps<EPI>::THREADS, smem, st>>>(ta, tw, a_s, w_s, out, ldo, n_rows, M, N, K, word_ok, split,
+                                                           kbs, (int32_t*)workspace, counters);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }
@@ -488,6 +492,11 @@ int pb_device_status(int* code, unsigned* where, int reset) {
 
 long pb_w8a8_workspace_bytes(int M, int N, int split) {
     if (M <= 0 || N <= 0 || split <= 1) return 0;
+    if (M > 64) {                                       // tile kernel: int32 [tiles][split][128][BN]
+        const int bn = N <= 128 ? 128 : 256;
+        const long tiles = (long)((M + 127) / 128) * ((N + bn - 1) / bn);
+        return tiles * split * 128 * bn * 4;
+    }
     const int nb = pick_nb(M);
     const long tiles = (long)((N + 127) / 128) * ((M + nb - 1) / nb);
     return (long)split * tiles * nb * 128 * 4;
@@ -495,6 +504,7 @@ long pb_w8a8_workspace_bytes(int M, int N, int split) {
 
 int pb_w8a8_counters(int M, int N) {
     if (M <= 0 || N <= 0) return 0;
+    if (M > 64) return ((M + 127) / 128) * ((N + (N <= 128 ? 128 : 256) - 1) / (N <= 128 ? 128 : 256));
     const int nb = pick_nb(M);
     return ((N + 127) / 128) * ((M + nb - 1) / nb);
 }
@@ -536,21 +546,26 @@ int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float
         return launch_pair<w8a8::EPI_ADD>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st);
     }
     if (M > 64) {
-        if (epi == PB_EPI_I32) {
-            // split z of K is a product over a K slice: run the tile kernel once per slice on offset pointers
-            if (split > 1) {
-                if (K % (split * 128)) return PB_UNSUPPORTED_SHAPE;
-                return PB_UNSUPPORTED_SHAPE;  // many rows never split K (tp.SPLIT_ROWS); callers pass split = 1
-            }
-            return N <= 128 ? launch_tile<128, w8a8::EPI_I32>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st)
-                            : launch_tile<256, w8a8::EPI_I32>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st);
+        // many rows: K splits (few tiles only: callers pick them, w8a8.pick_split) add their int32 partial sums in a
+        // workspace, exactly; the last CTA of a tile runs the epilogue
+        if (split > KB) split = KB;
+        if (split > 1) {
+            const int kbs = (KB + split - 1) / split;
+            split = (KB + kbs - 1) / kbs;
         }
-        if (split != 1) return PB_UNSUPPORTED_SHAPE;
+        if (split > 1) {
+            if (!workspace || !counters) return PB_BAD_ARGUMENT;
+            if (workspace_bytes < pb_w8a8_workspace_bytes(M, N, split) || n_counters < pb_w8a8_counters(M, N))
+                return PB_TOO_LARGE;
+        }
+        if (epi == PB_EPI_I32)
+            return N <= 128 ? launch_tile<128, w8a8::EPI_I32>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters)
+                            : launch_tile<256, w8a8::EPI_I32>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters);
         if (epi == PB_EPI_BF16)
-            return N <= 128 ? launch_tile<128, w8a8::EPI_BF16>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st)
-                            : launch_tile<256, w8a8::EPI_BF16>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st);
-        return N <= 128 ? launch_tile<128, w8a8::EPI_ADD>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st)
-                        : launch_tile<256, w8a8::EPI_ADD>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st);
+            return N <= 128 ? launch_tile<128, w8a8::EPI_BF16>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters)
+                            : launch_tile<256, w8a8::EPI_BF16>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters);
+        return N <= 128 ? launch_tile<128, w8a8::EPI_ADD>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters)
+                        : launch_tile<256, w8a8::EPI_ADD>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters);
     }
     // few rows: operands swapped, K split over blockIdx.y
     if (split > KB) split = KB;

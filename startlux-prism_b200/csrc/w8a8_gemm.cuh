@@ -240,6 +240,72 @@ __device__ __forceinline__ void drain_add(float* __restrict__ out, long ldo, int
     }
 }
 
+// Split-K in the tile kernel: the last CTA to finish a tile (a counter per tile) adds the K slices' int32 partial
+// accumulators ws[slice][128][BN] (exact, so the order is free) and runs the epilogue for rows [r_begin, r_begin + 32)
+// and columns [c_begin, c_end) of the tile.  Lane = column: every load and store is a full row segment.
+template <int BN, int EPI>
+__device__ __forceinline__ void reduce_store(void* __restrict__ out, long ldo, int N, int live, int m0, int n0, int q,
+                                             int lane, const int32_t* __restrict__ ws_tile, long slice_stride, int split,
+                                             const float* swb, float sa_lane, int c_begin, int c_end) {
+    // Lane = four consecutive columns: a warp instruction moves 512 contiguous bytes of one workspace row; eight rows
+    // are in flight together (the workspace is read from L2: latency, not bandwidth, is what this loop has to hide).
+    const int rows_here = live - (m0 + q * 32);
+    const bool vec_ok = (ldo % 4 == 0) && (((uintptr_t)out & 15) == 0);
+#pragma unroll 1
+    for (int c0 = c_begin; c0 < c_end; c0 += 128) {
+        const int cl = c0 + lane * 4;                                // column inside the tile
+        const int col = n0 + cl;
+        const float4 sw4 = *(const float4*)(swb + cl);
+#pragma unroll 1
+        for (int r0 = 0; r0 < 32; r0 += 8) {
+            if (r0 >= rows_here) break;
+            int4 tot[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) tot[i] = make_int4(0, 0, 0, 0);
+            const int4* src = (const int4*)(ws_tile + (long)(q * 32 + r0) * BN + cl);
+            for (int sl = 0; sl < split; ++sl) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int4 v = __ldcg(src + (sl * slice_stride + (long)i * BN) / 4);
+                    tot[i].x += v.x; tot[i].y += v.y; tot[i].z += v.z; tot[i].w += v.w;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float sa = __shfl_sync(0xffffffffu, sa_lane, r0 + i);
+                if (r0 + i >= rows_here || col >= N) continue;
+                const long off = (long)(m0 + q * 32 + r0 + i) * ldo + col;
+                const int t4[4] = {tot[i].x, tot[i].y, tot[i].z, tot[i].w};
+                const float w4[4] = {sw4.x, sw4.y, sw4.z, sw4.w};
+                if (vec_ok && col + 4 <= N && (EPI != EPI_BF16 || (off % 4) == 0)) {
+                    if (EPI == EPI_BF16) {
+                        __nv_bfloat162 lo = __floats2bfloat162_rn(scale2(t4[0], sa, w4[0]), scale2(t4[1], sa, w4[1]));
+                        __nv_bfloat162 hi = __floats2bfloat162_rn(scale2(t4[2], sa, w4[2]), scale2(t4[3], sa, w4[3]));
+                        *(uint2*)((__nv_bfloat16*)out + off) = make_uint2(*(uint32_t*)&lo, *(uint32_t*)&hi);
+                    } else if (EPI == EPI_ADD) {
+                        float4 o = *(float4*)((float*)out + off);
+                        o.x = __fadd_rn(o.x, scale2(t4[0], sa, w4[0]));
+                        o.y = __fadd_rn(o.y, scale2(t4[1], sa, w4[1]));
+                        o.z = __fadd_rn(o.z, scale2(t4[2], sa, w4[2]));
+                        o.w = __fadd_rn(o.w, scale2(t4[3], sa, w4[3]));
+                        *(float4*)((float*)out + off) = o;
+                    } else {
+                        *(int4*)((int32_t*)out + off) = tot[i];
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (col + j >= N) break;
+                        if (EPI == EPI_BF16) ((__nv_bfloat16*)out)[off + j] = __float2bfloat16_rn(scale2(t4[j], sa, w4[j]));
+                        else if (EPI == EPI_ADD) ((float*)out)[off + j] = __fadd_rn(((float*)out)[off + j], scale2(t4[j], sa, w4[j]));
+                        else ((int32_t*)out)[off + j] = t4[j];
+                    }
+                }
+            }
+        }
+    }
+}
+
 template <int BN>
 struct TileCfg {
     static constexpr int STAGES = (BN == 256) ? 4 : 6;
@@ -267,7 +333,8 @@ template <int BN, int EPI>
 __global__ void __launch_bounds__(TileWarps<EPI>::THREADS, 1)
 w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                  const float* __restrict__ a_s, const float* __restrict__ w_s, void* __restrict__ out, long ldo,
-                 const int* __restrict__ n_rows, int M, int N, int K, int word_ok) {
+                 const int* __restrict__ n_rows, int M, int N, int K, int word_ok, int split, int kb_per_split,
+                 int32_t* __restrict__ ws, int* __restrict__ counters) {
     using C = TileCfg<BN>;
     using W = TileWarps<EPI>;
     extern __shared__ uint8_t smem_raw[];
@@ -281,6 +348,8 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     live = live < M ? live : M;
     const int num_m = (live + BM - 1) / BM, num_n = (N + BN - 1) / BN;
     const int num_tiles = num_m * num_n, KB = (K + BK - 1) / BK;
+    // work units: (tile, K slice), the slices of a tile next to each other so that they finish together
+    const int num_units = num_tiles * split;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
@@ -314,9 +383,11 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+                const int t = u / split, z = u - t * split;
                 const int m0 = (t % num_m) * BM, n0 = (t / num_m) * BN;
-                for (int kb = 0; kb < KB; ++kb) {
+                const int kb_end = (z + 1) * kb_per_split < KB ? (z + 1) * kb_per_split : KB;
+                for (int kb = z * kb_per_split; kb < kb_end; ++kb) {
                     if (!mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1, abort_flag, 0x100 + stage)) {
                         ok = false;
                         break;
@@ -347,11 +418,14 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             // two MMAs.  So the test of the NEXT stage's barrier is issued before the current stage's MMAs and its
             // answer read after them: the thread stays ahead of the tensor core (512 cycles per stage).
             bool ready = mbar_test(smem_u32(&aux->full[0]), 0);
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+                const int z = u % split;
+                const int kb_begin = z * kb_per_split;
+                const int kb_end = kb_begin + kb_per_split < KB ? kb_begin + kb_per_split : KB;
                 if (!mbar_wait(smem_u32(&aux->tempty[buf]), bphase ^ 1, abort_flag, 0x200 + buf)) break;
                 tc_fence_after();
                 const uint32_t d = tmem_base + buf * BN;
-                for (int kb = 0; kb < KB; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!ready && !mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, 0x300 + stage)) {
                         ok = false;
                         break;
@@ -366,7 +440,7 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
 #pragma unroll
                     for (int k = 0; k < BK / 32; ++k)
                         umma_i8(d, umma_desc_advance(ad, k * 32), umma_desc_advance(bd, k * 32), idesc,
-                                (kb | k) ? 1u : 0u);
+                                ((kb - kb_begin) | k) ? 1u : 0u);
                     tc_commit(smem_u32(&aux->empty[stage]));
                     stage = nstage;
                     phase = nphase;
@@ -385,7 +459,8 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         const int half = (warp - 2) >> 2;                        // EPI_ADD: which half of the columns
         int buf = 0;
         uint32_t bphase = 0;
-        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
+            const int t = u / split, z = u - t * split;
             const int m0 = (t % num_m) * BM, n0 = (t / num_m) * BN;
             float* swb = sw_stash + (EPI == EPI_ADD ? 0 : buf * BN);
             if (EPI == EPI_ADD) {
@@ -397,11 +472,12 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             if (EPI == EPI_ADD) {
                 // the residual rows this CTA adds into one tile from now: pulled into L2 while that tile's main loop
                 // runs (the first tile's are requested as its main loop starts)
-                const int tn = (t == (int)blockIdx.x) ? t : t + (int)gridDim.x;
+                const int tn = (u == (int)blockIdx.x) ? u : u + (int)gridDim.x;
                 for (int pass = 0; pass < 2; ++pass) {
-                    const int tt = pass == 0 ? tn : tn + (int)gridDim.x;
-                    if (pass == 1 && t != (int)blockIdx.x) break;
-                    if (tt >= num_tiles) break;
+                    const int uu = pass == 0 ? tn : tn + (int)gridDim.x;
+                    if (pass == 1 && u != (int)blockIdx.x) break;
+                    if (uu >= num_units) break;
+                    const int tt = uu / split;
                     const int pm0 = (tt % num_m) * BM, pn0 = (tt / num_m) * BN;
                     for (int line = et; line < BM * (BN / 32); line += ET) {
                         const int pr = pm0 + line / (BN / 32), pc = pn0 + (line % (BN / 32)) * 32;
@@ -417,6 +493,36 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             const bool rok = row < live;
             const float sa = (rok && EPI != EPI_I32) ? a_s[row] : 0.0f;
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
+            if (split > 1) {
+                // this slice's int32 accumulator -> workspace (the four warps of the first column half do it all)
+                int32_t* ws_tile = ws + (long)t * split * (BM * BN);
+                if (half == 0) {
+                    uint32_t* stg = stage_buf + q * (32 * 33);
+                    drain_accumulator<BN, EPI_I32>(ws_tile + (long)z * (BM * BN), BN, BN, BM, 0, 0, q, lane, lane_addr,
+                                                   stg, swb, 0.0f, true);
+                }
+                // the accumulator buffer is free again: the next unit's MMAs may start while this tile is reduced
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&aux->tempty[buf]));
+                __threadfence();
+                asm volatile("bar.sync 1, %0;" ::"n"(ET) : "memory");
+                if (et == 0) {
+                    const int old = atomicAdd(counters + t, 1);
+                    aux->is_last = (old == split - 1);
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(ET) : "memory");
+                if (aux->is_last) {
+                    __threadfence();
+                    const int cb = EPI == EPI_ADD ? half * (BN / 2) : 0, ce = EPI == EPI_ADD ? (half + 1) * (BN / 2) : BN;
+                    reduce_store<BN, EPI>(out, ldo, N, live, m0, n0, q, lane, ws_tile, (long)BM * BN, split, swb, sa, cb,
+                                          ce);
+                    if (et == 0) counters[t] = 0;
+                }
+                buf ^= 1;
+                if (buf == 0) bphase ^= 1;
+                continue;
+            }
             if (EPI == EPI_ADD) {
                 uint32_t* stg = stage_buf + (warp - 2) * (32 * 32);
                 drain_add((float*)out, ldo, N, live, m0, n0, q, lane, lane_addr, stg, swb, sa, half * (BN / 2),

@@ -24,6 +24,7 @@ EPI_BF16, EPI_ADD, EPI_SWIGLU, EPI_I32 = 0, 1, 2, 3
 FEW_ROWS = 64                    # up to this many rows the operand-swapped kernel runs
 MAX_SPLIT = 8
 RESIDENT_CTAS = 296              # two CTAs of the few-rows kernel per SM on 148 SMs
+SM_COUNT = 148
 WS_BYTES = 96 << 20              # split-K workspace per device (allocated at the first call that needs it)
 
 _WORKSPACE = {}
@@ -52,11 +53,15 @@ def _workspace(device):
 
 
 def pick_split(M, N, K, limit=MAX_SPLIT):
-    """K splits of the few-rows kernel: as many CTAs as stay resident together, at least two 128-byte K blocks each."""
-    if M > FEW_ROWS:
-        return 1
-    tiles = -(-N // 128)
+    """K splits.  Few rows (operand-swapped kernel): as many CTAs as stay resident together, at least two 128-byte K
+    blocks each.  Many rows (tile kernel, one CTA per SM): only when the 128 x 256 tiles leave most SMs idle and K is
+    long (at least 32 K blocks per slice; measured: a gain for K = 17408 at 128-256 rows, a loss for K = 5120) - the
+    slices' int32 sums meet in the workspace, exactly."""
     kb = -(-K // 128)
+    if M > FEW_ROWS:
+        tiles = -(-M // 128) * -(-N // (128 if N <= 128 else 256))
+        return max(1, min(limit, SM_COUNT // tiles, kb // 32))
+    tiles = -(-N // 128)
     return max(1, min(limit, RESIDENT_CTAS // tiles, kb // 2))
 
 
@@ -118,8 +123,8 @@ def gemm(a, a_s, w, w_s, out, n_rows, gk, epi=0, outs=None, cfg=None, slots=None
         _call(a, a_s, w, w_s, out, out.stride(0), n_rows, gk, epi, split, 0, ws, counters, pdl=pdl)
         return None
     split = int(cfg) if cfg is not None else pick_split(M, N, K)
-    split = effective_split(K, split) if M <= FEW_ROWS else 1
-    if split > 1 and epi == EPI_ADD and slots is not None and slots.shape[1] >= M:
+    split = effective_split(K, split)
+    if split > 1 and M <= FEW_ROWS and epi == EPI_ADD and slots is not None and slots.shape[1] >= M:
         split = effective_split(K, min(split, slots.shape[0]))
         if split > 1:
             _check_slots(slots, M, N)
@@ -150,7 +155,17 @@ def gemm_i32(a, a_s, w, w_s, slots, n_rows, max_split=4, pdl=False, split=None):
     N = w.shape[0]
     _check_slots(slots, M, N)
     S = split if split is not None else pick_split(M, N, K, min(max_split, slots.shape[0]))
-    S = effective_split(K, max(1, min(S, max_split, slots.shape[0]))) if M <= FEW_ROWS else 1
+    if M > FEW_ROWS:
+        # many rows: one slot; K splits (when the tiles are few) meet in the workspace, exactly
+        inner = effective_split(K, pick_split(M, N, K) if split is None else split)
+        ws = counters = None
+        if inner > 1:
+            ws, counters = _workspace(a.device)
+            if _lib.lib().pb_w8a8_workspace_bytes(M, N, inner) > ws.numel():
+                inner, ws, counters = 1, None, None
+        _call(a, a_s, w, w_s, slots, N, n_rows, K, EPI_I32, inner, slots.stride(0), ws, counters, pdl=pdl)
+        return 1
+    S = effective_split(K, max(1, min(S, max_split, slots.shape[0])))
     _call(a, a_s, w, w_s, slots, N, n_rows, K, EPI_I32, S, slots.stride(0), pdl=pdl)
     return S
 

@@ -28,7 +28,7 @@ def test_gemm_one_group(dev, M, N, K, live):
     ref0 = oracle.w8a8_gemm(an, san, wn, swn, K, 0, live)
     base = torch.randn(M, N, generator=torch.Generator().manual_seed(1))
     ref1 = oracle.w8a8_gemm(an, san, wn, swn, K, 1, live, out=base.numpy())
-    splits = [None, 1] + ([2, 3, 8] if M <= 64 else [])
+    splits = [None, 1] + ([2, 3, 8] if M <= 64 else [2, 3])
     for split in splits:
         out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
         run(dev, a, w, sa, sw, out, live, K, 0, cfg=split)
@@ -50,10 +50,11 @@ def test_int32_slots_and_fold(dev, M, N, K, live):
     ref1 = oracle.w8a8_gemm(an, sa.numpy(), wn, sw.numpy(), K, 1, live, out=base.numpy())
     nr = n_rows(live, dev)
     ad, wd, sad, swd = a.to(dev), w.to(dev), sa.to(dev).view(-1), sw.to(dev).view(-1)
-    for split in ([1, 2, 4] if M <= 64 else [1]):
+    for split in ([1, 2, 4] if M <= 64 else [1, 3]):
         slots = torch.full((4, M, N), -(1 << 30), dtype=torch.int32, device=dev)
         S = w8a8.gemm_i32(ad, sad, wd, swd, slots, nr, max_split=4, split=split)
-        assert S == w8a8.effective_split(K, split)
+        # many rows: K slices meet inside the kernel (workspace), one slot comes back
+        assert S == (w8a8.effective_split(K, split) if M <= 64 else 1)
         tot = slots[:S, :live].sum(0, dtype=torch.int32)
         assert same(tot, exact[:live]), (split, first_diff(tot.cpu().numpy(), exact[:live]))
         assert bool((slots[:S, live:] == -(1 << 30)).all()) and bool((slots[S:] == -(1 << 30)).all())
