@@ -490,10 +490,17 @@ int pb_device_status(int* code, unsigned* where, int reset) {
     return PB_OK;
 }
 
+// Weight rows per tile of the many-rows kernel.
+int tile_bn(int M, int N) {
+    if (N <= 128) return 128;
+    const long tiles256 = (long)((M + 127) / 128) * ((N + 255) / 256);
+    return tiles256 * 2 <= sm_count() ? 128 : 256;
+}
+
 long pb_w8a8_workspace_bytes(int M, int N, int split) {
     if (M <= 0 || N <= 0 || split <= 1) return 0;
     if (M > 64) {                                       // tile kernel: int32 [tiles][split][128][BN]
-        const int bn = N <= 128 ? 128 : 256;
+        const int bn = tile_bn(M, N);
         const long tiles = (long)((M + 127) / 128) * ((N + bn - 1) / bn);
         return tiles * split * 128 * bn * 4;
     }
@@ -504,7 +511,7 @@ long pb_w8a8_workspace_bytes(int M, int N, int split) {
 
 int pb_w8a8_counters(int M, int N) {
     if (M <= 0 || N <= 0) return 0;
-    if (M > 64) return ((M + 127) / 128) * ((N + (N <= 128 ? 128 : 256) - 1) / (N <= 128 ? 128 : 256));
+    if (M > 64) return ((M + 127) / 128) * ((N + tile_bn(M, N) - 1) / tile_bn(M, N));
     const int nb = pick_nb(M);
     return ((N + 127) / 128) * ((M + nb - 1) / nb);
 }
@@ -558,14 +565,16 @@ int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float
             if (workspace_bytes < pb_w8a8_workspace_bytes(M, N, split) || n_counters < pb_w8a8_counters(M, N))
                 return PB_TOO_LARGE;
         }
+        // 128 x 256 tiles, or 128 x 128 when those would leave more than half of the SMs without a tile
+        const bool narrow = N <= 128 || tile_bn(M, N) == 128;
         if (epi == PB_EPI_I32)
-            return N <= 128 ? launch_tile<128, w8a8::EPI_I32>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters)
-                            : launch_tile<256, w8a8::EPI_I32>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters);
+            return narrow ? launch_tile<128, w8a8::EPI_I32>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters)
+                          : launch_tile<256, w8a8::EPI_I32>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters);
         if (epi == PB_EPI_BF16)
-            return N <= 128 ? launch_tile<128, w8a8::EPI_BF16>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters)
-                            : launch_tile<256, w8a8::EPI_BF16>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters);
-        return N <= 128 ? launch_tile<128, w8a8::EPI_ADD>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters)
-                        : launch_tile<256, w8a8::EPI_ADD>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters);
+            return narrow ? launch_tile<128, w8a8::EPI_BF16>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters)
+                          : launch_tile<256, w8a8::EPI_BF16>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters);
+        return narrow ? launch_tile<128, w8a8::EPI_ADD>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters)
+                      : launch_tile<256, w8a8::EPI_ADD>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters);
     }
     // few rows: operands swapped, K split over blockIdx.y
     if (split > KB) split = KB;

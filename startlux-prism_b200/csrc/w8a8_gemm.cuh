@@ -254,8 +254,9 @@ __device__ __forceinline__ void reduce_store(void* __restrict__ out, long ldo, i
 #pragma unroll 1
     for (int c0 = c_begin; c0 < c_end; c0 += 128) {
         const int cl = c0 + lane * 4;                                // column inside the tile
-        const int col = n0 + cl;
-        const float4 sw4 = *(const float4*)(swb + cl);
+        const bool mine = cl < c_end;                                // a 64-column range uses half of the lanes
+        const int col = mine ? n0 + cl : N;
+        const float4 sw4 = mine ? *(const float4*)(swb + cl) : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
         for (int r0 = 0; r0 < 32; r0 += 8) {
             if (r0 >= rows_here) break;
@@ -263,7 +264,7 @@ __device__ __forceinline__ void reduce_store(void* __restrict__ out, long ldo, i
 #pragma unroll
             for (int i = 0; i < 8; ++i) tot[i] = make_int4(0, 0, 0, 0);
             const int4* src = (const int4*)(ws_tile + (long)(q * 32 + r0) * BN + cl);
-            for (int sl = 0; sl < split; ++sl) {
+            for (int sl = 0; sl < split && mine; ++sl) {
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const int4 v = __ldcg(src + (sl * slice_stride + (long)i * BN) / 4);

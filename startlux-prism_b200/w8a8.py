@@ -59,7 +59,9 @@ def pick_split(M, N, K, limit=MAX_SPLIT):
     slices' int32 sums meet in the workspace, exactly."""
     kb = -(-K // 128)
     if M > FEW_ROWS:
-        tiles = -(-M // 128) * -(-N // (128 if N <= 128 else 256))
+        tiles = -(-M // 128) * -(-N // 256)
+        if N <= 128 or tiles * 2 <= SM_COUNT:                    # the library's rule: narrower tiles when they are few
+            tiles = -(-M // 128) * -(-N // 128)
         return max(1, min(limit, SM_COUNT // tiles, kb // 32))
     tiles = -(-N // 128)
     return max(1, min(limit, RESIDENT_CTAS // tiles, kb // 2))
