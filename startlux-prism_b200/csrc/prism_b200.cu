@@ -92,11 +92,12 @@ int tensor_map(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer
     cuuint64_t strides[1] = {stride_bytes};
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
+    // kinds: 0 bytes with the 128-byte swizzle, 1 fp32, 3 32-bit words, 4 fp32 with the 128-byte swizzle
     const CUtensorMapDataType dt = kind == 0 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
-                                   : kind == 1 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
+                                   : (kind == 1 || kind == 4) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_UINT32;
     CUresult r = fn(out, dt, 2,
                     const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    kind == 0 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    (kind == 0 || kind == 4) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         g_last_cuda_error = (int)r;
@@ -126,6 +127,18 @@ int set_smem(Kernel k, int bytes) {
 }
 
 // ------------------------------------------------------------------------------------------------- W8A8 launches
+// How the many-rows kernel adds into the fp32 residual.  PRISM_B200_ADD = regs: read, add, write through registers;
+// tma (default, measured fastest): 32 x 32 boxes reduced by the copy engine; red: per-row-segment reductions at the
+// memory side.
+int add_mode() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("PRISM_B200_ADD");
+        v = !e ? 1 : (e[0] == 'r' && e[2] == 'g') ? 0 : (e[0] == 't') ? 1 : 2;
+    }
+    return v;
+}
+
 template <int BN, int EPI>
 int launch_tile(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, void* out, long ldo,
                 const int* n_rows, int M, int N, int K, cudaStream_t st, int split = 1, void* workspace = nullptr,
@@ -144,13 +157,23 @@ int launch_tile(const int8_t* a, const float* a_s, const int8_t* w, const float*
         configured = true;
     }
     // the coalesced epilogue moves 32-bit words: bf16 outputs need an even row stride and a 4-byte aligned base
-    const int word_ok = EPI == w8a8::EPI_BF16 ? (((uintptr_t)out & 3) == 0 && ldo % 2 == 0) : 1;
+    int word_ok = EPI == w8a8::EPI_BF16 ? (((uintptr_t)out & 3) == 0 && ldo % 2 == 0) : 1;
+    // residual add: 32 x 32 fp32 boxes added into out by the copy engine (bit 1 of word_ok), when out can be a tensor map
+    CUtensorMap tout = ta;
+    if (EPI == w8a8::EPI_ADD && split == 1 && add_mode() == 1 && ((uintptr_t)out & 15) == 0 && ldo % 4 == 0) {
+        if ((rc = tensor_map(&tout, out, N, M, (uint64_t)ldo * 4, 32, 32, 4))) return rc;
+        word_ok |= 2;
+    } else if (EPI == w8a8::EPI_ADD && split == 1 && add_mode() == 2) {
+        word_ok |= 4;
+    }
+    // weight tiles fastest when the activations are the larger operand, do not fit in L2 and the weights do
+    if ((long)M * K > (long)N * K && (long)M * K > (64l << 20) && (long)N * K <= (100l << 20)) word_ok |= 8;
     const int KB = (K + 127) / 128;
     const int kbs = (KB + split - 1) / split;
     const int units = ((M + 127) / 128) * ((N + BN - 1) / BN) * split;
     const int grid = units < sm_count() ? units : sm_count();
-    kern<<<grid, w8a8::TileWarps<EPI>::THREADS, smem, st>>>(ta, tw, a_s, w_s, out, ldo, n_rows, M, N, K, word_ok, split,
-                                                           kbs, (int32_t*)workspace, counters);
+    kern<<<grid, w8a8::TileWarps<EPI>::THREADS, smem, st>>>(ta, tw, tout, a_s, w_s, out, ldo, n_rows, M, N, K, word_ok,
+                                                           split, kbs, (int32_t*)workspace, counters);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }

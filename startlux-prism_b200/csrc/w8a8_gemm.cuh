@@ -240,6 +240,83 @@ __device__ __forceinline__ void drain_add(float* __restrict__ out, long ldo, int
     }
 }
 
+// The residual add without a round trip through the SM: every warp scales 32 x 32 accumulator values into a
+// shared-memory box (row-major, 128-byte swizzle: conflict-free 16-byte stores) and the copy engine adds the box into
+// out (cp.reduce.async.bulk.tensor .add on fp32: one IEEE round-to-nearest add per element, each element touched
+// once, so the result does not depend on any order).  Rows past the live count hold -0.0f, which changes no value it is
+// added to.  A warp rewrites its box only after the engine has read the previous one (the wait sits after the
+// next chunk's values are already scaled in registers).
+// Note: the memory-side adder flushes subnormal inputs and results to zero (as fp32 atomics do); out values in the
+// normal range - any real residual stream - get the same bits as __fadd_rn.
+__device__ __forceinline__ void drain_add_tma(const CUtensorMap* tm_out, int N, int live, int m0, int n0, int q, int lane,
+                                              uint32_t lane_addr, uint32_t* box, const float* swb, float sa,
+                                              int c_begin, int c_end) {
+    const int row0 = m0 + q * 32;
+    if (row0 >= live) return;                                       // warp-uniform: no live row in this quarter
+    const bool rok = row0 + lane < live;
+#pragma unroll 1
+    for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+        if (n0 + c0 >= N) break;
+        uint32_t r[32];
+        tmem_ld32(lane_addr + c0, r);
+        tmem_ld_wait();
+        float4 o[8];
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+            o[v].x = rok ? scale2((int)r[4 * v + 0], sa, swb[c0 + 4 * v + 0]) : -0.0f;
+            o[v].y = rok ? scale2((int)r[4 * v + 1], sa, swb[c0 + 4 * v + 1]) : -0.0f;
+            o[v].z = rok ? scale2((int)r[4 * v + 2], sa, swb[c0 + 4 * v + 2]) : -0.0f;
+            o[v].w = rok ? scale2((int)r[4 * v + 3], sa, swb[c0 + 4 * v + 3]) : -0.0f;
+        }
+        // the engine must be done READING the box (the previous chunk's reduction) before it is rewritten
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        __syncwarp();
+        const uint32_t base = smem_u32(box) + lane * 128;
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};"
+                         : : "r"(base + (uint32_t)((v ^ (lane & 7)) << 4)), "f"(o[v].x), "f"(o[v].y), "f"(o[v].z), "f"(o[v].w)
+                         : "memory");
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                         : : "l"(tm_out), "r"(n0 + c0), "r"(row0), "r"(smem_u32(box)) : "memory");
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+    }
+}
+
+// The residual add as fire-and-forget reductions: no load, nothing to wait for.  Each warp instruction adds one row
+// segment of 32 consecutive fp32 values (128 bytes) at the memory side (red.global.add.f32: one round-to-nearest add per
+// element, every element touched once).  Same note on subnormals as drain_add_tma.
+__device__ __forceinline__ void drain_add_red(float* __restrict__ out, long ldo, int N, int live, int m0, int n0, int q,
+                                              int lane, uint32_t lane_addr, uint32_t* stg, const float* swb, float sa,
+                                              int c_begin, int c_end) {
+    const int rows_here = live - (m0 + q * 32);
+    if (rows_here <= 0) return;
+    float* base = out + (long)(m0 + q * 32) * ldo + n0 + lane;
+#pragma unroll 1
+    for (int c0 = c_begin; c0 < c_end; c0 += 32) {
+        if (n0 + c0 >= N) break;
+        uint32_t r[32];
+        tmem_ld32(lane_addr + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) stg[lane * 32 + (j ^ lane)] = __float_as_uint(scale2((int)r[j], sa, swb[c0 + j]));
+        __syncwarp();
+        if (n0 + c0 + lane < N) {
+#pragma unroll
+            for (int rr = 0; rr < 32; ++rr)
+                if (rr < rows_here)
+                    asm volatile("red.global.add.f32 [%0], %1;"
+                                 : : "l"(base + (long)rr * ldo + c0), "f"(__uint_as_float(stg[rr * 32 + (lane ^ rr)]))
+                                 : "memory");
+        }
+        __syncwarp();
+    }
+}
+
 // Split-K in the tile kernel: the last CTA to finish a tile (a counter per tile) adds the K slices' int32 partial
 // accumulators ws[slice][128][BN] (exact, so the order is free) and runs the epilogue for rows [r_begin, r_begin + 32)
 // and columns [c_begin, c_end) of the tile.  Lane = column: every load and store is a full row segment.
@@ -319,7 +396,8 @@ struct TileCfg {
     // + control block + scale stash + per-warp staging: (2 stashes, 4 x 33-word-pitch buffers) or, for the residual
     // add, (1 stash, 8 x 32-word-pitch buffers)
     static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + (int)sizeof(Aux) + 2 * BN * 4 + 4 * 32 * 33 * 4;
-    static constexpr int SMEM_ADD = STAGES * STAGE_BYTES + 1024 + (int)sizeof(Aux) + BN * 4 + 8 * 32 * 32 * 4;
+    // (the residual add's boxes are copy-engine sources with the 128-byte swizzle: 1024-byte aligned)
+    static constexpr int SMEM_ADD = 1024 + (STAGES * STAGE_BYTES + (int)sizeof(Aux) + BN * 4 + 1023) / 1024 * 1024 + 8 * 32 * 32 * 4;
 };
 
 // Epilogue warps: four (one per tensor-memory lane quarter), eight for the residual add (two per quarter, half the
@@ -333,7 +411,7 @@ struct TileWarps {
 template <int BN, int EPI>
 __global__ void __launch_bounds__(TileWarps<EPI>::THREADS, 1)
 w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
-                 const float* __restrict__ a_s, const float* __restrict__ w_s, void* __restrict__ out, long ldo,
+                 const __grid_constant__ CUtensorMap tm_out, const float* __restrict__ a_s, const float* __restrict__ w_s, void* __restrict__ out, long ldo,
                  const int* __restrict__ n_rows, int M, int N, int K, int word_ok, int split, int kb_per_split,
                  int32_t* __restrict__ ws, int* __restrict__ counters) {
     using C = TileCfg<BN>;
@@ -351,6 +429,11 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     const int num_tiles = num_m * num_n, KB = (K + BK - 1) / BK;
     // work units: (tile, K slice), the slices of a tile next to each other so that they finish together
     const int num_units = num_tiles * split;
+    // Tile order.  Row tiles fastest: a weight panel is read once and the activations come back from L2 for every
+    // panel - right while the activations fit in L2.  Weight tiles fastest (bit 3 of word_ok): a group of row tiles
+    // is read once and the weights come back from L2 - right when the activations are the larger operand and the
+    // weights fit (down projection at many rows).
+    const bool n_fastest = (word_ok & 8) != 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
@@ -386,7 +469,7 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             bool ok = true;
             for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
                 const int t = u / split, z = u - t * split;
-                const int m0 = (t % num_m) * BM, n0 = (t / num_m) * BN;
+                const int m0 = (n_fastest ? t / num_n : t % num_m) * BM, n0 = (n_fastest ? t % num_n : t / num_m) * BN;
                 const int kb_end = (z + 1) * kb_per_split < KB ? (z + 1) * kb_per_split : KB;
                 for (int kb = z * kb_per_split; kb < kb_end; ++kb) {
                     if (!mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1, abort_flag, 0x100 + stage)) {
@@ -462,7 +545,7 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         uint32_t bphase = 0;
         for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
             const int t = u / split, z = u - t * split;
-            const int m0 = (t % num_m) * BM, n0 = (t / num_m) * BN;
+            const int m0 = (n_fastest ? t / num_n : t % num_m) * BM, n0 = (n_fastest ? t % num_n : t / num_m) * BN;
             float* swb = sw_stash + (EPI == EPI_ADD ? 0 : buf * BN);
             if (EPI == EPI_ADD) {
                 // one scale stash: everyone must be done with the previous tile's before it is rewritten
@@ -479,7 +562,7 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     if (pass == 1 && u != (int)blockIdx.x) break;
                     if (uu >= num_units) break;
                     const int tt = uu / split;
-                    const int pm0 = (tt % num_m) * BM, pn0 = (tt / num_m) * BN;
+                    const int pm0 = (n_fastest ? tt / num_n : tt % num_m) * BM, pn0 = (n_fastest ? tt % num_n : tt / num_m) * BN;
                     for (int line = et; line < BM * (BN / 32); line += ET) {
                         const int pr = pm0 + line / (BN / 32), pc = pn0 + (line % (BN / 32)) * 32;
                         if (pr < live && pc < N)
@@ -524,13 +607,21 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 if (buf == 0) bphase ^= 1;
                 continue;
             }
-            if (EPI == EPI_ADD) {
+            if (EPI == EPI_ADD && (word_ok & 2)) {
+                uint32_t* box = (uint32_t*)(((uintptr_t)stage_buf + 1023) & ~(uintptr_t)1023) + (warp - 2) * (32 * 32);
+                drain_add_tma(&tm_out, N, live, m0, n0, q, lane, lane_addr, box, swb, sa, half * (BN / 2),
+                              (half + 1) * (BN / 2));
+            } else if (EPI == EPI_ADD && (word_ok & 4)) {
+                uint32_t* stg = stage_buf + (warp - 2) * (32 * 32);
+                drain_add_red((float*)out, ldo, N, live, m0, n0, q, lane, lane_addr, stg, swb, sa, half * (BN / 2),
+                              (half + 1) * (BN / 2));
+            } else if (EPI == EPI_ADD) {
                 uint32_t* stg = stage_buf + (warp - 2) * (32 * 32);
                 drain_add((float*)out, ldo, N, live, m0, n0, q, lane, lane_addr, stg, swb, sa, half * (BN / 2),
                           (half + 1) * (BN / 2));
             } else {
                 uint32_t* stg = stage_buf + q * (32 * 33);
-                drain_accumulator<BN, EPI>(out, ldo, N, live, m0, n0, q, lane, lane_addr, stg, swb, sa, word_ok != 0);
+                drain_accumulator<BN, EPI>(out, ldo, N, live, m0, n0, q, lane, lane_addr, stg, swb, sa, (word_ok & 1) != 0);
             }
             tc_fence_before();
             __syncwarp();
@@ -538,6 +629,8 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             buf ^= 1;
             if (buf == 0) bphase ^= 1;
         }
+        // reductions still in flight read this CTA's shared memory: they complete before the CTA ends
+        if (EPI == EPI_ADD && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
