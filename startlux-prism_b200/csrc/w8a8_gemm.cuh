@@ -254,6 +254,7 @@ __device__ __forceinline__ void drain_add_tma(const CUtensorMap* tm_out, int N, 
     const int row0 = m0 + q * 32;
     if (row0 >= live) return;                                       // warp-uniform: no live row in this quarter
     const bool rok = row0 + lane < live;
+    const uint64_t pol = policy_evict_first();
 #pragma unroll 1
     for (int c0 = c_begin; c0 < c_end; c0 += 32) {
         if (n0 + c0 >= N) break;
@@ -280,8 +281,10 @@ __device__ __forceinline__ void drain_add_tma(const CUtensorMap* tm_out, int N, 
         fence_async_smem();
         __syncwarp();
         if (lane == 0) {
-            asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
-                         : : "l"(tm_out), "r"(n0 + c0), "r"(row0), "r"(smem_u32(box)) : "memory");
+            // evict-first: the residual stream passes through L2 once and must not push out the operands
+            asm volatile(
+                "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group.L2::cache_hint [%0, {%1, %2}], [%3], %4;"
+                : : "l"(tm_out), "r"(n0 + c0), "r"(row0), "r"(smem_u32(box)), "l"(pol) : "memory");
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
     }
@@ -462,6 +465,7 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         if (lane == 0) {
             tma_prefetch_desc(&tm_a);
             tma_prefetch_desc(&tm_w);
+            const uint64_t pol_keep = policy_evict_last();
             uint32_t armed_parity[C::STAGES];
             uint32_t armed_mask = 0;
             int stage = 0;
@@ -479,8 +483,13 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     const uint32_t bar = smem_u32(&aux->full[stage]);
                     mbar_expect_tx(bar, C::STAGE_BYTES);
                     uint8_t* st = smem + stage * C::STAGE_BYTES;
-                    tma_load_2d(smem_u32(st), &tm_a, kb * BK, m0, bar);
-                    tma_load_2d(smem_u32(st + C::A_BYTES), &tm_w, kb * BK, n0, bar);
+                    if (EPI == EPI_ADD) {                     // keep the operands in L2 against the residual stream
+                        tma_load_2d_hint(smem_u32(st), &tm_a, kb * BK, m0, bar, pol_keep);
+                        tma_load_2d_hint(smem_u32(st + C::A_BYTES), &tm_w, kb * BK, n0, bar, pol_keep);
+                    } else {
+                        tma_load_2d(smem_u32(st), &tm_a, kb * BK, m0, bar);
+                        tma_load_2d(smem_u32(st + C::A_BYTES), &tm_w, kb * BK, n0, bar);
+                    }
                     armed_parity[stage] = phase;
                     armed_mask |= 1u << stage;
                     if (++stage == C::STAGES) {
@@ -553,7 +562,8 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             }
             if (EPI != EPI_I32)
                 for (int i = et; i < BN; i += ET) swb[i] = (n0 + i < N) ? w_s[n0 + i] : 0.0f;
-            if (EPI == EPI_ADD) {
+            if (EPI == EPI_ADD && !(word_ok & 6)) {
+                // (register path only: the memory-side adds need no early copy in L2, it measured as a loss there)
                 // the residual rows this CTA adds into one tile from now: pulled into L2 while that tile's main loop
                 // runs (the first tile's are requested as its main loop starts)
                 const int tn = (u == (int)blockIdx.x) ? u : u + (int)gridDim.x;
