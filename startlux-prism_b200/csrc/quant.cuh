@@ -69,11 +69,12 @@ __device__ __forceinline__ void load8(const void* x, long idx, float (&v)[8]) {
     }
 }
 
-// q = rint(v / scale) for 8 values, bit-identical to the IEEE division but far cheaper.  t = fma(v, 1 / scale, 1.5 * 2^23)
-// holds rint(v / scale) (computed from the exact product, half to even) in its low mantissa bits, so the int8 value is
-// the low byte of t: no conversion instruction.  y' = v * (1 / scale) is within 3e-5 of the true quotient for
-// |quotient| <= 128, so this can differ from rint(v / scale) only when y' lies that close to a rounding boundary
-// k + 0.5: d = y' - rint(y') is then near +-0.5, and those (rare) vectors take the exact division instead.
+// q = rint(v / scale) for 8 values, bit-identical to the IEEE division but far cheaper.  t = fma(v, r, 1.5 * 2^23)
+// holds rint(v * r) (computed from the exact product, half to even) in its low mantissa bits, so the int8 value is the
+// low byte of t: no conversion instruction.  r is taken twice, a little below and a little above 1 / scale
+// (rcp * (1 -+ 2^-22); rcp itself is within 2^-24 of 1 / scale): the true quotient and its fp32 rounding both lie
+// between v * r_lo and v * r_hi, rint is monotonic, so when both give the same integer that integer is
+// rint(v / scale).  The (rare: about one vector in two thousand) vectors where they differ take the exact division.
 template <bool FULL>
 __device__ __forceinline__ uint2 quant8(const float (&v)[8], float scale, float rcp) {
     if (FULL) {
@@ -83,16 +84,16 @@ __device__ __forceinline__ uint2 quant8(const float (&v)[8], float scale, float 
         return make_uint2(pack4(q[0], q[1], q[2], q[3]), pack4(q[4], q[5], q[6], q[7]));
     }
     const float magic = 12582912.0f;
+    const float r_lo = __fmul_rn(rcp, 0.99999976158142089844f);  // 1 - 2^-22
+    const float r_hi = __fmul_rn(rcp, 1.00000023841857910156f);  // 1 + 2^-22
     uint32_t t[8];
-    bool near = false;
+    uint32_t differ = 0;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
-        const float tf = __fmaf_rn(v[i], rcp, magic);
-        const float d = __fmaf_rn(v[i], rcp, -__fadd_rn(tf, -magic));
-        near |= fabsf(d) > 0.499f;
-        t[i] = __float_as_uint(tf);
+        t[i] = __float_as_uint(__fmaf_rn(v[i], r_lo, magic));
+        differ |= t[i] ^ __float_as_uint(__fmaf_rn(v[i], r_hi, magic));
     }
-    if (near) {                                                 // rare: one branch per 8 values
+    if (differ) {                                               // rare: one branch per 8 values
         int q[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) q[i] = __float2int_rn(__fdiv_rn(v[i], scale));
