@@ -374,19 +374,19 @@ int launch_w4a8_few(const int8_t* xq, const float* a, const int8_t* xs, int Ma, 
 }
 
 // Row-pipelined quantizers (quant_pipe.cuh): persistent CTAs, rows staged in shared memory by bulk copies.
-template <int KIND, int VPT, bool BF16, int THREADS>
-int launch_pipe_v(bool full, const quant::PipeArgs& p, int grid, int smem, cudaStream_t st) {
+template <int KIND, int VPT, bool BF16>
+int launch_pipe_v(bool full, const quant::PipeArgs& p, int grid, int threads, int smem, cudaStream_t st) {
     int rc;
     if (full) {
-        auto k = quant::row_pipe_kernel<KIND, VPT, BF16, true, THREADS>;
+        auto k = quant::row_pipe_kernel<KIND, VPT, BF16, true, 576>;
         static bool c = false;
         if (!c) { if ((rc = set_smem(k, 200 * 1024))) return rc; c = true; }
-        k<<<grid, THREADS, smem, st>>>(p);
+        k<<<grid, threads, smem, st>>>(p);
     } else {
-        auto k = quant::row_pipe_kernel<KIND, VPT, BF16, false, THREADS>;
+        auto k = quant::row_pipe_kernel<KIND, VPT, BF16, false, 576>;
         static bool c = false;
         if (!c) { if ((rc = set_smem(k, 200 * 1024))) return rc; c = true; }
-        k<<<grid, THREADS, smem, st>>>(p);
+        k<<<grid, threads, smem, st>>>(p);
     }
     return PB_OK;
 }
@@ -407,12 +407,21 @@ int launch_pipe(bool full, quant::PipeArgs p, cudaStream_t st) {
     const int smem = stages * p.row_bytes + 128;
     int grid = sm_count() * per_sm;
     if (grid > p.T) grid = p.T;
+    // vectors of 8 inputs per thread, then just enough threads (whole warps) to cover the row
+    const int vpt = (nvec + 575) / 576;
+    const int threads = ((nvec + vpt - 1) / vpt + 31) / 32 * 32;
     int rc;
-    if (nvec <= 256 * 3) rc = launch_pipe_v<KIND, 3, BF16, 256>(full, p, grid, smem, st);
-    else if (nvec <= 512 * 3) rc = launch_pipe_v<KIND, 3, BF16, 512>(full, p, grid, smem, st);
-    else if (nvec <= 512 * 5) rc = launch_pipe_v<KIND, 5, BF16, 512>(full, p, grid, smem, st);
-    else if (nvec <= 512 * 8) rc = launch_pipe_v<KIND, 8, BF16, 512>(full, p, grid, smem, st);
-    else return PB_UNSUPPORTED_SHAPE;
+    switch (vpt) {
+        case 1: rc = launch_pipe_v<KIND, 1, BF16>(full, p, grid, threads, smem, st); break;
+        case 2: rc = launch_pipe_v<KIND, 2, BF16>(full, p, grid, threads, smem, st); break;
+        case 3: rc = launch_pipe_v<KIND, 3, BF16>(full, p, grid, threads, smem, st); break;
+        case 4: rc = launch_pipe_v<KIND, 4, BF16>(full, p, grid, threads, smem, st); break;
+        case 5: rc = launch_pipe_v<KIND, 5, BF16>(full, p, grid, threads, smem, st); break;
+        case 6: rc = launch_pipe_v<KIND, 6, BF16>(full, p, grid, threads, smem, st); break;
+        case 7: rc = launch_pipe_v<KIND, 7, BF16>(full, p, grid, threads, smem, st); break;
+        case 8: rc = launch_pipe_v<KIND, 8, BF16>(full, p, grid, threads, smem, st); break;
+        default: return PB_UNSUPPORTED_SHAPE;
+    }
     if (rc) return rc;
     PB_CUDA(cudaGetLastError());
     return PB_OK;

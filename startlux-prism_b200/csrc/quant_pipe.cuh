@@ -55,9 +55,12 @@ __device__ __forceinline__ __nv_bfloat162 absmax_bf16x8(const uint4& u, __nv_bfl
     return m;
 }
 
-template <int KIND, int VPT, bool BF16, bool FULL, int THREADS>
-__global__ void __launch_bounds__(THREADS, 1)
+// The block size is chosen at launch so that blockDim.x * VPT just covers the row's vectors (a fixed size left up to
+// a quarter of the threads without a vector); MAXT bounds it for the register allocation.
+template <int KIND, int VPT, bool BF16, bool FULL, int MAXT>
+__global__ void __launch_bounds__(MAXT, 1)
 row_pipe_kernel(const PipeArgs p) {
+    const int THREADS = blockDim.x;
     extern __shared__ uint8_t pipe_smem_raw[];
     const uint32_t smem = (smem_u32(pipe_smem_raw) + 127u) & ~127u;
     __shared__ uint64_t full[8];
