@@ -456,6 +456,25 @@ def run_detail(args):
         b = 3.0 * T * K + 4 * T
         print(json.dumps({"kernel": "rows_q8", "T": T, "K": K, "us": round(us, 2), "gbs": round(b / us / 1e3, 1),
                           "frac_hbm_measured": round(b / us / 1e3 / pk["hbm"], 3)}), flush=True)
+    for T, K in ((8192, 5120), (64, 5120)):
+        h = torch.randn(T, K, device=dev, generator=gen)
+        wn = torch.rand(K, device=dev, generator=gen) + 0.5
+        q = torch.empty(T, K, dtype=torch.int8, device=dev)
+        s = torch.empty(T, device=dev)
+        nr = torch.tensor([T], dtype=torch.int32, device=dev)
+        us = graph_time(lambda c: quant.norm_q8(h, wn, q, s, nr, T, 1e-6), 1, iters=8)
+        b = 5.0 * T * K + 4 * T
+        print(json.dumps({"kernel": "norm_q8", "T": T, "K": K, "us": round(us, 2), "gbs": round(b / us / 1e3, 1),
+                          "frac_hbm_measured": round(b / us / 1e3 / pk["hbm"], 3)}), flush=True)
+    FF = 17408
+    gu = torch.randn(8192, 2 * FF, device=dev, generator=gen).to(torch.bfloat16)
+    q = torch.empty(8192, FF, dtype=torch.int8, device=dev)
+    s = torch.empty(8192, device=dev)
+    nr = torch.tensor([8192], dtype=torch.int32, device=dev)
+    us = graph_time(lambda c: quant.swiglu_q8(gu, None, q, s, nr, 8192), 1, iters=8)
+    b = 5.0 * 8192 * FF
+    print(json.dumps({"kernel": "swiglu_q8", "T": 8192, "FF": FF, "us": round(us, 2), "gbs": round(b / us / 1e3, 1),
+                      "frac_hbm_measured": round(b / us / 1e3 / pk["hbm"], 3)}), flush=True)
     code, where = _lib.device_status()
     print(json.dumps({"device_status": code, "where": where}))
 

@@ -71,6 +71,16 @@ int pb_fold(float* h, long ldh, const int32_t* slots, long slot_stride, int S, c
 int pb_quant_rows(const void* x, int x_fp32, long ldx, const float* inv_s, int8_t* q, float* s, const int* n_rows,
                   int T, int K, int gk, int mode, float* amax, void* stream);
 
+/* RMSNorm + per-token quantization, with a deferred residual add finished first.  Replaces quant.norm_q8 /
+ * _norm_q8_kernel (kernels/quant.py:145-171, :418-431): for output row i (input row rows[i] when rows != NULL, else i):
+ *   h = add_rn(h, mul_rn(mul_rn(float(sum_p parts[p]), psa[r]), psw[c]))  (n_parts > 0; stored back into h)
+ *   y = h * rsqrt(sum(h * h) / HID + eps) * w;  s[i] = max(|y|max, 1e-10) / 127;  q[i] = rint(y / s[i]).
+ * h fp32 [rows, HID] contiguous, w fp32 [HID] (the norm weight over the SmoothQuant factors), HID % 8 == 0.  The
+ * sum of squares is added in this library's fixed order (the reference's Triton reduction has no defined order). */
+int pb_norm_q8(float* h, const float* w, int8_t* q, float* s, const int* rows, const int* n_rows, int T, int HID,
+               float eps, const int32_t* parts, long part_stride, int n_parts, const float* psa, const float* psw,
+               void* stream);
+
 /* SwiGLU + per-token quantization.  Replaces quant.swiglu_q8 (kernels/quant.py:249-284, :473-478):
  * gu bf16 [T, 2 FF] -> q int8 [T, FF], s fp32 [T].  FF % 8 == 0. */
 int pb_swiglu_q8(const void* gu, const float* inv_s, int8_t* q, float* s, const int* n_rows, int T, int FF,

@@ -99,6 +99,22 @@ def swiglu_q8(gu_bits, inv_s=None, live=None):
     return q, s
 
 
+def norm_q8(h, w, eps, rows=None, live=None, parts=None, psa=None, psw=None):
+    """h fp32 [R, HID] (updated in place when parts are given) -> (q int8 [T, HID], s fp32 [T])."""
+    HID = h.shape[1]
+    T = len(rows) if rows is not None else h.shape[0]
+    live = T if live is None else live
+    q = np.zeros((T, HID), np.int8)
+    s = np.zeros(T, np.float32)
+    assert h.dtype == np.float32 and h.flags["C_CONTIGUOUS"]
+    n_parts = 0 if parts is None else parts.shape[0]
+    lib().orc_norm_q8(_p(h), _p(_c(w, np.float32)), _p(q), _p(s), _p(None if rows is None else _c(rows, np.int32)), live,
+                      HID, ctypes.c_float(eps), _p(None if parts is None else _c(parts, np.int32)),
+                      ctypes.c_long(0 if parts is None else parts.shape[1] * parts.shape[2]), n_parts,
+                      _p(None if psa is None else _c(psa, np.float32)), _p(None if psw is None else _c(psw, np.float32)))
+    return q, s
+
+
 def quant_g(x, live=None):
     """x bf16 bits or fp32 [M, K] -> (q int8 [M, K], a fp32 [K/256, M], xs int8 [K/256, M, 16])."""
     M, K = x.shape

@@ -142,6 +142,46 @@ void orc_swiglu_q8(const uint16_t *gu, const float *inv_s, int8_t *q, float *s, 
     }
 }
 
+/* ------------------------------------------------------------------------------------ norm_q8 (RMSNorm + quant)
+ * kernels/quant.py:145-171 (_norm_q8_kernel): after the optional deferred add (same roundings as orc_fold),
+ *   y = h * rsqrt(sum(h * h) / HID + eps) * w;  scale = max(max|y|, 1e-10) / 127;  q = rint(y / scale).
+ * The reference reduces h * h in an order its compiler picks; this restatement adds the squares in double precision
+ * (the order-free answer) and rounds once, so kernels are compared with it within one int8 step. */
+void orc_norm_q8(float *h, const float *w, int8_t *q, float *s, const int *rows, int live, int HID, float eps,
+                 const int32_t *parts, long part_stride, int n_parts, const float *psa, const float *psw) {
+#pragma omp parallel for schedule(static)
+    for (int i = 0; i < live; ++i) {
+        long r = rows ? rows[i] : i;
+        float *hr = h + r * HID;
+        if (n_parts > 0) {
+            for (int c = 0; c < HID; ++c) {
+                int32_t tot = 0;
+                for (int p = 0; p < n_parts; ++p) tot += parts[p * part_stride + r * HID + c];
+                float v = (float)tot * psa[r];
+                v = v * psw[c];
+                hr[c] = hr[c] + v;
+            }
+        }
+        double ss = 0.0;
+        for (int c = 0; c < HID; ++c) ss += (double)hr[c] * (double)hr[c];
+        float mean = (float)(ss / HID);
+        float rinv = (float)(1.0 / sqrt((double)(mean + eps)));
+        float amax = 0.0f;
+        for (int c = 0; c < HID; ++c) {
+            float y = hr[c] * rinv;
+            y = y * w[c];
+            if (fabsf(y) > amax) amax = fabsf(y);
+        }
+        float scale = (amax > 1e-10f ? amax : 1e-10f) / 127.0f;
+        for (int c = 0; c < HID; ++c) {
+            float y = hr[c] * rinv;
+            y = y * w[c];
+            q[(long)i * HID + c] = (int8_t)nearbyintf(y / scale);
+        }
+        s[i] = scale;
+    }
+}
+
 /* ------------------------------------------------------------------------------------ W4A8 activation quant (per 256)
  * kernels/quant.py:314-330 (_store_g) == kernels/w4a8.py:144-155 (quantize_ref):
  *   scale = div_rn(max(max|y|, 1e-10), 127) per 256 inputs; q = rint(div_rn(y, scale));

@@ -688,6 +688,30 @@ int pb_quant_rows(const void* x, int x_fp32, long ldx, const float* inv_s, int8_
     return PB_OK;
 }
 
+int pb_norm_q8(float* h, const float* w, int8_t* q, float* s, const int* rows, const int* n_rows, int T, int HID,
+               float eps, const int32_t* parts, long part_stride, int n_parts, const float* psa, const float* psw,
+               void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!h || !w || !q || !s || !n_rows || T <= 0 || HID <= 0 || n_parts < 0) return PB_BAD_ARGUMENT;
+    if (n_parts > 0 && (!parts || !psa || !psw || rows)) return PB_BAD_ARGUMENT;
+    if (HID % 8 || HID > 65536) return PB_UNSUPPORTED_SHAPE;
+    if (!aligned16(h) || !aligned16(w) || ((uintptr_t)q & 7) || (n_parts > 0 && (!aligned16(parts) || !aligned16(psw) || part_stride % 4)))
+        return PB_BAD_ARGUMENT;
+    const bool full = div_full();
+    const int nvec = HID / 8;
+    const int vpt = nvec <= 2048 ? 4 : 8;
+    const int threads = ((nvec + vpt - 1) / vpt + 31) / 32 * 32;
+    if (vpt == 4) {
+        if (full) quant::norm_q8_kernel<4, true><<<T, threads, 0, st>>>(h, w, q, s, rows, n_rows, HID, eps, parts, part_stride, n_parts, psa, psw);
+        else quant::norm_q8_kernel<4, false><<<T, threads, 0, st>>>(h, w, q, s, rows, n_rows, HID, eps, parts, part_stride, n_parts, psa, psw);
+    } else {
+        if (full) quant::norm_q8_kernel<8, true><<<T, threads, 0, st>>>(h, w, q, s, rows, n_rows, HID, eps, parts, part_stride, n_parts, psa, psw);
+        else quant::norm_q8_kernel<8, false><<<T, threads, 0, st>>>(h, w, q, s, rows, n_rows, HID, eps, parts, part_stride, n_parts, psa, psw);
+    }
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
 int pb_swiglu_q8(const void* gu, const float* inv_s, int8_t* q, float* s, const int* n_rows, int T, int FF, int mode,
                  float* amax, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;

@@ -241,6 +241,95 @@ swiglu_q8_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__
     if (threadIdx.x == 0) s[t] = scale;
 }
 
+// ------------------------------------------------------------------------------------------------- norm_q8
+// RMSNorm fused with the per-token quantizer, with the deferred residual add of a split-K projection finished first
+// (the reference's _norm_q8_kernel, kernels/quant.py:145-171):
+//   h[r, :] = add_rn(h, mul_rn(mul_rn(float(sum_p parts[p, r, :]), psa[r]), psw[:]))   (n_parts > 0; stored back)
+//   y = (h * rsqrt(sum(h * h) / HID + eps)) * w;  scale = max(|y|max, 1e-10) / 127;  q = rint(y / scale)
+// One CTA per output row i (input row rows[i] when gathering); the row stays in registers between the three passes.
+// The sum of squares is added in a fixed order (lane-strided partial sums, then a warp and a block tree): the
+// reference's Triton reduction leaves its order to the compiler, so this step is pinned by tolerance, not by bits.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = lane < nw ? red[lane] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+    __syncthreads();
+    return r;
+}
+
+template <int VPT, bool FULL>
+__global__ void __launch_bounds__(1024)
+norm_q8_kernel(float* __restrict__ h, const float* __restrict__ w, int8_t* __restrict__ q, float* __restrict__ s,
+               const int* __restrict__ rows, const int* __restrict__ n_rows, int HID, float eps,
+               const int32_t* __restrict__ parts, long part_stride, int n_parts, const float* __restrict__ psa,
+               const float* __restrict__ psw) {
+    __shared__ float red[32];
+    const long i = blockIdx.x;
+    if (i >= *n_rows) return;
+    const long r = rows ? (long)rows[i] : i;
+    const int nvec = HID >> 3;
+    float v[VPT][8];
+    float ss = 0.0f;
+    const float sa = n_parts > 0 ? psa[r] : 0.0f;                 // read before this row's new scale is written
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < nvec) {
+            float* hp = h + r * HID + (long)c * 8;
+            const float4 a = *(const float4*)hp, b = *(const float4*)(hp + 4);
+            v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w;
+            v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
+            if (n_parts > 0) {
+                int tot[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                for (int pidx = 0; pidx < n_parts; ++pidx) {
+                    const int4* pp = (const int4*)(parts + pidx * part_stride + r * HID + (long)c * 8);
+                    const int4 x0 = __ldcs(pp), x1 = __ldcs(pp + 1);
+                    tot[0] += x0.x; tot[1] += x0.y; tot[2] += x0.z; tot[3] += x0.w;
+                    tot[4] += x1.x; tot[5] += x1.y; tot[6] += x1.z; tot[7] += x1.w;
+                }
+                const float4 w0 = __ldg((const float4*)(psw + c * 8)), w1 = __ldg((const float4*)(psw + c * 8 + 4));
+                const float sw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[j][e] = __fadd_rn(v[j][e], scale2(tot[e], sa, sw[e]));
+                *(float4*)hp = make_float4(v[j][0], v[j][1], v[j][2], v[j][3]);
+                *(float4*)(hp + 4) = make_float4(v[j][4], v[j][5], v[j][6], v[j][7]);
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = __fmaf_rn(v[j][e], v[j][e], ss);
+        }
+    }
+    ss = block_sum(ss, red);
+    const float rinv = rsqrtf(__fadd_rn(__fdiv_rn(ss, (float)HID), eps));
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < nvec) {
+            const float4 w0 = __ldg((const float4*)(w + c * 8)), w1 = __ldg((const float4*)(w + c * 8 + 4));
+            const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                v[j][e] = __fmul_rn(__fmul_rn(v[j][e], rinv), ww[e]);
+                amax = fmaxf(amax, fabsf(v[j][e]));
+            }
+        }
+    }
+    amax = block_max(amax, red);
+    const float scale = fdiv<FULL>(fmaxf(amax, 1e-10f), 127.0f);
+    const float rcp = __fdiv_rn(1.0f, scale);
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < nvec) *(uint2*)(q + i * HID + (long)c * 8) = quant8<FULL>(v[j], scale, rcp);
+    }
+    if (threadIdx.x == 0) s[i] = scale;
+}
+
 // ------------------------------------------------------------------------------------------------- quant_g (W4A8)
 // One warp per 256 inputs of a row: lane l holds inputs 8 l .. 8 l + 7, so 4 neighbouring lanes make a group of 32.
 // Writes q int8 [T, K], a fp32 [K/256, Ma] and xs int8 [K/256, Ma, 16] (eight S & 63 then eight S >> 6), IEEE division.

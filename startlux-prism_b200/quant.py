@@ -51,6 +51,29 @@ def swiglu_q8(gu, inv_s, q, s, n, T, mode=0, amax=None, sync=None):
     _lib.check(rc, f"swiglu_q8 T={T} FF={FF} mode={mode}")
 
 
+def norm_q8(h, w_over_s, q, s, n, T, eps, rows=None, parts=None, pending=None):
+    """RMSNorm + per-token int8 (the reference's norm_q8, kernels/quant.py:418-431): h fp32 [rows, HID] -> q int8
+    [>= T, HID], s fp32 [>= T]; output row i reads h[rows[i]] when rows (int32, device) is given.  pending (a
+    w8a8.Deferred) with parts int32 [S, rows, HID]: the residual add a split-K projection left open is finished in h
+    first (and stored).  The deferred projection's activation scales may be `s` itself."""
+    HID = h.shape[1]
+    _lib.need_cuda(h, w_over_s, q, s, n)
+    if h.dtype != torch.float32 or not h.is_contiguous() or w_over_s.dtype != torch.float32 or q.shape[1] != HID:
+        raise RuntimeError("norm_q8: h fp32 [rows, HID] contiguous, w fp32 [HID], q int8 [T, HID]")
+    np_ = pending.n if pending else 0
+    if np_ and pending.parts is not None:
+        parts = pending.parts
+    if np_ and (parts is None or rows is not None or parts.dtype != torch.int32):
+        raise RuntimeError("norm_q8: a pending add needs its int32 slots and no row gather")
+    if np_ and getattr(pending, "sync", None) is not None:
+        raise NotImplementedError("norm_q8: in-kernel cross-rank exchanges are not part of this build (use tp.out_proj)")
+    rc = _lib.lib().pb_norm_q8(_lib.ptr(h), _lib.ptr(w_over_s), _lib.ptr(q), _lib.ptr(s), _lib.ptr(rows), _lib.ptr(n),
+                               T, HID, float(eps), _lib.ptr(parts) if np_ else None, parts.stride(0) if np_ else 0, np_,
+                               _lib.ptr(pending.a_s) if np_ else None, _lib.ptr(pending.w_s) if np_ else None,
+                               _lib.stream())
+    _lib.check(rc, f"norm_q8 T={T} HID={HID} parts={np_}")
+
+
 def rows_g(x, q, s, xs, n, T):
     """x bf16 / fp32 [>= T, K] -> q int8 [M, K], s fp32 [K/256, M], xs int8 [K/256, M, 16] (super-block-major)."""
     K = q.shape[1]

@@ -142,3 +142,24 @@ def test_cpu_emulation_fake_quantizers():
     x = torch.from_numpy(g["x"])
     assert np.array_equal(emulation.int8_rows(x).numpy(), g["int8_rows"])
     assert np.array_equal(emulation.int8_groups(32)(x).numpy(), g["int8_g32"])
+
+
+def test_norm_q8_against_float64():
+    """The norm_q8 restatement against the same formula in float64 (kernels/quant.py:166-170): at most one int8 step
+    apart on rare values, scales to 1e-6; the deferred add inside it is the fold's."""
+    rng = np.random.default_rng(5)
+    T, HID = 6, 1024
+    h = (rng.standard_normal((T, HID)) * 2).astype(np.float32)
+    w = (rng.random(HID) + 0.5).astype(np.float32)
+    q, s = oracle.norm_q8(h.copy(), w, 1e-6)
+    h64 = h.astype(np.float64)
+    y = h64 / np.sqrt((h64 * h64).mean(1, keepdims=True) + 1e-6) * w
+    scale = np.maximum(np.abs(y).max(1), 1e-10) / 127.0
+    assert np.allclose(s, scale, rtol=1e-6)
+    want = np.rint(y / scale[:, None])
+    assert np.abs(q - want).max() <= 1 and (q != want).mean() < 1e-3
+    slots = rng.integers(-10 ** 6, 10 ** 6, (2, T, HID), dtype=np.int32)
+    sa, sw = (rng.random(T) * 1e-2).astype(np.float32), (rng.random(HID) * 1e-3).astype(np.float32)
+    h2 = h.copy()
+    oracle.norm_q8(h2, w, 1e-6, parts=slots, psa=sa, psw=sw)
+    assert np.array_equal(h2, oracle.fold(h.copy(), slots, sa, sw))

@@ -144,3 +144,51 @@ def test_swiglu_q8_many_rows(dev, T, FF):
     s2 = torch.zeros(200, device=dev)
     quant.swiglu_q8(gu[:200].contiguous().to(dev), None, q2, s2, n_rows(200, dev), 200)
     assert same(q2, q[:200].contiguous()) and same(s2, s[:200].contiguous())
+
+
+@pytest.mark.parametrize("T,HID,live", [(7, 5120, 5), (64, 5120, 64), (33, 2048, 33), (3, 17408, 3)])
+def test_norm_q8(dev, T, HID, live):
+    """RMSNorm + per-token int8 (kernels/quant.py:145-171): within one int8 step of the oracle (the sum of squares has
+    no order the reference defines), the scale to 1e-5, rows >= live untouched; the row gather picks its rows."""
+    g = torch.Generator().manual_seed(HID + T)
+    h = torch.randn(T, HID, generator=g) * 3
+    w = torch.rand(HID, generator=g) + 0.5
+    rq, rs = oracle.norm_q8(h.numpy().copy(), w.numpy(), 1e-6, live=live)
+    q = torch.zeros(T, HID, dtype=torch.int8, device=dev)
+    s = torch.zeros(T, device=dev)
+    hd = h.to(dev)
+    quant.norm_q8(hd, w.to(dev), q, s, n_rows(live, dev), T, 1e-6)
+    assert np.abs(q.cpu().numpy().astype(int) - rq.astype(int)).max() <= 1
+    assert (q.cpu().numpy() != rq).mean() < 0.01
+    assert np.allclose(s.cpu().numpy()[:live], rs[:live], rtol=1e-5)
+    assert not bool(q[live:].any()) and same(hd, h)
+    # gather: output row i normalizes h[rows[i]]
+    rows = torch.tensor([T - 1, 0, T // 2], dtype=torch.int32)
+    rq2, rs2 = oracle.norm_q8(h.numpy().copy(), w.numpy(), 1e-6, rows=rows.numpy())
+    q2 = torch.zeros(3, HID, dtype=torch.int8, device=dev)
+    s2 = torch.zeros(3, device=dev)
+    quant.norm_q8(hd, w.to(dev), q2, s2, n_rows(3, dev), 3, 1e-6, rows=rows.to(dev))
+    assert np.abs(q2.cpu().numpy().astype(int) - rq2.astype(int)).max() <= 1
+    assert np.allclose(s2.cpu().numpy(), rs2, rtol=1e-5)
+
+
+def test_norm_q8_finishes_deferred_add(dev):
+    """A split-K projection's deferred residual add is finished inside norm_q8: h gets the unsplit add's bits (the
+    fold's contract), then the norm runs on it."""
+    T, HID, S = 9, 2048, 3
+    g = torch.Generator().manual_seed(11)
+    slots = torch.randint(-10 ** 6, 10 ** 6, (S, T, HID), generator=g, dtype=torch.int32)
+    sa, sw = torch.rand(T, generator=g) * 1e-2, torch.rand(HID, generator=g) * 1e-3
+    h = torch.randn(T, HID, generator=g)
+    w = torch.rand(HID, generator=g) + 0.5
+    href = h.numpy().copy()
+    rq, rs = oracle.norm_q8(href, w.numpy(), 1e-6, parts=slots.numpy(), psa=sa.numpy(), psw=sw.numpy())
+    assert np.array_equal(href, oracle.fold(h.numpy().copy(), slots.numpy(), sa.numpy(), sw.numpy()))
+    hd = h.to(dev)
+    q = torch.zeros(T, HID, dtype=torch.int8, device=dev)
+    s = torch.zeros(T, device=dev)
+    quant.norm_q8(hd, w.to(dev), q, s, n_rows(T, dev), T, 1e-6, parts=slots.to(dev),
+                  pending=w8a8.Deferred(S, sa.to(dev), sw.to(dev)))
+    assert same(hd, href)
+    assert np.abs(q.cpu().numpy().astype(int) - rq.astype(int)).max() <= 1
+    assert np.allclose(s.cpu().numpy(), rs, rtol=1e-5)
