@@ -348,4 +348,254 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// ------------------------------------------------------------------------------------------------- GEMM, 128 x 256 tiles
+// The 128 x 128 kernel above needs 32 KB of operands per four MMAs (256 cycles at the fp4 rate): shared memory is
+// written by the bulk copies and read by the tensor core at 128 bytes per cycle each, and that, not the tensor pipe,
+// bounds it (ncu: tensor pipe 29 % busy).  A 128 x 256 tile needs 48 KB per four MMAs of twice the work.  Tensor
+// memory then has room for ONE accumulator (256 columns; the scale factors need 48 more), so a tile's epilogue does
+// not overlap the next tile's MMAs: eight epilogue warps keep it short.
+//   tensor memory: accumulator columns 0..255 | scale factors from column 256: two alternating sets of
+//                  (A: 2 K blocks x 4 columns, B: 2 K blocks x 8 columns)
+//   stage: A 16 KB | B 32 KB | scales of A 1 KB | scales of B 2 KB (weight rows 0-127: K blocks 0, 1; rows 128-255: 0, 1)
+constexpr int BN2 = 256;
+constexpr int STAGES2 = 4;
+constexpr int B2_BYTES = BN2 * KB_BYTES;
+constexpr int STAGE2_BYTES = A_BYTES + B2_BYTES + SF_BYTES + 2 * SF_BYTES;
+constexpr int EPI2_WARPS = 8;
+constexpr int STG2_WORDS = 32 * 17;                                   // per warp: 32 rows x 16 words (+1: no conflicts)
+constexpr int SMEM2 = STAGES2 * STAGE2_BYTES + 1024 + 256 + EPI2_WARPS * STG2_WORDS * 4;
+static_assert(SMEM2 <= 232448, "shared memory");
+
+__global__ void __launch_bounds__(64 + 32 * EPI2_WARPS, 1)
+mxfp4_gemm256_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
+                     const __grid_constant__ CUtensorMap tm_out, const GemmArgs p, int out_by_copy_engine) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    AuxM* aux = (AuxM*)(smem + STAGES2 * STAGE2_BYTES);
+    uint32_t* stage_buf = (uint32_t*)(smem + STAGES2 * STAGE2_BYTES + 256);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN2 - 1) / BN2;
+    const int num_tiles = num_m * num_n, KB = p.K / 256, KA = p.K / 128;
+    const int n_blocks = (p.N + 127) / 128;                           // 128-row blocks of the tiled weight scales
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES2; ++s) {
+            mbar_init(smem_u32(&aux->full[s]), 1);
+            mbar_init(smem_u32(&aux->empty[s]), 1);
+        }
+        mbar_init(smem_u32(&aux->tfull[0]), 1);
+        mbar_init(smem_u32(&aux->tempty[0]), EPI2_WARPS);
+        aux->abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&aux->tmem_base), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = aux->tmem_base;
+    volatile int* abort_flag = &aux->abort_flag;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int mt = t % num_m, nt = t / num_m;
+                const bool second = 2 * nt + 1 < n_blocks;            // the tile's weight rows 128-255 exist
+                for (int kb = 0; kb < KB; ++kb) {
+                    if (!mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1, abort_flag, 0x1700 + stage)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t bar = smem_u32(&aux->full[stage]);
+                    mbar_expect_tx(bar, STAGE2_BYTES - (second ? 0 : SF_BYTES));
+                    const uint32_t st = smem_u32(smem + stage * STAGE2_BYTES);
+                    tma_load_2d(st, &tm_a, kb * KB_BYTES, mt * BM, bar);
+                    tma_load_2d(st + A_BYTES, &tm_b, kb * KB_BYTES, nt * BN2, bar);
+                    const uint32_t sf = st + A_BYTES + B2_BYTES;
+                    bulk_load(sf, p.sfa + ((long)mt * KA + kb * 2) * 512, SF_BYTES, bar);
+                    bulk_load(sf + SF_BYTES, p.sfb + ((long)(2 * nt) * KA + kb * 2) * 512, SF_BYTES, bar);
+                    if (second)
+                        bulk_load(sf + 2 * SF_BYTES, p.sfb + ((long)(2 * nt + 1) * KA + kb * 2) * 512, SF_BYTES, bar);
+                    if (++stage == STAGES2) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            if (!ok) {
+                unsigned long long t0 = global_timer_ns();
+                while (global_timer_ns() - t0 < 2000000ull) {
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int stage = 0, sfp = 0;
+            uint32_t phase = 0, tphase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                // one accumulator: the previous tile must be drained
+                if (!mbar_wait(smem_u32(&aux->tempty[0]), tphase ^ 1, abort_flag, 0x1710)) break;
+                tc_fence_after();
+                for (int kb = 0; kb < KB; ++kb) {
+                    if (!mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, 0x1720 + stage)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t st = smem_u32(smem + stage * STAGE2_BYTES);
+                    const uint32_t sf_smem = st + A_BYTES + B2_BYTES;
+                    const uint32_t sfa_t = tmem_base + 256 + sfp * 24, sfb_t = sfa_t + 8;
+                    tmem_cp_sf(sfa_t, sf_smem);                               // A rows, K block 0
+                    tmem_cp_sf(sfa_t + 4, sf_smem + 512);                     // A rows, K block 1
+                    tmem_cp_sf(sfb_t, sf_smem + SF_BYTES);                    // B rows 0-127, K block 0
+                    tmem_cp_sf(sfb_t + 4, sf_smem + 2 * SF_BYTES);            // B rows 128-255, K block 0
+                    tmem_cp_sf(sfb_t + 8, sf_smem + SF_BYTES + 512);          // B rows 0-127, K block 1
+                    tmem_cp_sf(sfb_t + 12, sf_smem + 2 * SF_BYTES + 512);     // B rows 128-255, K block 1
+                    const uint64_t ad = umma_desc_k128(st), bd = umma_desc_k128(st + A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {                 // K = 64 inputs = 32 bytes per instruction
+                        const uint32_t sf_id = (k & 1) * 2;
+                        umma_mxf4(tmem_base, umma_desc_advance(ad, k * 32), umma_desc_advance(bd, k * 32),
+                                  idesc_mxf4(BM, BN2, sf_id, sf_id), sfa_t + (k >> 1) * 4, sfb_t + (k >> 1) * 8,
+                                  (kb | k) ? 1u : 0u);
+                    }
+                    tc_commit(smem_u32(&aux->empty[stage]));
+                    sfp ^= 1;
+                    if (++stage == STAGES2) {
+                        stage = 0;
+                        phase ^= 1;
+                    }
+                }
+                if (!ok) break;
+                tc_commit(smem_u32(&aux->tfull[0]));
+                tphase ^= 1;
+            }
+        }
+    } else {
+        const int q = warp & 3, half = (warp - 2) >> 2;
+        uint32_t* stg = stage_buf + (warp - 2) * STG2_WORDS;
+        uint32_t tphase = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+            const int m0 = (t % num_m) * BM, n0 = (t / num_m) * BN2;
+            if (!mbar_wait(smem_u32(&aux->tfull[0]), tphase, abort_flag, 0x1730)) break;
+            tc_fence_after();
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+            const int rows_here = p.M - (m0 + q * 32);
+            const bool word_ok = p.epi != 0 || ((((uintptr_t)p.out & 3) == 0) && (p.ldo % 2 == 0));
+            const int cstep = p.epi == 0 ? 32 : 16;                   // columns per chunk: 16 words either way
+            if (out_by_copy_engine) {
+                // 32 rows x 64 bytes per chunk, parked densely in shared memory and handed to the copy engine: a plain
+                // tile store (bf16) or an add into the fp32 residual (one round-to-nearest add per element; the tensor
+                // map ends at row M and column N, so nothing outside is touched).  No load, no store loop.
+                if (m0 + q * 32 < p.M) {
+#pragma unroll 1
+                    for (int c0 = half * (BN2 / 2); c0 < (half + 1) * (BN2 / 2); c0 += cstep) {
+                        if (n0 + c0 >= p.N) break;
+                        uint32_t wv[16];
+                        if (p.epi == 0) {
+                            uint32_t r[32];
+                            tmem_ld32(lane_addr + c0, r);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) {
+                                __nv_bfloat162 b0 =
+                                    __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                                wv[j] = *(uint32_t*)&b0;
+                            }
+                        } else {
+                            tmem_ld16(lane_addr + c0, wv);
+                            tmem_ld_wait();
+                        }
+                        // the engine must be done reading the box (the previous chunk) before it is rewritten
+                        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                        __syncwarp();
+                        uint4* dst = (uint4*)(stg + lane * 16);
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) dst[v] = make_uint4(wv[4 * v], wv[4 * v + 1], wv[4 * v + 2], wv[4 * v + 3]);
+                        fence_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (p.epi == 0)
+                                // (the bf16 output is described as 32-bit words: two columns per element)
+                                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];"
+                                             : : "l"(&tm_out), "r"((n0 + c0) >> 1), "r"(m0 + q * 32), "r"(smem_u32(stg)) : "memory");
+                            else
+                                asm volatile(
+                                    "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                                    : : "l"(&tm_out), "r"(n0 + c0), "r"(m0 + q * 32), "r"(smem_u32(stg)) : "memory");
+                            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        }
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c0 = half * (BN2 / 2); c0 < (half + 1) * (BN2 / 2); c0 += cstep) {
+                    if (n0 + c0 >= p.N) break;
+                    if (p.epi == 0) {
+                        uint32_t r[32];
+                        tmem_ld32(lane_addr + c0, r);
+                        tmem_ld_wait();
+    #pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            __nv_bfloat162 b0 = __floats2bfloat162_rn(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+                            stg[lane * 17 + j] = *(uint32_t*)&b0;
+                        }
+                    } else {
+                        uint32_t r[16];
+                        tmem_ld16(lane_addr + c0, r);
+                        tmem_ld_wait();
+    #pragma unroll
+                        for (int j = 0; j < 16; ++j) stg[lane * 17 + j] = r[j];
+                    }
+                    __syncwarp();
+                    // half a warp per row: lanes 0-15 row rr, lanes 16-31 row rr + 1; 16 words = 64 contiguous bytes
+                    const int w = lane & 15, rsel = lane >> 4;
+                    if (p.epi == 0) {
+                        const int col = n0 + c0 + 2 * w;
+                        for (int rr = rsel; rr < 32 && rr < rows_here; rr += 2) {
+                            const long off = (long)(m0 + q * 32 + rr) * p.ldo + col;
+                            const uint32_t v = stg[rr * 17 + w];
+                            if (word_ok && col + 2 <= p.N) {
+                                *(uint32_t*)((__nv_bfloat16*)p.out + off) = v;
+                            } else {
+                                if (col < p.N) ((uint16_t*)p.out)[off] = (uint16_t)(v & 0xffff);
+                                if (col + 1 < p.N) ((uint16_t*)p.out)[off + 1] = (uint16_t)(v >> 16);
+                            }
+                        }
+                    } else {
+                        const int col = n0 + c0 + w;
+                        if (col < p.N) {
+                            float* base = (float*)p.out + (long)(m0 + q * 32) * p.ldo + col;
+                            float o[16];
+    #pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                if (rsel + 2 * i < rows_here) o[i] = __ldcg(base + (long)(rsel + 2 * i) * p.ldo);
+    #pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                if (rsel + 2 * i < rows_here)
+                                    base[(long)(rsel + 2 * i) * p.ldo] =
+                                        __fadd_rn(o[i], __uint_as_float(stg[(rsel + 2 * i) * 17 + w]));
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&aux->tempty[0]));
+            tphase ^= 1;
+        }
+        if (out_by_copy_engine && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
 }  // namespace mxfp4

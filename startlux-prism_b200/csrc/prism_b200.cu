@@ -189,6 +189,16 @@ bool pair_enabled() {
     return v == 1;
 }
 
+// PRISM_B200_MXFP4_NARROW=1: the 128 x 128 MXFP4 kernel for every shape (comparison runs).
+bool mxfp4_narrow_only() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("PRISM_B200_MXFP4_NARROW");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
+
 // PRISM_B200_W4A8_TILE=1 keeps the many-rows W4A8 kernel for every batch (comparison runs).
 bool w4a8_tile_only() {
     static int v = -1;
@@ -830,12 +840,38 @@ int pb_mxfp4_gemm(const void* aq, const void* a_sf, const void* bq, const void* 
     int rc;
     if ((rc = tensor_map(&ta, aq, K / 2, M, K / 2, 128, 128, 0))) return rc;
     if ((rc = tensor_map(&tb, bq, K / 2, N, K / 2, 128, 128, 0))) return rc;
+    mxfp4::GemmArgs p{(const uint8_t*)a_sf, (const uint8_t*)b_sf, out, ldo, M, N, K, epi};
+    // 128 x 256 tiles when there are enough of them to fill the SMs (the same K order either way: one accumulator
+    // over all of K, so a row's bits do not depend on the choice)
+    const long tiles256 = (long)((M + 127) / 128) * ((N + 255) / 256);
+    if (N > 128 && tiles256 >= sm_count() && !mxfp4_narrow_only()) {
+        CUtensorMap tb2;
+        if ((rc = tensor_map(&tb2, bq, K / 2, N, K / 2, 128, 256, 0))) return rc;
+        static bool configured2 = false;
+        if (!configured2) {
+            if ((rc = set_smem(mxfp4::mxfp4_gemm256_kernel, mxfp4::SMEM2))) return rc;
+            configured2 = true;
+        }
+        const int grid2 = tiles256 < sm_count() ? (int)tiles256 : sm_count();
+        // the epilogue hands 32 x 64-byte boxes to the copy engine when out can be described by a tensor map
+        CUtensorMap tout = ta;
+        int by_engine = 0;
+        const int esz = epi == 0 ? 2 : 4;
+        if (((uintptr_t)out & 15) == 0 && (ldo * esz) % 16 == 0) {
+            if (epi == 0) rc = tensor_map(&tout, out, (uint64_t)N / 2, M, (uint64_t)ldo * 2, 16, 32, 3);   // bf16 pairs as words
+            else rc = tensor_map(&tout, out, N, M, (uint64_t)ldo * 4, 16, 32, 1);
+            if (rc) return rc;
+            by_engine = (epi == 1 || N % 2 == 0) ? 1 : 0;
+        }
+        mxfp4::mxfp4_gemm256_kernel<<<grid2, 64 + 32 * mxfp4::EPI2_WARPS, mxfp4::SMEM2, (cudaStream_t)stream>>>(ta, tb2, tout, p, by_engine);
+        PB_CUDA(cudaGetLastError());
+        return PB_OK;
+    }
     static bool configured = false;
     if (!configured) {
         if ((rc = set_smem(mxfp4::mxfp4_gemm_kernel, mxfp4::SMEM))) return rc;
         configured = true;
     }
-    mxfp4::GemmArgs p{(const uint8_t*)a_sf, (const uint8_t*)b_sf, out, ldo, M, N, K, epi};
     const int tiles = ((M + 127) / 128) * ((N + 127) / 128);
     const int grid = tiles < sm_count() ? tiles : sm_count();
     mxfp4::mxfp4_gemm_kernel<<<grid, 192, mxfp4::SMEM, (cudaStream_t)stream>>>(ta, tb, p);

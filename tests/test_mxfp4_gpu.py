@@ -53,7 +53,7 @@ def rel_fro(got, ref):
 
 
 @pytest.mark.parametrize("M,N,K", [(32, 512, 256), (257, 1024, 512), (16, 5120, 5120), (300, 1000, 2560),
-                                   (1024, 4096, 4096)])
+                                   (1024, 4096, 4096), (1024, 4808, 512), (1000, 4664, 768), (2048, 5120, 1024)])
 def test_gemm(dev, M, N, K):
     w = mxfp4.pack(synth.weights(N, K, seed=N + K))
     x = synth.activations(M, K, seed=M)
@@ -99,3 +99,18 @@ def test_batch_invariance(dev):
     s3 = torch.cat([s] * 5)[:300].contiguous()
     mxfp4.gemm(q3, s3, wd, big, 300)
     assert same(big[:64].contiguous(), out64) and same(big[256:300].contiguous(), out64[:44].contiguous())
+
+
+def test_wide_tiles_same_bits(dev):
+    """Enough tiles for the 128 x 256 kernel (at least one per SM): every row's bits equal the 128 x 128 kernel's (which
+    runs when the same rows come in a small batch) - one accumulator over all of K either way."""
+    M, N, K = 2048, 5120, 1024
+    w = mxfp4.pack(synth.weights(N, K, seed=3))
+    wd = mxfp4.prepare(mxfp4.MX4(w.q.to(dev), w.s.to(dev), N, K))
+    q, s = quant_gpu(synth.activations(M, K, seed=4), dev)
+    big = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+    mxfp4.gemm(q, s, wd, big, M)
+    for r0 in (0, 900, 1984):
+        small = torch.zeros(64, N, dtype=torch.bfloat16, device=dev)
+        mxfp4.gemm(q[r0:r0 + 64].contiguous(), s[r0:r0 + 64].contiguous(), wd, small, 64)
+        assert same(big[r0:r0 + 64].contiguous(), small)
