@@ -314,17 +314,20 @@ w4a8_kernel(const __grid_constant__ Maps maps, const Args p) {
         const int q = warp & 3, ch = (warp - 6) >> 2;
         const int ml = q * 32 + lane;                                    // row in the tile
         const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16) + ch * 32;
-        float y[32];
+        // two output columns per instruction (packed fp32 multiply and fused multiply-add: each half rounds like its
+        // scalar twin, and the reference's definition has these fmas, so nothing is contracted that was not one)
+        float2 y2[16];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) y[j] = 0.0f;
+        for (int j = 0; j < 16; ++j) y2[j] = make_float2(0.0f, 0.0f);
         bool ok = true;
         for (int b = 0; b < NSB; ++b) {
             const int e = b & 1;
             const uint32_t eph = (b >> 1) & 1;
             const int slot = b & (C::SCL_SLOTS - 1);
-            const float* dv = (const float*)(smem + C::OFF_SCL + slot * C::SCL_BYTES) + ch * 32;
-            const float* dmv = dv + 64;
+            const float2* dv = (const float2*)(smem + C::OFF_SCL + slot * C::SCL_BYTES) + ch * 16;
+            const float2* dmv = dv + 32;
             const float am = (m0 + ml < p.Ma) ? __ldg(p.a + (long)b * p.Ma + m0 + ml) : 0.0f;
+            const float2 am2 = make_float2(am, am);
             if (!mbar_wait(smem_u32(&aux->acc_full[e]), eph, abort_flag, 0xD00 + e) ||
                 !mbar_wait(smem_u32(&aux->sfull[slot]), (b / C::SCL_SLOTS) & 1, abort_flag, 0xD20 + slot)) {
                 ok = false;
@@ -343,19 +346,23 @@ w4a8_kernel(const __grid_constant__ Maps maps, const Args p) {
                     tmem_ld16(set + 192 + c, l1);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int acc = (int)p0[j] + 8 * (int)p1[j];
-                        const int mins = (int)l0[j] + 64 * (int)l1[j];
-                        float t = __fmul_rn(dv[c + j], __int2float_rn(acc));
-                        t = __fmaf_rn(-dmv[c + j], __int2float_rn(mins), t);
-                        y[c + j] = __fmaf_rn(am, t, y[c + j]);
+                    for (int j = 0; j < 16; j += 2) {
+                        const float2 fa = make_float2(__int2float_rn((int)p0[j] + 8 * (int)p1[j]),
+                                                      __int2float_rn((int)p0[j + 1] + 8 * (int)p1[j + 1]));
+                        const float2 fm = make_float2(__int2float_rn((int)l0[j] + 64 * (int)l1[j]),
+                                                      __int2float_rn((int)l0[j + 1] + 64 * (int)l1[j + 1]));
+                        const float2 d2 = dv[(c + j) >> 1], dm2 = dmv[(c + j) >> 1];
+                        float2 t = __fmul2_rn(d2, fa);
+                        t = __ffma2_rn(make_float2(-dm2.x, -dm2.y), fm, t);
+                        y2[(c + j) >> 1] = __ffma2_rn(am2, t, y2[(c + j) >> 1]);
                     }
                 } else {
                     tmem_ld_wait();
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const int acc = (int)p0[j] + 64 * (int)p1[j];
-                        y[c + j] = __fmaf_rn(am, __fmul_rn(dv[c + j], __int2float_rn(acc)), y[c + j]);
+                    for (int j = 0; j < 16; j += 2) {
+                        const float2 fa = make_float2(__int2float_rn((int)p0[j] + 64 * (int)p1[j]),
+                                                      __int2float_rn((int)p0[j + 1] + 64 * (int)p1[j + 1]));
+                        y2[(c + j) >> 1] = __ffma2_rn(am2, __fmul2_rn(dv[(c + j) >> 1], fa), y2[(c + j) >> 1]);
                     }
                 }
             }
@@ -365,6 +372,12 @@ w4a8_kernel(const __grid_constant__ Maps maps, const Args p) {
                 mbar_arrive(smem_u32(&aux->acc_empty[e]));
                 mbar_arrive(smem_u32(&aux->sempty[slot]));
             }
+        }
+        float y[32];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            y[2 * j] = y2[j].x;
+            y[2 * j + 1] = y2[j].y;
         }
         if (ok) {
             // every MMA has completed (the last accumulator set was full): the expanded-operand buffers are free and
