@@ -81,6 +81,14 @@ int pb_norm_q8(float* h, const float* w, int8_t* q, float* s, const int* rows, c
                float eps, const int32_t* parts, long part_stride, int n_parts, const float* psa, const float* psw,
                void* stream);
 
+/* Gated RMSNorm of the linear-attention output + per-token quantization.  Replaces quant.gated_norm_q8 /
+ * _gated_norm_q8_kernel (kernels/quant.py:215-246, :460-470), modes 0 / 1 / 2 (mode 3, the in-kernel cross-rank
+ * exchange, is not part of this build).  o fp32 [T, HV * D]; z = bf16 proj[t * P + z_off + ...]; w fp32 [D];
+ * inv_s fp32 [HV * D]; D in {64, 128, 256}.  y = ((o * rsqrt(mean_D(o^2) + eps)) * w) * silu(z) * inv_s per head,
+ * s[t] = max(|y|max, 1e-10) / 127, q = rint(y / s[t]). */
+int pb_gated_norm_q8(const float* o, const void* proj, long P, long z_off, const float* w, const float* inv_s, int8_t* q,
+                     float* s, const int* n_rows, int T, int HV, int D, float eps, int mode, float* amax, void* stream);
+
 /* SwiGLU + per-token quantization.  Replaces quant.swiglu_q8 (kernels/quant.py:249-284, :473-478):
  * gu bf16 [T, 2 FF] -> q int8 [T, FF], s fp32 [T].  FF % 8 == 0. */
 int pb_swiglu_q8(const void* gu, const float* inv_s, int8_t* q, float* s, const int* n_rows, int T, int FF,
@@ -90,6 +98,15 @@ int pb_swiglu_q8(const void* gu, const float* inv_s, int8_t* q, float* s, const 
  * (kernels/quant.py:314-330, :381-411): q int8 [T, K], a fp32 [K/256, Ma], xs int8 [K/256, Ma, 16].  K % 256 == 0. */
 int pb_quant_g(const void* x, int x_fp32, int8_t* q, float* a, int8_t* xs, const int* n_rows, int T, int Ma, int K,
                void* stream);
+
+/* The W4A8 twins of the fused producers: the same values, quantized per 256 inputs with the group sums (the
+ * reference's swiglu_g, norm_g, gated_norm_g; kernels/quant.py:333-381, :397-411).  Outputs as pb_quant_g.
+ * FF, HID, HV * D multiples of 256; D in {64, 128, 256}; HID <= 8192. */
+int pb_swiglu_g(const void* gu, int8_t* q, float* a, int8_t* xs, const int* n_rows, int T, int Ma, int FF, void* stream);
+int pb_norm_g(const float* h, const float* w, int8_t* q, float* a, int8_t* xs, const int* n_rows, int T, int Ma, int HID,
+              float eps, void* stream);
+int pb_gated_norm_g(const float* o, const void* proj, long P, long z_off, const float* w, int8_t* q, float* a, int8_t* xs,
+                    const int* n_rows, int T, int Ma, int HV, int D, float eps, void* stream);
 
 /* W4A8 GEMM on k-quant weights.  Replaces torch.ops.startlux_prism.w4a8_gemm / w4a8_wgmma (csrc/w4a8_gemm.cu:963-969,
  * csrc/w4a8_wgmma.cu:744-748) behind kernels/w4a8.py:353-366 (gemm).  Operands in the repacked layout of

@@ -115,6 +115,45 @@ def norm_q8(h, w, eps, rows=None, live=None, parts=None, psa=None, psw=None):
     return q, s
 
 
+def gated_norm_q8(o, proj_bits, z_off, w, inv_s, HV, D, eps, live=None, amax_in=None, want_amax=False):
+    """o fp32 [T, HV * D], proj bf16 bits [T, P] -> (q int8 [T, HV * D], s fp32 [T][, amax fp32 [T]])."""
+    T, P = proj_bits.shape
+    live = T if live is None else live
+    q = np.zeros((T, HV * D), np.int8)
+    s = np.zeros(T, np.float32)
+    am = np.zeros(T, np.float32)
+    lib().orc_gated_norm_q8(_p(_c(o, np.float32)), _p(_c(proj_bits, np.uint16)), ctypes.c_long(P), ctypes.c_long(z_off),
+                            _p(_c(w, np.float32)), _p(_c(inv_s, np.float32)), _p(q), _p(s), live, HV, D,
+                            ctypes.c_float(eps), _p(None if amax_in is None else _c(amax_in, np.float32)), _p(am))
+    return (q, s, am) if want_amax else (q, s)
+
+
+def swiglu_g(gu_bits, live=None):
+    """gu bf16 bits [T, 2 FF] -> the W4A8 activation triple of silu(gate) * up (quant_g of the fp32 row)."""
+    T, F2 = gu_bits.shape
+    live = T if live is None else live
+    y = np.zeros((T, F2 // 2), np.float32)
+    lib().orc_swiglu_y(_p(_c(gu_bits, np.uint16)), _p(y), live, F2 // 2)
+    return quant_g(y, live)
+
+
+def norm_g(h, w, eps, live=None):
+    T, HID = h.shape
+    live = T if live is None else live
+    y = np.zeros((T, HID), np.float32)
+    lib().orc_norm_y(_p(_c(h, np.float32)), _p(_c(w, np.float32)), _p(y), live, HID, ctypes.c_float(eps))
+    return quant_g(y, live)
+
+
+def gated_norm_g(o, proj_bits, z_off, w, HV, D, eps, live=None):
+    T, P = proj_bits.shape
+    live = T if live is None else live
+    y = np.zeros((T, HV * D), np.float32)
+    lib().orc_gated_norm_y(_p(_c(o, np.float32)), _p(_c(proj_bits, np.uint16)), ctypes.c_long(P), ctypes.c_long(z_off),
+                           _p(_c(w, np.float32)), _p(y), live, HV, D, ctypes.c_float(eps))
+    return quant_g(y, live)
+
+
 def quant_g(x, live=None):
     """x bf16 bits or fp32 [M, K] -> (q int8 [M, K], a fp32 [K/256, M], xs int8 [K/256, M, 16])."""
     M, K = x.shape

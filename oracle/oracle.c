@@ -13,6 +13,7 @@
  * fp32 product and sum below must round on its own, as the reference's explicit mul_rn / add_rn do.
  */
 #include <math.h>
+#include <stdlib.h>
 #include <stdint.h>
 #include <string.h>
 
@@ -180,6 +181,88 @@ void orc_norm_q8(float *h, const float *w, int8_t *q, float *s, const int *rows,
         }
         s[i] = scale;
     }
+}
+
+/* ------------------------------------------------------------------------------------ gated_norm_q8
+ * kernels/quant.py:215-246 (_gated_norm_q8_kernel):
+ *   y = o * rsqrt(sum_D(o * o) / D + eps) * w[d] * (z / (1 + exp(-z)));  y = y * inv_s;  per-token scale and rint.
+ * Sum of squares in double (the reference's order is its compiler's), libm expf: compared within one int8 step. */
+void orc_gated_norm_q8(const float *o, const uint16_t *proj, long P, long z_off, const float *w, const float *inv_s,
+                       int8_t *q, float *s, int live, int HV, int D, float eps, const float *amax_in, float *amax_out) {
+#pragma omp parallel for schedule(static)
+    for (int t = 0; t < live; ++t) {
+        float amax = 0.0f;
+        float *y = (float *)malloc(sizeof(float) * HV * D);
+        for (int h = 0; h < HV; ++h) {
+            const float *oh = o + ((long)t * HV + h) * D;
+            double ss = 0.0;
+            for (int d = 0; d < D; ++d) ss += (double)oh[d] * (double)oh[d];
+            float mean = (float)(ss / D);
+            float rinv = (float)(1.0 / sqrt((double)(mean + eps)));
+            for (int d = 0; d < D; ++d) {
+                float z = bf16_to_f32(proj[(long)t * P + z_off + (long)h * D + d]);
+                float g = z / (1.0f + expf(-z));
+                float v = oh[d] * rinv;
+                v = v * w[d];
+                v = v * g;
+                v = v * inv_s[h * D + d];
+                y[h * D + d] = v;
+                if (fabsf(v) > amax) amax = fabsf(v);
+            }
+        }
+        if (amax_out) amax_out[t] = amax;
+        if (amax_in && amax_in[t] > amax) amax = amax_in[t];
+        float scale = (amax > 1e-10f ? amax : 1e-10f) / 127.0f;
+        for (int i = 0; i < HV * D; ++i) q[(long)t * HV * D + i] = (int8_t)nearbyintf(y[i] / scale);
+        s[t] = scale;
+        free(y);
+    }
+}
+
+/* ------------------------------------------------------------------------------------ the producers' fp32 rows
+ * y of swiglu (kernels/quant.py:256), RMSNorm (:166) and the gated norm (:236-237) before any quantizer, for the W4A8
+ * twins (swiglu_g, norm_g, gated_norm_g: the same rows through the per-256 quantizer orc_quant_g). */
+void orc_swiglu_y(const uint16_t *gu, float *y, int live, int FF) {
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < live; ++r)
+        for (int c = 0; c < FF; ++c) {
+            float g = bf16_to_f32(gu[(long)r * 2 * FF + c]), u = bf16_to_f32(gu[(long)r * 2 * FF + FF + c]);
+            y[(long)r * FF + c] = g / (1.0f + expf(-g)) * u;
+        }
+}
+
+void orc_norm_y(const float *h, const float *w, float *y, int live, int HID, float eps) {
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < live; ++r) {
+        const float *hr = h + (long)r * HID;
+        double ss = 0.0;
+        for (int c = 0; c < HID; ++c) ss += (double)hr[c] * (double)hr[c];
+        float mean = (float)(ss / HID);
+        float rinv = (float)(1.0 / sqrt((double)(mean + eps)));
+        for (int c = 0; c < HID; ++c) {
+            float v = hr[c] * rinv;
+            y[(long)r * HID + c] = v * w[c];
+        }
+    }
+}
+
+void orc_gated_norm_y(const float *o, const uint16_t *proj, long P, long z_off, const float *w, float *y, int live,
+                      int HV, int D, float eps) {
+#pragma omp parallel for schedule(static)
+    for (int t = 0; t < live; ++t)
+        for (int h = 0; h < HV; ++h) {
+            const float *oh = o + ((long)t * HV + h) * D;
+            double ss = 0.0;
+            for (int d = 0; d < D; ++d) ss += (double)oh[d] * (double)oh[d];
+            float mean = (float)(ss / D);
+            float rinv = (float)(1.0 / sqrt((double)(mean + eps)));
+            for (int d = 0; d < D; ++d) {
+                float z = bf16_to_f32(proj[(long)t * P + z_off + (long)h * D + d]);
+                float v = oh[d] * rinv;
+                v = v * w[d];
+                y[((long)t * HV + h) * D + d] = v * (z / (1.0f + expf(-z)));
+            }
+        }
 }
 
 /* ------------------------------------------------------------------------------------ W4A8 activation quant (per 256)

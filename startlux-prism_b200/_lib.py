@@ -21,6 +21,10 @@ _SIGS = {
     "pb_fold": ([_vp, _l, _vp, _l, _i, _vp, _vp, _vp, _i, _i, _vp], _i),
     "pb_quant_rows": ([_vp, _i, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp], _i),
     "pb_swiglu_q8": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp], _i),
+    "pb_gated_norm_q8": ([_vp, _vp, _l, _l, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, ctypes.c_float, _i, _vp, _vp], _i),
+    "pb_swiglu_g": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
+    "pb_norm_g": ([_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, ctypes.c_float, _vp], _i),
+    "pb_gated_norm_g": ([_vp, _vp, _l, _l, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, ctypes.c_float, _vp], _i),
     "pb_norm_q8": ([_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, ctypes.c_float, _vp, _l, _i, _vp, _vp, _vp], _i),
     "pb_quant_g": ([_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
     "pb_mxfp4_sf_bytes": ([_i, _i], _l),

@@ -722,6 +722,31 @@ int pb_norm_q8(float* h, const float* w, int8_t* q, float* s, const int* rows, c
     return PB_OK;
 }
 
+int pb_gated_norm_q8(const float* o, const void* proj, long P, long z_off, const float* w, const float* inv_s, int8_t* q,
+                     float* s, const int* n_rows, int T, int HV, int D, float eps, int mode, float* amax, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!o || !proj || !w || !inv_s || !q || !s || !n_rows || T <= 0 || HV <= 0) return PB_BAD_ARGUMENT;
+    if (mode < 0 || mode > 2 || (mode != 0 && !amax)) return PB_BAD_ARGUMENT;
+    if (D != 64 && D != 128 && D != 256) return PB_UNSUPPORTED_SHAPE;
+    if (!aligned16(o) || !aligned16(w) || !aligned16(inv_s) || ((uintptr_t)q & 7) || !aligned16(proj) || (P * 2) % 16 ||
+        (z_off * 2) % 16)
+        return PB_BAD_ARGUMENT;
+    const bool full = div_full();
+    const int nvec = HV * D / 8;
+    if (nvec > 4 * 1024) return PB_UNSUPPORTED_SHAPE;
+    // whole warps, and a head's lanes never straddle two of a thread's vectors: blockDim is a multiple of 32 >= D / 8
+    const int vpt = nvec <= 1024 ? 1 : nvec <= 2048 ? 2 : 4;
+    const int threads = ((nvec + vpt - 1) / vpt + 31) / 32 * 32;
+    const __nv_bfloat16* pj = (const __nv_bfloat16*)proj;
+#define PB_GN(V, F) quant::gated_norm_q8_kernel<V, F><<<T, threads, 0, st>>>(o, pj, P, z_off, w, inv_s, q, s, n_rows, HV, D, eps, mode, amax)
+    if (vpt == 1) { if (full) PB_GN(1, true); else PB_GN(1, false); }
+    else if (vpt == 2) { if (full) PB_GN(2, true); else PB_GN(2, false); }
+    else { if (full) PB_GN(4, true); else PB_GN(4, false); }
+#undef PB_GN
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
 int pb_swiglu_q8(const void* gu, const float* inv_s, int8_t* q, float* s, const int* n_rows, int T, int FF, int mode,
                  float* amax, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
@@ -750,6 +775,37 @@ int pb_quant_g(const void* x, int x_fp32, int8_t* q, float* a, int8_t* xs, const
     dim3 grid((K / 256 + 7) / 8, T);
     if (x_fp32) quant::quant_g_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>(x, q, a, xs, n_rows, Ma, K);
     else quant::quant_g_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>(x, q, a, xs, n_rows, Ma, K);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+int pb_swiglu_g(const void* gu, int8_t* q, float* a, int8_t* xs, const int* n_rows, int T, int Ma, int FF, void* stream) {
+    if (!gu || !q || !a || !xs || !n_rows || T <= 0 || FF <= 0 || Ma < T) return PB_BAD_ARGUMENT;
+    if (FF % 256 || !aligned16(gu) || ((uintptr_t)q & 7)) return PB_UNSUPPORTED_SHAPE;
+    dim3 grid((FF / 256 + 7) / 8, T);
+    quant::swiglu_g_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)gu, q, a, xs, n_rows, Ma, FF);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+int pb_norm_g(const float* h, const float* w, int8_t* q, float* a, int8_t* xs, const int* n_rows, int T, int Ma, int HID,
+              float eps, void* stream) {
+    if (!h || !w || !q || !a || !xs || !n_rows || T <= 0 || HID <= 0 || Ma < T) return PB_BAD_ARGUMENT;
+    if (HID % 256 || HID > 8192 || !aligned16(h) || !aligned16(w) || ((uintptr_t)q & 7)) return PB_UNSUPPORTED_SHAPE;
+    quant::norm_g_kernel<<<T, HID / 8, 0, (cudaStream_t)stream>>>(h, w, q, a, xs, n_rows, Ma, HID, eps);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+int pb_gated_norm_g(const float* o, const void* proj, long P, long z_off, const float* w, int8_t* q, float* a, int8_t* xs,
+                    const int* n_rows, int T, int Ma, int HV, int D, float eps, void* stream) {
+    if (!o || !proj || !w || !q || !a || !xs || !n_rows || T <= 0 || HV <= 0 || Ma < T) return PB_BAD_ARGUMENT;
+    if ((D != 64 && D != 128 && D != 256) || (HV * D) % 256) return PB_UNSUPPORTED_SHAPE;
+    if (!aligned16(o) || !aligned16(w) || !aligned16(proj) || (P * 2) % 16 || (z_off * 2) % 16 || ((uintptr_t)q & 7))
+        return PB_BAD_ARGUMENT;
+    dim3 grid((HV * D / 256 + 7) / 8, T);
+    quant::gated_norm_g_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(o, (const __nv_bfloat16*)proj, P, z_off, w, q, a, xs,
+                                                                       n_rows, Ma, HV, D, eps);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }

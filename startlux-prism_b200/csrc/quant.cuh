@@ -330,20 +330,79 @@ norm_q8_kernel(float* __restrict__ h, const float* __restrict__ w, int8_t* __res
     if (threadIdx.x == 0) s[i] = scale;
 }
 
+// ------------------------------------------------------------------------------------------------- gated_norm_q8
+// The gated RMSNorm of the linear-attention output fused with the per-token quantizer (the reference's
+// _gated_norm_q8_kernel, kernels/quant.py:215-246): per token, for every value head h (HV heads of D values):
+//   y[h, d] = ((o[h, d] * rsqrt(sum_d o[h, :]^2 / D + eps)) * w[d]) * silu(z[h, d]) * inv_s[h, d]
+// then scale = max(|y|max over the whole row, 1e-10) / 127 and q = rint(y / scale) (modes 1 / 2 as rows_q8).
+// o fp32 [T, HV * D]; z bf16 at proj + t * P + z_off; one CTA per token, a thread owns 8 consecutive values, so the D / 8
+// neighbouring lanes of a head reduce its sum of squares with shuffles (D = 64, 128 or 256).  The sum's order is this
+// kernel's own (the reference's is its compiler's): pinned by tolerance, like norm_q8.
+template <int VPT, bool FULL>
+__global__ void __launch_bounds__(1024)
+gated_norm_q8_kernel(const float* __restrict__ o, const __nv_bfloat16* __restrict__ proj, long P, long z_off,
+                     const float* __restrict__ w, const float* __restrict__ inv_s, int8_t* __restrict__ q,
+                     float* __restrict__ s, const int* __restrict__ n_rows, int HV, int D, float eps, int mode,
+                     float* __restrict__ amax_io) {
+    __shared__ float red[32];
+    const long t = blockIdx.x;
+    if (t >= *n_rows) return;
+    const int nvec = (HV * D) >> 3, lanes = D >> 3;                // lanes of one head (8, 16 or 32)
+    float v[VPT][8];
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        const bool on = c < nvec;
+        float ss = 0.0f;
+        if (on) {
+            const float* op = o + t * HV * D + (long)c * 8;
+            const float4 a = __ldg((const float4*)op), b = __ldg((const float4*)(op + 4));
+            v[j][0] = a.x; v[j][1] = a.y; v[j][2] = a.z; v[j][3] = a.w;
+            v[j][4] = b.x; v[j][5] = b.y; v[j][6] = b.z; v[j][7] = b.w;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = __fmaf_rn(v[j][e], v[j][e], ss);
+        }
+        // every lane takes part in the shuffles (whole heads are on or off together: nvec is a multiple of lanes)
+        for (int off = lanes >> 1; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+        if (on) {
+            const float rinv = rsqrtf(__fadd_rn(__fdiv_rn(ss, (float)D), eps));
+            const int d0 = (c * 8) % D;
+            float z[8];
+            load8<true>(proj, t * P + z_off + (long)c * 8, z);
+            const float4 w0 = __ldg((const float4*)(w + d0)), w1 = __ldg((const float4*)(w + d0 + 4));
+            const float4 i0 = __ldg((const float4*)(inv_s + c * 8)), i1 = __ldg((const float4*)(inv_s + c * 8 + 4));
+            const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+            const float iv[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float g = fdiv<true>(z[e], 1.0f + __expf(-z[e]));
+                float y = __fmul_rn(__fmul_rn(__fmul_rn(v[j][e], rinv), ww[e]), g);
+                y = __fmul_rn(y, iv[e]);
+                v[j][e] = y;
+                amax = fmaxf(amax, fabsf(y));
+            }
+        }
+    }
+    amax = block_max(amax, red);
+    if (mode == MODE_STORE_AMAX && threadIdx.x == 0) amax_io[t] = amax;
+    if (mode == MODE_USE_AMAX) amax = fmaxf(amax_io[t], amax);
+    const float scale = fdiv<FULL>(fmaxf(amax, 1e-10f), 127.0f);
+    const float rcp = __fdiv_rn(1.0f, scale);
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < nvec) *(uint2*)(q + t * HV * D + (long)c * 8) = quant8<FULL>(v[j], scale, rcp);
+    }
+    if (threadIdx.x == 0) s[t] = scale;
+}
+
 // ------------------------------------------------------------------------------------------------- quant_g (W4A8)
 // One warp per 256 inputs of a row: lane l holds inputs 8 l .. 8 l + 7, so 4 neighbouring lanes make a group of 32.
-// Writes q int8 [T, K], a fp32 [K/256, Ma] and xs int8 [K/256, Ma, 16] (eight S & 63 then eight S >> 6), IEEE division.
-template <bool BF16>
-__global__ void __launch_bounds__(256)
-quant_g_kernel(const void* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ a, int8_t* __restrict__ xs,
-               const int* __restrict__ n_rows, int Ma, int K) {
-    const long t = blockIdx.y;
-    if (t >= *n_rows) return;
-    const int lane = threadIdx.x & 31;
-    const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);     // super-block
-    if (b >= (K >> 8)) return;
-    float v[8];
-    load8<BF16>(x, t * K + (long)b * 256 + lane * 8, v);
+// Writes q int8 [T, K], a fp32 [K/256, Ma] and xs int8 [K/256, Ma, 16] (eight S & 63 then eight S >> 6), IEEE division
+// (the reference's _store_g, kernels/quant.py:315-330).
+__device__ __forceinline__ void store_g_warp(const float (&v)[8], int8_t* __restrict__ q, float* __restrict__ a,
+                                             int8_t* __restrict__ xs, long t, int b, int lane, int Ma, int K) {
     float amax = 0.0f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
@@ -365,6 +424,90 @@ quant_g_kernel(const void* __restrict__ x, int8_t* __restrict__ q, float* __rest
         o[0] = (int8_t)(S & 63);
         o[8] = (int8_t)(S >> 6);
     }
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+quant_g_kernel(const void* __restrict__ x, int8_t* __restrict__ q, float* __restrict__ a, int8_t* __restrict__ xs,
+               const int* __restrict__ n_rows, int Ma, int K) {
+    const long t = blockIdx.y;
+    if (t >= *n_rows) return;
+    const int lane = threadIdx.x & 31;
+    const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);     // super-block
+    if (b >= (K >> 8)) return;
+    float v[8];
+    load8<BF16>(x, t * K + (long)b * 256 + lane * 8, v);
+    store_g_warp(v, q, a, xs, t, b, lane, Ma, K);
+}
+
+// SwiGLU + the per-256 quantizer (the reference's _swiglu_g_kernel, kernels/quant.py:371-381): gu bf16 [T, 2 FF]
+// (gate columns then up columns) -> the W4A8 activation triple of silu(gate) * up.  Nothing row-wide: a warp per 256.
+__global__ void __launch_bounds__(256)
+swiglu_g_kernel(const __nv_bfloat16* __restrict__ gu, int8_t* __restrict__ q, float* __restrict__ a,
+                int8_t* __restrict__ xs, const int* __restrict__ n_rows, int Ma, int FF) {
+    const long t = blockIdx.y;
+    if (t >= *n_rows) return;
+    const int lane = threadIdx.x & 31;
+    const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (b >= (FF >> 8)) return;
+    float g[8], u[8], v[8];
+    load8<true>(gu, t * 2 * FF + (long)b * 256 + lane * 8, g);
+    load8<true>(gu, t * 2 * FF + FF + (long)b * 256 + lane * 8, u);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(fdiv<true>(g[e], 1.0f + __expf(-g[e])), u[e]);
+    store_g_warp(v, q, a, xs, t, b, lane, Ma, FF);
+}
+
+// RMSNorm + the per-256 quantizer (the reference's _norm_g_kernel, kernels/quant.py:333-345): one CTA per row, a warp
+// per 256 inputs (HID / 256 warps), the row's sum of squares through the block.
+__global__ void __launch_bounds__(1024)
+norm_g_kernel(const float* __restrict__ h, const float* __restrict__ w, int8_t* __restrict__ q, float* __restrict__ a,
+              int8_t* __restrict__ xs, const int* __restrict__ n_rows, int Ma, int HID, float eps) {
+    __shared__ float red[32];
+    const long t = blockIdx.x;
+    if (t >= *n_rows) return;
+    const int lane = threadIdx.x & 31, b = threadIdx.x >> 5;
+    float v[8];
+    load8<false>(h, t * HID + (long)b * 256 + lane * 8, v);
+    float ss = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss = __fmaf_rn(v[e], v[e], ss);
+    ss = block_sum(ss, red);
+    const float rinv = rsqrtf(__fadd_rn(__fdiv_rn(ss, (float)HID), eps));
+    const float4 w0 = __ldg((const float4*)(w + b * 256 + lane * 8)), w1 = __ldg((const float4*)(w + b * 256 + lane * 8 + 4));
+    const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = __fmul_rn(__fmul_rn(v[e], rinv), ww[e]);
+    store_g_warp(v, q, a, xs, t, b, lane, Ma, HID);
+}
+
+// Gated RMSNorm + the per-256 quantizer (the reference's _gated_norm_g_kernel, kernels/quant.py:348-368): a warp per
+// 256 values = 256 / D heads (D = 64, 128 or 256), the head's sum of squares over its D / 8 lanes.
+__global__ void __launch_bounds__(256)
+gated_norm_g_kernel(const float* __restrict__ o, const __nv_bfloat16* __restrict__ proj, long P, long z_off,
+                    const float* __restrict__ w, int8_t* __restrict__ q, float* __restrict__ a, int8_t* __restrict__ xs,
+                    const int* __restrict__ n_rows, int Ma, int HV, int D, float eps) {
+    const long t = blockIdx.y;
+    if (t >= *n_rows) return;
+    const int lane = threadIdx.x & 31, K = HV * D;
+    const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (b >= (K >> 8)) return;
+    const int c = b * 32 + lane;                                   // vector of 8 values in the row
+    float v[8], z[8];
+    load8<false>(o, t * K + (long)c * 8, v);
+    load8<true>(proj, t * P + z_off + (long)c * 8, z);
+    float ss = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss = __fmaf_rn(v[e], v[e], ss);
+    for (int off = D >> 4; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    const float rinv = rsqrtf(__fadd_rn(__fdiv_rn(ss, (float)D), eps));
+    const int d0 = (c * 8) % D;
+    const float4 w0 = __ldg((const float4*)(w + d0)), w1 = __ldg((const float4*)(w + d0 + 4));
+    const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+    for (int e = 0; e < 8; ++e)
+        v[e] = __fmul_rn(__fmul_rn(__fmul_rn(v[e], rinv), ww[e]), fdiv<true>(z[e], 1.0f + __expf(-z[e])));
+    store_g_warp(v, q, a, xs, t, b, lane, Ma, K);
 }
 
 // ------------------------------------------------------------------------------------------------- fold

@@ -74,6 +74,23 @@ def norm_q8(h, w_over_s, q, s, n, T, eps, rows=None, parts=None, pending=None):
     _lib.check(rc, f"norm_q8 T={T} HID={HID} parts={np_}")
 
 
+def gated_norm_q8(o, proj, z_off, w, inv_s, q, s, n, T, cfg, mode=0, amax=None, sync=None):
+    """The gated RMSNorm of the linear-attention output + per-token int8 (the reference's gated_norm_q8,
+    kernels/quant.py:460-470): o fp32 [>= T, v_heads * gdn_dim], the gate z = proj[:, z_off : z_off + v_heads * gdn_dim]
+    (bf16, proj's row stride honoured), w fp32 [gdn_dim], inv_s fp32 [v_heads * gdn_dim] -> q int8, s fp32 [>= T].
+    cfg: anything with v_heads, gdn_dim, eps.  Modes as rows_q8."""
+    HV, D = cfg.v_heads, cfg.gdn_dim
+    _lib.need_cuda(o, proj, q, s, n)
+    amax = _mode_args(mode, amax, sync, T)
+    if o.dtype != torch.float32 or not o.is_contiguous() or o.shape[1] != HV * D or proj.dtype != torch.bfloat16 \
+            or proj.stride(1) != 1 or q.shape[1] != HV * D:
+        raise RuntimeError("gated_norm_q8: o fp32 [T, v_heads * gdn_dim] contiguous, proj bf16 with unit column stride")
+    rc = _lib.lib().pb_gated_norm_q8(_lib.ptr(o), _lib.ptr(proj), proj.stride(0), int(z_off), _lib.ptr(w), _lib.ptr(inv_s),
+                                     _lib.ptr(q), _lib.ptr(s), _lib.ptr(n), T, HV, D, float(cfg.eps), mode, _lib.ptr(amax),
+                                     _lib.stream())
+    _lib.check(rc, f"gated_norm_q8 T={T} heads={HV} dim={D} mode={mode}")
+
+
 def rows_g(x, q, s, xs, n, T):
     """x bf16 / fp32 [>= T, K] -> q int8 [M, K], s fp32 [K/256, M], xs int8 [K/256, M, 16] (super-block-major)."""
     K = q.shape[1]
@@ -86,6 +103,50 @@ def rows_g(x, q, s, xs, n, T):
     rc = _lib.lib().pb_quant_g(_lib.ptr(x), int(x.dtype == torch.float32), _lib.ptr(q), _lib.ptr(s), _lib.ptr(xs),
                                _lib.ptr(n), T, Ma, K, _lib.stream())
     _lib.check(rc, f"rows_g T={T} K={K}")
+
+
+def _g_outputs(q, s, xs, K, what):
+    Ma = s.shape[1]
+    if K % 256 or q.shape[1] != K or s.shape[0] != K // 256 or xs.shape != (K // 256, Ma, 16) or not q.is_contiguous() \
+            or not s.is_contiguous() or not xs.is_contiguous():
+        raise RuntimeError(f"{what}: q int8 [M, K], s fp32 [K/256, M], xs int8 [K/256, M, 16], contiguous, K % 256 == 0")
+    return Ma
+
+
+def swiglu_g(gu, q, s, xs, n, T):
+    """SwiGLU into the W4A8 activation triple (the reference's swiglu_g, kernels/quant.py:407-409): gu bf16
+    [>= T, 2 FF] -> q int8 [M, FF], s fp32 [FF/256, M], xs int8 [FF/256, M, 16]."""
+    FF = q.shape[1]
+    _lib.need_cuda(gu, q, s, xs, n)
+    Ma = _g_outputs(q, s, xs, FF, "swiglu_g")
+    if gu.dtype != torch.bfloat16 or gu.shape[1] != 2 * FF or not gu.is_contiguous():
+        raise RuntimeError("swiglu_g: gu must be contiguous bf16 [T, 2 FF]")
+    rc = _lib.lib().pb_swiglu_g(_lib.ptr(gu), _lib.ptr(q), _lib.ptr(s), _lib.ptr(xs), _lib.ptr(n), T, Ma, FF, _lib.stream())
+    _lib.check(rc, f"swiglu_g T={T} FF={FF}")
+
+
+def norm_g(h, w, q, s, xs, n, T, eps):
+    """RMSNorm into the W4A8 activation triple (the reference's norm_g, kernels/quant.py:397-399)."""
+    HID = h.shape[1]
+    _lib.need_cuda(h, w, q, s, xs, n)
+    Ma = _g_outputs(q, s, xs, HID, "norm_g")
+    if h.dtype != torch.float32 or not h.is_contiguous():
+        raise RuntimeError("norm_g: h must be contiguous fp32 [T, HID]")
+    rc = _lib.lib().pb_norm_g(_lib.ptr(h), _lib.ptr(w), _lib.ptr(q), _lib.ptr(s), _lib.ptr(xs), _lib.ptr(n), T, Ma, HID,
+                              float(eps), _lib.stream())
+    _lib.check(rc, f"norm_g T={T} HID={HID}")
+
+
+def gated_norm_g(o, proj, z_off, w, q, s, xs, n, T, cfg):
+    """The gated norm into the W4A8 activation triple (the reference's gated_norm_g, kernels/quant.py:402-404)."""
+    HV, D = cfg.v_heads, cfg.gdn_dim
+    _lib.need_cuda(o, proj, q, s, xs, n)
+    Ma = _g_outputs(q, s, xs, HV * D, "gated_norm_g")
+    if o.dtype != torch.float32 or not o.is_contiguous() or proj.dtype != torch.bfloat16 or proj.stride(1) != 1:
+        raise RuntimeError("gated_norm_g: o fp32 contiguous, proj bf16 with unit column stride")
+    rc = _lib.lib().pb_gated_norm_g(_lib.ptr(o), _lib.ptr(proj), proj.stride(0), int(z_off), _lib.ptr(w), _lib.ptr(q),
+                                    _lib.ptr(s), _lib.ptr(xs), _lib.ptr(n), T, Ma, HV, D, float(cfg.eps), _lib.stream())
+    _lib.check(rc, f"gated_norm_g T={T} heads={HV} dim={D}")
 
 
 def fold(h, parts, pending, n, T):

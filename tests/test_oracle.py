@@ -163,3 +163,22 @@ def test_norm_q8_against_float64():
     h2 = h.copy()
     oracle.norm_q8(h2, w, 1e-6, parts=slots, psa=sa, psw=sw)
     assert np.array_equal(h2, oracle.fold(h.copy(), slots, sa, sw))
+
+
+def test_gated_norm_q8_against_float64():
+    rng = np.random.default_rng(9)
+    T, HV, D, P, z_off = 4, 6, 128, 1000, 40
+    o = (rng.standard_normal((T, HV * D)) * 2).astype(np.float32)
+    z32 = (rng.standard_normal((T, P)) * 1.5).astype(np.float32)
+    zb = oracle.bf16_bits(z32)
+    w = (rng.random(D) + 0.5).astype(np.float32)
+    inv = np.exp(rng.standard_normal(HV * D) * 0.1).astype(np.float32)
+    q, s = oracle.gated_norm_q8(o, zb, z_off, w, inv, HV, D, 1e-6)
+    o64 = o.astype(np.float64).reshape(T, HV, D)
+    z = oracle.bf16_to_f32(zb).astype(np.float64)[:, z_off:z_off + HV * D].reshape(T, HV, D)
+    y = o64 / np.sqrt((o64 * o64).mean(2, keepdims=True) + 1e-6) * w * (z / (1 + np.exp(-z))) * inv.reshape(HV, D)
+    y = y.reshape(T, -1)
+    scale = np.maximum(np.abs(y).max(1), 1e-10) / 127.0
+    assert np.allclose(s, scale, rtol=1e-5)
+    want = np.rint(y / scale[:, None])
+    assert np.abs(q - want).max() <= 1 and (q != want).mean() < 5e-3

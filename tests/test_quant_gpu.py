@@ -192,3 +192,92 @@ def test_norm_q8_finishes_deferred_add(dev):
     assert same(hd, href)
     assert np.abs(q.cpu().numpy().astype(int) - rq.astype(int)).max() <= 1
     assert np.allclose(s.cpu().numpy(), rs, rtol=1e-5)
+
+
+class _GdnCfg:
+    def __init__(self, v_heads, gdn_dim, eps=1e-6):
+        self.v_heads, self.gdn_dim, self.eps = v_heads, gdn_dim, eps
+
+
+@pytest.mark.parametrize("T,HV,D,live", [(5, 48, 128, 4), (64, 6, 128, 64), (3, 16, 64, 3), (2, 4, 256, 2)])
+def test_gated_norm_q8(dev, T, HV, D, live):
+    """The gated norm + quantizer (kernels/quant.py:215-246) within one int8 step of the oracle (its exponential and
+    sum order differ), scales to 1e-5, the gate read from a column window of a wider projection buffer; the
+    tensor-parallel modes 1 / 2 reproduce a whole-row quantization from two head shards."""
+    g = torch.Generator().manual_seed(T * 100 + HV)
+    o = torch.randn(T, HV * D, generator=g) * 2
+    P, z_off = HV * D + 264, 136
+    proj = (torch.randn(T, P, generator=g) * 1.5).to(torch.bfloat16)
+    w = torch.rand(D, generator=g) + 0.5
+    inv = torch.exp(torch.randn(HV * D, generator=g) * 0.1)
+    rq, rs = oracle.gated_norm_q8(o.numpy(), np_bits(proj), z_off, w.numpy(), inv.numpy(), HV, D, 1e-6, live=live)
+    q = torch.zeros(T, HV * D, dtype=torch.int8, device=dev)
+    s = torch.zeros(T, device=dev)
+    cfg = _GdnCfg(HV, D)
+    quant.gated_norm_q8(o.to(dev), proj.to(dev), z_off, w.to(dev), inv.to(dev), q, s, n_rows(live, dev), T, cfg)
+    assert np.abs(q.cpu().numpy().astype(int) - rq.astype(int)).max() <= 1
+    assert (q.cpu().numpy() != rq).mean() < 0.02
+    assert np.allclose(s.cpu().numpy()[:live], rs[:live], rtol=1e-5)
+    assert not bool(q[live:].any())
+    if HV % 2 == 0:
+        # two shards of heads: maxima stored (mode 1), combined, used (mode 2)
+        h2 = HV // 2
+        c2 = _GdnCfg(h2, D)
+        amax = torch.zeros(2, T, device=dev)
+        parts = []
+        for r in range(2):
+            sl = slice(r * h2 * D, (r + 1) * h2 * D)
+            qs = torch.zeros(T, h2 * D, dtype=torch.int8, device=dev)
+            ss = torch.zeros(T, device=dev)
+            args = (o[:, sl].contiguous().to(dev), proj.to(dev), z_off + r * h2 * D, w.to(dev), inv[sl].contiguous().to(dev))
+            quant.gated_norm_q8(*args, qs, ss, n_rows(live, dev), T, c2, mode=1, amax=amax[r])
+            parts.append((args, qs, ss))
+        both = torch.maximum(amax[0], amax[1])
+        for r, (args, qs, ss) in enumerate(parts):
+            quant.gated_norm_q8(*args, qs, ss, n_rows(live, dev), T, c2, mode=2, amax=both)
+            assert same(qs[:live].contiguous(), q[:live, r * h2 * D:(r + 1) * h2 * D].contiguous())
+            assert same(ss[:live].contiguous(), s[:live].contiguous())
+
+
+def _check_g(q, s, xs, rq, rs, live):
+    """A W4A8 activation triple against the oracle's: values within one int8 step, scales to 1e-5, and the group sums
+    are exactly those of the kernel's own q (split as S & 63, S >> 6)."""
+    qn, sn, xn = q.cpu().numpy(), s.cpu().numpy(), xs.cpu().numpy()
+    assert np.abs(qn[:live].astype(int) - rq[:live].astype(int)).max() <= 1
+    assert (qn[:live] != rq[:live]).mean() < 0.02
+    assert np.allclose(sn[:, :live], rs[:, :live], rtol=1e-5)
+    K = qn.shape[1]
+    S = qn[:live].astype(np.int32).reshape(live, K // 256, 8, 32).sum(-1)          # [live, K/256, 8]
+    got = xn[:, :live].astype(np.int32)                                               # [K/256, live, 16]
+    assert np.array_equal(got[..., :8], (S & 63).transpose(1, 0, 2))
+    assert np.array_equal(got[..., 8:], (S >> 6).transpose(1, 0, 2))
+
+
+def test_w4a8_producer_twins(dev):
+    """swiglu_g, norm_g, gated_norm_g (kernels/quant.py:333-411): the fused producers through the per-256 quantizer."""
+    g = torch.Generator().manual_seed(21)
+    T, live = 9, 7
+    nr = n_rows(live, dev)
+
+    def outs(K):
+        return (torch.zeros(T, K, dtype=torch.int8, device=dev), torch.zeros(K // 256, T, device=dev),
+                torch.zeros(K // 256, T, 16, dtype=torch.int8, device=dev))
+    FF = 1536
+    gu = (torch.randn(T, 2 * FF, generator=g) * 2).to(torch.bfloat16)
+    q, s, xs = outs(FF)
+    quant.swiglu_g(gu.to(dev), q, s, xs, nr, T)
+    _check_g(q, s, xs, *oracle.swiglu_g(np_bits(gu), live)[:2], live)
+    HID = 5120
+    h = torch.randn(T, HID, generator=g) * 3
+    w = torch.rand(HID, generator=g) + 0.5
+    q, s, xs = outs(HID)
+    quant.norm_g(h.to(dev), w.to(dev), q, s, xs, nr, T, 1e-6)
+    _check_g(q, s, xs, *oracle.norm_g(h.numpy(), w.numpy(), 1e-6, live)[:2], live)
+    HV, D = 48, 128
+    o = torch.randn(T, HV * D, generator=g) * 2
+    P, z_off = HV * D + 264, 136
+    proj = (torch.randn(T, P, generator=g) * 1.5).to(torch.bfloat16)
+    wd = torch.rand(D, generator=g) + 0.5
+    q, s, xs = outs(HV * D)
+    quant.gated_norm_g(o.to(dev), proj.to(dev), z_off, wd.to(dev), q, s, xs, nr, T, _GdnCfg(HV, D))
+    _check_g(q, s, xs, *oracle.gated_norm_g(o.numpy(), np_bits(proj), z_off, wd.numpy(), HV, D, 1e-6, live)[:2], live)
