@@ -475,6 +475,24 @@ def run_detail(args):
     b = 5.0 * 8192 * FF
     print(json.dumps({"kernel": "swiglu_q8", "T": 8192, "FF": FF, "us": round(us, 2), "gbs": round(b / us / 1e3, 1),
                       "frac_hbm_measured": round(b / us / 1e3 / pk["hbm"], 3)}), flush=True)
+    if args.detail_head:
+        # the vocabulary head (Q8_0, per-32 groups, N = 248,320): 1.27 GB of weights + 159 MB of group scales per step
+        from prism_b200 import decode
+        N, K = 248320, 5120
+        w = torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev, generator=gen)
+        ws = torch.rand(N, K // 32, device=dev, generator=gen) * 1e-3
+        for M in (1, 16, 64):
+            a = torch.randint(-127, 128, (M, K), dtype=torch.int8, device=dev, generator=gen)
+            sa = torch.rand(M, K // 32, device=dev, generator=gen) * 1e-2
+            out = torch.zeros(M, N, device=dev)
+            nr = torch.tensor([M], dtype=torch.int32, device=dev)
+            us = graph_time(lambda c: decode.head_q8(a, sa, w, ws, out, nr, M), 1, iters=4)
+            b = N * K * 34.0 / 32 + M * K + 4.0 * M * N
+            print(json.dumps({"kernel": "head_q8", "M": M, "N": N, "K": K, "us": round(us, 2),
+                              "gbs": round(b / us / 1e3, 1), "frac_hbm_measured": round(b / us / 1e3 / pk["hbm"], 3)}),
+                  flush=True)
+        del w, ws
+        torch.cuda.empty_cache()
     code, where = _lib.device_status()
     print(json.dumps({"device_status": code, "where": where}))
 
@@ -634,6 +652,7 @@ def main():
     ap.add_argument("--detail", action="store_true", help="per-shape GEMM table instead of the JSON line")
     ap.add_argument("--probe", default=None, help="one kernel case, a few eager launches (for ncu)")
     ap.add_argument("--detail-rows", default=None)
+    ap.add_argument("--detail-head", action="store_true", help="add the vocabulary head (head_q8) to --detail")
     ap.add_argument("--detail-shapes", default=None)
     ap.add_argument("--detail-gk", default=None, help="comma list; 0 = one group per row (gk == K), 32 = Q8_0 blocks")
     ap.add_argument("--detail-split", type=int, default=None)

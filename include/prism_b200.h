@@ -23,6 +23,7 @@ extern "C" {
 #define PB_EPI_BF16 0 /* out bf16 [M, N] = v */
 #define PB_EPI_ADD 1  /* out fp32 [M, N] = add_rn(out, v) */
 #define PB_EPI_I32 3  /* out int32 = the raw integer sums */
+#define PB_EPI_F32 4  /* out fp32 [M, N] = v (gk == 32, M <= 64: the vocabulary head's logits) */
 
 #define PB_MODE_PLAIN 0
 #define PB_MODE_STORE_AMAX 1
@@ -88,6 +89,13 @@ int pb_norm_q8(float* h, const float* w, int8_t* q, float* s, const int* rows, c
  * s[t] = max(|y|max, 1e-10) / 127, q = rint(y / s[t]). */
 int pb_gated_norm_q8(const float* o, const void* proj, long P, long z_off, const float* w, const float* inv_s, int8_t* q,
                      float* s, const int* n_rows, int T, int HV, int D, float eps, int mode, float* amax, void* stream);
+
+/* Final RMSNorm of a residual row, then int8 per 32 inputs: the vocabulary head's activations.  Replaces head_quant /
+ * _head_quant_kernel (kernels/decode.py:113-133): y = h * rsqrt(sum(h * h) / HID + eps) * w;
+ * s[r, g] = max(|y_g|max, 1e-10) / 127, q = rint(y / s).  h fp32 [B, HID], q int8 [B, HID], s fp32 [B, HID / 32];
+ * HID % 32 == 0.  (The head GEMM itself is pb_w8a8_gemm with gk = 32 and PB_EPI_F32.) */
+int pb_head_quant(const float* h, const float* w, int8_t* q, float* s, const int* n_rows, int B, int HID, float eps,
+                  void* stream);
 
 /* SwiGLU + per-token quantization.  Replaces quant.swiglu_q8 (kernels/quant.py:249-284, :473-478):
  * gu bf16 [T, 2 FF] -> q int8 [T, FF], s fp32 [T].  FF % 8 == 0. */

@@ -154,6 +154,16 @@ def gated_norm_g(o, proj_bits, z_off, w, HV, D, eps, live=None):
     return quant_g(y, live)
 
 
+def head_quant(h, w, eps, live=None):
+    """h fp32 [B, HID] -> (q int8 [B, HID], s fp32 [B, HID / 32]): final RMSNorm + int8 per 32 inputs."""
+    B, HID = h.shape
+    live = B if live is None else live
+    q = np.zeros((B, HID), np.int8)
+    s = np.zeros((B, HID // 32), np.float32)
+    lib().orc_head_quant(_p(_c(h, np.float32)), _p(_c(w, np.float32)), _p(q), _p(s), live, HID, ctypes.c_float(eps))
+    return q, s
+
+
 def quant_g(x, live=None):
     """x bf16 bits or fp32 [M, K] -> (q int8 [M, K], a fp32 [K/256, M], xs int8 [K/256, M, 16])."""
     M, K = x.shape

@@ -265,6 +265,31 @@ void orc_gated_norm_y(const float *o, const uint16_t *proj, long P, long z_off, 
         }
 }
 
+/* ------------------------------------------------------------------------------------ head_quant
+ * kernels/decode.py:113-133 (_head_quant_kernel): y = h * rsqrt(sum(h * h) / HID + eps) * w, then per 32 inputs
+ * scale = max(max|y|, 1e-10) / 127, q = rint(y / scale).  Sum of squares in double (order-free). */
+void orc_head_quant(const float *h, const float *w, int8_t *q, float *s, int live, int HID, float eps) {
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < live; ++r) {
+        const float *hr = h + (long)r * HID;
+        double ss = 0.0;
+        for (int c = 0; c < HID; ++c) ss += (double)hr[c] * (double)hr[c];
+        float mean = (float)(ss / HID);
+        float rinv = (float)(1.0 / sqrt((double)(mean + eps)));
+        for (int g = 0; g < HID / 32; ++g) {
+            float y[32], amax = 0.0f;
+            for (int k = 0; k < 32; ++k) {
+                float v = hr[g * 32 + k] * rinv;
+                y[k] = v * w[g * 32 + k];
+                if (fabsf(y[k]) > amax) amax = fabsf(y[k]);
+            }
+            float scale = (amax > 1e-10f ? amax : 1e-10f) / 127.0f;
+            for (int k = 0; k < 32; ++k) q[(long)r * HID + g * 32 + k] = (int8_t)nearbyintf(y[k] / scale);
+            s[(long)r * (HID / 32) + g] = scale;
+        }
+    }
+}
+
 /* ------------------------------------------------------------------------------------ W4A8 activation quant (per 256)
  * kernels/quant.py:314-330 (_store_g) == kernels/w4a8.py:144-155 (quantize_ref):
  *   scale = div_rn(max(max|y|, 1e-10), 127) per 256 inputs; q = rint(div_rn(y, scale));

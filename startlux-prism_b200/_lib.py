@@ -25,6 +25,7 @@ _SIGS = {
     "pb_swiglu_g": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
     "pb_norm_g": ([_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, ctypes.c_float, _vp], _i),
     "pb_gated_norm_g": ([_vp, _vp, _l, _l, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, ctypes.c_float, _vp], _i),
+    "pb_head_quant": ([_vp, _vp, _vp, _vp, _vp, _i, _i, ctypes.c_float, _vp], _i),
     "pb_norm_q8": ([_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, ctypes.c_float, _vp, _l, _i, _vp, _vp, _vp], _i),
     "pb_quant_g": ([_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp], _i),
     "pb_mxfp4_sf_bytes": ([_i, _i], _l),

@@ -563,7 +563,8 @@ int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float
                  void* workspace, long workspace_bytes, int* counters, int n_counters, int pdl, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     if (!a || !w || !out || !n_rows || M <= 0 || N <= 0 || K <= 0 || split < 1) return PB_BAD_ARGUMENT;
-    if (epi != PB_EPI_BF16 && epi != PB_EPI_ADD && epi != PB_EPI_I32) return PB_BAD_ARGUMENT;
+    if (epi != PB_EPI_BF16 && epi != PB_EPI_ADD && epi != PB_EPI_I32 && epi != PB_EPI_F32) return PB_BAD_ARGUMENT;
+    if (epi == PB_EPI_F32 && (gk != 32 || M > 64)) return PB_UNSUPPORTED_SHAPE;
     if (epi != PB_EPI_I32 && (!a_s || !w_s)) return PB_BAD_ARGUMENT;
     if (!aligned16(a) || !aligned16(w)) return PB_BAD_ARGUMENT;
     if (K % 16) return PB_UNSUPPORTED_SHAPE;
@@ -743,6 +744,26 @@ int pb_gated_norm_q8(const float* o, const void* proj, long P, long z_off, const
     else if (vpt == 2) { if (full) PB_GN(2, true); else PB_GN(2, false); }
     else { if (full) PB_GN(4, true); else PB_GN(4, false); }
 #undef PB_GN
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+int pb_head_quant(const float* h, const float* w, int8_t* q, float* s, const int* n_rows, int B, int HID, float eps,
+                  void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!h || !w || !q || !s || !n_rows || B <= 0 || HID <= 0) return PB_BAD_ARGUMENT;
+    if (HID % 32 || HID > 65536 || !aligned16(h) || !aligned16(w) || ((uintptr_t)q & 7)) return PB_UNSUPPORTED_SHAPE;
+    const bool full = div_full();
+    const int nvec = HID / 8;
+    const int vpt = nvec <= 2048 ? 4 : 8;
+    const int threads = ((nvec + vpt - 1) / vpt + 31) / 32 * 32;
+    if (vpt == 4) {
+        if (full) quant::head_quant_kernel<4, true><<<B, threads, 0, st>>>(h, w, q, s, n_rows, HID, eps);
+        else quant::head_quant_kernel<4, false><<<B, threads, 0, st>>>(h, w, q, s, n_rows, HID, eps);
+    } else {
+        if (full) quant::head_quant_kernel<8, true><<<B, threads, 0, st>>>(h, w, q, s, n_rows, HID, eps);
+        else quant::head_quant_kernel<8, false><<<B, threads, 0, st>>>(h, w, q, s, n_rows, HID, eps);
+    }
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }

@@ -397,6 +397,57 @@ gated_norm_q8_kernel(const float* __restrict__ o, const __nv_bfloat16* __restric
     if (threadIdx.x == 0) s[t] = scale;
 }
 
+// ------------------------------------------------------------------------------------------------- head_quant
+// The final RMSNorm of a residual row, then int8 per group of 32 inputs (the reference's _head_quant_kernel,
+// kernels/decode.py:113-133): one CTA per row, the row in registers; a group of 32 is four neighbouring lanes.
+template <int VPT, bool FULL>
+__global__ void __launch_bounds__(1024)
+head_quant_kernel(const float* __restrict__ h, const float* __restrict__ w, int8_t* __restrict__ q,
+                  float* __restrict__ s, const int* __restrict__ n_rows, int HID, float eps) {
+    __shared__ float red[32];
+    const long r = blockIdx.x;
+    if (r >= *n_rows) return;
+    const int nvec = HID >> 3;
+    float v[VPT][8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        if (c < nvec) {
+            load8<false>(h, r * HID + (long)c * 8, v[j]);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = __fmaf_rn(v[j][e], v[j][e], ss);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[j][e] = 0.0f;
+        }
+    }
+    ss = block_sum(ss, red);
+    const float rinv = rsqrtf(__fadd_rn(__fdiv_rn(ss, (float)HID), eps));
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int c = threadIdx.x + j * blockDim.x;
+        const bool on = c < nvec;
+        float amax = 0.0f;
+        if (on) {
+            const float4 w0 = __ldg((const float4*)(w + c * 8)), w1 = __ldg((const float4*)(w + c * 8 + 4));
+            const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                v[j][e] = __fmul_rn(__fmul_rn(v[j][e], rinv), ww[e]);
+                amax = fmaxf(amax, fabsf(v[j][e]));
+            }
+        }
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        const float scale = fdiv<FULL>(fmaxf(amax, 1e-10f), 127.0f);
+        if (on) {
+            *(uint2*)(q + r * HID + (long)c * 8) = quant8<FULL>(v[j], scale, __fdiv_rn(1.0f, scale));
+            if ((c & 3) == 0) s[r * (HID >> 5) + (c >> 2)] = scale;
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------- quant_g (W4A8)
 // One warp per 256 inputs of a row: lane l holds inputs 8 l .. 8 l + 7, so 4 neighbouring lanes make a group of 32.
 // Writes q int8 [T, K], a fp32 [K/256, Ma] and xs int8 [K/256, Ma, 16] (eight S & 63 then eight S >> 6), IEEE division

@@ -26,6 +26,7 @@ constexpr int BK = 128;        // bytes (= int8 values) of K per pipeline stage:
 constexpr int EPI_BF16 = 0;    // out bf16 [M, N] = v
 constexpr int EPI_ADD = 1;     // out fp32 [M, N] = add_rn(out, v)
 constexpr int EPI_I32 = 3;     // out int32 [M, N] = acc (no scales)
+constexpr int EPI_F32 = 4;     // out fp32 [M, N] = v (the vocabulary head's logits; per-32 groups, few rows)
 
 struct Aux {                   // shared-memory control block placed after the stages
     uint64_t full[12];
@@ -879,6 +880,8 @@ __device__ __forceinline__ void swap_store(const SwapArgs& p, int n, int m0, int
         if (m < live) {
             if (p.epi == EPI_BF16)
                 ((__nv_bfloat16*)p.out)[(long)m * p.ldo + n] = __float2bfloat16_rn(v[j]);
+            else if (p.epi == EPI_F32)
+                ((float*)p.out)[(long)m * p.ldo + n] = v[j];
             else {
                 float* o = (float*)p.out + (long)m * p.ldo + n;
                 *o = __fadd_rn(*o, v[j]);

@@ -20,7 +20,7 @@ import torch
 
 from . import _lib
 
-EPI_BF16, EPI_ADD, EPI_SWIGLU, EPI_I32 = 0, 1, 2, 3
+EPI_BF16, EPI_ADD, EPI_SWIGLU, EPI_I32, EPI_F32 = 0, 1, 2, 3, 4
 FEW_ROWS = 64                    # up to this many rows the operand-swapped kernel runs
 MAX_SPLIT = 8
 RESIDENT_CTAS = 296              # two CTAs of the few-rows kernel per SM on 148 SMs
@@ -108,8 +108,8 @@ def gemm(a, a_s, w, w_s, out, n_rows, gk, epi=0, outs=None, cfg=None, slots=None
     N = w.shape[0]
     if epi == EPI_SWIGLU:
         raise NotImplementedError("the fused SwiGLU epilogue (epi 2) is not part of this build: use quant.swiglu_q8")
-    if epi not in (EPI_BF16, EPI_ADD):
-        raise ValueError(f"epi {epi}")
+    if epi not in (EPI_BF16, EPI_ADD, EPI_F32) or (epi == EPI_F32 and (gk != 32 or M > FEW_ROWS)):
+        raise ValueError(f"epi {epi}")                 # EPI_F32 (plain fp32 store): the vocabulary head, decode.head_q8
     want = torch.bfloat16 if epi == EPI_BF16 else torch.float32
     if out.dtype != want or out.shape[0] < M or out.shape[1] != N or out.stride(1) != 1:
         raise RuntimeError(f"w8a8.gemm: out must be {want} [>= {M}, {N}] with unit column stride")
