@@ -183,7 +183,7 @@ def run_gpu(args):
     sync()
     ms = e0.elapsed_time(e1) / args.steps
     # ---- per-GEMM durations for the roofline (events around each launch, same stream)
-    gemm_ms = time_gemms(stack, h0, args.steps) if world == 1 else None
+    gemm_ms = time_gemms(stack, h0, args.steps)
     # ---- end to end: host buffers, copies inside the timed region, pipelined over three streams
     e2e_ms, h2d, d2h = time_e2e(stack, h0, args.steps, sync)
     clocks = sampler.stop() if rank == 0 else None
@@ -203,12 +203,12 @@ def run_gpu(args):
                         "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
                 "gpu_launches": launches_per_step(world) * args.steps, "clocks": clocks}
         if gemm_ms is not None:
-            achieved = ops / (gemm_ms * 1e-3) / 1e12
+            achieved = ops / world / (gemm_ms * 1e-3) / 1e12    # per GPU: this rank's share of the products / its GEMM time
             peak = 2.0 * pk["bf16"]
             # DRAM traffic per launch of the dominant kernel (the gate|up GEMM): ncu measured 1.00 x the algorithmic
             # read bytes on the M = 2048 capture (profiles/w8a8_tile_kernel_gate_up_M2048.md); scaled to this M by the
             # units processed: weights once + activations + bf16 output
-            n_gu, k_gu = 34816, 5120
+            n_gu, k_gu = 34816 // world, 5120
             traffic = n_gu * k_gu + M * k_gu + 2 * M * n_gu
             line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                                 "frac": achieved / peak, "traffic": traffic,
@@ -243,22 +243,24 @@ def time_gemms(stack, h0, steps):
 
     from prism_b200 import w8a8
     events = []
-    orig = w8a8.gemm
+    orig, orig_i32 = w8a8.gemm, w8a8.gemm_i32
 
-    def timed(*a, **k):
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        r = orig(*a, **k)
-        e.record()
-        events.append((s, e))
-        return r
-    w8a8.gemm = timed
+    def wrap(fn):
+        def timed(*a, **k):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            r = fn(*a, **k)
+            e.record()
+            events.append((s, e))
+            return r
+        return timed
+    w8a8.gemm, w8a8.gemm_i32 = wrap(orig), wrap(orig_i32)
     try:
         for _ in range(steps):
             stack(h0)
         torch.cuda.synchronize()
     finally:
-        w8a8.gemm = orig
+        w8a8.gemm, w8a8.gemm_i32 = orig, orig_i32
     return sum(s.elapsed_time(e) for s, e in events) / steps
 
 

@@ -122,10 +122,16 @@ int pb_gated_norm_g(const float* o, const void* proj, long P, long z_off, const 
  * kind 1 (Q6_K): wq int8 [N, K], wsc int8 [K/256, N, 16], wd fp32 [K/256, N] (wmn, wdm, xs unused).  Activations as
  * pb_quant_g writes them: xq int8 [M, K], a fp32 [K/256, Ma], xs int8 [K/256, Ma, 16].  out bf16 (epi 0) or fp32 +=
  * (epi 1), row stride ldo.  K % 256 == 0, N % 4 == 0, 16-byte aligned operands.  Bit-identical to the reference's
- * gemm_ref (kernels/w4a8.py:177-199) for every M (batch invariance). */
+ * gemm_ref (kernels/w4a8.py:177-199) for every M (batch invariance).
+ * split > 1 (Q4_K, M <= 16 only; ignored otherwise): K is split over CTAs; the slices leave the per-super-block terms
+ * of the reference's chain in `workspace` (pb_w4a8_workspace_bytes) and the last CTA of a tile (counters: one int per
+ * tile, zero on entry and on return) runs the chain in super-block order - the same bits as split == 1. */
 int pb_w4a8_gemm(const int8_t* xq, const float* a, const int8_t* xs, int Ma, int kind, const void* wq,
                  const void* wsc, const void* wmn, const float* wd, const float* wdm, void* out, long ldo,
-                 const int* n_rows, int M, int N, int K, int epi, void* stream);
+                 const int* n_rows, int M, int N, int K, int epi, int split, void* workspace, long workspace_bytes,
+                 int* counters, int n_counters, void* stream);
+long pb_w4a8_workspace_bytes(int M, int N, int K);
+int pb_w4a8_counters(int M, int N);
 
 /* MXFP4.  Replace the reference's ctypes ABI (csrc/mxfp4_gemm.cu:121-168: mxfp4_sfa_bytes / mxfp4_sfb_bytes,
  * mxfp4_prepare_sfa / mxfp4_prepare_sfb, mxfp4_gemm) and its Triton kernels (kernels/mxfp4.py:119-185 quantize_act,

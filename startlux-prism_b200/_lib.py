@@ -32,7 +32,10 @@ _SIGS = {
     "pb_mxfp4_prepare_sf": ([_vp, _vp, _i, _i, _vp], _i),
     "pb_mxfp4_quant": ([_vp, _i, _vp, _vp, _vp, _i, _i, _vp], _i),
     "pb_mxfp4_gemm": ([_vp, _vp, _vp, _vp, _vp, _l, _i, _i, _i, _i, _vp], _i),
-    "pb_w4a8_gemm": ([_vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _l, _vp, _i, _i, _i, _i, _vp], _i),
+    "pb_w4a8_gemm": ([_vp, _vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _l, _vp, _i, _i, _i, _i, _i, _vp, _l, _vp, _i,
+                      _vp], _i),
+    "pb_w4a8_workspace_bytes": ([_i, _i, _i], _l),
+    "pb_w4a8_counters": ([_i, _i], _i),
 }
 # entry points added by later sections of the header; bound when present in the built library
 _OPTIONAL = {

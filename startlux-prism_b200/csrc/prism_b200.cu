@@ -327,7 +327,7 @@ int launch_w4a8(const int8_t* xq, const float* a, const int8_t* xs, int Ma, cons
         if ((rc = set_smem(kern, C::SMEM))) return rc;
         configured = true;
     }
-    w4a8::Args p{a, out, ldo, n_rows, M, N, K, Ma, epi, nullptr, nullptr, nullptr, nullptr};
+    w4a8::Args p{a, out, ldo, n_rows, M, N, K, Ma, epi, nullptr, nullptr, nullptr, nullptr, 1, K / 256, nullptr, nullptr};
     const int grid = ((M + 127) / 128) * ((N + 63) / 64);
     kern<<<grid, w4a8::THREADS, C::SMEM, st>>>(m, p);
     PB_CUDA(cudaGetLastError());
@@ -338,7 +338,7 @@ int launch_w4a8(const int8_t* xq, const float* a, const int8_t* xs, int Ma, cons
 template <int KIND>
 int launch_w4a8_few(const int8_t* xq, const float* a, const int8_t* xs, int Ma, const void* wq, const void* wsc,
                     const void* wmn, const float* wd, const float* wdm, void* out, long ldo, const int* n_rows, int M,
-                    int N, int K, int epi, cudaStream_t st) {
+                    int N, int K, int epi, cudaStream_t st, int split = 1, float* ws = nullptr, int* counters = nullptr) {
     using C = w4a8::FewCfg<KIND>;
     w4a8::FewMaps m;
     int rc;
@@ -358,17 +358,25 @@ int launch_w4a8_few(const int8_t* xq, const float* a, const int8_t* xs, int Ma, 
         m.dm = m.x;
     }
     if ((rc = tensor_map(&m.d, wd, N, NSB, (uint64_t)N * 4, C::TILE_N, 1, 1))) return rc;
-    w4a8::Args p{a, out, ldo, n_rows, M, N, K, Ma, epi, (const uint8_t*)wsc, (const uint8_t*)wmn, wd, wdm};
+    const int nsb = K / 256;
+    if (split > nsb) split = nsb;
+    const int sps = (nsb + split - 1) / split;
+    split = (nsb + sps - 1) / sps;                                    // no empty slice
+    w4a8::Args p{a, out, ldo, n_rows, M, N, K, Ma, epi, (const uint8_t*)wsc, (const uint8_t*)wmn, wd, wdm, split, sps, ws,
+                 counters};
     // the row tiles of one weight tile are neighbours in launch order: the weights of all but the first come from L2
     dim3 grid((M + w4a8::FEW_NB - 1) / w4a8::FEW_NB, (N + C::TILE_N - 1) / C::TILE_N);
     if (KIND == w4a8::KIND_Q4K && !w4a8_few_staged()) {
         // Q4_K: the expanded operand goes through tensor memory
         static bool configured_tm = false;
         if (!configured_tm) {
-            if ((rc = set_smem(w4a8::w4a8_few_q4k_tm_kernel, w4a8::TmCfg::SMEM))) return rc;
+            if ((rc = set_smem(w4a8::w4a8_few_q4k_tm_kernel<false>, w4a8::TmCfg::SMEM))) return rc;
+            if ((rc = set_smem(w4a8::w4a8_few_q4k_tm_kernel<true>, w4a8::TmCfg::SMEM))) return rc;
             configured_tm = true;
         }
-        w4a8::w4a8_few_q4k_tm_kernel<<<grid, w4a8::FEW_THREADS, w4a8::TmCfg::SMEM, st>>>(m, p);
+        grid.z = split;
+        if (split > 1) w4a8::w4a8_few_q4k_tm_kernel<true><<<grid, w4a8::FEW_THREADS, w4a8::TmCfg::SMEM, st>>>(m, p);
+        else w4a8::w4a8_few_q4k_tm_kernel<false><<<grid, w4a8::FEW_THREADS, w4a8::TmCfg::SMEM, st>>>(m, p);
         PB_CUDA(cudaGetLastError());
         return PB_OK;
     }
@@ -378,6 +386,8 @@ int launch_w4a8_few(const int8_t* xq, const float* a, const int8_t* xs, int Ma, 
         if ((rc = set_smem(kern, C::SMEM))) return rc;
         configured = true;
     }
+    if (KIND == w4a8::KIND_Q6K) grid.z = split;
+    else p.split = 1;
     kern<<<grid, w4a8::FEW_THREADS, C::SMEM, st>>>(m, p);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
@@ -831,9 +841,17 @@ int pb_gated_norm_g(const float* o, const void* proj, long P, long z_off, const 
     return PB_OK;
 }
 
+long pb_w4a8_workspace_bytes(int M, int N, int K) {
+    if (M <= 0 || M > 16 || N <= 0 || K <= 0) return 0;
+    return (long)((N + 127) / 128) * (K / 256) * 16 * 128 * 4;
+}
+
+int pb_w4a8_counters(int M, int N) { return (M <= 0 || M > 16 || N <= 0) ? 0 : (N + 63) / 64; }
+
 int pb_w4a8_gemm(const int8_t* xq, const float* a, const int8_t* xs, int Ma, int kind, const void* wq,
                  const void* wsc, const void* wmn, const float* wd, const float* wdm, void* out, long ldo,
-                 const int* n_rows, int M, int N, int K, int epi, void* stream) {
+                 const int* n_rows, int M, int N, int K, int epi, int split, void* workspace, long workspace_bytes,
+                 int* counters, int n_counters, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     if (!xq || !a || !wq || !wsc || !wd || !out || !n_rows || M <= 0 || N <= 0 || K <= 0 || Ma < M) return PB_BAD_ARGUMENT;
     if (kind != 0 && kind != 1) return PB_BAD_ARGUMENT;
@@ -843,9 +861,25 @@ int pb_w4a8_gemm(const int8_t* xq, const float* a, const int8_t* xs, int Ma, int
     if (!aligned16(xq) || !aligned16(wq) || !aligned16(wsc) || !aligned16(wd) || (kind == 0 && (!aligned16(xs) ||
         !aligned16(wmn) || !aligned16(wdm)))) return PB_BAD_ARGUMENT;
     if (M <= 32 && !w4a8_tile_only()) {                            // measured: the many-rows kernel is faster from 64 rows
-        if (kind == 0)
-            return launch_w4a8_few<w4a8::KIND_Q4K>(xq, a, xs, Ma, wq, wsc, wmn, wd, wdm, out, ldo, n_rows, M, N, K, epi, st);
-        return launch_w4a8_few<w4a8::KIND_Q6K>(xq, a, xs, Ma, wq, wsc, wmn, wd, wdm, out, ldo, n_rows, M, N, K, epi, st);
+        if (kind == 0) {
+            // K split (exact): Q4_K through tensor memory, one tile of 16 rows
+            if (split > 1 && M <= 16 && !w4a8_few_staged()) {
+                if (!workspace || !counters) return PB_BAD_ARGUMENT;
+                if (workspace_bytes < pb_w4a8_workspace_bytes(M, N, K) || n_counters < pb_w4a8_counters(M, N)) return PB_TOO_LARGE;
+            } else {
+                split = 1;
+            }
+            return launch_w4a8_few<w4a8::KIND_Q4K>(xq, a, xs, Ma, wq, wsc, wmn, wd, wdm, out, ldo, n_rows, M, N, K, epi, st,
+                                                   split, (float*)workspace, counters);
+        }
+        if (split > 1 && M <= 16) {
+            if (!workspace || !counters) return PB_BAD_ARGUMENT;
+            if (workspace_bytes < pb_w4a8_workspace_bytes(M, N, K) || n_counters < pb_w4a8_counters(M, N)) return PB_TOO_LARGE;
+        } else {
+            split = 1;
+        }
+        return launch_w4a8_few<w4a8::KIND_Q6K>(xq, a, xs, Ma, wq, wsc, wmn, wd, wdm, out, ldo, n_rows, M, N, K, epi, st,
+                                               split, (float*)workspace, counters);
     }
     if (kind == 0)
         return launch_w4a8<w4a8::KIND_Q4K>(xq, a, xs, Ma, wq, wsc, wmn, wd, wdm, out, ldo, n_rows, M, N, K, epi, st);

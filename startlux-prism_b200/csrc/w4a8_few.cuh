@@ -69,6 +69,7 @@ struct AuxFew {
     uint64_t sfull[8], sempty[8];
     uint32_t tmem_base;
     int abort_flag;
+    int is_last;
 };
 
 struct FewMaps {
@@ -89,7 +90,11 @@ w4a8_few_kernel(const __grid_constant__ FewMaps maps, const Args p) {
     live = live < p.M ? live : p.M;
     const int m0 = blockIdx.x * NB, n0 = blockIdx.y * C::TILE_N;
     if (m0 >= live) return;                                              // whole CTA, before any barrier or allocation
-    const int NSB = p.K / 256;
+    // this CTA's super-blocks: [b0, b0 + NSB) of the row's NSBT (K split over blockIdx.z: Q6_K only, see TmCfg's kernel)
+    const int NSBT = p.K / 256;
+    const bool split = KIND == KIND_Q6K && p.split > 1;
+    const int b0 = split ? (int)blockIdx.z * p.sb_per_split : 0;
+    const int NSB = split ? (b0 + p.sb_per_split < NSBT ? p.sb_per_split : NSBT - b0) : NSBT;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
@@ -138,13 +143,13 @@ w4a8_few_kernel(const __grid_constant__ FewMaps maps, const Args p) {
                 mbar_expect_tx(bar, C::TX_BYTES);
                 const uint32_t st = smem_u32(smem + stage * C::STAGE_BYTES);
                 if (KIND == KIND_Q4K) {
-                    tma_load_2d_hint(st, &maps.wq, b * 128, n0, bar, pol_w);
+                    tma_load_2d_hint(st, &maps.wq, (b0 + b) * 128, n0, bar, pol_w);
                 } else {
-                    tma_load_2d_hint(st, &maps.wq, b * 256, n0, bar, pol_w);
-                    tma_load_2d_hint(st + 64 * 128, &maps.wq, b * 256 + 128, n0, bar, pol_w);
+                    tma_load_2d_hint(st, &maps.wq, (b0 + b) * 256, n0, bar, pol_w);
+                    tma_load_2d_hint(st + 64 * 128, &maps.wq, (b0 + b) * 256 + 128, n0, bar, pol_w);
                 }
-                tma_load_2d(st + C::OFF_X, &maps.x, b * 256, m0, bar);
-                tma_load_2d(st + C::OFF_X + NB * 128, &maps.x, b * 256 + 128, m0, bar);
+                tma_load_2d(st + C::OFF_X, &maps.x, (b0 + b) * 256, m0, bar);
+                tma_load_2d(st + C::OFF_X + NB * 128, &maps.x, (b0 + b) * 256 + 128, m0, bar);
                 const int slot = b & (C::SCL_SLOTS - 1);
                 if (!mbar_wait(smem_u32(&aux->sempty[slot]), ((b / C::SCL_SLOTS) & 1) ^ 1, abort_flag, 0xE40 + slot)) {
                     ok = false;
@@ -154,14 +159,14 @@ w4a8_few_kernel(const __grid_constant__ FewMaps maps, const Args p) {
                 mbar_expect_tx(sbar, C::SCL_TX);
                 const uint32_t sdst = smem_u32(smem + C::OFF_SCL + slot * C::SCL_BYTES);
                 if (KIND == KIND_Q4K) {
-                    tma_load_2d(sdst, &maps.sc, n0 * 2, b, sbar);
-                    tma_load_2d(sdst + C::SOFF_MN, &maps.mn, n0 * 2, b, sbar);
-                    tma_load_2d(sdst + C::SOFF_D, &maps.d, n0, b, sbar);
-                    tma_load_2d(sdst + C::SOFF_DM, &maps.dm, n0, b, sbar);
-                    tma_load_2d(sdst + C::SOFF_XS, &maps.xs, m0 * 4, b, sbar);
+                    tma_load_2d(sdst, &maps.sc, n0 * 2, b0 + b, sbar);
+                    tma_load_2d(sdst + C::SOFF_MN, &maps.mn, n0 * 2, b0 + b, sbar);
+                    tma_load_2d(sdst + C::SOFF_D, &maps.d, n0, b0 + b, sbar);
+                    tma_load_2d(sdst + C::SOFF_DM, &maps.dm, n0, b0 + b, sbar);
+                    tma_load_2d(sdst + C::SOFF_XS, &maps.xs, m0 * 4, b0 + b, sbar);
                 } else {
-                    tma_load_2d(sdst, &maps.sc, n0 * 4, b, sbar);
-                    tma_load_2d(sdst + C::SOFF_D, &maps.d, n0, b, sbar);
+                    tma_load_2d(sdst, &maps.sc, n0 * 4, b0 + b, sbar);
+                    tma_load_2d(sdst + C::SOFF_D, &maps.d, n0, b0 + b, sbar);
                 }
                 if (++stage == C::STAGES) {
                     stage = 0;
@@ -296,7 +301,7 @@ w4a8_few_kernel(const __grid_constant__ FewMaps maps, const Args p) {
         bool ok = true;
         // lane l carries the activation scale of row m0 + (l & 15) of the coming super-block
         const int ml = m0 + (lane & 15);
-        float am_next = (NSB > 0 && ml < p.Ma) ? __ldg(p.a + ml) : 0.0f;
+        float am_next = (NSB > 0 && ml < p.Ma) ? __ldg(p.a + (long)b0 * p.Ma + ml) : 0.0f;
         if (KIND == KIND_Q4K) {
             const int n = n0 + nl;
             for (int b = 0; b < NSB; ++b) {
@@ -304,7 +309,7 @@ w4a8_few_kernel(const __grid_constant__ FewMaps maps, const Args p) {
                 const uint32_t aph = (b / FEW_SETS) & 1;
                 const int slot = b & (C::SCL_SLOTS - 1);
                 const float am_l = am_next;
-                if (b + 1 < NSB && ml < p.Ma) am_next = __ldg(p.a + (long)(b + 1) * p.Ma + ml);
+                if (b + 1 < NSB && ml < p.Ma) am_next = __ldg(p.a + (long)(b0 + b + 1) * p.Ma + ml);
                 if (!mbar_wait(smem_u32(&aux->sfull[slot]), (b / C::SCL_SLOTS) & 1, abort_flag, 0x1120 + slot) ||
                     !mbar_wait(smem_u32(&aux->acc_full[a]), aph, abort_flag, 0x1100 + a)) {
                     ok = false;
@@ -365,12 +370,14 @@ w4a8_few_kernel(const __grid_constant__ FewMaps maps, const Args p) {
             const bool upper = q >= 2;                                   // lanes 64-127: plane 1 of weight row nl - 64
             const int row = nl & 63;
             const int n = n0 + row;
+            const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+            float* ws_tile = split ? p.ws + (long)tile * NSBT * NB * 64 : nullptr;
             for (int b = 0; b < NSB; ++b) {
                 const int a = b & (FEW_SETS - 1);
                 const uint32_t aph = (b / FEW_SETS) & 1;
                 const int slot = b & (C::SCL_SLOTS - 1);
                 const float am_l = am_next;
-                if (b + 1 < NSB && ml < p.Ma) am_next = __ldg(p.a + (long)(b + 1) * p.Ma + ml);
+                if (b + 1 < NSB && ml < p.Ma) am_next = __ldg(p.a + (long)(b0 + b + 1) * p.Ma + ml);
                 if (!mbar_wait(smem_u32(&aux->acc_full[a]), aph, abort_flag, 0x1200 + a)) {
                     ok = false;
                     break;
@@ -408,7 +415,9 @@ w4a8_few_kernel(const __grid_constant__ FewMaps maps, const Args p) {
                         for (int j = 0; j < 8; ++j) {
                             const int acc = (int)pv[j] + 64 * (int)h8[j];
                             const float am = __shfl_sync(0xffffffffu, am_l, c0 + j);
-                            y[j] = __fmaf_rn(am, __fmul_rn(dv, __int2float_rn(acc)), y[j]);
+                            const float tb = __fmul_rn(dv, __int2float_rn(acc));
+                            if (split) ws_tile[((long)(b0 + b) * NB + c0 + j) * 64 + row] = tb;   // the chain runs later
+                            else y[j] = __fmaf_rn(am, tb, y[j]);
                         }
                     }
                     tc_fence_before();
@@ -417,6 +426,32 @@ w4a8_few_kernel(const __grid_constant__ FewMaps maps, const Args p) {
                         mbar_arrive(smem_u32(&aux->acc_empty[a]));
                         mbar_arrive(smem_u32(&aux->sempty[slot]));
                     }
+                }
+            }
+            if (split) {
+                // the hand-over of TmCfg's kernel: slices' terms in the workspace, the tile's last CTA runs the chain
+                __threadfence();
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (threadIdx.x == 320) {
+                    const int old = ok ? atomicAdd(p.counters + tile, 1) : -1;
+                    aux->is_last = (old == p.split - 1);
+                }
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                if (!aux->is_last) ok = false;
+                else {
+                    __threadfence();
+                    if (rows_live && !upper) {
+                        for (int b = 0; b < NSBT; ++b) {
+                            const float am_l = ml < p.Ma ? __ldg(p.a + (long)b * p.Ma + ml) : 0.0f;
+                            float tv[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) tv[j] = __ldcg(ws_tile + ((long)b * NB + c0 + j) * 64 + row);
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                y[j] = __fmaf_rn(__shfl_sync(0xffffffffu, am_l, c0 + j), tv[j], y[j]);
+                        }
+                    }
+                    if (threadIdx.x == 320) p.counters[tile] = 0;
                 }
             }
             if (ok && !upper && n < p.N) {
@@ -474,8 +509,11 @@ struct AuxTm {
     uint64_t acc_full[3], acc_empty[3];
     uint32_t tmem_base;
     int abort_flag;
+    int is_last;
 };
 
+// SPLIT: K split over blockIdx.z (two instantiations: the unsplit one keeps its registers for the fp32 chain).
+template <bool SPLIT>
 __global__ void __launch_bounds__(FEW_THREADS, 1)
 w4a8_few_q4k_tm_kernel(const __grid_constant__ FewMaps maps, const Args p) {
     using C = TmCfg;
@@ -489,7 +527,10 @@ w4a8_few_q4k_tm_kernel(const __grid_constant__ FewMaps maps, const Args p) {
     live = live < p.M ? live : p.M;
     const int m0 = blockIdx.x * NB, n0 = blockIdx.y * 128;
     if (m0 >= live) return;                                              // whole CTA, before any barrier or allocation
-    const int NSB = p.K / 256;
+    // this CTA's super-blocks: [b0, b0 + NSB) of the row's NSBT (all of them without a K split)
+    const int NSBT = p.K / 256;
+    const int b0 = SPLIT ? (int)blockIdx.z * p.sb_per_split : 0;
+    const int NSB = SPLIT ? (b0 + p.sb_per_split < NSBT ? p.sb_per_split : NSBT - b0) : NSBT;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::W_STAGES; ++s) {
@@ -532,7 +573,7 @@ w4a8_few_q4k_tm_kernel(const __grid_constant__ FewMaps maps, const Args p) {
                 }
                 const uint32_t wbar = smem_u32(&aux->wfull[ws]);
                 mbar_expect_tx(wbar, C::W_BYTES);
-                tma_load_2d_hint(smem_u32(smem + ws * C::W_BYTES), &maps.wq, b * 128, n0, wbar, pol_w);
+                tma_load_2d_hint(smem_u32(smem + ws * C::W_BYTES), &maps.wq, (b0 + b) * 128, n0, wbar, pol_w);
                 if (!mbar_wait(smem_u32(&aux->sempty[slot]), ph ^ 1, abort_flag, 0x1340 + slot)) {
                     ok = false;
                     break;
@@ -540,9 +581,9 @@ w4a8_few_q4k_tm_kernel(const __grid_constant__ FewMaps maps, const Args p) {
                 const uint32_t sbar = smem_u32(&aux->sfull[slot]);
                 mbar_expect_tx(sbar, C::SCL_TX);
                 const uint32_t sdst = smem_u32(smem + C::OFF_SCL + slot * C::SCL_BYTES);
-                tma_load_2d(sdst, &maps.x, b * 256, m0, sbar);
-                tma_load_2d(sdst + NB * 128, &maps.x, b * 256 + 128, m0, sbar);
-                tma_load_2d(sdst + C::SOFF_XS, &maps.xs, m0 * 4, b, sbar);
+                tma_load_2d(sdst, &maps.x, (b0 + b) * 256, m0, sbar);
+                tma_load_2d(sdst + NB * 128, &maps.x, (b0 + b) * 256 + 128, m0, sbar);
+                tma_load_2d(sdst + C::SOFF_XS, &maps.xs, m0 * 4, b0 + b, sbar);
             }
             if (!ok) {                                       // let armed copies land before the CTA can exit
                 unsigned long long t0 = global_timer_ns();
@@ -633,14 +674,14 @@ w4a8_few_q4k_tm_kernel(const __grid_constant__ FewMaps maps, const Args p) {
         for (int j = 0; j < 8; ++j) y[j] = 0.0f;
         bool ok = true;
         const int ml = m0 + (lane & 15);                                 // lane l carries the scale of activation row m0 + (l & 15)
-        float am_next = (NSB > 0 && ml < p.Ma) ? __ldg(p.a + ml) : 0.0f;
+        float am_next = (NSB > 0 && ml < p.Ma) ? __ldg(p.a + (long)b0 * p.Ma + ml) : 0.0f;
         const int n = n0 + nl;
         // this weight row's scales, one super-block ahead: sc, mn uint8 [K/256, N, 8]; d, dmin fp32 [K/256, N]
         const long nn = n < p.N ? n : 0;
-        const uint2* scp = (const uint2*)p.sc + nn;
-        const uint2* mnp = (const uint2*)p.mn + nn;
-        const float* dp = p.d + nn;
-        const float* dmp = p.dm + nn;
+        const uint2* scp = (const uint2*)p.sc + (long)b0 * p.N + nn;
+        const uint2* mnp = (const uint2*)p.mn + (long)b0 * p.N + nn;
+        const float* dp = p.d + (long)b0 * p.N + nn;
+        const float* dmp = p.dm + (long)b0 * p.N + nn;
         uint2 sc_next = make_uint2(0, 0), mn_next = make_uint2(0, 0);
         float d_next = 0.0f, dm_next = 0.0f;
         if (NSB > 0) {
@@ -649,6 +690,8 @@ w4a8_few_q4k_tm_kernel(const __grid_constant__ FewMaps maps, const Args p) {
             d_next = __ldg(dp);
             dm_next = __ldg(dmp);
         }
+        const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+        float* ws_tile = SPLIT ? p.ws + (long)tile * NSBT * NB * 128 : nullptr;
         int a = 0;
         uint32_t aph = 0;
         for (int b = 0; b < NSB; ++b) {
@@ -657,7 +700,7 @@ w4a8_few_q4k_tm_kernel(const __grid_constant__ FewMaps maps, const Args p) {
             const uint2 sc8 = sc_next, mn8 = mn_next;
             const float dv = d_next, ndm = -dm_next;
             if (b + 1 < NSB) {
-                if (ml < p.Ma) am_next = __ldg(p.a + (long)(b + 1) * p.Ma + ml);
+                if (ml < p.Ma) am_next = __ldg(p.a + (long)(b0 + b + 1) * p.Ma + ml);
                 sc_next = __ldg(scp + (long)(b + 1) * p.N);
                 mn_next = __ldg(mnp + (long)(b + 1) * p.N);
                 d_next = __ldg(dp + (long)(b + 1) * p.N);
@@ -688,10 +731,11 @@ w4a8_few_q4k_tm_kernel(const __grid_constant__ FewMaps maps, const Args p) {
                     const int mlo = __dp4a((int)mn8.x, (int)s16.x, __dp4a((int)mn8.y, (int)s16.y, 0));
                     const int mhi = __dp4a((int)mn8.x, (int)s16.z, __dp4a((int)mn8.y, (int)s16.w, 0));
                     const int mins = mlo + 64 * mhi;
-                    const float am = __shfl_sync(0xffffffffu, am_l, c0 + j);
+                    const float am = SPLIT ? 0.0f : __shfl_sync(0xffffffffu, am_l, c0 + j);
                     float t = __fmul_rn(dv, __int2float_rn(acc));
                     t = __fmaf_rn(ndm, __int2float_rn(mins), t);
-                    y[j] = __fmaf_rn(am, t, y[j]);
+                    if (SPLIT) ws_tile[((long)(b0 + b) * NB + c0 + j) * 128 + nl] = t;   // the chain runs later
+                    else y[j] = __fmaf_rn(am, t, y[j]);
                 }
             }
             tc_fence_before();
@@ -703,6 +747,33 @@ w4a8_few_q4k_tm_kernel(const __grid_constant__ FewMaps maps, const Args p) {
             if (++a == C::D_SETS) {
                 a = 0;
                 aph ^= 1;
+            }
+        }
+        if (SPLIT) {
+            // every epilogue thread takes part in the hand-over (the abort path too: it then reports not-last)
+            __threadfence();
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (threadIdx.x == 320) {
+                const int old = ok ? atomicAdd(p.counters + tile, 1) : -1;
+                aux->is_last = (old == p.split - 1);
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (!aux->is_last) ok = false;                               // another CTA finishes this tile
+            else {
+                __threadfence();
+                if (rows_live) {
+                    // the reference's chain, in super-block order, over every slice's terms (read from L2)
+                    for (int b = 0; b < NSBT; ++b) {
+                        const float am_l = ml < p.Ma ? __ldg(p.a + (long)b * p.Ma + ml) : 0.0f;
+                        float tv[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) tv[j] = __ldcg(ws_tile + ((long)b * NB + c0 + j) * 128 + nl);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            y[j] = __fmaf_rn(__shfl_sync(0xffffffffu, am_l, c0 + j), tv[j], y[j]);
+                    }
+                }
+                if (threadIdx.x == 320) p.counters[tile] = 0;
             }
         }
         if (ok && n < p.N) {

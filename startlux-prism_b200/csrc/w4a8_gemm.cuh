@@ -77,6 +77,11 @@ struct Args {
     const uint8_t* mn;
     const float* d;
     const float* dm;
+    // few-rows Q4_K kernel, K split over blockIdx.z: the slices leave their per-super-block terms t_b (exact, the same
+    // three roundings) in ws [tile][K/256][16][128]; the tile's last CTA runs the chain y = fma(a_b, t_b, y) in b order
+    int split, sb_per_split;
+    float* ws;
+    int* counters;
 };
 
 // K-major operand without swizzle: 8-row x 16-byte core matrices, `sbo` bytes between 8-row groups, `lbo` bytes

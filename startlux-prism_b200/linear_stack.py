@@ -74,6 +74,14 @@ class LinearStack:
         self.s_max = tp.MAX_SPLIT if M <= tp.SPLIT_ROWS else 1
         self.slots = self.parts[:self.s_max * M * hidden].view(self.s_max, M, hidden)
         self.n_rows = torch.tensor([M], dtype=torch.int32, device=device)
+        # several ranks and many rows: row-parallel projections run in row chunks so that a chunk's all-reduce overlaps
+        # the next chunk's GEMM
+        self.chunks = 4 if (n > 1 and M >= 2048 and M % 512 == 0) else 1
+        if self.chunks > 1:
+            self.comm = torch.cuda.Stream(device)
+            self.ev_g = [torch.cuda.Event() for _ in range(self.chunks)]
+            self.ev_c = [torch.cuda.Event() for _ in range(self.chunks)]
+            self.nr_chunk = [torch.tensor([M // self.chunks], dtype=torch.int32, device=device) for _ in range(self.chunks)]
 
     def __call__(self, h_in):
         """One pass: h_in fp32 [M, hidden] is copied into the working residual, which is returned (a view of an
@@ -101,6 +109,34 @@ class LinearStack:
         """A row-parallel projection into the residual: one rank adds in the GEMM's epilogue (or defers a K split to
         the fold); several ranks all-reduce int32 sums and fold."""
         w, w_s = wt
+        if self.n > 1 and self.chunks > 1:
+            return self._out_chunked(a, a_s, w, w_s)
         if self.n > 1:
             return tp.out_proj(self.g, a, a_s, w, w_s, self.parts, self.M, self.n_rows)
         return w8a8.gemm(a, a_s, w, w_s, self.h, self.n_rows, a.shape[1], epi=1, slots=self.slots)
+
+    def _out_chunked(self, a, a_s, w, w_s):
+        """Many rows on several ranks: the int32 all-reduce of a row chunk travels (on its own stream) while the next
+        chunk's GEMM runs; every chunk is folded into the residual as soon as its sums are back.  The integer sums and
+        the fold's roundings are those of the unchunked path: the same bits."""
+        comp, comm = torch.cuda.current_stream(), self.comm
+        rows = self.M // self.chunks
+
+        def gemm(i):
+            r0 = i * rows
+            w8a8.gemm_i32(a[r0:r0 + rows], a_s[r0:r0 + rows], w, w_s, self.slots[:1, r0:r0 + rows], self.nr_chunk[i],
+                          max_split=1)
+            self.ev_g[i].record(comp)
+        gemm(0)
+        for i in range(self.chunks):
+            r0 = i * rows
+            with torch.cuda.stream(comm):
+                comm.wait_event(self.ev_g[i])
+                self.g.sum_(self.slots[0, r0:r0 + rows])
+                self.ev_c[i].record(comm)
+            if i + 1 < self.chunks:
+                gemm(i + 1)
+            comp.wait_event(self.ev_c[i])
+            quant.fold(self.h[r0:r0 + rows], None, w8a8.Deferred(1, a_s[r0:r0 + rows], w_s, self.slots[:1, r0:r0 + rows]),
+                       self.nr_chunk[i], rows)
+        return None

@@ -124,9 +124,19 @@ def gemm_segs(xq, a, xs, segs, out, n_rows, epi=0, pdl=0):
         gemm(xq, a, xs, w, out[:, off:off + w.n], n_rows, epi, pdl=pdl)
 
 
+def pick_split(M, N, K, tile=128):
+    """K splits of the few-rows Q4_K kernel (M <= 16): one CTA per SM, so as many slices as fit the SMs over the weight
+    tiles, at least four super-blocks each.  Exact (the per-super-block terms meet in a workspace): always on."""
+    if M > 16:
+        return 1
+    tiles = -(-N // tile)
+    return max(1, min(8, 148 // tiles, (K // 256) // 4))
+
+
 def gemm(xq, a, xs, w: W4, out, n_rows, epi=0, cfg=None, pdl=0):
     """xq int8 [M, K], a fp32 [K/256, M], xs int8 [K/256, M, 16], w W4 [N, K] -> out [M, N]: bf16 (epi 0) or added
-    into fp32 (epi 1); out may be a column slice.  cfg and pdl are accepted for signature parity (one kernel shape)."""
+    into fp32 (epi 1); out may be a column slice.  cfg: None (pick) or the number of K splits of the few-rows Q4_K kernel
+    (Q4_K and Q6_K, M <= 16; exact: the same bits for every split); pdl is accepted for signature parity."""
     M, K = xq.shape
     _lib.need_cuda(xq, a, w.q, out, n_rows)
     if K != w.k or a.shape[0] != K // QK_K or not xq.is_contiguous() or not a.is_contiguous():
@@ -140,7 +150,18 @@ def gemm(xq, a, xs, w: W4, out, n_rows, epi=0, cfg=None, pdl=0):
     for t in (w.q, w.sc, w.mn, w.d, w.dm):
         if t is not None and not t.is_contiguous():
             raise RuntimeError("w4a8.gemm: W4 tensors must be contiguous (W4.rows copies the scales)")
+    split = pick_split(M, w.n, K, 128 if q4 else 64) if cfg is None else max(1, int(cfg))
+    ws = counters = None
+    if split > 1 and M <= 16:
+        from . import w8a8 as KW
+        ws, counters = KW._workspace(xq.device)
+        if _lib.lib().pb_w4a8_workspace_bytes(M, w.n, K) > ws.numel():
+            split, ws, counters = 1, None, None
+    else:
+        split = 1
     rc = _lib.lib().pb_w4a8_gemm(_lib.ptr(xq), _lib.ptr(a), _lib.ptr(xs) if q4 else None, a.shape[1], 0 if q4 else 1,
                                  _lib.ptr(w.q), _lib.ptr(w.sc), _lib.ptr(w.mn), _lib.ptr(w.d), _lib.ptr(w.dm),
-                                 _lib.ptr(out), out.stride(0), _lib.ptr(n_rows), M, w.n, K, epi, _lib.stream())
+                                 _lib.ptr(out), out.stride(0), _lib.ptr(n_rows), M, w.n, K, epi, split, _lib.ptr(ws),
+                                 0 if ws is None else ws.numel(), _lib.ptr(counters),
+                                 0 if counters is None else counters.numel(), _lib.stream())
     _lib.check(rc, f"w4a8 gemm {w.kind} M={M} N={w.n} K={K} epi={epi}")

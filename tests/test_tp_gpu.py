@@ -64,7 +64,7 @@ def _run(cmd, env=None):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
 
 
-@pytest.mark.parametrize("rows", [1, 64, 700])
+@pytest.mark.parametrize("rows", [1, 64, 700, 2048])
 def test_real_ranks_bit_identical(dev, tmp_path, rows):
     n = torch.cuda.device_count()
     if n < 2:

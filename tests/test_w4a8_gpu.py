@@ -42,6 +42,16 @@ def test_gemm_bits(dev, kind, m, live, n, k):
     res = base.to(dev)
     w4a8.gemm(xqd, ad, xsd, wd, res, nr, epi=1)
     assert same(res, ref1), first_diff(res.cpu().numpy(), ref1)
+    if m <= 16:
+        # K splits of the few-rows kernel leave the chain's terms in a workspace and one CTA adds them in order: the
+        # same bits for every split
+        for cfg in (1, 2, 5):
+            out = torch.zeros(m, n, dtype=torch.bfloat16, device=dev)
+            w4a8.gemm(xqd, ad, xsd, wd, out, nr, epi=0, cfg=cfg)
+            assert same(out, bf16_from_bits(ref0)), (cfg, first_diff(np_bits(out), ref0))
+            res = base.to(dev)
+            w4a8.gemm(xqd, ad, xsd, wd, res, nr, epi=1, cfg=cfg)
+            assert same(res, ref1), (cfg, first_diff(res.cpu().numpy(), ref1))
     # the quantized product stays close to the unquantized one (tests/test_w4a8.py:73-75: a few per cent)
     kq = synth.q4_k(wf) if kind == "q4k" else synth.q6_k(wf)
     true = x[:live].float() @ kq.dequant().T
