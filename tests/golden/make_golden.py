@@ -23,7 +23,9 @@ import types
 os.environ["TRITON_INTERPRET"] = "1"
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2:
+    raise SystemExit("usage: make_golden.py <path to a StartLux-Prism checkout>")
+REF = sys.argv[1]
 sys.path.insert(0, ROOT)
 sys.path.insert(0, REF)
 sys.path.insert(0, os.path.join(REF, "tests"))

@@ -126,7 +126,7 @@ def test_graph_replay_live_rows(dev):
 
 
 def test_config0_synthetic(dev):
-    """BASELINE config 0: Q8_0 weights [5120, 5120] ~ N(0, 0.02^2), bf16 activations [16, 5120] with 8 outlier
+    """The reference's own CPU-runnable case: Q8_0 weights [5120, 5120] ~ N(0, 0.02^2), bf16 activations [16, 5120] with 8 outlier
     channels, per-token int8, per-32 block scales, bf16 out."""
     from prism_b200 import synth
     q8 = synth.q8_0(synth.weights(5120, 5120, synth.seed_w(0, 1)))
