@@ -227,6 +227,7 @@ def run_gpu(args):
         print(json.dumps(line), flush=True)
     if group is not None:
         sync()
+        stack.close()
         group.close()
 
 
@@ -238,12 +239,13 @@ def launches_per_step(world):
 
 
 def time_gemms(stack, h0, steps):
-    """Sum of the GEMM kernels' durations per step: CUDA events around each w8a8.gemm call of a pass."""
+    """Sum of the GEMM kernels' durations per step: CUDA events around each w8a8.gemm / gemm_i32 / gemm_scatter call of
+    a pass."""
     import torch
 
     from prism_b200 import w8a8
     events = []
-    orig, orig_i32 = w8a8.gemm, w8a8.gemm_i32
+    orig, orig_i32, orig_sc = w8a8.gemm, w8a8.gemm_i32, w8a8.gemm_scatter
 
     def wrap(fn):
         def timed(*a, **k):
@@ -254,13 +256,13 @@ def time_gemms(stack, h0, steps):
             events.append((s, e))
             return r
         return timed
-    w8a8.gemm, w8a8.gemm_i32 = wrap(orig), wrap(orig_i32)
+    w8a8.gemm, w8a8.gemm_i32, w8a8.gemm_scatter = wrap(orig), wrap(orig_i32), wrap(orig_sc)
     try:
         for _ in range(steps):
             stack(h0)
         torch.cuda.synchronize()
     finally:
-        w8a8.gemm, w8a8.gemm_i32 = orig, orig_i32
+        w8a8.gemm, w8a8.gemm_i32, w8a8.gemm_scatter = orig, orig_i32, orig_sc
     return sum(s.elapsed_time(e) for s, e in events) / steps
 
 
@@ -529,7 +531,7 @@ def run_probe(args):
         fn = lambda: w8a8.gemm(a, sa, w, sw, out, nr, gk, epi=epi, slots=slots)                   # noqa: E731
         ops, nbytes = 2.0 * M * N * K, N * K + M * K
     elif case in ("w4a8_q4k", "w4a8_q6k", "w4a8_q4k_decode", "w4a8_q6k_decode"):
-        M, N, K = (16, 34816, 5120) if case.endswith("decode") else (2048, 8192, 5120)
+        M, N, K = (args.probe_rows or 16, 34816, 5120) if case.endswith("decode") else (2048, 8192, 5120)
         wcpu = synth.weights(N, K, 3)
         w = w4a8.repack((synth.q4_k if "q4k" in case else synth.q6_k)(wcpu)).to(dev)
         x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
@@ -653,6 +655,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
     ap.add_argument("--detail", action="store_true", help="per-shape GEMM table instead of the JSON line")
     ap.add_argument("--probe", default=None, help="one kernel case, a few eager launches (for ncu)")
+    ap.add_argument("--probe-rows", type=int, default=None, help="activation rows of the W4A8 decode probes")
     ap.add_argument("--detail-rows", default=None)
     ap.add_argument("--detail-head", action="store_true", help="add the vocabulary head (head_q8) to --detail")
     ap.add_argument("--detail-shapes", default=None)

@@ -60,6 +60,23 @@ int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float
                  const int* n_rows, int M, int N, int K, int gk, int epi, int split, long slot_stride,
                  void* workspace, long workspace_bytes, int* counters, int n_counters, int pdl, void* stream);
 
+/* The int32 partial sums of a row-parallel projection on several GPUs, stored where they will be folded: output rows
+ * [o * block_rows, (o + 1) * block_rows) go to blocks[o] (int32 [block_rows, N], row stride ldo), which may be another
+ * GPU's memory (pb_peer_open): the tile kernel's epilogue stores over NVLink as each tile is drained, so the exchange
+ * of tp.out_proj (tp.py:159-180: gemm_i32, then an int32 all-reduce) overlaps the GEMM and moves half the bytes (each
+ * sum travels once, to the rank that folds it).  The receiving rank adds the ranks' blocks with pb_fold (S = ranks),
+ * after a barrier over the ranks.  M > 64, block_rows % 128 == 0, n_blocks <= 8, n_blocks * block_rows >= M. */
+int pb_w8a8_gemm_scatter(const int8_t* a, const int8_t* w, void* const* blocks, int n_blocks, int block_rows, long ldo,
+                         const int* n_rows, int M, int N, int K, void* stream);
+
+/* Device memory other processes can map: pb_peer_alloc allocates (zeroed) and writes a 64-byte handle to pass to the
+ * other ranks (any host channel); pb_peer_open maps another rank's handle on the current device with peer access
+ * enabled (the role of the reference's symmetric-memory rendezvous, tp.py:381-403); pb_peer_close / pb_peer_free undo. */
+int pb_peer_alloc(long bytes, void** ptr, void* handle64);
+int pb_peer_open(const void* handle64, void** ptr);
+int pb_peer_close(void* ptr);
+int pb_peer_free(void* ptr);
+
 /* Deferred residual add.  Replaces quant.fold / _fold_kernel (kernels/quant.py:128-141, :434-457):
  * h[r, c] = add_rn(h[r, c], mul_rn(mul_rn(float(sum_p slots[p, r, c]), a_s[r]), w_s[c])).  N % 4 == 0, 16-byte aligned. */
 int pb_fold(float* h, long ldh, const int32_t* slots, long slot_stride, int S, const float* a_s, const float* w_s,

@@ -18,6 +18,11 @@ _SIGS = {
     "pb_w8a8_workspace_bytes": ([_i, _i, _i], _l),
     "pb_w8a8_counters": ([_i, _i], _i),
     "pb_w8a8_gemm": ([_vp, _vp, _vp, _vp, _vp, _l, _vp, _i, _i, _i, _i, _i, _i, _l, _vp, _l, _vp, _i, _i, _vp], _i),
+    "pb_w8a8_gemm_scatter": ([_vp, _vp, _vp, _i, _i, _l, _vp, _i, _i, _i, _vp], _i),
+    "pb_peer_alloc": ([_l, _vp, _vp], _i),
+    "pb_peer_open": ([_vp, _vp], _i),
+    "pb_peer_close": ([_vp], _i),
+    "pb_peer_free": ([_vp], _i),
     "pb_fold": ([_vp, _l, _vp, _l, _i, _vp, _vp, _vp, _i, _i, _vp], _i),
     "pb_quant_rows": ([_vp, _i, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp], _i),
     "pb_swiglu_q8": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp], _i),

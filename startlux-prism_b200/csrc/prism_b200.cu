@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdlib.h>
+#include <string.h>
 
 #include <mutex>
 #include <unordered_map>
@@ -15,6 +16,7 @@
 #include "w8a8_gemm.cuh"
 #include "w4a8_gemm.cuh"
 #include "w4a8_few.cuh"
+#include "w4a8_gemv.cuh"
 #include "mxfp4_gemm.cuh"
 
 namespace {
@@ -142,7 +144,7 @@ int add_mode() {
 template <int BN, int EPI>
 int launch_tile(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, void* out, long ldo,
                 const int* n_rows, int M, int N, int K, cudaStream_t st, int split = 1, void* workspace = nullptr,
-                int* counters = nullptr) {
+                int* counters = nullptr, const w8a8::RowBlocks* blocks = nullptr) {
     using C = w8a8::TileCfg<BN>;
     CUtensorMap ta, tw;
     int rc;
@@ -172,8 +174,10 @@ int launch_tile(const int8_t* a, const float* a_s, const int8_t* w, const float*
     const int kbs = (KB + split - 1) / split;
     const int units = ((M + 127) / 128) * ((N + BN - 1) / BN) * split;
     const int grid = units < sm_count() ? units : sm_count();
+    w8a8::RowBlocks rb{};
+    if (blocks) rb = *blocks;
     kern<<<grid, w8a8::TileWarps<EPI>::THREADS, smem, st>>>(ta, tw, tout, a_s, w_s, out, ldo, n_rows, M, N, K, word_ok,
-                                                           split, kbs, (int32_t*)workspace, counters);
+                                                           split, kbs, (int32_t*)workspace, counters, rb);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }
@@ -391,6 +395,34 @@ int launch_w4a8_few(const int8_t* xq, const float* a, const int8_t* xs, int Ma, 
     kern<<<grid, w4a8::FEW_THREADS, C::SMEM, st>>>(m, p);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
+}
+
+// One to four activation rows: integer dot products on the CUDA cores (w4a8_gemv.cuh).
+template <int MR>
+int launch_w4a8_gemv(int kind, const w4a8::GemvArgs& p, cudaStream_t st) {
+    constexpr int R = w4a8::GEMV_R;
+    const int grid = (p.N + 4 * R - 1) / (4 * R);                  // eight weight rows per CTA
+    // few rows: four warps per CTA share the rows' super-blocks (exact: the chain runs in order afterwards)
+    const size_t smem = (size_t)(p.K >> 8) * 4 * R * MR * sizeof(float);
+    if (grid < 8 * sm_count() && smem <= 48 * 1024) {
+        if (kind == 0) w4a8::w4a8_gemv_q4k_kernel<MR, R, 4><<<grid, 128, smem, st>>>(p);
+        else w4a8::w4a8_gemv_q6k_kernel<MR, R, 4><<<grid, 128, smem, st>>>(p);
+    } else {
+        if (kind == 0) w4a8::w4a8_gemv_q4k_kernel<MR, R, 1><<<grid, 32, 0, st>>>(p);
+        else w4a8::w4a8_gemv_q6k_kernel<MR, R, 1><<<grid, 32, 0, st>>>(p);
+    }
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+// PRISM_B200_W4A8_NO_GEMV=1 keeps the tensor-core kernels for one to four rows (comparison runs).
+bool w4a8_no_gemv() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("PRISM_B200_W4A8_NO_GEMV");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
 }
 
 // Row-pipelined quantizers (quant_pipe.cuh): persistent CTAs, rows staged in shared memory by bulk copies.
@@ -649,6 +681,66 @@ int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float
     return launch_swap_nb<false>(nb, a, a_s, w, w_s, p, split, st);
 }
 
+int pb_w8a8_gemm_scatter(const int8_t* a, const int8_t* w, void* const* blocks, int n_blocks, int block_rows, long ldo,
+                         const int* n_rows, int M, int N, int K, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!a || !w || !blocks || !n_rows || M <= 0 || N <= 0 || K <= 0) return PB_BAD_ARGUMENT;
+    if (n_blocks < 1 || n_blocks > 8 || block_rows <= 0 || (long)n_blocks * block_rows < M) return PB_BAD_ARGUMENT;
+    if (block_rows % 128) return PB_UNSUPPORTED_SHAPE;             // a tile lies in one block
+    if (M <= 64) return PB_UNSUPPORTED_SHAPE;                      // the many-rows kernel only
+    if (!aligned16(a) || !aligned16(w) || ldo < N) return PB_BAD_ARGUMENT;
+    if (K % 16) return PB_UNSUPPORTED_SHAPE;
+    w8a8::RowBlocks rb{};
+    for (int i = 0; i < n_blocks; ++i) {
+        if (!blocks[i] || !aligned16(blocks[i])) return PB_BAD_ARGUMENT;
+        rb.base[i] = blocks[i];
+    }
+    rb.rows = block_rows;
+    const bool narrow = N <= 128 || tile_bn(M, N) == 128;
+    return narrow ? launch_tile<128, w8a8::EPI_I32>(a, nullptr, w, nullptr, blocks[0], ldo, n_rows, M, N, K, st, 1, nullptr, nullptr, &rb)
+                  : launch_tile<256, w8a8::EPI_I32>(a, nullptr, w, nullptr, blocks[0], ldo, n_rows, M, N, K, st, 1, nullptr, nullptr, &rb);
+}
+
+// Device memory that other processes' GPUs can store into (CUDA IPC; peer access over NVLink).
+int pb_peer_alloc(long bytes, void** ptr, void* handle64) {
+    if (bytes <= 0 || !ptr || !handle64) return PB_BAD_ARGUMENT;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    void* p = nullptr;
+    PB_CUDA(cudaMalloc(&p, (size_t)bytes));
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaMemset(p, 0, (size_t)bytes);
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) {
+        cudaFree(p);
+        PB_CUDA(e);
+    }
+    memcpy(handle64, &h, 64);
+    *ptr = p;
+    return PB_OK;
+}
+
+int pb_peer_open(const void* handle64, void** ptr) {
+    if (!handle64 || !ptr) return PB_BAD_ARGUMENT;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, 64);
+    void* p = nullptr;
+    PB_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *ptr = p;
+    return PB_OK;
+}
+
+int pb_peer_close(void* ptr) {
+    if (!ptr) return PB_BAD_ARGUMENT;
+    PB_CUDA(cudaIpcCloseMemHandle(ptr));
+    return PB_OK;
+}
+
+int pb_peer_free(void* ptr) {
+    if (!ptr) return PB_BAD_ARGUMENT;
+    PB_CUDA(cudaFree(ptr));
+    return PB_OK;
+}
+
 int pb_fold(float* h, long ldh, const int32_t* slots, long slot_stride, int S, const float* a_s, const float* w_s,
             const int* n_rows, int rows, int N, void* stream) {
     if (!h || !slots || !a_s || !w_s || !n_rows || rows <= 0 || N <= 0 || S < 1 || ldh < N) return PB_BAD_ARGUMENT;
@@ -860,6 +952,13 @@ int pb_w4a8_gemm(const int8_t* xq, const float* a, const int8_t* xs, int Ma, int
     if (K % 256 || N % 4 || ldo < N) return PB_UNSUPPORTED_SHAPE;
     if (!aligned16(xq) || !aligned16(wq) || !aligned16(wsc) || !aligned16(wd) || (kind == 0 && (!aligned16(xs) ||
         !aligned16(wmn) || !aligned16(wdm)))) return PB_BAD_ARGUMENT;
+    if (M <= 4 && !w4a8_tile_only() && !w4a8_no_gemv()) {
+        w4a8::GemvArgs g{xq, a, xs, (const uint8_t*)wq, (const uint8_t*)wsc, (const uint8_t*)wmn, wd, wdm, out, ldo, n_rows, M, N,
+                         K, Ma, epi};
+        if (M == 1) return launch_w4a8_gemv<1>(kind, g, st);
+        if (M == 2) return launch_w4a8_gemv<2>(kind, g, st);
+        return launch_w4a8_gemv<4>(kind, g, st);
+    }
     if (M <= 32 && !w4a8_tile_only()) {                            // measured: the many-rows kernel is faster from 64 rows
         if (kind == 0) {
             // K split (exact): Q4_K through tensor memory, one tile of 16 rows

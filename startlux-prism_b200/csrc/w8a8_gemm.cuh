@@ -404,6 +404,15 @@ struct TileCfg {
     static constexpr int SMEM_ADD = 1024 + (STAGES * STAGE_BYTES + (int)sizeof(Aux) + BN * 4 + 1023) / 1024 * 1024 + 8 * 32 * 32 * 4;
 };
 
+// Row blocks of an int32 output that live in different buffers (a row-parallel projection on several GPUs: the rows
+// another GPU will fold go straight into that GPU's memory, peer stores over NVLink, as each tile is drained).  Block
+// o covers output rows [o * rows, (o + 1) * rows) and starts at base[o]; rows is a multiple of the tile height, so a
+// tile never straddles two blocks.  rows == 0: one buffer (`out`).
+struct RowBlocks {
+    void* base[8];
+    int rows;
+};
+
 // Epilogue warps: four (one per tensor-memory lane quarter), eight for the residual add (two per quarter, half the
 // columns each: its global round trips are what the main loop must hide).
 template <int EPI>
@@ -417,7 +426,7 @@ __global__ void __launch_bounds__(TileWarps<EPI>::THREADS, 1)
 w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                  const __grid_constant__ CUtensorMap tm_out, const float* __restrict__ a_s, const float* __restrict__ w_s, void* __restrict__ out, long ldo,
                  const int* __restrict__ n_rows, int M, int N, int K, int word_ok, int split, int kb_per_split,
-                 int32_t* __restrict__ ws, int* __restrict__ counters) {
+                 int32_t* __restrict__ ws, int* __restrict__ counters, const __grid_constant__ RowBlocks rb) {
     using C = TileCfg<BN>;
     using W = TileWarps<EPI>;
     extern __shared__ uint8_t smem_raw[];
@@ -557,6 +566,13 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             const int t = u / split, z = u - t * split;
             const int m0 = (n_fastest ? t / num_n : t % num_m) * BM, n0 = (n_fastest ? t % num_n : t / num_m) * BN;
             float* swb = sw_stash + (EPI == EPI_ADD ? 0 : buf * BN);
+            void* out_t = out;
+            if (EPI == EPI_I32 && rb.rows > 0) {
+                // this tile's row block: its buffer, moved back by the block's first row so that the global row
+                // index addresses it
+                const int o = m0 / rb.rows;
+                out_t = (int32_t*)rb.base[o] - (long)o * rb.rows * ldo;
+            }
             if (EPI == EPI_ADD) {
                 // one scale stash: everyone must be done with the previous tile's before it is rewritten
                 asm volatile("bar.sync 1, %0;" ::"n"(ET) : "memory");
@@ -610,7 +626,7 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 if (aux->is_last) {
                     __threadfence();
                     const int cb = EPI == EPI_ADD ? half * (BN / 2) : 0, ce = EPI == EPI_ADD ? (half + 1) * (BN / 2) : BN;
-                    reduce_store<BN, EPI>(out, ldo, N, live, m0, n0, q, lane, ws_tile, (long)BM * BN, split, swb, sa, cb,
+                    reduce_store<BN, EPI>(out_t, ldo, N, live, m0, n0, q, lane, ws_tile, (long)BM * BN, split, swb, sa, cb,
                                           ce);
                     if (et == 0) counters[t] = 0;
                 }
@@ -632,7 +648,7 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                           (half + 1) * (BN / 2));
             } else {
                 uint32_t* stg = stage_buf + q * (32 * 33);
-                drain_accumulator<BN, EPI>(out, ldo, N, live, m0, n0, q, lane, lane_addr, stg, swb, sa, (word_ok & 1) != 0);
+                drain_accumulator<BN, EPI>(out_t, ldo, N, live, m0, n0, q, lane, lane_addr, stg, swb, sa, (word_ok & 1) != 0);
             }
             tc_fence_before();
             __syncwarp();
@@ -642,6 +658,7 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         }
         // reductions still in flight read this CTA's shared memory: they complete before the CTA ends
         if (EPI == EPI_ADD && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (EPI == EPI_I32 && rb.rows > 0) __threadfence_system();   // stores into other GPUs' memory
     }
     tc_fence_before();
     __syncthreads();

@@ -5,7 +5,9 @@ tensor-parallel identity tests.  Per layer, on an fp32 residual stream h [M, hid
     q|k|v  GEMM, column-parallel      -> bf16 [M, 7168 / n]
     mixer stand-in                    -> this rank's q columns of that output (attention itself is not on the path)
     quantize_rows(rows_q8)            -> int8, scale from the row maximum over all ranks
-    o      GEMM, row-parallel         -> h += ...   (one rank: fused residual epilogue; more: int32 sums, all-reduce, fold)
+    o      GEMM, row-parallel         -> h += ...   (one rank: fused residual epilogue; more: int32 sums, all-reduce, fold;
+                                                     more ranks and many rows: reduce-scatter, the residual stream split
+                                                     by rows until the next projection's int8 input is all-gathered)
     rows_q8(h)                        -> int8 input of gate|up
     gate|up GEMM, column-parallel     -> bf16 [M, 34816 / n]
     quantize_rows(swiglu_q8)          -> int8 [M, 17408 / n]
@@ -14,6 +16,8 @@ tensor-parallel identity tests.  Per layer, on an fp32 residual stream h [M, hid
 Weights are quantized whole (Q8_0 -> one scale per output row) and sliced afterwards, so every rank count computes the
 single-GPU bits.  All buffers are allocated at construction; a pass allocates nothing and can be graph-captured.
 """
+import os
+
 import torch
 
 from . import quant, synth, tp, w8a8
@@ -74,20 +78,40 @@ class LinearStack:
         self.s_max = tp.MAX_SPLIT if M <= tp.SPLIT_ROWS else 1
         self.slots = self.parts[:self.s_max * M * hidden].view(self.s_max, M, hidden)
         self.n_rows = torch.tensor([M], dtype=torch.int32, device=device)
-        # several ranks and many rows: row-parallel projections run in row chunks so that a chunk's all-reduce overlaps
-        # the next chunk's GEMM
-        self.chunks = 4 if (n > 1 and M >= 2048 and M % 512 == 0) else 1
-        if self.chunks > 1:
-            self.comm = torch.cuda.Stream(device)
-            self.ev_g = [torch.cuda.Event() for _ in range(self.chunks)]
-            self.ev_c = [torch.cuda.Event() for _ in range(self.chunks)]
-            self.nr_chunk = [torch.tensor([M // self.chunks], dtype=torch.int32, device=device) for _ in range(self.chunks)]
+        # several ranks and many rows: the residual stream stays split by rows between the projections (each rank
+        # folds, normalises and quantizes M / n rows), a row-parallel projection's int32 sums are reduce-scattered and
+        # the int8 rows of the next projection's input all-gathered: 5/8 of an all-reduce's bytes, and 1 / n of the
+        # quantizer work per rank.  PRISM_B200_TP_ALLREDUCE=1 keeps the all-reduce path at every size.
+        self.by_rows = (n > 1 and M % n == 0 and M // n >= 64 and os.environ.get("PRISM_B200_TP_ALLREDUCE", "0") != "1")
+        if self.by_rows:
+            self.Ml = M // n
+            self.r0 = group.rank * self.Ml
+            self.own = e(1, self.Ml, hidden, dtype=torch.int32)
+            self.nr_own = torch.tensor([self.Ml], dtype=torch.int32, device=device)
+        # ... and the reduce-scatter itself disappears into the GEMM: every rank's tile kernel stores the rows another
+        # rank will fold straight into that rank's memory (peer stores over NVLink, tile by tile), the fold adds the n
+        # ranks' blocks.  Needs own-row blocks of whole tiles and CUDA IPC between the ranks; otherwise (or with
+        # PRISM_B200_TP_FUSED=0) NCCL's reduce-scatter.
+        self.peer = None
+        if (self.by_rows and self.Ml % 128 == 0 and n <= 8 and group.backend == "nccl"
+                and os.environ.get("PRISM_B200_TP_FUSED", "1") != "0"):
+            peer = tp.PeerBuffer(group, n * self.Ml * hidden * 4)
+            if peer.ok:
+                self.peer = peer
+                self.sym = peer.tensor(torch.int32, (n, self.Ml, hidden))
+                mine = group.rank * self.Ml * hidden * 4               # this rank's block inside every rank's buffer
+                self.blocks = [p + mine for p in peer.ptrs]
+                self.token = torch.zeros(1, dtype=torch.int32, device=device)
+            elif group.rank == 0:
+                print(f"prism_b200: peer memory unavailable ({peer.error}); NCCL reduce-scatter instead", flush=True)
 
     def __call__(self, h_in):
         """One pass: h_in fp32 [M, hidden] is copied into the working residual, which is returned (a view of an
         internal buffer, overwritten by the next pass)."""
         M, nr, g = self.M, self.n_rows, self.g
         self.h.copy_(h_in, non_blocking=True)
+        if self.by_rows:
+            return self._pass_by_rows()
         pend = None
         for lw in self.layers:
             quant.fold(self.h, self.slots, pend, nr, M)
@@ -105,38 +129,53 @@ class LinearStack:
         quant.fold(self.h, self.slots, pend, nr, M)
         return self.h
 
+    def close(self):
+        if self.peer is not None:
+            self.peer.close()
+            self.peer = None
+
     def _out(self, a, a_s, wt):
         """A row-parallel projection into the residual: one rank adds in the GEMM's epilogue (or defers a K split to
         the fold); several ranks all-reduce int32 sums and fold."""
         w, w_s = wt
-        if self.n > 1 and self.chunks > 1:
-            return self._out_chunked(a, a_s, w, w_s)
         if self.n > 1:
             return tp.out_proj(self.g, a, a_s, w, w_s, self.parts, self.M, self.n_rows)
         return w8a8.gemm(a, a_s, w, w_s, self.h, self.n_rows, a.shape[1], epi=1, slots=self.slots)
 
-    def _out_chunked(self, a, a_s, w, w_s):
-        """Many rows on several ranks: the int32 all-reduce of a row chunk travels (on its own stream) while the next
-        chunk's GEMM runs; every chunk is folded into the residual as soon as its sums are back.  The integer sums and
-        the fold's roundings are those of the unchunked path: the same bits."""
-        comp, comm = torch.cuda.current_stream(), self.comm
-        rows = self.M // self.chunks
+    def _pass_by_rows(self):
+        """Several ranks, many rows.  Between a row-parallel projection and the next column-parallel one every rank
+        works on its own M / n rows of the residual stream: int32 partial sums -> reduce-scatter -> fold into the own
+        rows -> quantize them -> all-gather the int8 rows and their scales.  Every element sees the operations of the
+        one-GPU pass in the same order (exact integer sums, the same fold and quantizer roundings): the same bits."""
+        M, nr, g, Ml, r0 = self.M, self.n_rows, self.g, self.Ml, self.r0
+        h_own, xq_own, xs_own = self.h[r0:r0 + Ml], self.xq[r0:r0 + Ml], self.xs[r0:r0 + Ml]
+        pend = None
 
-        def gemm(i):
-            r0 = i * rows
-            w8a8.gemm_i32(a[r0:r0 + rows], a_s[r0:r0 + rows], w, w_s, self.slots[:1, r0:r0 + rows], self.nr_chunk[i],
-                          max_split=1)
-            self.ev_g[i].record(comp)
-        gemm(0)
-        for i in range(self.chunks):
-            r0 = i * rows
-            with torch.cuda.stream(comm):
-                comm.wait_event(self.ev_g[i])
-                self.g.sum_(self.slots[0, r0:r0 + rows])
-                self.ev_c[i].record(comm)
-            if i + 1 < self.chunks:
-                gemm(i + 1)
-            comp.wait_event(self.ev_c[i])
-            quant.fold(self.h[r0:r0 + rows], None, w8a8.Deferred(1, a_s[r0:r0 + rows], w_s, self.slots[:1, r0:r0 + rows]),
-                       self.nr_chunk[i], rows)
-        return None
+        def gathered_input():
+            quant.fold(h_own, None, pend, self.nr_own, Ml)
+            quant.rows_q8(h_own, None, xq_own, xs_own, self.nr_own, Ml)
+            g.gather_(self.xq, xq_own)
+            g.gather_(self.xs, xs_own)
+
+        def out(a, a_s, wt):
+            w, w_s = wt
+            if self.peer is not None:
+                w8a8.gemm_scatter(a, w, self.blocks, Ml, self.hidden, nr)
+                g.sum_(self.token)                 # a barrier: every rank's stores have landed before anyone folds
+                return w8a8.Deferred(self.n, a_s[r0:r0 + Ml], w_s, self.sym)
+            w8a8.gemm_i32(a, a_s, w, w_s, self.slots[:1], nr, max_split=1)
+            g.scatter_sum_(self.own[0], self.slots[0])
+            return w8a8.Deferred(1, a_s[r0:r0 + Ml], w_s, self.own)
+
+        for lw in self.layers:
+            gathered_input()
+            w8a8.gemm(self.xq, self.xs, *lw["qkv"], self.qkv, nr, self.hidden)
+            tp.quantize_rows(g, quant.rows_q8, M, self.amax, self.qkv[:, :self.ql], None, self.aq, self.as_, nr, M)
+            pend = out(self.aq, self.as_, lw["o"])
+            gathered_input()
+            w8a8.gemm(self.xq, self.xs, *lw["gate_up"], self.gu, nr, self.hidden)
+            tp.quantize_rows(g, quant.swiglu_q8, M, self.amax, self.gu, None, self.dq, self.ds, nr, M)
+            pend = out(self.dq, self.ds, lw["down"])
+        quant.fold(h_own, None, pend, self.nr_own, Ml)
+        g.gather_(self.h, h_own)
+        return self.h

@@ -3,6 +3,9 @@ projection, one process per GPU over torch.distributed (NCCL over NVLink; gloo o
 
     shard_config(cfg, n), shard_index(cfg, n, r)     which rows / columns a rank holds          (tp.py:83-125)
     Group(rank, world, ...)                          process group: sum_, max_                   (tp.py:333-357, :435-439)
+                                                     scatter_sum_, gather_: the two halves of an all-reduce, for passes
+                                                     that keep the residual stream split by rows between them
+    PeerBuffer(g, nbytes)                            device memory the other ranks' kernels store into  (tp.py:381-403)
     quantize_rows(g, fn, rows, amax, *args)          global row maximum before quantizing        (tp.py:143-156)
     out_proj(g, a, a_s, w, w_s, flat, rows, n_rows)  int32 partial sums -> all-reduce -> Deferred (tp.py:159-180)
 
@@ -13,7 +16,8 @@ the max over all ranks (exact).  Outputs are therefore bit-identical at every GP
 reference's in-kernel protocols (4 ranks at most) nothing here depends on the group size.
 
 Not built (engine orchestration, outside the linear-layer path): the shared-memory channel to follower processes, the
-mirrored-object RPC, the fused in-kernel exchanges over symmetric memory (quant.Sync).
+mirrored-object RPC, the reference's fused in-kernel exchanges for a few rows (quant.Sync: flag words and peer reads
+inside the fold; this build's fused exchange is the many-rows one, w8a8.gemm_scatter).
 """
 from __future__ import annotations
 
@@ -117,6 +121,34 @@ class Group:
         if self.world > 1:
             dist.all_reduce(x, op=dist.ReduceOp.MAX, group=self.pg)
 
+    def scatter_sum_(self, own, x):
+        """own [rows / world, ...] = this rank's row block of the sum of x [rows, ...] over the ranks (reduce-scatter:
+        half an all-reduce's traffic).  gloo has no reduce-scatter: all-reduce a copy and slice."""
+        if self.world == 1:
+            own.copy_(x)
+        elif self.backend == "nccl":
+            dist.reduce_scatter_tensor(own, x, op=dist.ReduceOp.SUM, group=self.pg)
+        else:
+            t = x.clone()
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.pg)
+            rows = x.shape[0] // self.world
+            own.copy_(t[self.rank * rows:(self.rank + 1) * rows])
+
+    def gather_(self, full, own):
+        """full [rows, ...] = the ranks' row blocks own [rows / world, ...] in rank order; `own` may be full's own
+        block (in place)."""
+        if self.world == 1:
+            if own.data_ptr() != full.data_ptr():
+                full.copy_(own)
+        elif self.backend == "nccl":
+            dist.all_gather_into_tensor(full, own, group=self.pg)
+        else:
+            rows = full.shape[0] // self.world
+            parts = [torch.empty_like(own) for _ in range(self.world)]
+            dist.all_gather(parts, own.clone(), group=self.pg)
+            for r, t in enumerate(parts):
+                full[r * rows:(r + 1) * rows].copy_(t)
+
     def barrier(self):
         if self.world > 1:
             dist.barrier(group=self.pg)
@@ -124,6 +156,69 @@ class Group:
     def close(self):
         if dist.is_initialized():
             dist.destroy_process_group()
+
+
+class _Raw:
+    """A device address as a CUDA-array-interface object (torch.as_tensor wraps it without a copy)."""
+
+    def __init__(self, ptr, nbytes):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 2}
+
+
+class PeerBuffer:
+    """nbytes of this rank's device memory (zeroed) that every rank of the group can store into from its own kernels:
+    ptrs[r] is rank r's buffer as an address valid on this rank's GPU (peer access over NVLink), ptrs[rank] the own
+    one.  The role of the reference's symmetric-memory buffers (tp.py:381-403), through CUDA IPC handles exchanged over
+    the process group.  Collective: every rank of the group constructs it at the same point."""
+
+    def __init__(self, g, nbytes):
+        import ctypes
+        from . import _lib
+        L = _lib.lib()
+        self.g, self.nbytes, self.ptrs, self._open = g, nbytes, [], []
+        own, handle = ctypes.c_void_p(), ctypes.create_string_buffer(64)
+        _lib.check(L.pb_peer_alloc(nbytes, ctypes.byref(own), handle), f"peer buffer of {nbytes} bytes")
+        self.ptr = own.value
+        handles = [None] * g.world
+        dist.all_gather_object(handles, bytes(handle.raw), group=g.pg)
+        err = None
+        for r, h in enumerate(handles):
+            if r == g.rank:
+                self.ptrs.append(self.ptr)
+                continue
+            p = ctypes.c_void_p()
+            rc = L.pb_peer_open(ctypes.create_string_buffer(h, 64), ctypes.byref(p))
+            if rc:
+                err = err or _lib.PrismError(rc, f"mapping rank {r}'s buffer")
+                self.ptrs.append(None)
+            else:
+                self.ptrs.append(p.value)
+                self._open.append(p.value)
+        # every rank must agree that the mapping worked before any kernel uses it
+        ok = torch.tensor([0 if err else 1], dtype=torch.int32, device=g.device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=g.pg)
+        self.ok = bool(ok.item())
+        self.error = err
+        if not self.ok:
+            self.close()
+
+    def tensor(self, dtype, shape):
+        """The own buffer as a tensor."""
+        return torch.as_tensor(_Raw(self.ptr, self.nbytes), device=self.g.device).view(dtype).view(*shape)
+
+    def close(self):
+        from . import _lib
+        L = _lib.lib()
+        if self.ptr is None:
+            return
+        torch.cuda.synchronize(self.g.device)
+        for p in self._open:
+            L.pb_peer_close(p)
+        self._open = []
+        if dist.is_initialized():
+            self.g.barrier()                       # nobody still maps this rank's memory
+        L.pb_peer_free(self.ptr)
+        self.ptr = None
 
 
 def quantize_rows(g, fn, rows, amax, *args):

@@ -172,6 +172,23 @@ def gemm_i32(a, a_s, w, w_s, slots, n_rows, max_split=4, pdl=False, split=None):
     return S
 
 
+def gemm_scatter(a, w, blocks, block_rows, ldo, n_rows):
+    """The int32 products a w^T of a row-parallel shard, written where they will be folded: output rows
+    [o * block_rows, (o + 1) * block_rows) go to the device address blocks[o] (int32 [block_rows, N], row stride ldo),
+    which may be another GPU's memory (tp.PeerBuffer): the tile kernel stores them over NVLink as it drains each tile.
+    More than 64 rows, block_rows a multiple of 128, at most 8 blocks."""
+    import ctypes
+    M, K = a.shape
+    N = w.shape[0]
+    _lib.need_cuda(a, w, n_rows)
+    if a.dtype != torch.int8 or w.dtype != torch.int8 or w.shape[1] != K or not a.is_contiguous() or not w.is_contiguous():
+        raise RuntimeError("gemm_scatter: a int8 [M, K], w int8 [N, K], contiguous")
+    arr = (ctypes.c_void_p * len(blocks))(*[int(b) for b in blocks])
+    rc = _lib.lib().pb_w8a8_gemm_scatter(_lib.ptr(a), _lib.ptr(w), arr, len(blocks), block_rows, ldo, _lib.ptr(n_rows),
+                                         M, N, K, _lib.stream())
+    _lib.check(rc, f"w8a8 gemm_scatter M={M} N={N} K={K} blocks={len(blocks)}x{block_rows}")
+
+
 def quant_rows(x, gk, n_rows=None):
     """x [M, K] bf16 / fp32 -> (int8 [M, K], fp32 scales [M, K / gk]), symmetric per group of gk inputs."""
     M, K = x.shape

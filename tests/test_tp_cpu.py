@@ -1,5 +1,5 @@
 """The tensor-parallel host logic on CPU ranks (gloo, world size 2): the process group's exact int32 SUM / fp32 MAX,
-tp.out_proj and tp.quantize_rows plumbing.  The GPU kernels are replaced by the CPU oracle inside this test only
+tp.out_proj and tp.quantize_rows plumbing, the reduce-scatter / all-gather pair of the row-split pass.  The GPU kernels are replaced by the CPU oracle inside this test only
 (monkeypatched in the child processes): what is checked is that the two exchange steps compose to the one-rank bits."""
 import os
 import sys
@@ -56,7 +56,21 @@ def _rank(rank, world, port):
         h = torch.randn(M, N, generator=torch.Generator().manual_seed(1))
         folded = oracle.fold(h.numpy(), d.parts.numpy(), sa.numpy(), sw.numpy())
         ok_fold = np.array_equal(folded, oracle.w8a8_gemm(wq, ws, w.numpy(), sw.numpy()[:, None], K, 1, out=h.numpy()))
-        res = (rank, bool(ok_quant), bool(ok_sum), bool(ok_fold))
+        # --- the row-split exchange: reduce-scatter the sums, fold this rank's rows, gather them
+        part = torch.from_numpy(oracle.w8a8_gemm(wq[:, rank * k:(rank + 1) * k].copy(), np.ones((M, 1), np.float32),
+                                                 w[:, rank * k:(rank + 1) * k].contiguous().numpy(),
+                                                 np.ones((N, 1), np.float32), k, 3))
+        rows = M // world
+        own = torch.zeros(rows, N, dtype=torch.int32)
+        g.scatter_sum_(own, part)
+        ok_rs = np.array_equal(own.numpy(), exact[rank * rows:(rank + 1) * rows])
+        mine = oracle.fold(h.numpy()[rank * rows:(rank + 1) * rows].copy(), own.numpy()[None],
+                           sa.numpy()[rank * rows:(rank + 1) * rows].copy(), sw.numpy())
+        full = torch.zeros(M, N)
+        full[rank * rows:(rank + 1) * rows] = torch.from_numpy(mine)
+        g.gather_(full, full[rank * rows:(rank + 1) * rows])
+        ok_rows = ok_rs and np.array_equal(full.numpy(), folded)
+        res = (rank, bool(ok_quant), bool(ok_sum), bool(ok_fold and ok_rows))
     finally:
         g.barrier()
         g.close()

@@ -59,6 +59,26 @@ def test_column_parallel_emulated(dev, ranks):
         assert same(part, whole[:, idx.to(dev)].contiguous())
 
 
+@pytest.mark.parametrize("M,N,K,blocks,live", [(512, 1024, 1024, 2, 512), (1024, 5120, 640, 8, 1024), (768, 384, 2176, 3, 700),
+                                               (512, 100, 512, 4, 300)])
+def test_scatter_blocks_emulated(dev, M, N, K, blocks, live):
+    """gemm_scatter's row blocks (on one GPU: separate local buffers standing in for the ranks' memory) hold the rows
+    of the exact integer product; rows past the live count are not written."""
+    a, w, sa, sw = rand_w8a8(M, N, K, seed=blocks + N)
+    exact = oracle.w8a8_gemm(a.numpy(), sa.numpy(), w.numpy(), sw.numpy(), K, 3, live)
+    rows = M // blocks
+    assert rows % 128 == 0
+    nr = n_rows(live, dev)
+    bufs = [torch.full((rows + 1, N), -7, dtype=torch.int32, device=dev) for _ in range(blocks)]
+    w8a8.gemm_scatter(a.to(dev), w.to(dev), [b.data_ptr() for b in bufs], rows, N, nr)
+    torch.cuda.synchronize()
+    for o, b in enumerate(bufs):
+        lo, hi = o * rows, min((o + 1) * rows, live)
+        if hi > lo:
+            assert same(b[:hi - lo], exact[lo:hi]), o
+        assert bool((b[max(hi - lo, 0):] == -7).all()), o
+
+
 def _run(cmd, env=None):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]

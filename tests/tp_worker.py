@@ -37,6 +37,7 @@ def main():
         torch.save(h.cpu(), out)
     if group is not None:
         group.barrier()
+        stack.close()
         group.close()
 
 
