@@ -402,14 +402,28 @@ template <int MR>
 int launch_w4a8_gemv(int kind, const w4a8::GemvArgs& p, cudaStream_t st) {
     constexpr int R = w4a8::GEMV_R;
     const int grid = (p.N + 4 * R - 1) / (4 * R);                  // eight weight rows per CTA
-    // few rows: four warps per CTA share the rows' super-blocks (exact: the chain runs in order afterwards)
+    auto split_k = kind == 0 ? w4a8::w4a8_gemv_q4k_kernel<MR, R, true> : w4a8::w4a8_gemv_q6k_kernel<MR, R, true>;
+    auto whole_k = kind == 0 ? w4a8::w4a8_gemv_q4k_kernel<MR, R, false> : w4a8::w4a8_gemv_q6k_kernel<MR, R, false>;
+    // few rows: two to four warps per CTA share the rows' super-blocks (exact: the chain runs in order afterwards);
+    // the most warps with which the whole grid is resident at once (a second, short wave would double the time)
     const size_t smem = (size_t)(p.K >> 8) * 4 * R * MR * sizeof(float);
     if (grid < 8 * sm_count() && smem <= 48 * 1024) {
-        if (kind == 0) w4a8::w4a8_gemv_q4k_kernel<MR, R, 4><<<grid, 128, smem, st>>>(p);
-        else w4a8::w4a8_gemv_q6k_kernel<MR, R, 4><<<grid, 128, smem, st>>>(p);
+        static int resident[2][5] = {};                            // [kind][warps] CTAs per SM, 0 = not asked yet
+        int kw = 2;
+        for (int k = 4; k >= 2; --k) {
+            if (!resident[kind][k]) {
+                int nb = 0;
+                PB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, split_k, 32 * k, 16 * 1024));
+                resident[kind][k] = nb > 0 ? nb : 1;
+            }
+            if ((long)grid <= (long)resident[kind][k] * sm_count()) {
+                kw = k;
+                break;
+            }
+        }
+        split_k<<<grid, 32 * kw, smem, st>>>(p);
     } else {
-        if (kind == 0) w4a8::w4a8_gemv_q4k_kernel<MR, R, 1><<<grid, 32, 0, st>>>(p);
-        else w4a8::w4a8_gemv_q6k_kernel<MR, R, 1><<<grid, 32, 0, st>>>(p);
+        whole_k<<<grid, 32, 0, st>>>(p);
     }
     PB_CUDA(cudaGetLastError());
     return PB_OK;
@@ -952,7 +966,9 @@ int pb_w4a8_gemm(const int8_t* xq, const float* a, const int8_t* xs, int Ma, int
     if (K % 256 || N % 4 || ldo < N) return PB_UNSUPPORTED_SHAPE;
     if (!aligned16(xq) || !aligned16(wq) || !aligned16(wsc) || !aligned16(wd) || (kind == 0 && (!aligned16(xs) ||
         !aligned16(wmn) || !aligned16(wdm)))) return PB_BAD_ARGUMENT;
-    if (M <= 4 && !w4a8_tile_only() && !w4a8_no_gemv()) {
+    // one or two rows, or up to four against a matrix of few rows: the CUDA-core kernel (measured: from three rows on a
+    // 34816-row matrix the tensor-core kernel below is level or ahead)
+    if ((M <= 2 || (M <= 4 && (N + 7) / 8 < 8 * sm_count())) && !w4a8_tile_only() && !w4a8_no_gemv()) {
         w4a8::GemvArgs g{xq, a, xs, (const uint8_t*)wq, (const uint8_t*)wsc, (const uint8_t*)wmn, wd, wdm, out, ldo, n_rows, M, N,
                          K, Ma, epi};
         if (M == 1) return launch_w4a8_gemv<1>(kind, g, st);

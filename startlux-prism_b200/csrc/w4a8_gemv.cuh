@@ -22,8 +22,8 @@
 // (A rolling register prefetch, one super-block consumed and one requested per step, measured at a third of the HBM
 // rate: a wait for the oldest request also waits for the younger ones that share its scoreboard.)  Activations, their
 // group sums and scales are small and stay in L1.  A CTA is one warp: eight rows, so that even a 5120-row projection
-// spreads evenly over the SMs; for matrices of few rows (KW = 4) a CTA is four warps on the same eight rows, each
-// taking every fourth super-block: its terms of the chain meet in shared memory and are added in order by one thread
+// spreads evenly over the SMs; for matrices of few rows a CTA is two to four warps on the same eight rows, each
+// taking every KW-th super-block: its terms of the chain meet in shared memory and are added in order by one thread
 // per output, so the bits do not depend on the split.
 #pragma once
 #include "common.cuh"
@@ -117,7 +117,7 @@ __device__ __forceinline__ void gemv_store(const GemvArgs& p, float y, long n, i
     }
 }
 
-// KW > 1: the CTA's warps took every KW-th super-block of the same rows and left each super-block's term t_b in shared
+// SPLIT: the CTA's KW warps took every KW-th super-block of the same rows and left each super-block's term t_b in shared
 // memory; one thread per (row, activation row) pair now runs the chain y = fma(a_b, t_b, y) over all b in order - the
 // unsplit kernel's operations on the same values.
 template <int MR, int R>
@@ -132,11 +132,12 @@ __device__ __forceinline__ void gemv_chain(const GemvArgs& p, const float* terms
     gemv_store(p, y, (long)blockIdx.x * 4 * R + t / MR, m, live, true);
 }
 
-template <int MR, int R, int KW>
-__global__ void __launch_bounds__(32 * KW)
+template <int MR, int R, bool SPLIT>
+__global__ void __launch_bounds__(SPLIT ? 128 : 32)
 w4a8_gemv_q4k_kernel(const GemvArgs p) {
     constexpr int NV = R * MR, PD = GEMV_PD;
-    extern __shared__ float gemv_terms[];                          // KW > 1: [K / 256][4 * R * MR] chain terms
+    extern __shared__ float gemv_terms[];                          // SPLIT: [K / 256][4 * R * MR] chain terms
+    const int KW = SPLIT ? (int)(blockDim.x >> 5) : 1;             // warps sharing the CTA's rows
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane & 7;                                        // sub-block of the super-block
     const long n0 = ((long)blockIdx.x * 4 + (lane >> 3)) * R;
@@ -213,20 +214,21 @@ w4a8_gemv_q4k_kernel(const GemvArgs p) {
                 reduce8<NV>(v, lane);
                 float t = __fmul_rn(dvb, __int2float_rn(v[0]));
                 t = __fmaf_rn(ndm, __int2float_rn(mins), t);
-                if (KW == 1) y = __fmaf_rn(am, t, y);
+                if (!SPLIT) y = __fmaf_rn(am, t, y);
                 else if (reduce8_owner<NV>(lane)) gemv_terms[b * (4 * NV) + ((lane >> 3) * R + r_o) * MR + m_o] = t;
             }
         }
     }
-    if (KW == 1) gemv_store(p, y, n0 + r_o, m_o, live, reduce8_owner<NV>(lane));
+    if (!SPLIT) gemv_store(p, y, n0 + r_o, m_o, live, reduce8_owner<NV>(lane));
     else gemv_chain<MR, R>(p, gemv_terms, NSB, live);
 }
 
-template <int MR, int R, int KW>
-__global__ void __launch_bounds__(32 * KW)
+template <int MR, int R, bool SPLIT>
+__global__ void __launch_bounds__(SPLIT ? 128 : 32)
 w4a8_gemv_q6k_kernel(const GemvArgs p) {
     constexpr int NV = R * MR, PD = GEMV_PD;
-    extern __shared__ float gemv_terms[];                          // KW > 1: [K / 256][4 * R * MR] chain terms
+    extern __shared__ float gemv_terms[];                          // SPLIT: [K / 256][4 * R * MR] chain terms
+    const int KW = SPLIT ? (int)(blockDim.x >> 5) : 1;             // warps sharing the CTA's rows
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane & 7;                                        // 32 of the super-block's 256 inputs
     const long n0 = ((long)blockIdx.x * 4 + (lane >> 3)) * R;
@@ -303,12 +305,12 @@ w4a8_gemv_q6k_kernel(const GemvArgs p) {
                 }
                 reduce8<NV>(v, lane);
                 const float t = __fmul_rn(dvb, __int2float_rn(v[0]));
-                if (KW == 1) y = __fmaf_rn(__ldg(p.a + (long)b * p.Ma + mm_o), t, y);
+                if (!SPLIT) y = __fmaf_rn(__ldg(p.a + (long)b * p.Ma + mm_o), t, y);
                 else if (reduce8_owner<NV>(lane)) gemv_terms[b * (4 * NV) + ((lane >> 3) * R + r_o) * MR + m_o] = t;
             }
         }
     }
-    if (KW == 1) gemv_store(p, y, n0 + r_o, m_o, live, reduce8_owner<NV>(lane));
+    if (!SPLIT) gemv_store(p, y, n0 + r_o, m_o, live, reduce8_owner<NV>(lane));
     else gemv_chain<MR, R>(p, gemv_terms, NSB, live);
 }
 
