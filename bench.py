@@ -440,8 +440,9 @@ def run_detail(args):
                     sc = torch.empty(M, K // 32, dtype=torch.uint8, device=dev)
                     mxfp4.quantize_act(x, q, sc)
                     out = torch.zeros(M, N, dtype=torch.bfloat16 if epi == 0 else torch.float32, device=dev)
-                    mxfp4.gemm(q, sc, wm, out, M, epi=epi)
-                    us = graph_time(lambda c: mxfp4.gemm(q, sc, wm, out, M, epi=epi), 1, iters=4)
+                    msplit = "auto" if args.detail_mx_split else None
+                    mxfp4.gemm(q, sc, wm, out, M, epi=epi, split=msplit)
+                    us = graph_time(lambda c: mxfp4.gemm(q, sc, wm, out, M, epi=epi, split=msplit), 1, iters=4)
                     ops = 2.0 * M * N * K
                     nbytes = (N + M) * K * 17 / 32 + (2 if epi == 0 else 8) * M * N
                     print(json.dumps({"format": "mxfp4", "shape": name, "M": M, "us": round(us, 2),
@@ -661,6 +662,7 @@ def main():
     ap.add_argument("--detail-shapes", default=None)
     ap.add_argument("--detail-gk", default=None, help="comma list; 0 = one group per row (gk == K), 32 = Q8_0 blocks")
     ap.add_argument("--detail-split", type=int, default=None)
+    ap.add_argument("--detail-mx-split", action="store_true", help="MXFP4 GEMMs with split=\"auto\" (K slices per tile)")
     ap.add_argument("--detail-formats", default=None, help="comma list of extra formats: w4a8,mxfp4")
     ap.add_argument("--detail-pdl", action="store_true", help="few-rows GEMMs as programmatic dependent launches")
     args = ap.parse_args()

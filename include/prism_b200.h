@@ -165,6 +165,15 @@ int pb_mxfp4_quant(const void* x, int x_fp32, const float* inv, void* q, void* s
 int pb_mxfp4_gemm(const void* aq, const void* a_sf, const void* bq, const void* b_sf, void* out, long ldo, int M,
                   int N, int K, int epi, void* stream);
 
+/* The same with K split over `split` CTAs per 128 x 128 tile (few rows, few tiles: the HBM-bound decode shapes): the
+ * slices' fp32 accumulators meet in `workspace` and the CTA that finishes a tile last adds them in slice order
+ * (deterministic for a given split; within fp32 rounding of the unsplit sum).  counters: zeroed int32, left zeroed. */
+long pb_mxfp4_workspace_bytes(int M, int N, int split);
+int pb_mxfp4_counters(int M, int N);
+int pb_mxfp4_gemm_split(const void* aq, const void* a_sf, const void* bq, const void* b_sf, void* out, long ldo, int M,
+                        int N, int K, int epi, int split, void* workspace, long workspace_bytes, int* counters,
+                        int n_counters, void* stream);
+
 /* Measurement aid: the int8 tensor-core rate with shared-memory-resident operands and no loads (one CTA per SM, `iters`
  * batches of four 128 x mma_n x 32 MMAs each, mma_n a multiple of 16 up to 256; pattern 0 = zero operands, 1 =
  * pseudo-random bytes).  ops = 2 * 128 * mma_n * 128 * iters per SM.  Counterpart of the reference's bench/csrc/mma_peak.cu.  cycles (device, one per SM) may be NULL. */

@@ -127,6 +127,7 @@ struct AuxM {
     uint64_t full[8], empty[8], tfull[2], tempty[2];
     uint32_t tmem_base;
     int abort_flag;
+    int is_last;
 };
 constexpr int SMEM = STAGES * STAGE_BYTES + 1024 + 256 + 4 * 32 * 33 * 4;
 
@@ -168,6 +169,12 @@ struct GemmArgs {
     void* out;
     long ldo;
     int M, N, K, epi;
+    // K split of the 128 x 128 kernel (few rows, few tiles): slice z of a tile covers K blocks [z * kbs, (z + 1) * kbs);
+    // the slices' fp32 accumulators meet in ws [tile][slice][128][128] and the CTA that finishes a tile last adds them
+    // in slice order (deterministic; the sum's rounding differs from the unsplit order within fp32)
+    int split, kbs;
+    float* ws;
+    int* counters;
 };
 
 __global__ void __launch_bounds__(192, 1)
@@ -180,6 +187,7 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_m = (p.M + BM - 1) / BM, num_n = (p.N + BN - 1) / BN;
     const int num_tiles = num_m * num_n, KB = p.K / 256, KA = p.K / 128;
+    const int num_units = num_tiles * p.split;                        // (tile, K slice)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -208,9 +216,11 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+                const int t = u / p.split, z = u - t * p.split;
                 const int mt = t % num_m, nt = t / num_m;
-                for (int kb = 0; kb < KB; ++kb) {
+                const int kb_end = (z + 1) * p.kbs < KB ? (z + 1) * p.kbs : KB;
+                for (int kb = z * p.kbs; kb < kb_end; ++kb) {
                     if (!mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1, abort_flag, 0xE00 + stage)) {
                         ok = false;
                         break;
@@ -239,11 +249,13 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             int stage = 0, buf = 0, sfp = 0;
             uint32_t phase = 0, bphase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+                const int z = u % p.split;
+                const int kb_begin = z * p.kbs, kb_end = (z + 1) * p.kbs < KB ? (z + 1) * p.kbs : KB;
                 if (!mbar_wait(smem_u32(&aux->tempty[buf]), bphase ^ 1, abort_flag, 0xE10 + buf)) break;
                 tc_fence_after();
                 const uint32_t d = tmem_base + buf * BN;
-                for (int kb = 0; kb < KB; ++kb) {
+                for (int kb = kb_begin; kb < kb_end; ++kb) {
                     if (!mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, 0xE20 + stage)) {
                         ok = false;
                         break;
@@ -262,7 +274,7 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
                         const uint32_t sf_id = (k & 1) * 2;
                         umma_mxf4(d, umma_desc_advance(ad, k * 32), umma_desc_advance(bd, k * 32),
                                   idesc_mxf4(BM, BN, sf_id, sf_id), sfa_t + (k >> 1) * 4, sfb_t + (k >> 1) * 4,
-                                  (kb | k) ? 1u : 0u);
+                                  (kb > kb_begin || k) ? 1u : 0u);
                     }
                     tc_commit(smem_u32(&aux->empty[stage]));
                     sfp ^= 1;
@@ -282,7 +294,8 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
         uint32_t* stg = stage_buf + q * (32 * 33);
         int buf = 0;
         uint32_t bphase = 0;
-        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+        for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
+            const int t = u / p.split, z = u - t * p.split;
             const int m0 = (t % num_m) * BM, n0 = (t / num_m) * BN;
             if (!mbar_wait(smem_u32(&aux->tfull[buf]), bphase, abort_flag, 0xE30 + buf)) break;
             tc_fence_after();
@@ -290,6 +303,94 @@ mxfp4_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constan
             const int rows_here = p.M - (m0 + q * 32);
             const bool word_ok = p.epi != 0 || ((((uintptr_t)p.out & 3) == 0) && (p.ldo % 2 == 0));
             const int cpw = p.epi == 0 ? 2 : 1;
+            float* ws_tile = p.ws + (long)t * p.split * (BM * BN);
+            if (p.split > 1) {
+                // this slice's accumulator -> workspace (live rows only), then the tile's last CTA adds the slices
+                float* mine = ws_tile + (long)z * (BM * BN) + (long)(q * 32) * BN;
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    if (n0 + c0 >= p.N) break;
+                    uint32_t r[32];
+                    tmem_ld32(lane_addr + c0, r);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) stg[lane * 33 + j] = r[j];
+                    __syncwarp();
+                    for (int rr = 0; rr < 32 && rr < rows_here; ++rr)
+                        __stcg(mine + rr * BN + c0 + lane, __uint_as_float(stg[rr * 33 + lane]));
+                    __syncwarp();
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&aux->tempty[buf]));
+                buf ^= 1;
+                if (buf == 0) bphase ^= 1;
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) aux->is_last = (atomicAdd(p.counters + t, 1) == p.split - 1);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (!aux->is_last) continue;
+                __threadfence();
+                if (threadIdx.x == 64) p.counters[t] = 0;
+                // the slices in order, eight rows' loads in flight at a time; a lane owns four consecutive columns
+                const int col = n0 + lane * 4;
+                const bool vec = col + 4 <= p.N && (p.ldo & 3) == 0 && ((uintptr_t)p.out & 15) == 0;
+#pragma unroll 1
+                for (int rr0 = 0; rr0 < 32 && rr0 < rows_here; rr0 += 8) {
+                    float4 acc[8];
+                    const float* src = ws_tile + (long)(q * 32 + rr0) * BN + lane * 4;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (rr0 + j < rows_here) acc[j] = __ldcg((const float4*)(src + j * BN));
+                    for (int zz = 1; zz < p.split; ++zz) {
+                        float4 v[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (rr0 + j < rows_here) v[j] = __ldcg((const float4*)(src + (long)zz * (BM * BN) + j * BN));
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (rr0 + j < rows_here) {
+                                acc[j].x = __fadd_rn(acc[j].x, v[j].x);
+                                acc[j].y = __fadd_rn(acc[j].y, v[j].y);
+                                acc[j].z = __fadd_rn(acc[j].z, v[j].z);
+                                acc[j].w = __fadd_rn(acc[j].w, v[j].w);
+                            }
+                    }
+                    float4 old[8];
+                    if (p.epi != 0 && vec) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (rr0 + j < rows_here)
+                                old[j] = __ldcg((const float4*)((float*)p.out + (long)(m0 + q * 32 + rr0 + j) * p.ldo + col));
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (rr0 + j >= rows_here) continue;
+                        const long off = (long)(m0 + q * 32 + rr0 + j) * p.ldo + col;
+                        const float a4[4] = {acc[j].x, acc[j].y, acc[j].z, acc[j].w};
+                        if (p.epi == 0) {
+                            if (vec) {
+                                __nv_bfloat162 b0 = __floats2bfloat162_rn(a4[0], a4[1]), b1 = __floats2bfloat162_rn(a4[2], a4[3]);
+                                *(uint2*)((__nv_bfloat16*)p.out + off) = make_uint2(*(uint32_t*)&b0, *(uint32_t*)&b1);
+                            } else {
+                                for (int e = 0; e < 4; ++e)
+                                    if (col + e < p.N) ((__nv_bfloat16*)p.out)[off + e] = __float2bfloat16_rn(a4[e]);
+                            }
+                        } else if (vec) {
+                            float4 o = old[j];
+                            o.x = __fadd_rn(o.x, a4[0]);
+                            o.y = __fadd_rn(o.y, a4[1]);
+                            o.z = __fadd_rn(o.z, a4[2]);
+                            o.w = __fadd_rn(o.w, a4[3]);
+                            *(float4*)((float*)p.out + off) = o;
+                        } else {
+                            for (int e = 0; e < 4; ++e)
+                                if (col + e < p.N) ((float*)p.out)[off + e] = __fadd_rn(((float*)p.out)[off + e], a4[e]);
+                        }
+                    }
+                }
+                continue;
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32 * cpw) {
                 if (n0 + c0 >= p.N) break;

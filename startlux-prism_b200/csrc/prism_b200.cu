@@ -1058,6 +1058,22 @@ int pb_mxfp4_quant(const void* x, int x_fp32, const float* inv, void* q, void* s
 
 int pb_mxfp4_gemm(const void* aq, const void* a_sf, const void* bq, const void* b_sf, void* out, long ldo, int M,
                   int N, int K, int epi, void* stream) {
+    return pb_mxfp4_gemm_split(aq, a_sf, bq, b_sf, out, ldo, M, N, K, epi, 1, nullptr, 0, nullptr, 0, stream);
+}
+
+long pb_mxfp4_workspace_bytes(int M, int N, int split) {
+    if (M <= 0 || N <= 0 || split <= 1) return 0;
+    return (long)((M + 127) / 128) * ((N + 127) / 128) * split * 128 * 128 * 4;
+}
+
+int pb_mxfp4_counters(int M, int N) {
+    if (M <= 0 || N <= 0) return 0;
+    return ((M + 127) / 128) * ((N + 127) / 128);
+}
+
+int pb_mxfp4_gemm_split(const void* aq, const void* a_sf, const void* bq, const void* b_sf, void* out, long ldo, int M,
+                        int N, int K, int epi, int split, void* workspace, long workspace_bytes, int* counters,
+                        int n_counters, void* stream) {
     if (!aq || !a_sf || !bq || !b_sf || !out || M <= 0 || N <= 0 || K <= 0 || ldo < N) return PB_BAD_ARGUMENT;
     if (epi != 0 && epi != 1) return PB_BAD_ARGUMENT;
     if (K % 256) return PB_UNSUPPORTED_SHAPE;
@@ -1066,11 +1082,21 @@ int pb_mxfp4_gemm(const void* aq, const void* a_sf, const void* bq, const void* 
     int rc;
     if ((rc = tensor_map(&ta, aq, K / 2, M, K / 2, 128, 128, 0))) return rc;
     if ((rc = tensor_map(&tb, bq, K / 2, N, K / 2, 128, 128, 0))) return rc;
-    mxfp4::GemmArgs p{(const uint8_t*)a_sf, (const uint8_t*)b_sf, out, ldo, M, N, K, epi};
+    if (split < 1) return PB_BAD_ARGUMENT;
+    const int KB = K / 256;
+    if (split > KB) split = KB;
+    int kbs = (KB + split - 1) / split;
+    split = (KB + kbs - 1) / kbs;                                  // every slice non-empty
+    if (split > 1) {
+        if (!workspace || !counters) return PB_BAD_ARGUMENT;
+        if (workspace_bytes < pb_mxfp4_workspace_bytes(M, N, split) || n_counters < pb_mxfp4_counters(M, N))
+            return PB_TOO_LARGE;
+    }
+    mxfp4::GemmArgs p{(const uint8_t*)a_sf, (const uint8_t*)b_sf, out, ldo, M, N, K, epi, split, kbs, (float*)workspace, counters};
     // 128 x 256 tiles when there are enough of them to fill the SMs (the same K order either way: one accumulator
     // over all of K, so a row's bits do not depend on the choice)
     const long tiles256 = (long)((M + 127) / 128) * ((N + 255) / 256);
-    if (N > 128 && tiles256 >= sm_count() && !mxfp4_narrow_only()) {
+    if (N > 128 && tiles256 >= sm_count() && !mxfp4_narrow_only() && split == 1) {
         CUtensorMap tb2;
         if ((rc = tensor_map(&tb2, bq, K / 2, N, K / 2, 128, 256, 0))) return rc;
         static bool configured2 = false;
@@ -1098,7 +1124,7 @@ int pb_mxfp4_gemm(const void* aq, const void* a_sf, const void* bq, const void* 
         if ((rc = set_smem(mxfp4::mxfp4_gemm_kernel, mxfp4::SMEM))) return rc;
         configured = true;
     }
-    const int tiles = ((M + 127) / 128) * ((N + 127) / 128);
+    const int tiles = ((M + 127) / 128) * ((N + 127) / 128) * split;
     const int grid = tiles < sm_count() ? tiles : sm_count();
     mxfp4::mxfp4_gemm_kernel<<<grid, 192, mxfp4::SMEM, (cudaStream_t)stream>>>(ta, tb, p);
     PB_CUDA(cudaGetLastError());

@@ -130,9 +130,23 @@ def prepare(w: MX4) -> MX4:
 cutlass_prepare = prepare       # the reference's name for the same step (kernels/mxfp4.py:214)
 
 
-def gemm(a_q, a_s, w: MX4, out, n_rows, epi=0, out_stride=None):
+def pick_split(M, N, K):
+    """K slices per 128 x 128 tile: only where one row tile's tiles leave most SMs idle (decode shapes against the
+    5120-row projections); every slice keeps at least 4 K blocks of 256."""
+    from .w8a8 import SM_COUNT
+    tiles = ((M + 127) // 128) * ((N + 127) // 128)
+    if M > 128 or tiles * 2 > SM_COUNT:
+        return 1
+    return max(1, min(SM_COUNT // tiles, (K // 256) // 4, 8))
+
+
+def gemm(a_q, a_s, w: MX4, out, n_rows, epi=0, out_stride=None, split=None):
     """a_q uint8 [>= n_rows, k/2], a_s uint8 [>= n_rows, k/32]; w MX4 [N, k] (prepare()d, or prepared here on every
-    call).  epi 0 writes bf16 into out, epi 1 adds into the fp32 residual out; out's row stride is honoured."""
+    call).  epi 0 writes bf16 into out, epi 1 adds into the fp32 residual out; out's row stride is honoured.
+    split: K slices per tile; None or 1: one accumulator over all of K, so a row's bits do not depend on the batch it
+    came in (the reference's batch invariance); "auto": pick_split (decode shapes against few-row matrices run several
+    times faster); the slices' fp32 sums are added in slice order: deterministic, and within fp32 rounding of the
+    unsplit sum."""
     M, K, N = int(n_rows), w.k, w.n
     _lib.need_cuda(a_q, a_s, w.q, out)
     if w.cs is None:
@@ -152,6 +166,14 @@ def gemm(a_q, a_s, w: MX4, out, n_rows, epi=0, out_stride=None):
     L = _lib.lib()
     _lib.check(L.pb_mxfp4_prepare_sf(_lib.ptr(a_s), _lib.ptr(sfa), a_q.shape[0], K, _lib.stream()), "mxfp4 prepare_sf")
     ldo = out.stride(0) if out_stride is None else out_stride
-    rc = L.pb_mxfp4_gemm(_lib.ptr(a_q), _lib.ptr(sfa), _lib.ptr(w.q), _lib.ptr(w.cs), _lib.ptr(out), ldo, M, N, K, epi,
-                         _lib.stream())
+    split = 1 if split is None else pick_split(M, N, K) if split == "auto" else max(1, int(split))
+    ws = counters = None
+    if split > 1:
+        from . import w8a8 as KW
+        ws, counters = KW._workspace(a_q.device)
+        if L.pb_mxfp4_workspace_bytes(M, N, split) > ws.numel() or L.pb_mxfp4_counters(M, N) > counters.numel():
+            split, ws, counters = 1, None, None
+    rc = L.pb_mxfp4_gemm_split(_lib.ptr(a_q), _lib.ptr(sfa), _lib.ptr(w.q), _lib.ptr(w.cs), _lib.ptr(out), ldo, M, N, K,
+                               epi, split, _lib.ptr(ws), 0 if ws is None else ws.numel(), _lib.ptr(counters),
+                               0 if counters is None else counters.numel(), _lib.stream())
     _lib.check(rc, f"mxfp4 gemm M={M} N={N} K={K} epi={epi}")

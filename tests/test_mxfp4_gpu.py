@@ -71,6 +71,32 @@ def test_gemm(dev, M, N, K):
     assert err1 < 1e-3, err1                              # the fp32 accumulators against the float64 product
 
 
+@pytest.mark.parametrize("M,N,K", [(16, 5120, 5120), (1, 1000, 2560), (64, 384, 4352), (100, 256, 1024)])
+def test_gemm_k_split(dev, M, N, K):
+    """K slices per tile, added in slice order by the tile's last CTA: the same tolerances as the unsplit product, the
+    same bits on every run (a poisoned workspace in between), counters left zeroed."""
+    from prism_b200 import w8a8
+    w = mxfp4.pack(synth.weights(N, K, seed=N + K))
+    q, s = quant_gpu(synth.activations(M, K, seed=M), dev)
+    wd = mxfp4.prepare(mxfp4.MX4(w.q.to(dev), w.s.to(dev), N, K))
+    _, ref = oracle.mxfp4_gemm(q.cpu().numpy(), s.cpu().numpy(), w.q.numpy(), w.s.numpy())
+    ws, counters = w8a8._workspace(dev)
+    for split in (2, 3, 5, "auto"):
+        h0 = torch.randn(M, N, generator=torch.Generator().manual_seed(1))
+        runs = []
+        for rep in range(2):
+            ws.fill_(0x7f)
+            h = h0.to(dev)
+            mxfp4.gemm(q, s, wd, h, M, epi=1, split=split)
+            runs.append(h)
+        assert same(runs[0], runs[1]), split
+        assert rel_fro(runs[0].cpu().numpy() - h0.numpy(), ref) < 1e-5, split
+        out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+        mxfp4.gemm(q, s, wd, out, M, epi=0, split=split)
+        assert rel_fro(out.float().cpu().numpy(), ref) < 3e-3, split
+        assert int(counters.abs().sum()) == 0
+
+
 def test_gemm_fp32_path_tight(dev):
     """Against the float64 product the fp32-accumulated result is within 1e-5 (no operand rounding happens inside the
     MMA: e2m1 products and power-of-two scales are exact; only the fp32 sums round)."""
