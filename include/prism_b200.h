@@ -168,6 +168,13 @@ int pb_mxfp4_gemm(const void* aq, const void* a_sf, const void* bq, const void* 
 /* The same with K split over `split` CTAs per 128 x 128 tile (few rows, few tiles: the HBM-bound decode shapes): the
  * slices' fp32 accumulators meet in `workspace` and the CTA that finishes a tile last adds them in slice order
  * (deterministic for a given split; within fp32 rounding of the unsplit sum).  counters: zeroed int32, left zeroed. */
+/* One to four activation rows on the CUDA cores (exact integer dot products per 32-input block, one fp32 multiply-add
+ * per block): a_s / b_s are the plain row-major scale bytes [rows, K/32], not the tiled order.  The result differs from
+ * pb_mxfp4_gemm's only in the order of the fp32 additions; no counterpart in the reference (its decode path pads the
+ * tensor-core GEMM, kernels/mxfp4.py:292-317).  K % 256 == 0, M <= 4. */
+int pb_mxfp4_gemv(const void* aq, const void* a_s, const void* bq, const void* b_s, void* out, long ldo, int M, int N,
+                  int K, int epi, void* stream);
+
 long pb_mxfp4_workspace_bytes(int M, int N, int split);
 int pb_mxfp4_counters(int M, int N);
 int pb_mxfp4_gemm_split(const void* aq, const void* a_sf, const void* bq, const void* b_sf, void* out, long ldo, int M,

@@ -37,6 +37,7 @@ _SIGS = {
     "pb_mxfp4_prepare_sf": ([_vp, _vp, _i, _i, _vp], _i),
     "pb_mxfp4_quant": ([_vp, _i, _vp, _vp, _vp, _i, _i, _vp], _i),
     "pb_mxfp4_gemm": ([_vp, _vp, _vp, _vp, _vp, _l, _i, _i, _i, _i, _vp], _i),
+    "pb_mxfp4_gemv": ([_vp, _vp, _vp, _vp, _vp, _l, _i, _i, _i, _i, _vp], _i),
     "pb_mxfp4_workspace_bytes": ([_i, _i, _i], _l),
     "pb_mxfp4_counters": ([_i, _i], _i),
     "pb_mxfp4_gemm_split": ([_vp, _vp, _vp, _vp, _vp, _l, _i, _i, _i, _i, _i, _vp, _l, _vp, _i, _vp], _i),

@@ -18,6 +18,7 @@
 #include "w4a8_few.cuh"
 #include "w4a8_gemv.cuh"
 #include "mxfp4_gemm.cuh"
+#include "mxfp4_gemv.cuh"
 
 namespace {
 
@@ -424,6 +425,32 @@ int launch_w4a8_gemv(int kind, const w4a8::GemvArgs& p, cudaStream_t st) {
         split_k<<<grid, 32 * kw, smem, st>>>(p);
     } else {
         whole_k<<<grid, 32, 0, st>>>(p);
+    }
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+template <int MR>
+int launch_mxfp4_gemv(const mxfp4::GemvArgs& p, cudaStream_t st) {
+    const int grid = (p.N + 7) / 8;                                // eight weight rows per CTA
+    if (grid < 8 * sm_count()) {
+        // few rows: the most warps per CTA with which the whole grid is resident at once
+        static int resident[5] = {};
+        int kw = 2;
+        for (int k = 4; k >= 2; --k) {
+            if (!resident[k]) {
+                int nb = 0;
+                PB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, mxfp4::mxfp4_gemv_kernel<MR, true>, 32 * k, 1024));
+                resident[k] = nb > 0 ? nb : 1;
+            }
+            if ((long)grid <= (long)resident[k] * sm_count()) {
+                kw = k;
+                break;
+            }
+        }
+        mxfp4::mxfp4_gemv_kernel<MR, true><<<grid, 32 * kw, (size_t)kw * 8 * MR * sizeof(float), st>>>(p);
+    } else {
+        mxfp4::mxfp4_gemv_kernel<MR, false><<<grid, 32, 0, st>>>(p);
     }
     PB_CUDA(cudaGetLastError());
     return PB_OK;
@@ -1129,6 +1156,19 @@ int pb_mxfp4_gemm_split(const void* aq, const void* a_sf, const void* bq, const 
     mxfp4::mxfp4_gemm_kernel<<<grid, 192, mxfp4::SMEM, (cudaStream_t)stream>>>(ta, tb, p);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
+}
+
+int pb_mxfp4_gemv(const void* aq, const void* a_s, const void* bq, const void* b_s, void* out, long ldo, int M, int N,
+                  int K, int epi, void* stream) {
+    if (!aq || !a_s || !bq || !b_s || !out || M <= 0 || N <= 0 || K <= 0 || ldo < N) return PB_BAD_ARGUMENT;
+    if (epi != 0 && epi != 1) return PB_BAD_ARGUMENT;
+    if (M > 4 || K % 256) return PB_UNSUPPORTED_SHAPE;
+    if (!aligned16(aq) || !aligned16(bq)) return PB_BAD_ARGUMENT;
+    mxfp4::GemvArgs p{(const uint8_t*)aq, (const uint8_t*)a_s, (const uint8_t*)bq, (const uint8_t*)b_s, out, ldo, M, N, K, epi};
+    cudaStream_t st = (cudaStream_t)stream;
+    if (M == 1) return launch_mxfp4_gemv<1>(p, st);
+    if (M == 2) return launch_mxfp4_gemv<2>(p, st);
+    return launch_mxfp4_gemv<4>(p, st);
 }
 
 int pb_int8_peak_probe(int iters, int pattern, int mma_n, unsigned long long* cycles, void* stream) {

@@ -235,7 +235,6 @@ w4a8_few_kernel(const __grid_constant__ FewMaps maps, const Args p) {
         uint32_t phase = 0;
         for (int b = 0; b < NSB; ++b) {
             const int e = b & 1;
-            const uint32_t eph = (b >> 1) & 1;
             if (!mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, 0x1000 + stage)) break;
             // buffer e was last read by the MMAs of super-block b - 2: their commit completed that accumulator set
             if (b >= 2 && !mbar_wait(smem_u32(&aux->acc_full[(b - 2) & (FEW_SETS - 1)]), ((b - 2) / FEW_SETS) & 1, abort_flag,

@@ -7,6 +7,7 @@
     quantize_act_scaled(x, inv, q, s)   with a per-column pre-scale                                      (mxfp4.py:174-179)
     prepare(w)                          MX4 with its scales in the tensor core's tiled order (cs)        (mxfp4.py:214-224)
     gemm(a_q, a_s, w, out, n_rows, epi) out = deq(a) deq(w)^T, fp32 accumulate                           (mxfp4.py:292-317)
+    gemv(a_q, a_s, w, out, n_rows, epi) the same for one to four rows on the CUDA cores (no counterpart)
 
 Values: e2m1 grid 0, .5, 1, 1.5, 2, 3, 4, 6 with sign bit 8, nearest with strict thresholds; block scale
 2^ceil(log2(amax / 6)) clipped to 2^+-127, stored as e + 127; byte = code[2i] | code[2i + 1] << 4.
@@ -130,6 +131,28 @@ def prepare(w: MX4) -> MX4:
 cutlass_prepare = prepare       # the reference's name for the same step (kernels/mxfp4.py:214)
 
 
+def _sm_count():
+    from .w8a8 import SM_COUNT
+    return SM_COUNT
+
+
+def gemv(a_q, a_s, w: MX4, out, n_rows, epi=0, out_stride=None):
+    """gemm for one to four rows on the CUDA cores: exact integer products per 32-input block, one fp32 multiply-add
+    per block (mxfp4_gemv_kernel).  Takes the plain scale bytes (w.s, a_s), not the tiled order; differs from gemm
+    only in the order of the fp32 additions."""
+    M, K, N = int(n_rows), w.k, w.n
+    _lib.need_cuda(a_q, a_s, w.q, w.s, out)
+    want = torch.bfloat16 if epi == 0 else torch.float32
+    if out.dtype != want or out.stride(-1) != 1:
+        raise RuntimeError(f"mxfp4.gemv: out must be {want} with unit column stride")
+    if not a_q.is_contiguous() or not a_s.is_contiguous() or a_q.shape[1] != K // 2 or not w.s.is_contiguous():
+        raise RuntimeError("mxfp4.gemv: a_q [rows, k/2], a_s [rows, k/32] and w.s must be contiguous")
+    ldo = out.stride(0) if out_stride is None else out_stride
+    rc = _lib.lib().pb_mxfp4_gemv(_lib.ptr(a_q), _lib.ptr(a_s), _lib.ptr(w.q), _lib.ptr(w.s), _lib.ptr(out), ldo, M, N, K,
+                                  epi, _lib.stream())
+    _lib.check(rc, f"mxfp4 gemv M={M} N={N} K={K} epi={epi}")
+
+
 def pick_split(M, N, K):
     """K slices per 128 x 128 tile: only where one row tile's tiles leave most SMs idle (decode shapes against the
     5120-row projections); every slice keeps at least 4 K blocks of 256."""
@@ -144,8 +167,8 @@ def gemm(a_q, a_s, w: MX4, out, n_rows, epi=0, out_stride=None, split=None):
     """a_q uint8 [>= n_rows, k/2], a_s uint8 [>= n_rows, k/32]; w MX4 [N, k] (prepare()d, or prepared here on every
     call).  epi 0 writes bf16 into out, epi 1 adds into the fp32 residual out; out's row stride is honoured.
     split: K slices per tile; None or 1: one accumulator over all of K, so a row's bits do not depend on the batch it
-    came in (the reference's batch invariance); "auto": pick_split (decode shapes against few-row matrices run several
-    times faster); the slices' fp32 sums are added in slice order: deterministic, and within fp32 rounding of the
+    came in (the reference's batch invariance); "auto": one row against a matrix of few rows on the CUDA cores (gemv), otherwise
+    pick_split (decode shapes against few-row matrices run several times faster); the slices' fp32 sums are added in slice order: deterministic, and within fp32 rounding of the
     unsplit sum."""
     M, K, N = int(n_rows), w.k, w.n
     _lib.need_cuda(a_q, a_s, w.q, out)
@@ -156,6 +179,10 @@ def gemm(a_q, a_s, w: MX4, out, n_rows, epi=0, out_stride=None, split=None):
         raise RuntimeError(f"mxfp4.gemm: out must be {want} with unit column stride")
     if not a_q.is_contiguous() or not a_s.is_contiguous() or a_q.shape[1] != K // 2:
         raise RuntimeError("mxfp4.gemm: a_q [rows, k/2] and a_s [rows, k/32] must be contiguous")
+    if split == "auto" and M == 1 and K % 256 == 0 and (N + 7) // 8 < 8 * _sm_count():
+        # one row against a matrix of few rows: the CUDA-core kernel (measured: level with the tensor-core kernel on a
+        # 34816-row matrix and behind it from two rows, where its decode arithmetic is the bound)
+        return gemv(a_q, a_s, w, out, M, epi, out_stride)
     key = (a_q.shape[0], K, a_q.device.index)
     need = _lib.lib().pb_mxfp4_sf_bytes(a_q.shape[0], K)
     sfa = _ACT_SF.get(key)

@@ -125,12 +125,18 @@ def gemm_segs(xq, a, xs, segs, out, n_rows, epi=0, pdl=0):
 
 
 def pick_split(M, N, K, tile=128):
-    """K splits of the few-rows Q4_K kernel (M <= 16): one CTA per SM, so as many slices as fit the SMs over the weight
-    tiles, at least four super-blocks each.  Exact (the per-super-block terms meet in a workspace): always on."""
+    """K splits of the few-rows kernels (M <= 16): one CTA per SM, so the time goes as (waves of CTAs) / (slices):
+    the slice count that makes that smallest, at least four super-blocks per slice, the fewest slices among equals.
+    Exact (the per-super-block terms meet in a workspace): always on."""
     if M > 16:
         return 1
     tiles = -(-N // tile)
-    return max(1, min(8, 148 // tiles, (K // 256) // 4))
+    best, cost = 1, float(-(-tiles // 148))
+    for s in range(2, min(8, (K // 256) // 4) + 1):
+        c = -(-tiles * s // 148) / s
+        if c < cost - 1e-9:
+            best, cost = s, c
+    return best
 
 
 def gemm(xq, a, xs, w: W4, out, n_rows, epi=0, cfg=None, pdl=0):

@@ -97,6 +97,38 @@ def test_gemm_k_split(dev, M, N, K):
         assert int(counters.abs().sum()) == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 5120, 5120), (2, 1000, 2560), (1, 133, 256), (2, 34816, 512), (4, 7168, 1024),
+                                   (3, 300, 768)])
+def test_gemv_rows(dev, M, N, K):
+    """One to four rows on the CUDA-core kernel (exact integer block products, fp32 over the blocks) against the
+    float64 product, both epilogues; deterministic; rows past M and columns past N untouched."""
+    w = mxfp4.pack(synth.weights(N, K, seed=N + K))
+    q, s = quant_gpu(synth.activations(M, K, seed=M + 7, outliers=K // 64), dev)
+    wd = mxfp4.prepare(mxfp4.MX4(w.q.to(dev), w.s.to(dev), N, K))
+    _, ref = oracle.mxfp4_gemm(q.cpu().numpy(), s.cpu().numpy(), w.q.numpy(), w.s.numpy())
+    h0 = torch.randn(M + 1, N + 3, generator=torch.Generator().manual_seed(1))
+    runs = []
+    for rep in range(2):
+        h = h0.to(dev)
+        mxfp4.gemv(q, s, wd, h[:M, :N], M, epi=1)
+        runs.append(h)
+    assert same(runs[0], runs[1])
+    got = runs[0].cpu().numpy()
+    assert rel_fro(got[:M, :N] - h0.numpy()[:M, :N], ref) < 1e-5
+    assert np.array_equal(got[M:], h0.numpy()[M:]) and np.array_equal(got[:, N:], h0.numpy()[:, N:])
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+    mxfp4.gemv(q, s, wd, out, M, epi=0)
+    assert rel_fro(out.float().cpu().numpy(), ref) < 3e-3
+    if M == 1:                                            # split="auto" routes one row against few weight rows here
+        auto = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+        mxfp4.gemm(q, s, wd, auto, M, epi=0, split="auto")
+        assert rel_fro(auto.float().cpu().numpy(), ref) < 3e-3
+    # and close to the tensor-core kernel's bits: the same exact block products, another order of fp32 additions
+    out_tc = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+    mxfp4.gemm(q, s, wd, out_tc, M, epi=0)
+    assert rel_fro(out.float().cpu().numpy(), out_tc.float().cpu().numpy().astype(np.float64)) < 3e-3
+
+
 def test_gemm_fp32_path_tight(dev):
     """Against the float64 product the fp32-accumulated result is within 1e-5 (no operand rounding happens inside the
     MMA: e2m1 products and power-of-two scales are exact; only the fp32 sums round)."""
