@@ -1105,10 +1105,6 @@ int pb_mxfp4_gemm_split(const void* aq, const void* a_sf, const void* bq, const 
     if (epi != 0 && epi != 1) return PB_BAD_ARGUMENT;
     if (K % 256) return PB_UNSUPPORTED_SHAPE;
     if (!aligned16(aq) || !aligned16(bq) || !aligned16(a_sf) || !aligned16(b_sf)) return PB_BAD_ARGUMENT;
-    CUtensorMap ta, tb;
-    int rc;
-    if ((rc = tensor_map(&ta, aq, K / 2, M, K / 2, 128, 128, 0))) return rc;
-    if ((rc = tensor_map(&tb, bq, K / 2, N, K / 2, 128, 128, 0))) return rc;
     if (split < 1) return PB_BAD_ARGUMENT;
     const int KB = K / 256;
     if (split > KB) split = KB;
@@ -1119,6 +1115,10 @@ int pb_mxfp4_gemm_split(const void* aq, const void* a_sf, const void* bq, const 
         if (workspace_bytes < pb_mxfp4_workspace_bytes(M, N, split) || n_counters < pb_mxfp4_counters(M, N))
             return PB_TOO_LARGE;
     }
+    CUtensorMap ta, tb;
+    int rc;
+    if ((rc = tensor_map(&ta, aq, K / 2, M, K / 2, 128, 128, 0))) return rc;
+    if ((rc = tensor_map(&tb, bq, K / 2, N, K / 2, 128, 128, 0))) return rc;
     mxfp4::GemmArgs p{(const uint8_t*)a_sf, (const uint8_t*)b_sf, out, ldo, M, N, K, epi, split, kbs, (float*)workspace, counters};
     // 128 x 256 tiles when there are enough of them to fill the SMs (the same K order either way: one accumulator
     // over all of K, so a row's bits do not depend on the choice)

@@ -48,6 +48,27 @@ def test_argument_checks_without_gpu(lib):
     assert lib.pb_quant_rows(p16, 0, 32, None, p16, p16, p16, 4, 64, 64, 1, None, None) == 1   # mode 1 without amax
     assert lib.pb_w8a8_workspace_bytes(16, 5120, 4) == 4 * 40 * 16 * 128 * 4
     assert lib.pb_w8a8_counters(64, 7168) == 56
+    # row blocks of the scattered int32 output: whole tiles, at most eight, covering every row
+    blocks = (ctypes.c_void_p * 8)(*([p16] * 8))
+    assert lib.pb_w8a8_gemm_scatter(p16, p16, blocks, 2, 100, 64, p16, 200, 64, 128, None) == 2      # block rows % 128
+    assert lib.pb_w8a8_gemm_scatter(p16, p16, blocks, 9, 128, 64, p16, 256, 64, 128, None) == 1      # more than 8 blocks
+    assert lib.pb_w8a8_gemm_scatter(p16, p16, blocks, 2, 128, 64, p16, 512, 64, 128, None) == 1      # rows not covered
+    assert lib.pb_w8a8_gemm_scatter(p16, p16, blocks, 1, 128, 64, p16, 64, 64, 128, None) == 2       # few rows
+    # MXFP4: split needs its workspace; the CUDA-core kernel takes up to four rows
+    assert lib.pb_mxfp4_gemm_split(p16, p16, p16, p16, p16, 128, 16, 128, 2048, 0, 2, None, 0, None, 0, None) == 1
+    assert lib.pb_mxfp4_workspace_bytes(16, 5120, 3) == 40 * 3 * 128 * 128 * 4 and lib.pb_mxfp4_counters(16, 5120) == 40
+    assert lib.pb_mxfp4_gemv(p16, p16, p16, p16, p16, 128, 5, 128, 256, 0, None) == 2
+    assert lib.pb_mxfp4_gemv(p16, p16, p16, p16, p16, 128, 1, 128, 128, 0, None) == 2                # K % 256
+
+
+def test_split_rules_of_the_other_formats():
+    from prism_b200 import mxfp4, w4a8
+    # few-rows W4A8: time goes as waves / slices; Q6_K's 80 tiles of the down projection take 7 slices (4 waves)
+    assert w4a8.pick_split(8, 5120, 5120, 128) == 3 and w4a8.pick_split(8, 34816, 5120, 128) == 1
+    assert w4a8.pick_split(8, 5120, 17408, 64) == 7 and w4a8.pick_split(17, 5120, 17408, 64) == 1
+    # MXFP4: only where one row tile's tiles leave most SMs idle
+    assert mxfp4.pick_split(16, 5120, 5120) == 3 and mxfp4.pick_split(16, 34816, 5120) == 1
+    assert mxfp4.pick_split(300, 5120, 5120) == 1 and mxfp4.pick_split(1, 5120, 512) == 1
 
 
 def test_split_rule():
