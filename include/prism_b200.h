@@ -25,6 +25,9 @@ extern "C" {
 #define PB_EPI_I32 3  /* out int32 = the raw integer sums */
 #define PB_EPI_F32 4  /* out fp32 [M, N] = v (gk == 32, M <= 64: the vocabulary head's logits) */
 
+#define PB_W8A8_GEMV_ROWS 1 /* pb_w8a8_gemm, gk == K, split == 1, no pdl: this many rows against a matrix of fewer than
+                               9,472 rows run on the CUDA cores (the same bits) */
+
 #define PB_MODE_PLAIN 0
 #define PB_MODE_STORE_AMAX 1
 #define PB_MODE_USE_AMAX 2

@@ -17,6 +17,7 @@
 #include "w4a8_gemm.cuh"
 #include "w4a8_few.cuh"
 #include "w4a8_gemv.cuh"
+#include "w8a8_gemv.cuh"
 #include "mxfp4_gemm.cuh"
 #include "mxfp4_gemv.cuh"
 
@@ -456,6 +457,42 @@ int launch_mxfp4_gemv(const mxfp4::GemvArgs& p, cudaStream_t st) {
     return PB_OK;
 }
 
+template <int MR>
+int launch_w8a8_gemv(const w8a8::GemvArgs& p, cudaStream_t st) {
+    const int grid = (p.N + 7) / 8;                                // eight weight rows per CTA
+    if (grid < 8 * sm_count()) {
+        // few rows: the most warps per CTA with which the whole grid is resident at once
+        static int resident[5] = {};
+        int kw = 2;
+        for (int k = 4; k >= 2; --k) {
+            if (!resident[k]) {
+                int nb = 0;
+                PB_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, w8a8::w8a8_gemv_kernel<MR, true>, 32 * k, 2048));
+                resident[k] = nb > 0 ? nb : 1;
+            }
+            if ((long)grid <= (long)resident[k] * sm_count()) {
+                kw = k;
+                break;
+            }
+        }
+        w8a8::w8a8_gemv_kernel<MR, true><<<grid, 32 * kw, (size_t)kw * 8 * MR * sizeof(int), st>>>(p);
+    } else {
+        w8a8::w8a8_gemv_kernel<MR, false><<<grid, 32, 0, st>>>(p);
+    }
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+// PRISM_B200_W8A8_NO_GEMV=1 keeps the tensor-core kernel for one to eight rows (comparison runs).
+bool w8a8_no_gemv() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("PRISM_B200_W8A8_NO_GEMV");
+        v = (e && e[0] == '1') ? 1 : 0;
+    }
+    return v == 1;
+}
+
 // PRISM_B200_W4A8_NO_GEMV=1 keeps the tensor-core kernels for one to four rows (comparison runs).
 bool w4a8_no_gemv() {
     static int v = -1;
@@ -673,6 +710,15 @@ int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float
         return launch_swap_nb<true>(pick_nb(M), a, a_s, w, w_s, p, split, st);
     }
     if (gk != K) return PB_UNSUPPORTED_SHAPE;
+    if (M <= PB_W8A8_GEMV_ROWS && (N + 7) / 8 < 8 * sm_count() && split == 1 && !pdl && K % 256 == 0 &&
+        (epi == PB_EPI_BF16 || epi == PB_EPI_ADD) && !w8a8_no_gemv()) {
+        // one row against a matrix of few rows, no K split asked for: the CUDA-core kernel (the same bits: exact
+        // integer sums, the same two multiplies).  Measured at one row: qkv 9.8 / o 7.6 / down 18.4 µs against the
+        // tensor-core kernel's 12.4 / 10.9 / 20.7 with its fold; level on the 34816-row gate|up; behind from two rows
+        // on (its dp4a work grows with the rows: 61 µs at four rows of gate|up against 31).
+        w8a8::GemvArgs g{a, a_s, w, w_s, out, ldo, n_rows, M, N, K, epi};
+        return launch_w8a8_gemv<1>(g, st);
+    }
     if (M >= 512 && N >= 256 && pair_enabled() && split == 1) {
         if (epi == PB_EPI_I32) return launch_pair<w8a8::EPI_I32>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st);
         if (epi == PB_EPI_BF16) return launch_pair<w8a8::EPI_BF16>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st);

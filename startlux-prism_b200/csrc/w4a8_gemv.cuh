@@ -55,9 +55,9 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     return v;
 }
 
-// Sum v[0..NV) (NV = 1, 2, 4 or 8) over the eight lanes that differ in bits 2, 1, 0.  While more than one value is left a
+// Sum v[0..NV) (NV = 1, 2, 4, 8 or 16) over the eight lanes that differ in bits 2, 1, 0.  While more than one value is left a
 // step halves them (the lane whose bit is set keeps the upper half); after that the steps are plain butterflies.  On
-// return v[0] holds the total of the original index reduce8_index<NV>(lane).
+// return v[0] (and v[1] for sixteen values) hold the totals of the original indices reduce8_index<NV>(lane) (+ 1).
 template <int NV>
 __device__ __forceinline__ void reduce8(int (&v)[NV], int lane) {
     int n = NV;
@@ -82,17 +82,17 @@ __device__ __forceinline__ void reduce8(int (&v)[NV], int lane) {
 
 template <int NV>
 __device__ __forceinline__ int reduce8_index(int lane) {
-    static_assert(NV == 1 || NV == 2 || NV == 4 || NV == 8, "one, two, four or eight values");
+    static_assert(NV == 1 || NV == 2 || NV == 4 || NV == 8 || NV == 16, "a power of two up to sixteen values");
     int base = (lane & 4) ? NV / 2 : 0;
     if (NV >= 4) base += (lane & 2) ? NV / 4 : 0;
-    if (NV >= 8) base += (lane & 1);
+    if (NV >= 8) base += (lane & 1) ? NV / 8 : 0;
     return base;
 }
 
 template <int NV>
 __device__ __forceinline__ bool reduce8_owner(int lane) {
     // with fewer than eight values the butterfly steps leave copies: the lane with the low bits clear stores
-    return (lane & (8 / NV - 1)) == 0;
+    return NV >= 8 ? true : (lane & (8 / (NV >= 8 ? 8 : NV) - 1)) == 0;
 }
 
 __device__ __forceinline__ int dot32(const uint4& w0, const uint4& w1, const uint4& x0, const uint4& x1) {

@@ -52,6 +52,9 @@ def _workspace(device):
     return _WORKSPACE[key]
 
 
+GEMV_ROWS = 1        # gk == K: this many rows against few weight rows run on the CUDA cores (PB_W8A8_GEMV_ROWS)
+
+
 def pick_split(M, N, K, limit=MAX_SPLIT):
     """K splits.  Few rows (operand-swapped kernel): as many CTAs as stay resident together, at least two 128-byte K
     blocks each.  Many rows (tile kernel, one CTA per SM): only when the 128 x 256 tiles leave most SMs idle and K is
@@ -123,6 +126,10 @@ def gemm(a, a_s, w, w_s, out, n_rows, gk, epi=0, outs=None, cfg=None, slots=None
         if split > 1:
             ws, counters = _workspace(a.device)
         _call(a, a_s, w, w_s, out, out.stride(0), n_rows, gk, epi, split, 0, ws, counters, pdl=pdl)
+        return None
+    if cfg is None and not pdl and K % 256 == 0 and M <= GEMV_ROWS and (N + 7) // 8 < 8 * SM_COUNT:
+        # one row against few weight rows: the library's CUDA-core kernel (no K split: its CTAs already cover the SMs); same bits
+        _call(a, a_s, w, w_s, out, out.stride(0), n_rows, gk, epi, 1)
         return None
     split = int(cfg) if cfg is not None else pick_split(M, N, K)
     split = effective_split(K, split)

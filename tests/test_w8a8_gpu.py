@@ -14,7 +14,11 @@ pytestmark = pytest.mark.gpu
 # (M, N, K, live)
 SHAPES = [(8, 128, 256, 3), (1, 8192, 2560, 1), (16, 5120, 5120, 16), (64, 12352, 2560, 64), (64, 5120, 5120, 50),
           (33, 1000, 1024, 33), (100, 2560, 9216, 77), (256, 5120, 6144, 256), (384, 4608, 2560, 361),
-          (130, 328, 400, 129)]
+          (130, 328, 400, 129),
+          # one row with K % 256 == 0 against fewer than 9,472 weight rows: the CUDA-core kernel (cfg None / 1); N past
+          # a whole warp of rows; the others stay on the tensor-core kernel
+          (1, 5120, 5120, 1), (2, 1000, 1024, 2), (1, 34816, 512, 1), (1, 7168, 2560, 1), (1, 133, 256, 1),
+          (1, 5120, 17408, 1), (1, 9000, 2560, 1)]
 
 
 def run(dev, a, w, sa, sw, out, live, gk, epi, **kw):
