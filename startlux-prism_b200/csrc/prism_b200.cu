@@ -1039,14 +1039,15 @@ int pb_w4a8_gemm(const int8_t* xq, const float* a, const int8_t* xs, int Ma, int
     if (K % 256 || N % 4 || ldo < N) return PB_UNSUPPORTED_SHAPE;
     if (!aligned16(xq) || !aligned16(wq) || !aligned16(wsc) || !aligned16(wd) || (kind == 0 && (!aligned16(xs) ||
         !aligned16(wmn) || !aligned16(wdm)))) return PB_BAD_ARGUMENT;
-    // one or two rows, or up to four against a matrix of few rows: the CUDA-core kernel (measured: from three rows on a
-    // 34816-row matrix the tensor-core kernel below is level or ahead)
-    if ((M <= 2 || (M <= 4 && (N + 7) / 8 < 8 * sm_count())) && !w4a8_tile_only() && !w4a8_no_gemv()) {
+    // one or two rows, or up to eight against a matrix of few rows: the CUDA-core kernel (measured: from three rows on
+    // a 34816-row matrix the tensor-core kernel below is level or ahead)
+    if ((M <= 2 || (M <= 8 && (N + 7) / 8 < 8 * sm_count())) && !w4a8_tile_only() && !w4a8_no_gemv()) {
         w4a8::GemvArgs g{xq, a, xs, (const uint8_t*)wq, (const uint8_t*)wsc, (const uint8_t*)wmn, wd, wdm, out, ldo, n_rows, M, N,
                          K, Ma, epi};
         if (M == 1) return launch_w4a8_gemv<1>(kind, g, st);
         if (M == 2) return launch_w4a8_gemv<2>(kind, g, st);
-        return launch_w4a8_gemv<4>(kind, g, st);
+        if (M <= 4) return launch_w4a8_gemv<4>(kind, g, st);
+        return launch_w4a8_gemv<8>(kind, g, st);
     }
     if (M <= 32 && !w4a8_tile_only()) {                            // measured: the many-rows kernel is faster from 64 rows
         if (kind == 0) {

@@ -135,7 +135,7 @@ __device__ __forceinline__ void gemv_chain(const GemvArgs& p, const float* terms
 template <int MR, int R, bool SPLIT>
 __global__ void __launch_bounds__(SPLIT ? 128 : 32)
 w4a8_gemv_q4k_kernel(const GemvArgs p) {
-    constexpr int NV = R * MR, PD = GEMV_PD;
+    constexpr int NV = R * MR, PD = GEMV_PD, NF = NV >= 8 ? NV / 8 : 1;   // NF: (row, activation row) pairs per lane
     extern __shared__ float gemv_terms[];                          // SPLIT: [K / 256][4 * R * MR] chain terms
     const int KW = SPLIT ? (int)(blockDim.x >> 5) : 1;             // warps sharing the CTA's rows
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -145,9 +145,8 @@ w4a8_gemv_q4k_kernel(const GemvArgs p) {
     live = live < p.M ? live : p.M;
     if (live <= 0) return;
     const int NSB = p.K >> 8;
-    // the (row, activation row) pair whose fp32 chain this lane owns
+    // the (row, activation row) pairs whose fp32 chains this lane owns: NF consecutive activation rows of one row
     const int mine = reduce8_index<NV>(lane), r_o = mine / MR, m_o = mine % MR;
-    const int mm_o = m_o < p.M ? m_o : p.M - 1;
     const long row_o = n0 + r_o < p.N ? n0 + r_o : p.N - 1;        // rows past N read the last row and store nothing
     const uint8_t* wrow[R];
     const uint8_t* scrow[R];
@@ -162,7 +161,9 @@ w4a8_gemv_q4k_kernel(const GemvArgs p) {
     int sc[PD][R];
     uint2 mn[PD];
     float dv[PD], dmv[PD];
-    float y = 0.0f;
+    float y[NF];
+#pragma unroll
+    for (int i = 0; i < NF; ++i) y[i] = 0.0f;
     for (int b0 = warp; b0 < NSB; b0 += PD * KW) {
 #pragma unroll
         for (int j = 0; j < PD; ++j)
@@ -207,26 +208,33 @@ w4a8_gemv_q4k_kernel(const GemvArgs p) {
 #pragma unroll
                     for (int m = 0; m < MR; ++m) v[r * MR + m] = scb[r] * dot32(lo, hi, x0[m], x1[m]);
                 }
-                const uint4 s = __ldg((const uint4*)(p.xs + ((long)b * p.Ma + mm_o) * 16));
-                const float am = __ldg(p.a + (long)b * p.Ma + mm_o);
-                const int mins = __dp4a((int)mnb.x, (int)s.x, __dp4a((int)mnb.y, (int)s.y, 0)) +
-                                 64 * __dp4a((int)mnb.x, (int)s.z, __dp4a((int)mnb.y, (int)s.w, 0));
                 reduce8<NV>(v, lane);
-                float t = __fmul_rn(dvb, __int2float_rn(v[0]));
-                t = __fmaf_rn(ndm, __int2float_rn(mins), t);
-                if (!SPLIT) y = __fmaf_rn(am, t, y);
-                else if (reduce8_owner<NV>(lane)) gemv_terms[b * (4 * NV) + ((lane >> 3) * R + r_o) * MR + m_o] = t;
+#pragma unroll
+                for (int i = 0; i < NF; ++i) {                     // this lane's pairs: the same row, consecutive m
+                    const int mi = m_o + i < p.M ? m_o + i : p.M - 1;
+                    const uint4 s = __ldg((const uint4*)(p.xs + ((long)b * p.Ma + mi) * 16));
+                    const int mins = __dp4a((int)mnb.x, (int)s.x, __dp4a((int)mnb.y, (int)s.y, 0)) +
+                                     64 * __dp4a((int)mnb.x, (int)s.z, __dp4a((int)mnb.y, (int)s.w, 0));
+                    float t = __fmul_rn(dvb, __int2float_rn(v[i]));
+                    t = __fmaf_rn(ndm, __int2float_rn(mins), t);
+                    if (!SPLIT) y[i] = __fmaf_rn(__ldg(p.a + (long)b * p.Ma + mi), t, y[i]);
+                    else if (reduce8_owner<NV>(lane)) gemv_terms[b * (4 * NV) + ((lane >> 3) * R + r_o) * MR + m_o + i] = t;
+                }
             }
         }
     }
-    if (!SPLIT) gemv_store(p, y, n0 + r_o, m_o, live, reduce8_owner<NV>(lane));
-    else gemv_chain<MR, R>(p, gemv_terms, NSB, live);
+    if (!SPLIT) {
+#pragma unroll
+        for (int i = 0; i < NF; ++i) gemv_store(p, y[i], n0 + r_o, m_o + i, live, reduce8_owner<NV>(lane));
+    } else {
+        gemv_chain<MR, R>(p, gemv_terms, NSB, live);
+    }
 }
 
 template <int MR, int R, bool SPLIT>
 __global__ void __launch_bounds__(SPLIT ? 128 : 32)
 w4a8_gemv_q6k_kernel(const GemvArgs p) {
-    constexpr int NV = R * MR, PD = GEMV_PD;
+    constexpr int NV = R * MR, PD = GEMV_PD, NF = NV >= 8 ? NV / 8 : 1;   // NF: (row, activation row) pairs per lane
     extern __shared__ float gemv_terms[];                          // SPLIT: [K / 256][4 * R * MR] chain terms
     const int KW = SPLIT ? (int)(blockDim.x >> 5) : 1;             // warps sharing the CTA's rows
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -237,7 +245,6 @@ w4a8_gemv_q6k_kernel(const GemvArgs p) {
     if (live <= 0) return;
     const int NSB = p.K >> 8;
     const int mine = reduce8_index<NV>(lane), r_o = mine / MR, m_o = mine % MR;
-    const int mm_o = m_o < p.M ? m_o : p.M - 1;
     const long row_o = n0 + r_o < p.N ? n0 + r_o : p.N - 1;
     const uint8_t* wrow[R];
     const uint8_t* scrow[R];
@@ -251,7 +258,9 @@ w4a8_gemv_q6k_kernel(const GemvArgs p) {
     uint4 ring[PD][R][2];
     short sc[PD][R];                                               // two int8 sub-block scales
     float dv[PD];
-    float y = 0.0f;
+    float y[NF];
+#pragma unroll
+    for (int i = 0; i < NF; ++i) y[i] = 0.0f;
     for (int b0 = warp; b0 < NSB; b0 += PD * KW) {
 #pragma unroll
         for (int j = 0; j < PD; ++j)
@@ -304,14 +313,22 @@ w4a8_gemv_q6k_kernel(const GemvArgs p) {
                     }
                 }
                 reduce8<NV>(v, lane);
-                const float t = __fmul_rn(dvb, __int2float_rn(v[0]));
-                if (!SPLIT) y = __fmaf_rn(__ldg(p.a + (long)b * p.Ma + mm_o), t, y);
-                else if (reduce8_owner<NV>(lane)) gemv_terms[b * (4 * NV) + ((lane >> 3) * R + r_o) * MR + m_o] = t;
+#pragma unroll
+                for (int i = 0; i < NF; ++i) {
+                    const int mi = m_o + i < p.M ? m_o + i : p.M - 1;
+                    const float t = __fmul_rn(dvb, __int2float_rn(v[i]));
+                    if (!SPLIT) y[i] = __fmaf_rn(__ldg(p.a + (long)b * p.Ma + mi), t, y[i]);
+                    else if (reduce8_owner<NV>(lane)) gemv_terms[b * (4 * NV) + ((lane >> 3) * R + r_o) * MR + m_o + i] = t;
+                }
             }
         }
     }
-    if (!SPLIT) gemv_store(p, y, n0 + r_o, m_o, live, reduce8_owner<NV>(lane));
-    else gemv_chain<MR, R>(p, gemv_terms, NSB, live);
+    if (!SPLIT) {
+#pragma unroll
+        for (int i = 0; i < NF; ++i) gemv_store(p, y[i], n0 + r_o, m_o + i, live, reduce8_owner<NV>(lane));
+    } else {
+        gemv_chain<MR, R>(p, gemv_terms, NSB, live);
+    }
 }
 
 }  // namespace w4a8

@@ -26,7 +26,8 @@ def ref_gemm(xq, a, xs, w, epi, live, out=None):
 @pytest.mark.parametrize("m,live,n,k", [(1, 1, 256, 512), (7, 7, 320, 2560), (64, 50, 1024, 5120), (300, 300, 192, 1024),
                                         (130, 127, 4100, 512), (17, 17, 1000, 1024), (48, 33, 132, 768),
                                         (16, 16, 5120, 5120), (2, 2, 1000, 1024), (4, 3, 4100, 2560), (3, 3, 132, 768),
-                                        (4, 4, 100, 512), (1, 1, 5120, 5120)])
+                                        (4, 4, 100, 512), (1, 1, 5120, 5120), (8, 8, 1000, 1024), (6, 5, 320, 2560),
+                                        (8, 8, 5120, 5120), (5, 5, 132, 768)])
 def test_gemm_bits(dev, kind, m, live, n, k):
     w, wf = weights(kind, n, k, seed=n + k)
     x = synth.activations(m, k, seed=m, outliers=k // 64)
