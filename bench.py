@@ -170,6 +170,16 @@ def run_gpu(args):
     code, where = _lib.device_status()
     if code:
         raise SystemExit(f"device status {code} at {where:#x}")
+    step = lambda: stack(h0)                                      # noqa: E731
+    if args.graph:
+        # the whole pass (collectives included) as one CUDA graph: what a decode loop replays per token
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            stack(h0)
+        step = graph.replay
+        for _ in range(3):
+            step()
+        sync()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -178,7 +188,7 @@ def run_gpu(args):
     sync()
     e0.record()
     for _ in range(args.steps):
-        stack(h0)
+        step()
     e1.record()
     sync()
     ms = e0.elapsed_time(e1) / args.steps
@@ -197,7 +207,7 @@ def run_gpu(args):
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
                 "vs_baseline": None, "dtype": "s8", "data": "synthetic",
-                "config": {"workload": "w8a8-27b-layer-set", "rows": M, "layers": LAYERS,
+                "config": {"workload": "w8a8-27b-layer-set", "rows": M, "layers": LAYERS, "graph": bool(args.graph),
                            "parallelism": f"tp{world}", "l2": "inputs larger than L2 (1.3 GB of weights per pass)"},
                 "e2e": {"value": ops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
                         "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
@@ -225,6 +235,11 @@ def run_gpu(args):
             line["cpu_baseline"] = {"value": cops / dt / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
                                     "sample": f"{rows} of {M} rows through 1 of {LAYERS} layers"}
         print(json.dumps(line), flush=True)
+    if args.graph:
+        # a live graph holds the communicator's kernels: it goes before the process group does
+        step = None
+        del graph
+        torch.cuda.synchronize()
     if group is not None:
         sync()
         stack.close()
@@ -654,6 +669,7 @@ def main():
     ap.add_argument("--impl", default="prism_b200", choices=["prism_b200", "reference"])
     ap.add_argument("--rows", type=int, default=M_DEFAULT)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--graph", action="store_true", help="time the pass as a replayed CUDA graph (decode rows)")
     ap.add_argument("--detail", action="store_true", help="per-shape GEMM table instead of the JSON line")
     ap.add_argument("--probe", default=None, help="one kernel case, a few eager launches (for ncu)")
     ap.add_argument("--probe-rows", type=int, default=None, help="activation rows of the W4A8 decode probes")
