@@ -119,8 +119,8 @@ def run_reference(args):
     line = {"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "s8", "data": "synthetic",
-            "config": {"workload": "w8a8-27b-layer-set", "rows": M_DEFAULT, "layers": LAYERS,
-                       "l2": "inputs larger than L2"},
+            "config": {"workload": "w8a8-27b-layer-set", "rows": M_DEFAULT, "layers": LAYERS, "graph": False,
+                       "parallelism": f"tp{args.gpus}", "l2": "inputs larger than L2 (1.3 GB of weights per pass)"},
             "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
                              "sample": f"{rows} of {M_DEFAULT} rows through 1 of {LAYERS} layers per step"},
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
