@@ -101,6 +101,56 @@ def cpu_layer_pass(rows):
 CPU_SAMPLE_ROWS = 256
 
 
+def reference_gpu_kernels(rows):
+    """The reference's own GPU kernel for this path on this GPU, when a checkout of its package travelled with the
+    repository (baseline/_ref, never committed): its Triton W8A8 kernel (kernels/w8a8.py:31-98, what a B200 runs there:
+    it has no dispatch table for this GPU and its wgmma kernels are sm_90a-only) on the four projections at `rows`
+    rows, CUDA events, weights rotated over copies larger than L2.  Reported beside the CPU number; never the
+    measured product.  Any failure is reported as the reason it is unavailable."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "startlux_prism")):
+        return {"unavailable": "no reference checkout under baseline/_ref on this machine"}
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return {"unavailable": "no GPU"}
+        sys.path.insert(0, ref)
+        os.environ["STARTLUX_PRISM_GEMM"] = "triton"
+        from startlux_prism.kernels import w8a8 as RW8
+        dev = torch.device("cuda", 0)
+        gen = torch.Generator(device=dev).manual_seed(3)
+        out = {}
+        tot_ops = tot_s = 0.0
+        for name, (N, K, epi) in SHAPES.items():
+            copies = max(2, -(-2 * (126 << 20) // (N * K)))
+            ws = [torch.randint(-127, 128, (N, K), dtype=torch.int8, device=dev, generator=gen) for _ in range(copies)]
+            a = torch.randint(-127, 128, (rows, K), dtype=torch.int8, device=dev, generator=gen)
+            sa = torch.rand(rows, 1, device=dev, generator=gen) * 1e-2
+            sw = torch.rand(N, 1, device=dev, generator=gen) * 1e-3
+            o = torch.zeros(rows, N, dtype=torch.float32 if epi else torch.bfloat16, device=dev)
+            nr = torch.tensor([rows], dtype=torch.int32, device=dev)
+            cfg = RW8.pick(rows, N, K, epi)
+            for c in range(copies):
+                RW8.gemm(a, sa, ws[c], sw, o, nr, K, epi=epi, cfg=cfg)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for c in range(copies):
+                RW8.gemm(a, sa, ws[c], sw, o, nr, K, epi=epi, cfg=cfg)
+            e1.record()
+            torch.cuda.synchronize()
+            sec = e0.elapsed_time(e1) * 1e-3 / copies
+            out[name] = round(2.0 * rows * N * K / sec / 1e12, 1)
+            tot_ops += 2.0 * rows * N * K
+            tot_s += sec
+            del ws, a, o
+            torch.cuda.empty_cache()
+        return {"kernel": "the reference's Triton _w8a8_kernel (kernels/w8a8.py:31-98), unmodified", "rows": rows,
+                "tops_per_projection": out, "tops_layer_set": round(tot_ops / tot_s / 1e12, 1), "unit": UNIT}
+    except Exception as e:                              # noqa: BLE001
+        return {"unavailable": f"{type(e).__name__}: {str(e)[:200]}"}
+
+
 def run_reference(args):
     """The reference arm: the reference's CPU emulation of the path (restated in oracle/emulation.py; the reference's own
     is Python that needs its model files) on every host core, a bounded sample of the workload per step."""
@@ -125,6 +175,8 @@ def run_reference(args):
                              "sample": f"{rows} of {M_DEFAULT} rows through 1 of {LAYERS} layers per step"},
             "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
+    if not args.no_ref_gpu:
+        line["reference_gpu_kernels"] = reference_gpu_kernels(args.rows)
     print(json.dumps(line), flush=True)
 
 
@@ -170,6 +222,7 @@ def run_gpu(args):
     code, where = _lib.device_status()
     if code:
         raise SystemExit(f"device status {code} at {where:#x}")
+    int8_peak = measure_int8_peak() if rank == 0 else None
     step = lambda: stack(h0)                                      # noqa: E731
     if args.graph:
         # the whole pass (collectives included) as one CUDA graph: what a decode loop replays per token
@@ -185,13 +238,22 @@ def run_gpu(args):
         sampler.start()
     # ---- device-resident timing
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     sync()
     e0.record()
-    for _ in range(args.steps):
+    for i in range(args.steps):
         step()
+        marks[i].record()
     e1.record()
     sync()
     ms = e0.elapsed_time(e1) / args.steps
+    per_step = sorted(a.elapsed_time(b) for a, b in zip([e0] + marks[:-1], marks))
+    ms_median = per_step[len(per_step) // 2]
+    # the step's result as a checksum: every GPU count must print the same one (tensor-parallel bit-identity)
+    import zlib
+    final = stack(h0)
+    torch.cuda.synchronize()
+    crc = zlib.crc32(final.cpu().numpy().tobytes()) if rank == 0 else 0
     # ---- per-GEMM durations for the roofline (events around each launch, same stream)
     gemm_ms = time_gemms(stack, h0, args.steps)
     # ---- end to end: host buffers, copies inside the timed region, pipelined over three streams
@@ -211,23 +273,35 @@ def run_gpu(args):
                            "parallelism": f"tp{world}", "l2": "inputs larger than L2 (1.3 GB of weights per pass)"},
                 "e2e": {"value": ops / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
                         "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms},
-                "gpu_launches": launches_per_step(world) * args.steps, "clocks": clocks}
+                "gpu_launches": launches_per_step(world) * args.steps, "clocks": clocks,
+                "ms_per_step_median": ms_median, "value_at_median_step": ops / (ms_median * 1e-3) / 1e12,
+                "check": {"residual_crc32": f"{crc:08x}", "of": "fp32 residual [rows, 5120] after one pass of the seeded "
+                          "input; identical at every GPU count"}}
         if gemm_ms is not None:
             achieved = ops / world / (gemm_ms * 1e-3) / 1e12    # per GPU: this rank's share of the products / its GEMM time
-            peak = 2.0 * pk["bf16"]
-            # DRAM traffic per launch of the dominant kernel (the gate|up GEMM): ncu measured 1.00 x the algorithmic
-            # read bytes on the M = 2048 capture (profiles/w8a8_tile_kernel_gate_up_M2048.md); scaled to this M by the
-            # units processed: weights once + activations + bf16 output
+            peak, peak_mean = int8_peak
+            # DRAM bytes per launch of the dominant kernel (the gate|up GEMM): its algorithmic bytes (weights once +
+            # activations + bf16 output) times the ratio ncu measured on the one-launch capture at M = 2048 (300 MB of
+            # DRAM traffic against 332 MB algorithmic: part of the output was still in L2 when the capture ended)
             n_gu, k_gu = 34816 // world, 5120
-            traffic = n_gu * k_gu + M * k_gu + 2 * M * n_gu
+            algorithmic = n_gu * k_gu + M * k_gu + 2 * M * n_gu
             line["roofline"] = {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                                "frac": achieved / peak, "traffic": traffic,
+                                "frac": achieved / peak, "traffic": int(algorithmic * 0.90),
                                 "kernel": "w8a8_tile_kernel<256>", "gemm_ms_per_step": gemm_ms,
-                                "peak_note": f"2 x {pk['src']} sustained bf16 ({pk['bf16']}): the int8 tcgen05 rate is "
-                                             "twice the bf16 rate; nominal dense int8 4500; measured with "
-                                             "bench.py --probe peak: 4590 with zero operands at 1965 MHz, 3727 "
-                                             "sustained with random operands under the 1 kW cap (no memory traffic)",
-                                "traffic_note": "scaled from the ncu capture at M = 2048 (reads = 1.00 x algorithmic)"}
+                                "algorithmic_bytes": algorithmic,
+                                "peak_note": "int8 tensor-core rate measured in this process before the timed region: "
+                                             "tcgen05 kind::i8 128x256x32 on shared-memory-resident random operands, "
+                                             f"one CTA per SM, 0.3 s of launches; highest launch {peak:.0f} (used), "
+                                             f"mean {peak_mean:.0f}.  For context: 2 x {pk['src']} bf16 burst = "
+                                             f"{2 * pk['bf16_burst']:.0f}, 2 x sustained = {2 * pk['bf16']:.0f}, nominal "
+                                             "dense int8 4500",
+                                "frac_of_nominal_4500": achieved / 4500.0,
+                                "traffic_note": "algorithmic bytes x 0.90, the DRAM / algorithmic ratio of the ncu "
+                                                "capture at M = 2048; not measured at this M"}
+            if achieved > peak:
+                line["roofline"]["flag"] = "achieved above the measured peak: the probe ran at a lower clock than the step"
+        if world == 1 and not args.no_detail:
+            line["detail"] = quick_detail(dev, pk)
         if world == 1 and not args.no_cpu:
             rows = CPU_SAMPLE_ROWS
             cpu_layer_pass(rows)
@@ -244,6 +318,31 @@ def run_gpu(args):
         sync()
         stack.close()
         group.close()
+
+
+def measure_int8_peak(seconds=0.3):
+    """The int8 tensor-core ceiling of THIS GPU in THIS process: pb_int8_peak_probe (128 x 256 x 32 tcgen05 MMAs on
+    shared-memory-resident pseudo-random operands, one CTA per SM, no memory traffic) launched back to back for
+    `seconds`; returns (highest, mean) TOPS over the launches.  The highest is used as the roofline's denominator."""
+    import torch
+
+    from prism_b200 import _lib
+    L = _lib.lib()
+    iters = 4000
+    sms = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    ops = 2.0 * 128 * 256 * 128 * iters * sms
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(L.pb_int8_peak_probe(200, 1, 256, None, st), "peak probe")
+    torch.cuda.synchronize()
+    rates, t_end = [], time.time() + seconds
+    while time.time() < t_end:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        _lib.check(L.pb_int8_peak_probe(iters, 1, 256, None, st), "peak probe")
+        e1.record()
+        torch.cuda.synchronize()
+        rates.append(ops / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+    return max(rates), sum(rates) / len(rates)
 
 
 def launches_per_step(world):
@@ -286,10 +385,14 @@ def time_e2e(stack, h0, steps, sync):
     the timed region; copies of neighbouring steps overlap the compute on their own streams (two device buffers)."""
     import torch
     dev = h0.device
-    host_in = h0.cpu().pin_memory()
+    # several ranks on the row-split pass: a rank needs only its own M / n rows in and gives only those back (the
+    # int8 inputs of the column-parallel projections are what the ranks exchange), so the host copies shrink with n
+    own = bool(getattr(stack, "by_rows", False))
+    src = h0[stack.r0:stack.r0 + stack.Ml] if own else h0
+    host_in = src.cpu().pin_memory()
     host_out = torch.empty_like(host_in).pin_memory()
-    d_in = [torch.empty_like(h0) for _ in range(2)]
-    d_out = [torch.empty_like(h0) for _ in range(2)]
+    d_in = [torch.empty_like(src) for _ in range(2)]
+    d_out = [torch.empty_like(src) for _ in range(2)]
     s_in, s_out, s_c = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.current_stream(dev)
     ev_in = [torch.cuda.Event() for _ in range(2)]
     ev_c = [torch.cuda.Event() for _ in range(2)]
@@ -310,7 +413,7 @@ def time_e2e(stack, h0, steps, sync):
         s_c.wait_event(ev_in[b])
         if i >= 2:
             s_c.wait_event(ev_out[b])
-        out = stack(d_in[b])
+        out = stack(d_in[b], own_rows=True) if own else stack(d_in[b])
         ev_free_in[b].record(s_c)
         d_out[b].copy_(out, non_blocking=True)
         ev_c[b].record(s_c)
@@ -322,7 +425,7 @@ def time_e2e(stack, h0, steps, sync):
     s_c.wait_stream(s_in)
     t1.record(s_c)
     sync()
-    nbytes = h0.numel() * h0.element_size()
+    nbytes = src.numel() * src.element_size()
     return t0.elapsed_time(t1) / steps, nbytes, nbytes
 
 
@@ -352,6 +455,136 @@ def graph_time(fn_of_copy, copies, iters=None, reps=5):
         torch.cuda.synchronize()
         best = min(best, e0.elapsed_time(e1) * 1e3 / iters)
     return best
+
+
+def quick_detail(dev, pk):
+    """The rest of the metric in the contract line, a few seconds in all: per format (W8A8 one group / per-32 groups,
+    W4A8 on the Q4_K_M assignment, MXFP4) the GEMM rate at 8192 and 2048 rows and the algorithmic HBM rate at 16 rows
+    on the four projection shapes, config 0 itself (Q8_0 groups, 5120 x 5120, 16 rows), and the FP4 tensor-core ceiling.
+    Graph-timed with weight copies rotating through more than L2 (graph_time)."""
+    import torch
+
+    from prism_b200 import _lib, mxfp4, quant, w4a8, w8a8
+    L2 = 126 << 20
+    gen = torch.Generator(device=dev).manual_seed(11)
+    hbm = pk["hbm"]
+    out = {"hbm_peak_gbs": hbm, "note": "tops at M = 8192 / 2048 (prefill), us and fraction of the measured HBM copy rate "
+           "at M = 16 (decode; weights at GGUF density); o and down include the fp32 residual add"}
+    u8 = lambda *sh, lo=0, hi=256: torch.randint(lo, hi, sh, dtype=torch.uint8, device=dev, generator=gen)   # noqa: E731
+    i8 = lambda *sh: torch.randint(-127, 128, sh, dtype=torch.int8, device=dev, generator=gen)               # noqa: E731
+    f = lambda *sh, m=1e-3: torch.rand(*sh, device=dev, generator=gen) * m                                    # noqa: E731
+    kinds = {"qkv": [("q4k", 6144), ("q6k", 1024)], "o": [("q4k", 5120)], "gate_up": [("q4k", 34816)], "down": [("q6k", 5120)]}
+
+    def rand_w4(kind, n, k):
+        if kind == "q4k":
+            return w4a8.W4("q4k", u8(n, k // 2), u8(k // 256, n, 8, hi=64), u8(k // 256, n, 8, hi=64), f(k // 256, n),
+                           f(k // 256, n), n, k)
+        return w4a8.W4("q6k", torch.randint(-32, 32, (n, k), dtype=torch.int8, device=dev, generator=gen),
+                       torch.randint(-128, 128, (k // 256, n, 16), dtype=torch.int8, device=dev, generator=gen), None,
+                       f(k // 256, n), None, n, k)
+    for name, (N, K, epi) in SHAPES.items():
+        row = {}
+        odt = torch.bfloat16 if epi == 0 else torch.float32
+        # ---- W8A8, one scale group (the engine's mode) and Q8_0's own groups
+        copies = max(4, -(-3 * L2 // (N * K)))
+        ws = [i8(N, K) for _ in range(copies)]
+        sw1, sw32 = f(N), f(N, K // 32)
+        for M in (8192, 2048, 16):
+            a, sa1, nr = i8(M, K), f(M, m=1e-2), torch.tensor([M], dtype=torch.int32, device=dev)
+            o = torch.zeros(M, N, dtype=odt, device=dev)
+            slots = torch.zeros(4, M, N, dtype=torch.int32, device=dev) if (epi == 1 and M <= 64) else None
+            pend = {}
+
+            def call(c):
+                pend[0] = w8a8.gemm(a, sa1, ws[c], sw1, o, nr, K, epi=epi, slots=slots)
+            us = graph_time(call, copies, reps=3)
+            if M > 64:
+                row[f"w8a8_tops_M{M}"] = round(2.0 * M * N * K / us / 1e6)
+            else:
+                if pend[0] is not None:
+                    us += graph_time(lambda c: quant.fold(o, slots, pend[0], nr, M), 1, iters=8, reps=3)
+                nbytes = N * K + 4 * N + M * K + 4 * M + (2 if epi == 0 else 8) * M * N
+                row["w8a8_M16_us"], row["w8a8_M16_hbm_frac"] = round(us, 1), round(nbytes / us / 1e3 / hbm, 3)
+                sa32 = f(M, K // 32, m=1e-2)
+                us = graph_time(lambda c: w8a8.gemm(a, sa32, ws[c], sw32, o, nr, 32, epi=epi), copies, reps=3)
+                nbytes = N * K * 34 / 32 + M * K * 36 / 32 + (2 if epi == 0 else 8) * M * N
+                row["w8a8_q8_0_groups_M16_us"], row["w8a8_q8_0_groups_M16_hbm_frac"] = round(us, 1), round(nbytes / us / 1e3 / hbm, 3)
+            del a, o, slots
+        del ws
+        torch.cuda.empty_cache()
+        # ---- W4A8
+        wbytes = sum(n * K * (144 if kind == "q4k" else 210) // 256 for kind, n in kinds[name])
+        copies = max(2, -(-2 * L2 // wbytes))
+        segsets = []
+        for _ in range(copies):
+            segs, off = [], 0
+            for kind, n in kinds[name]:
+                segs.append((rand_w4(kind, n, K), off))
+                off += n
+            segsets.append(segs)
+        for M in (8192, 16):
+            x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
+            q = torch.empty(M, K, dtype=torch.int8, device=dev)
+            sa = torch.empty(K // 256, M, device=dev)
+            xs = torch.empty(K // 256, M, 16, dtype=torch.int8, device=dev)
+            nr = torch.tensor([M], dtype=torch.int32, device=dev)
+            quant.rows_g(x, q, sa, xs, nr, M)
+            o = torch.zeros(M, N, dtype=odt, device=dev)
+            us = graph_time(lambda c: w4a8.gemm_segs(q, sa, xs, segsets[c], o, nr, epi), copies, reps=3)
+            if M > 64:
+                row[f"w4a8_tops_M{M}"] = round(2.0 * M * N * K / us / 1e6)
+            else:
+                nbytes = wbytes + M * K * (1 + 20 / 256) + (2 if epi == 0 else 8) * M * N
+                row["w4a8_M16_us"], row["w4a8_M16_hbm_frac"] = round(us, 1), round(nbytes / us / 1e3 / hbm, 3)
+            del x, q, o
+        del segsets
+        torch.cuda.empty_cache()
+        # ---- MXFP4
+        copies = max(2, -(-2 * L2 // (N * K * 17 // 32)))
+        wms = [mxfp4.prepare(mxfp4.MX4(u8(N, K // 2), u8(N, K // 32, lo=118, hi=126), N, K)) for _ in range(copies)]
+        for M in (8192, 16):
+            x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
+            q = torch.empty(M, K // 2, dtype=torch.uint8, device=dev)
+            sc = torch.empty(M, K // 32, dtype=torch.uint8, device=dev)
+            mxfp4.quantize_act(x, q, sc)
+            o = torch.zeros(M, N, dtype=odt, device=dev)
+            mxfp4.gemm(q, sc, wms[0], o, M, epi=epi)
+            us = graph_time(lambda c: mxfp4.gemm(q, sc, wms[c], o, M, epi=epi), copies, reps=3)
+            if M > 64:
+                row[f"mxfp4_tflops_M{M}"] = round(2.0 * M * N * K / us / 1e6)
+            else:
+                nbytes = (N + M) * K * 17 / 32 + (2 if epi == 0 else 8) * M * N
+                row["mxfp4_M16_us"], row["mxfp4_M16_hbm_frac"] = round(us, 1), round(nbytes / us / 1e3 / hbm, 3)
+            del x, q, o
+        del wms
+        torch.cuda.empty_cache()
+        out[name] = row
+    out["config0_q8_0_5120x5120_M16_us"] = out["o"].get("w8a8_q8_0_groups_M16_us")
+    L = _lib.lib()
+    if hasattr(L, "pb_mxf4_peak_probe"):
+        sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        iters = 4000
+        st = torch.cuda.current_stream().cuda_stream
+        _lib.check(L.pb_mxf4_peak_probe(200, 1, None, st), "mxf4 peak probe")
+        torch.cuda.synchronize()
+        rates, t_end = [], time.time() + 0.3
+        while time.time() < t_end:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            _lib.check(L.pb_mxf4_peak_probe(iters, 1, None, st), "mxf4 peak probe")
+            e1.record()
+            torch.cuda.synchronize()
+            rates.append(2.0 * 128 * 256 * 256 * iters * sms / (e0.elapsed_time(e1) * 1e-3) / 1e12)
+        out["fp4_peak_tflops_measured"] = round(max(rates))
+        out["fp4_peak_note"] = ("tcgen05 kind::mxf4.block_scale 128x256x64 on shared-memory-resident operands, one CTA per "
+                                f"SM, 0.3 s: highest launch {max(rates):.0f}, mean {sum(rates) / len(rates):.0f}; nominal "
+                                "dense FP4 9000")
+        for name in SHAPES:
+            if "mxfp4_tflops_M8192" in out[name]:
+                out[name]["mxfp4_frac_of_measured_fp4_peak"] = round(out[name]["mxfp4_tflops_M8192"] / max(rates), 3)
+    code, where = _lib.device_status()
+    out["device_status"] = code
+    return out
 
 
 def run_detail(args):
@@ -520,7 +753,9 @@ def run_detail(args):
 # ------------------------------------------------------------------------------------------------------ probes
 def run_probe(args):
     """A few eager launches of one kernel on a case larger than L2 but small in memory: the command ncu captures
-    (`ncu -k regex:<kernel> -c 3 python bench.py --probe <case>`); also prints the CUDA-event time per launch."""
+    (`ncu --clock-control none --metrics gpu__time_duration.sum -k regex:<kernel> -c 3 python bench.py --probe <case>`;
+    sections or more metrics only with `-c 1`, and only after the same command has exited 0 without ncu); also prints
+    the CUDA-event time per launch."""
     import torch
 
     from prism_b200 import _lib, mxfp4, quant, synth, w4a8, w8a8
@@ -664,11 +899,13 @@ def run_peak(dev):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="prism_b200", choices=["prism_b200", "reference"])
     ap.add_argument("--rows", type=int, default=M_DEFAULT)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU-baseline leg")
+    ap.add_argument("--no-ref-gpu", action="store_true", help="reference arm: skip timing the reference's Triton kernel")
+    ap.add_argument("--no-detail", action="store_true", help="skip the short per-format detail object of the JSON line")
     ap.add_argument("--graph", action="store_true", help="time the pass as a replayed CUDA graph (decode rows)")
     ap.add_argument("--detail", action="store_true", help="per-shape GEMM table instead of the JSON line")
     ap.add_argument("--probe", default=None, help="one kernel case, a few eager launches (for ncu)")

@@ -22,6 +22,7 @@ extern "C" {
 
 #define PB_EPI_BF16 0 /* out bf16 [M, N] = v */
 #define PB_EPI_ADD 1  /* out fp32 [M, N] = add_rn(out, v) */
+#define PB_EPI_SWIGLU 2 /* pb_w8a8_gemm_swiglu only */
 #define PB_EPI_I32 3  /* out int32 = the raw integer sums */
 #define PB_EPI_F32 4  /* out fp32 [M, N] = v (gk == 32, M <= 64: the vocabulary head's logits) */
 
@@ -40,6 +41,18 @@ int pb_last_cuda_error(void);
  * expires.  Synchronizes the device: for tests and error paths, not for the hot path. */
 int pb_device_status(int* code, unsigned* where, int reset);
 
+/* Every device-side wait (an mbarrier a copy or an MMA completes, a flag or word another GPU writes) is bounded: when
+ * the bound runs out the kernel records PB_DEVICE_TIMEOUT with a code for the place, every role of the CTA leaves its
+ * loop, copies already requested are given the same bound to land, tensor memory is freed and the kernel returns - no
+ * trap, the context stays usable.  The reference's waits are unbounded spins (kernels/quant.py:105-108, :204-206).
+ *   pb_set_wait_limit_ns  the bound on the current device (default 4 s; 0 restores it).  Synchronous.
+ *   pb_test_drop_loads    failure injection for tests, on the host: while on, the many-rows W8A8 kernel's producers
+ *                         request no tiles, so its consumers' waits run out.  Results of such launches are undefined.
+ * After a PB_DEVICE_TIMEOUT the split-K counters of the launch that gave up may be left non-zero: zero them (and the
+ * status word, pb_device_status) before the workspace is used again. */
+int pb_set_wait_limit_ns(unsigned long long ns);
+int pb_test_drop_loads(int on);
+
 /* Bytes of workspace and number of int32 counters pb_w8a8_gemm needs for a split-K product whose splits are added
  * inside the kernel (epi 0 / 1 with split > 1).  Stands in for kernels/cuda_ext.py:22-23,139-143 (_workspace). */
 long pb_w8a8_workspace_bytes(int M, int N, int split);
@@ -49,6 +62,8 @@ int pb_w8a8_counters(int M, int N);
  * csrc/w8a8_wgmma.cu:709-713) and the Triton kernel behind kernels/w8a8.py:183-231 (gemm) and :234-261 (gemm_i32).
  *   a int8 [M, K], w int8 [N, K] (both K-contiguous, 16-byte aligned, K % 16 == 0);
  *   gk == K: a_s fp32 [M], w_s fp32 [N];  gk == 32: a_s fp32 [M, K/32], w_s fp32 [N, K/32] (K % 128 == 0);
+ *   any other gk that is a multiple of 32 and divides K (K % 128 == 0): a_s fp32 [M, K/gk], w_s fp32 [N, K/gk], the
+ *   groups' scaled sums added in fp32 in group order (kernels/w8a8.py:64-76); epi 0 / 1, split == 1;
  *   epi PB_EPI_BF16 / PB_EPI_ADD: out [M, N] with row stride ldo elements;
  *   epi PB_EPI_I32: out = slots int32 [split, rows, N] (ldo = N, slot_stride = rows * N elements): split z's sums.
  *   split > 1 with epi 0 / 1 (gk == K, M <= 64): the splits are added inside the kernel through `workspace`
@@ -62,6 +77,15 @@ int pb_w8a8_counters(int M, int N);
 int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, void* out, long ldo,
                  const int* n_rows, int M, int N, int K, int gk, int epi, int split, long slot_stride,
                  void* workspace, long workspace_bytes, int* counters, int n_counters, int pdl, void* stream);
+
+/* The gate|up projection with the SwiGLU and the next projection's activation quantization fused into its epilogue.
+ * Replaces the Triton kernel's EPI 2 (kernels/w8a8.py:9-11,86-98): w int8 [N = 2 FF, K] holds, per tile of bn rows,
+ * bn / 2 gate rows and then the matching bn / 2 up rows (w8a8.interleave_gate_up, kernels/w8a8.py:289-294), w_s fp32
+ * [N] in the same order, one scale group over K (a_s fp32 [M]).  For every row and tile:
+ *   act = silu(gate) * up of the scaled fp32 sums; s[m, tile] = max(|act|max, 1e-10) / 127; q = rint(act / s)
+ * q int8 [M, FF] (row stride ldq), s fp32 [M, N / bn]: the input of a down projection with gk = bn / 2.  bn 64 or 128. */
+int pb_w8a8_gemm_swiglu(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, int8_t* q, long ldq, float* s,
+                        const int* n_rows, int M, int N, int K, int bn, void* stream);
 
 /* The int32 partial sums of a row-parallel projection on several GPUs, stored where they will be folded: output rows
  * [o * block_rows, (o + 1) * block_rows) go to blocks[o] (int32 [block_rows, N], row stride ldo), which may be another
@@ -188,6 +212,10 @@ int pb_mxfp4_gemm_split(const void* aq, const void* a_sf, const void* bq, const 
  * batches of four 128 x mma_n x 32 MMAs each, mma_n a multiple of 16 up to 256; pattern 0 = zero operands, 1 =
  * pseudo-random bytes).  ops = 2 * 128 * mma_n * 128 * iters per SM.  Counterpart of the reference's bench/csrc/mma_peak.cu.  cycles (device, one per SM) may be NULL. */
 int pb_int8_peak_probe(int iters, int pattern, int mma_n, unsigned long long* cycles, void* stream);
+
+/* The same for the FP4 tensor-core rate: `iters` batches of four 128 x 256 x 64 tcgen05 kind::mxf4.block_scale MMAs
+ * per SM on shared-memory-resident operands with unit scales.  ops = 2 * 128 * 256 * 256 * iters per SM. */
+int pb_mxf4_peak_probe(int iters, int pattern, unsigned long long* cycles, void* stream);
 
 /* pb_w8a8_gemm for callers that cannot allocate device memory.  No counterpart in the reference (its stream-K
  * workspace is always a torch allocation, kernels/cuda_ext.py:139-143).

@@ -62,6 +62,19 @@ def w8a8_gemm(a, a_s, w, w_s, gk, epi, live=None, out=None):
     return o
 
 
+def w8a8_swiglu_epi(a, a_s, w, w_s, bn, live=None):
+    """The GEMM's fused SwiGLU epilogue on interleaved gate|up rows (tiles of bn): a int8 [M, K], a_s fp32 [M], w int8
+    [N, K], w_s fp32 [N] -> (q int8 [M, N / 2], s fp32 [M, N / bn])."""
+    M, K = a.shape
+    N = w.shape[0]
+    live = M if live is None else live
+    q = np.zeros((M, N // 2), np.int8)
+    s = np.zeros((M, N // bn), np.float32)
+    lib().orc_w8a8_swiglu_epi(_p(_c(a, np.int8)), _p(_c(np.ravel(a_s), np.float32)), _p(_c(w, np.int8)),
+                              _p(_c(np.ravel(w_s), np.float32)), _p(q), _p(s), live, N, K, bn)
+    return q, s
+
+
 def fold(h, slots, a_s, w_s, live=None):
     """h fp32 [rows, N] (a copy is returned), slots int32 [S, rows, N]."""
     h = np.array(h, dtype=np.float32, copy=True, order="C")

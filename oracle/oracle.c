@@ -69,6 +69,42 @@ void orc_w8a8_gemm(const int8_t *a, const float *a_s, const int8_t *w, const flo
     }
 }
 
+/* The fused SwiGLU epilogue, kernels/w8a8.py:86-98 (EPI 2), one scale group over K: the weight rows come in tiles of
+ * bn rows, bn / 2 gate rows then the matching up rows (interleave_gate_up, w8a8.py:289-294).  Per row and tile:
+ *   acc = mul_rn(mul_rn(float(acci), sa[m]), sw[n]);  act = gate / (1 + exp(-gate)) * up;
+ *   scale = max(max|act|, 1e-10) / 127;  q = rint(act / scale).
+ * q [M, N / 2] int8, s [M, N / bn] fp32.  exp is the C library's expf here: kernels are compared within one int8 step. */
+void orc_w8a8_swiglu_epi(const int8_t *a, const float *a_s, const int8_t *w, const float *w_s, int8_t *q, float *s,
+                         int live, int N, int K, int bn) {
+    int hb = bn / 2, tiles = N / bn;
+#pragma omp parallel for schedule(static)
+    for (long idx = 0; idx < (long)live * tiles; ++idx) {
+        int m = (int)(idx / tiles), t = (int)(idx % tiles);
+        const int8_t *ar = a + (long)m * K;
+        float act[128];
+        float amax = 0.0f;
+        for (int c = 0; c < hb; ++c) {
+            const int8_t *gr = w + (long)(t * bn + c) * K, *ur = w + (long)(t * bn + hb + c) * K;
+            int32_t gi = 0, ui = 0;
+            for (int k = 0; k < K; ++k) {
+                gi += (int32_t)ar[k] * (int32_t)gr[k];
+                ui += (int32_t)ar[k] * (int32_t)ur[k];
+            }
+            float g = (float)gi * a_s[m];
+            g = g * w_s[t * bn + c];
+            float u = (float)ui * a_s[m];
+            u = u * w_s[t * bn + hb + c];
+            float v = g / (1.0f + expf(-g));
+            v = v * u;
+            act[c] = v;
+            if (fabsf(v) > amax) amax = fabsf(v);
+        }
+        float scale = (amax > 1e-10f ? amax : 1e-10f) / 127.0f;
+        for (int c = 0; c < hb; ++c) q[(long)m * (N / 2) + (long)t * hb + c] = (int8_t)nearbyintf(act[c] / scale);
+        s[(long)m * tiles + t] = scale;
+    }
+}
+
 /* ------------------------------------------------------------------------------------------- deferred residual add
  * kernels/quant.py:128-141 (_fold_parts), :434-446 (_fold_kernel): tot = sum over slots (int32, exact);
  * h = add_rn(h, mul_rn(mul_rn(float(tot), a_s[r]), w_s[c])).  slots [S, rows, N] with slot stride `ss` elements. */

@@ -15,9 +15,12 @@ _SIGS = {
     "pb_status_string": ([_i], ctypes.c_char_p),
     "pb_last_cuda_error": ([], _i),
     "pb_device_status": ([ctypes.POINTER(_i), ctypes.POINTER(ctypes.c_uint), _i], _i),
+    "pb_set_wait_limit_ns": ([ctypes.c_ulonglong], _i),
+    "pb_test_drop_loads": ([_i], _i),
     "pb_w8a8_workspace_bytes": ([_i, _i, _i], _l),
     "pb_w8a8_counters": ([_i, _i], _i),
     "pb_w8a8_gemm": ([_vp, _vp, _vp, _vp, _vp, _l, _vp, _i, _i, _i, _i, _i, _i, _l, _vp, _l, _vp, _i, _i, _vp], _i),
+    "pb_w8a8_gemm_swiglu": ([_vp, _vp, _vp, _vp, _vp, _l, _vp, _vp, _i, _i, _i, _i, _vp], _i),
     "pb_w8a8_gemm_scatter": ([_vp, _vp, _vp, _i, _i, _l, _vp, _i, _i, _i, _vp], _i),
     "pb_peer_alloc": ([_l, _vp, _vp], _i),
     "pb_peer_open": ([_vp, _vp], _i),
@@ -49,6 +52,7 @@ _SIGS = {
 # entry points added by later sections of the header; bound when present in the built library
 _OPTIONAL = {
     "pb_int8_peak_probe": ([_i, _i, _i, _vp, _vp], _i),
+    "pb_mxf4_peak_probe": ([_i, _i, _vp, _vp], _i),
     "pb_w8a8_static_scratch_bytes": ([], _l),
     "pb_w8a8_gemm_static": ([_vp, _vp, _vp, _vp, _vp, _l, _vp, _i, _i, _i, _i, _i, _vp], _i),
 }
@@ -103,4 +107,9 @@ def device_status(reset=True):
     """(code, where) of the current device's status word (synchronizes)."""
     c, w = ctypes.c_int(0), ctypes.c_uint(0)
     check(lib().pb_device_status(ctypes.byref(c), ctypes.byref(w), int(reset)), "pb_device_status")
+    if c.value and reset:
+        # a launch that gave up may have left split-K arrival counters non-zero: later products would skip their
+        # epilogue.  Every module's counters on this device start again from zero.
+        from . import w8a8
+        w8a8.reset_workspace()
     return c.value, w.value

@@ -17,6 +17,9 @@
 __device__ int g_pb_device_status = 0;
 __device__ unsigned int g_pb_device_status_where = 0;
 
+// The bound of every device-side wait in nanoseconds (pb_set_wait_limit_ns; read only on a wait's slow path).
+__device__ unsigned long long g_pb_wait_ns = 4000000000ull;
+
 __device__ __forceinline__ void pb_report(int code, unsigned int where) {
     atomicCAS(&g_pb_device_status, 0, code);
     atomicCAS(&g_pb_device_status_where, 0u, where);
@@ -77,7 +80,7 @@ __device__ __forceinline__ bool mbar_test_sleep(uint32_t bar, uint32_t parity, u
     return ok != 0;
 }
 
-// A wait with a wall-clock bound (about 4 s).  On expiry it records PB_DEVICE_TIMEOUT with `where`, raises the CTA's
+// A wait with a wall-clock bound (g_pb_wait_ns: 4 s unless pb_set_wait_limit_ns changed it).  On expiry it records PB_DEVICE_TIMEOUT with `where`, raises the CTA's
 // abort flag (a shared-memory word every role polls) and returns false; the caller leaves its loop and the kernel
 // runs to its normal end (tensor memory freed, no trap).  Also returns false at once when another role aborted.
 #define PB_WAIT_NS 4000000000ull
@@ -93,7 +96,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_test(bar, parity)) return true;
         if ((it & 0x3ff) == 0) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > PB_WAIT_NS) {
+            if (global_timer_ns() - t0 > *(volatile unsigned long long*)&g_pb_wait_ns) {
                 *abort_flag = 1;
                 pb_report(PB_DEVICE_TIMEOUT, where);
                 return false;

@@ -699,4 +699,62 @@ mxfp4_gemm256_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// ================================================================================================= peak probe
+// The FP4 tensor-core rate with no operand traffic: every CTA fills one stage of shared memory once (pattern 0: zeros,
+// 1: pseudo-random e2m1 codes), copies unit scale factors (UE8M0 127 = 1.0) into tensor memory, and its MMA thread
+// issues `iters` batches of four 128 x 256 x 64 block-scaled MMAs on it.  ops = 2 * 128 * 256 * 256 * iters per SM.
+// The ceiling the MXFP4 GEMMs are quoted against (the method of the reference's bench/csrc/mma_peak.cu, on tcgen05
+// kind::mxf4).
+__global__ void __launch_bounds__(128, 1) mxf4_peak_kernel(int iters, int pattern, unsigned long long* cycles) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ uint64_t done;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    const int warp = threadIdx.x >> 5;
+    constexpr int OPER = (128 + 256) * 128;                    // A 128 rows + B 256 rows, 128 bytes of K each
+    for (int i = threadIdx.x; i < OPER / 4; i += blockDim.x) {
+        uint32_t v = (uint32_t)i * 2654435761u + blockIdx.x * 40503u;
+        v ^= v >> 13;
+        v *= 0x9E3779B1u;
+        ((uint32_t*)smem)[i] = pattern ? (v ^ (v >> 15)) : 0u;
+    }
+    for (int i = threadIdx.x; i < 512 / 4; i += blockDim.x) ((uint32_t*)(smem + OPER))[i] = 0x7f7f7f7fu;   // scales 1.0
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&done), 1);
+        abort_flag = 0;
+        mbar_fence_init();
+    }
+    if (warp == 0) {
+        tmem_alloc(smem_u32(&tmem_slot), 512);
+        tmem_relinquish();
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    if (threadIdx.x == 0) {
+        const uint32_t sf = smem_u32(smem + OPER);
+        const uint32_t sfa_t = tmem_base + 256, sfb_t = sfa_t + 8;
+        for (int c = 0; c < 6; ++c) tmem_cp_sf(sfa_t + 4 * c, sf);         // A: 2 K blocks; B: 2 x 2 (rows 0-127, 128-255)
+        const uint64_t ad = umma_desc_k128(smem_u32(smem)), bd = umma_desc_k128(smem_u32(smem + 128 * 128));
+        const long long c0 = clock64();
+        for (int it = 0; it < iters; ++it) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t sf_id = (k & 1) * 2;
+                umma_mxf4(tmem_base, umma_desc_advance(ad, k * 32), umma_desc_advance(bd, k * 32),
+                          idesc_mxf4(128, 256, sf_id, sf_id), sfa_t + (k >> 1) * 4, sfb_t + (k >> 1) * 8, (it | k) ? 1u : 0u);
+            }
+        }
+        tc_commit(smem_u32(&done));
+        mbar_wait(smem_u32(&done), 0, &abort_flag, 0x1a00);
+        if (cycles) cycles[blockIdx.x] = (unsigned long long)(clock64() - c0);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) tmem_dealloc(tmem_base, 512);
+}
+
 }  // namespace mxfp4

@@ -14,6 +14,7 @@
 #include "quant.cuh"
 #include "quant_pipe.cuh"
 #include "w8a8_gemm.cuh"
+#include "w8a8_groups.cuh"
 #include "w4a8_gemm.cuh"
 #include "w4a8_few.cuh"
 #include "w4a8_gemv.cuh"
@@ -113,22 +114,56 @@ int tensor_map(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer
     return PB_OK;
 }
 
+// Per-device state.  One process may drive several GPUs (one context each): the SM count, a kernel's opt-in to more
+// than 48 KB of dynamic shared memory (cudaFuncSetAttribute applies to the current device only) and the occupancy
+// answers are therefore kept per device ordinal, looked up with the device current at the call.
+constexpr int kMaxDevices = 64;
+
+int current_device() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+    return dev;
+}
+
 int sm_count() {
-    static int n = 0;
-    if (!n) {
-        int dev = 0;
-        cudaGetDevice(&dev);
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        if (n <= 0) n = 148;
+    static int n[kMaxDevices] = {};
+    const int dev = current_device();
+    if (!n[dev]) {
+        int v = 0;
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+        n[dev] = v > 0 ? v : 148;
     }
-    return n;
+    return n[dev];
+}
+
+// Opt a kernel in to `bytes` of dynamic shared memory on the current device, once per (device, kernel).
+int set_smem_raw(const void* fn, int bytes) {
+    struct Key {
+        const void* fn;
+        int dev;
+        bool operator==(const Key& o) const { return fn == o.fn && dev == o.dev; }
+    };
+    struct Hash {
+        size_t operator()(const Key& k) const { return (size_t)k.fn * 31 + (size_t)k.dev; }
+    };
+    static std::mutex mu;
+    static std::unordered_map<Key, int, Hash> done;
+    const Key key{fn, current_device()};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = done.find(key);
+    if (it != done.end() && it->second >= bytes) return PB_OK;
+    PB_CUDA(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    done[key] = bytes;
+    return PB_OK;
 }
 
 template <typename Kernel>
 int set_smem(Kernel k, int bytes) {
-    PB_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
-    return PB_OK;
+    return set_smem_raw((const void*)k, bytes);
 }
+
+// Failure injection from the host (pb_test_drop_loads): the many-rows W8A8 kernel's producers request no tiles.
+int g_drop_loads = 0;
 
 // ------------------------------------------------------------------------------------------------- W8A8 launches
 // How the many-rows kernel adds into the fp32 residual.  PRISM_B200_ADD = regs: read, add, write through registers;
@@ -146,7 +181,7 @@ int add_mode() {
 template <int BN, int EPI>
 int launch_tile(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, void* out, long ldo,
                 const int* n_rows, int M, int N, int K, cudaStream_t st, int split = 1, void* workspace = nullptr,
-                int* counters = nullptr, const w8a8::RowBlocks* blocks = nullptr) {
+                int* counters = nullptr, const w8a8::RowBlocks* blocks = nullptr, float* souts = nullptr, int gbn = 0) {
     using C = w8a8::TileCfg<BN>;
     CUtensorMap ta, tw;
     int rc;
@@ -155,11 +190,7 @@ int launch_tile(const int8_t* a, const float* a_s, const int8_t* w, const float*
     auto kern = w8a8::w8a8_tile_kernel<BN, EPI>;
     constexpr int smem = EPI == w8a8::EPI_ADD ? C::SMEM_ADD : C::SMEM;
     static_assert(smem <= 232448, "tile kernel shared memory");
-    static bool configured = false;
-    if (!configured) {
-        if ((rc = set_smem(kern, smem))) return rc;
-        configured = true;
-    }
+    if ((rc = set_smem(kern, smem))) return rc;
     // the coalesced epilogue moves 32-bit words: bf16 outputs need an even row stride and a 4-byte aligned base
     int word_ok = EPI == w8a8::EPI_BF16 ? (((uintptr_t)out & 3) == 0 && ldo % 2 == 0) : 1;
     // residual add: 32 x 32 fp32 boxes added into out by the copy engine (bit 1 of word_ok), when out can be a tensor map
@@ -170,6 +201,7 @@ int launch_tile(const int8_t* a, const float* a_s, const int8_t* w, const float*
     } else if (EPI == w8a8::EPI_ADD && split == 1 && add_mode() == 2) {
         word_ok |= 4;
     }
+    if (g_drop_loads) word_ok |= 16;                               // failure injection (pb_test_drop_loads)
     // weight tiles fastest when the activations are the larger operand, do not fit in L2 and the weights do
     if ((long)M * K > (long)N * K && (long)M * K > (64l << 20) && (long)N * K <= (100l << 20)) word_ok |= 8;
     const int KB = (K + 127) / 128;
@@ -179,7 +211,7 @@ int launch_tile(const int8_t* a, const float* a_s, const int8_t* w, const float*
     w8a8::RowBlocks rb{};
     if (blocks) rb = *blocks;
     kern<<<grid, w8a8::TileWarps<EPI>::THREADS, smem, st>>>(ta, tw, tout, a_s, w_s, out, ldo, n_rows, M, N, K, word_ok,
-                                                           split, kbs, (int32_t*)workspace, counters, rb);
+                                                           split, kbs, (int32_t*)workspace, counters, rb, souts, gbn);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }
@@ -233,11 +265,7 @@ int launch_pair(const int8_t* a, const float* a_s, const int8_t* w, const float*
     if ((rc = tensor_map(&ta, a, K, M, K, w8a8::BK, w8a8::BM, 0))) return rc;
     if ((rc = tensor_map(&tw, w, K, N, K, w8a8::BK, w8a8::BM, 0))) return rc;
     auto kern = w8a8::w8a8_pair_kernel<EPI>;
-    static bool configured = false;
-    if (!configured) {
-        if ((rc = set_smem(kern, w8a8::PAIR_SMEM))) return rc;
-        configured = true;
-    }
+    if ((rc = set_smem(kern, w8a8::PAIR_SMEM))) return rc;
     const int word_ok = EPI == w8a8::EPI_BF16 ? (((uintptr_t)out & 3) == 0 && ldo % 2 == 0) : 1;
     const int tiles = ((M + 255) / 256) * ((N + 255) / 256);
     int pairs = sm_count() / 2;
@@ -265,11 +293,7 @@ int launch_swap(const int8_t* a, const float* a_s, const int8_t* w, const float*
         tsa = tx;
     }
     auto kern = w8a8::w8a8_swap_kernel<NB, GROUPED>;
-    static bool configured = false;
-    if (!configured) {
-        if ((rc = set_smem(kern, C::smem_bytes(C::STAGES_DEEP)))) return rc;
-        configured = true;
-    }
+    if ((rc = set_smem(kern, C::smem_bytes(C::STAGES_DEEP)))) return rc;
     dim3 grid((p.N + 127) / 128, split, (p.M + NB - 1) / NB);
     // a grid no larger than the SM count gets one CTA per SM and the deepest pipeline; a larger one two CTAs per SM
     p.stages = (long)grid.x * grid.y * grid.z <= sm_count() ? C::STAGES_DEEP : C::STAGES;
@@ -304,6 +328,22 @@ int launch_swap_nb(int nb, const int8_t* a, const float* a_s, const int8_t* w, c
 }
 
 
+// Scale groups of gk = 32 * gblocks inputs (w8a8_groups.cuh): any gk that is neither 32 nor K.
+template <int NB>
+int launch_groups(const int8_t* a, const int8_t* w, w8a8::SwapArgs p, cudaStream_t st) {
+    using C = w8a8::GroupsCfg<NB>;
+    CUtensorMap tw, tx;
+    int rc;
+    if ((rc = tensor_map(&tw, w, p.K, p.N, p.K, w8a8::BK, w8a8::BM, 0))) return rc;
+    if ((rc = tensor_map(&tx, a, p.K, p.M, p.K, w8a8::BK, NB, 0))) return rc;
+    auto kern = w8a8::w8a8_groups_kernel<NB>;
+    if ((rc = set_smem(kern, C::SMEM))) return rc;
+    dim3 grid((p.N + 127) / 128, 1, (p.M + NB - 1) / NB);
+    kern<<<grid, C::THREADS, C::SMEM, st>>>(tw, tx, p);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
 template <int KIND>
 int launch_w4a8(const int8_t* xq, const float* a, const int8_t* xs, int Ma, const void* wq, const void* wsc,
                 const void* wmn, const float* wd, const float* wdm, void* out, long ldo, const int* n_rows, int M,
@@ -328,11 +368,7 @@ int launch_w4a8(const int8_t* xq, const float* a, const int8_t* xs, int Ma, cons
     }
     if ((rc = tensor_map(&m.d, wd, N, NSB, (uint64_t)N * 4, 64, 1, 1))) return rc;
     auto kern = w4a8::w4a8_kernel<KIND>;
-    static bool configured = false;
-    if (!configured) {
-        if ((rc = set_smem(kern, C::SMEM))) return rc;
-        configured = true;
-    }
+    if ((rc = set_smem(kern, C::SMEM))) return rc;
     w4a8::Args p{a, out, ldo, n_rows, M, N, K, Ma, epi, nullptr, nullptr, nullptr, nullptr, 1, K / 256, nullptr, nullptr};
     const int grid = ((M + 127) / 128) * ((N + 63) / 64);
     kern<<<grid, w4a8::THREADS, C::SMEM, st>>>(m, p);
@@ -374,12 +410,8 @@ int launch_w4a8_few(const int8_t* xq, const float* a, const int8_t* xs, int Ma, 
     dim3 grid((M + w4a8::FEW_NB - 1) / w4a8::FEW_NB, (N + C::TILE_N - 1) / C::TILE_N);
     if (KIND == w4a8::KIND_Q4K && !w4a8_few_staged()) {
         // Q4_K: the expanded operand goes through tensor memory
-        static bool configured_tm = false;
-        if (!configured_tm) {
-            if ((rc = set_smem(w4a8::w4a8_few_q4k_tm_kernel<false>, w4a8::TmCfg::SMEM))) return rc;
-            if ((rc = set_smem(w4a8::w4a8_few_q4k_tm_kernel<true>, w4a8::TmCfg::SMEM))) return rc;
-            configured_tm = true;
-        }
+        if ((rc = set_smem(w4a8::w4a8_few_q4k_tm_kernel<false>, w4a8::TmCfg::SMEM))) return rc;
+        if ((rc = set_smem(w4a8::w4a8_few_q4k_tm_kernel<true>, w4a8::TmCfg::SMEM))) return rc;
         grid.z = split;
         if (split > 1) w4a8::w4a8_few_q4k_tm_kernel<true><<<grid, w4a8::FEW_THREADS, w4a8::TmCfg::SMEM, st>>>(m, p);
         else w4a8::w4a8_few_q4k_tm_kernel<false><<<grid, w4a8::FEW_THREADS, w4a8::TmCfg::SMEM, st>>>(m, p);
@@ -387,11 +419,7 @@ int launch_w4a8_few(const int8_t* xq, const float* a, const int8_t* xs, int Ma, 
         return PB_OK;
     }
     auto kern = w4a8::w4a8_few_kernel<KIND>;
-    static bool configured = false;
-    if (!configured) {
-        if ((rc = set_smem(kern, C::SMEM))) return rc;
-        configured = true;
-    }
+    if ((rc = set_smem(kern, C::SMEM))) return rc;
     if (KIND == w4a8::KIND_Q6K) grid.z = split;
     else p.split = 1;
     kern<<<grid, w4a8::FEW_THREADS, C::SMEM, st>>>(m, p);
@@ -410,7 +438,8 @@ int launch_w4a8_gemv(int kind, const w4a8::GemvArgs& p, cudaStream_t st) {
     // the most warps with which the whole grid is resident at once (a second, short wave would double the time)
     const size_t smem = (size_t)(p.K >> 8) * 4 * R * MR * sizeof(float);
     if (grid < 8 * sm_count() && smem <= 48 * 1024) {
-        static int resident[2][5] = {};                            // [kind][warps] CTAs per SM, 0 = not asked yet
+        static int resident_dev[kMaxDevices][2][5] = {};           // [device][kind][warps] CTAs per SM, 0 = not asked yet
+        int (&resident)[2][5] = resident_dev[current_device()];
         int kw = 2;
         for (int k = 4; k >= 2; --k) {
             if (!resident[kind][k]) {
@@ -436,7 +465,8 @@ int launch_mxfp4_gemv(const mxfp4::GemvArgs& p, cudaStream_t st) {
     const int grid = (p.N + 7) / 8;                                // eight weight rows per CTA
     if (grid < 8 * sm_count()) {
         // few rows: the most warps per CTA with which the whole grid is resident at once
-        static int resident[5] = {};
+        static int resident_dev[kMaxDevices][5] = {};
+        int (&resident)[5] = resident_dev[current_device()];
         int kw = 2;
         for (int k = 4; k >= 2; --k) {
             if (!resident[k]) {
@@ -462,7 +492,8 @@ int launch_w8a8_gemv(const w8a8::GemvArgs& p, cudaStream_t st) {
     const int grid = (p.N + 7) / 8;                                // eight weight rows per CTA
     if (grid < 8 * sm_count()) {
         // few rows: the most warps per CTA with which the whole grid is resident at once
-        static int resident[5] = {};
+        static int resident_dev[kMaxDevices][5] = {};
+        int (&resident)[5] = resident_dev[current_device()];
         int kw = 2;
         for (int k = 4; k >= 2; --k) {
             if (!resident[k]) {
@@ -509,13 +540,11 @@ int launch_pipe_v(bool full, const quant::PipeArgs& p, int grid, int threads, in
     int rc;
     if (full) {
         auto k = quant::row_pipe_kernel<KIND, VPT, BF16, true, 576>;
-        static bool c = false;
-        if (!c) { if ((rc = set_smem(k, 200 * 1024))) return rc; c = true; }
+        if ((rc = set_smem(k, 200 * 1024))) return rc;
         k<<<grid, threads, smem, st>>>(p);
     } else {
         auto k = quant::row_pipe_kernel<KIND, VPT, BF16, false, 576>;
-        static bool c = false;
-        if (!c) { if ((rc = set_smem(k, 200 * 1024))) return rc; c = true; }
+        if ((rc = set_smem(k, 200 * 1024))) return rc;
         k<<<grid, threads, smem, st>>>(p);
     }
     return PB_OK;
@@ -596,7 +625,6 @@ void launch_rows(bool bf16, bool full, int threads, const void* x, long ldx, con
 static __device__ __align__(256) unsigned char g_static_scratch[PB_STATIC_WS_BYTES + PB_STATIC_COUNTERS * 4];
 
 namespace {
-constexpr int kMaxDevices = 64;
 void* g_static_scratch_addr[kMaxDevices] = {};
 std::mutex g_static_scratch_mu;
 
@@ -649,6 +677,17 @@ int pb_device_status(int* code, unsigned* where, int reset) {
         PB_CUDA(cudaMemcpyToSymbol(g_pb_device_status, &z, sizeof(int)));
         PB_CUDA(cudaMemcpyToSymbol(g_pb_device_status_where, &zw, sizeof(unsigned)));
     }
+    return PB_OK;
+}
+
+int pb_set_wait_limit_ns(unsigned long long ns) {
+    if (ns == 0) ns = PB_WAIT_NS;
+    PB_CUDA(cudaMemcpyToSymbol(g_pb_wait_ns, &ns, sizeof(ns)));
+    return PB_OK;
+}
+
+int pb_test_drop_loads(int on) {
+    g_drop_loads = on ? 1 : 0;
     return PB_OK;
 }
 
@@ -709,7 +748,17 @@ int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float
         }
         return launch_swap_nb<true>(pick_nb(M), a, a_s, w, w_s, p, split, st);
     }
-    if (gk != K) return PB_UNSUPPORTED_SHAPE;
+    if (gk != K) {
+        // any other group size (a multiple of 32 that divides K): one accumulator slot per group, fp32 sums in group
+        // order.  No K split, no int32 output.
+        if (gk <= 0 || gk % 32 || K % gk || K % 128 || epi == PB_EPI_I32 || epi == PB_EPI_F32) return PB_UNSUPPORTED_SHAPE;
+        if (split > 1) return PB_UNSUPPORTED_SHAPE;
+        w8a8::SwapArgs p{a_s, w_s, out, ldo, 0, nullptr, nullptr, n_rows, M, N, K, KB, epi, w8a8::MODE_DIRECT, 0, 0, gk / 32};
+        const int nb = pick_nb(M);
+        if (nb == 16) return launch_groups<16>(a, w, p, st);
+        if (nb == 32) return launch_groups<32>(a, w, p, st);
+        return launch_groups<64>(a, w, p, st);
+    }
     if (M <= PB_W8A8_GEMV_ROWS && (N + 7) / 8 < 8 * sm_count() && split == 1 && !pdl && K % 256 == 0 &&
         (epi == PB_EPI_BF16 || epi == PB_EPI_ADD) && !w8a8_no_gemv()) {
         // one row against a matrix of few rows, no K split asked for: the CUDA-core kernel (the same bits: exact
@@ -766,6 +815,19 @@ int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float
             return PB_TOO_LARGE;
     }
     return launch_swap_nb<false>(nb, a, a_s, w, w_s, p, split, st);
+}
+
+int pb_w8a8_gemm_swiglu(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, int8_t* q, long ldq, float* s,
+                        const int* n_rows, int M, int N, int K, int bn, void* stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    if (!a || !a_s || !w || !w_s || !q || !s || !n_rows || M <= 0 || N <= 0 || K <= 0) return PB_BAD_ARGUMENT;
+    if (bn != 64 && bn != 128) return PB_UNSUPPORTED_SHAPE;
+    if (N % bn || K % 16 || ldq < N / 2) return PB_UNSUPPORTED_SHAPE;
+    if (!aligned16(a) || !aligned16(w)) return PB_BAD_ARGUMENT;
+    // 128 x 256 tiles (two or four interleave tiles each), or 128 x 128 when those would leave most SMs idle
+    const bool narrow = N <= 128 || tile_bn(M, N) == 128;
+    return narrow ? launch_tile<128, w8a8::EPI_SWIGLU>(a, a_s, w, w_s, q, ldq, n_rows, M, N, K, st, 1, nullptr, nullptr, nullptr, s, bn)
+                  : launch_tile<256, w8a8::EPI_SWIGLU>(a, a_s, w, w_s, q, ldq, n_rows, M, N, K, st, 1, nullptr, nullptr, nullptr, s, bn);
 }
 
 int pb_w8a8_gemm_scatter(const int8_t* a, const int8_t* w, void* const* blocks, int n_blocks, int block_rows, long ldo,
@@ -1173,11 +1235,7 @@ int pb_mxfp4_gemm_split(const void* aq, const void* a_sf, const void* bq, const 
     if (N > 128 && tiles256 >= sm_count() && !mxfp4_narrow_only() && split == 1) {
         CUtensorMap tb2;
         if ((rc = tensor_map(&tb2, bq, K / 2, N, K / 2, 128, 256, 0))) return rc;
-        static bool configured2 = false;
-        if (!configured2) {
-            if ((rc = set_smem(mxfp4::mxfp4_gemm256_kernel, mxfp4::SMEM2))) return rc;
-            configured2 = true;
-        }
+        if ((rc = set_smem(mxfp4::mxfp4_gemm256_kernel, mxfp4::SMEM2))) return rc;
         const int grid2 = tiles256 < sm_count() ? (int)tiles256 : sm_count();
         // the epilogue hands 32 x 64-byte boxes to the copy engine when out can be described by a tensor map
         CUtensorMap tout = ta;
@@ -1193,11 +1251,7 @@ int pb_mxfp4_gemm_split(const void* aq, const void* a_sf, const void* bq, const 
         PB_CUDA(cudaGetLastError());
         return PB_OK;
     }
-    static bool configured = false;
-    if (!configured) {
-        if ((rc = set_smem(mxfp4::mxfp4_gemm_kernel, mxfp4::SMEM))) return rc;
-        configured = true;
-    }
+    if ((rc = set_smem(mxfp4::mxfp4_gemm_kernel, mxfp4::SMEM))) return rc;
     const int tiles = ((M + 127) / 128) * ((N + 127) / 128) * split;
     const int grid = tiles < sm_count() ? tiles : sm_count();
     mxfp4::mxfp4_gemm_kernel<<<grid, 192, mxfp4::SMEM, (cudaStream_t)stream>>>(ta, tb, p);
@@ -1221,13 +1275,19 @@ int pb_mxfp4_gemv(const void* aq, const void* a_s, const void* bq, const void* b
 int pb_int8_peak_probe(int iters, int pattern, int mma_n, unsigned long long* cycles, void* stream) {
     if (iters <= 0 || mma_n < 16 || mma_n > 256 || mma_n % 16) return PB_BAD_ARGUMENT;
     const int smem = (128 + 256) * 128 + 1024;
-    static bool configured = false;
-    if (!configured) {
-        int rc = set_smem(w8a8::int8_peak_kernel, smem);
-        if (rc) return rc;
-        configured = true;
-    }
+    int rc = set_smem(w8a8::int8_peak_kernel, smem);
+    if (rc) return rc;
     w8a8::int8_peak_kernel<<<sm_count(), 128, smem, (cudaStream_t)stream>>>(iters, pattern, mma_n, cycles);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+int pb_mxf4_peak_probe(int iters, int pattern, unsigned long long* cycles, void* stream) {
+    if (iters <= 0) return PB_BAD_ARGUMENT;
+    const int smem = (128 + 256) * 128 + 512 + 1024;
+    int rc = set_smem(mxfp4::mxf4_peak_kernel, smem);
+    if (rc) return rc;
+    mxfp4::mxf4_peak_kernel<<<sm_count(), 128, smem, (cudaStream_t)stream>>>(iters, pattern, cycles);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }

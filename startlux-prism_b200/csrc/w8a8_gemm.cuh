@@ -25,6 +25,7 @@ constexpr int BM = 128;        // MMA M: rows of the operand that owns the tenso
 constexpr int BK = 128;        // bytes (= int8 values) of K per pipeline stage: one 128-byte swizzle row
 constexpr int EPI_BF16 = 0;    // out bf16 [M, N] = v
 constexpr int EPI_ADD = 1;     // out fp32 [M, N] = add_rn(out, v)
+constexpr int EPI_SWIGLU = 2;  // out int8 [M, N / 2] = per-tile quantized silu(gate) * up, one scale per row and tile
 constexpr int EPI_I32 = 3;     // out int32 [M, N] = acc (no scales)
 constexpr int EPI_F32 = 4;     // out fp32 [M, N] = v (the vocabulary head's logits; per-32 groups, few rows)
 
@@ -47,10 +48,11 @@ __device__ __forceinline__ uint8_t* align1024(uint8_t* p) {
 // must not be handed to another CTA with a bulk copy still writing into it).
 __device__ __forceinline__ void drain_armed(Aux* aux, int stages, const uint32_t* armed_parity, uint32_t armed_mask) {
     unsigned long long t0 = global_timer_ns();
+    const unsigned long long limit = *(volatile unsigned long long*)&g_pb_wait_ns;
     for (int s = 0; s < stages; ++s) {
         if (!(armed_mask >> s & 1)) continue;
         while (!mbar_test(smem_u32(&aux->full[s]), armed_parity[s])) {
-            if (global_timer_ns() - t0 > PB_WAIT_NS) return;
+            if (global_timer_ns() - t0 > limit) return;
         }
     }
 }
@@ -321,6 +323,69 @@ __device__ __forceinline__ void drain_add_red(float* __restrict__ out, long ldo,
     }
 }
 
+// The fused SwiGLU epilogue (the reference's EPI 2, kernels/w8a8.py:86-98) of one 128 x BN accumulator.  The weight
+// rows are interleaved in tiles of `gbn` rows (w8a8.interleave_gate_up): gbn / 2 gate rows, then the matching up rows.
+// For every such tile the thread (= output row) computes act = silu(gate) * up from the scaled fp32 values, takes the
+// maximum over the tile's gbn / 2 columns, and stores them as int8 with one scale per (row, tile):
+//   scale = max(amax, 1e-10) / 127, q = rint(act / scale)   (IEEE divisions)
+// q int8 [M, N / 2] with row stride ldq, scales fp32 [M, N / gbn].  HB = gbn / 2 is 32 or 64.
+template <int BN, int HB>
+__device__ __forceinline__ void drain_swiglu(int8_t* __restrict__ qout, long ldq, float* __restrict__ souts, int N, int live,
+                                             int m0, int n0, int q, int lane, uint32_t lane_addr, const float* swb,
+                                             float sa) {
+    constexpr int GBN = 2 * HB;
+    const int row = m0 + q * 32 + lane;
+    const bool rok = row < live;
+    const int tiles_n = N / GBN;
+    const bool vec_ok = (((uintptr_t)qout & 15) == 0) && (ldq % 16 == 0);
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += GBN) {
+        if (n0 + c0 >= N) break;
+        float act[HB];
+        float amax = 0.0f;
+#pragma unroll
+        for (int h = 0; h < HB; h += 32) {
+            uint32_t rg[32], ru[32];
+            tmem_ld32(lane_addr + c0 + h, rg);
+            tmem_ld32(lane_addr + c0 + HB + h, ru);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                const float g = scale2((int)rg[j], sa, swb[c0 + h + j]);
+                const float u = scale2((int)ru[j], sa, swb[c0 + HB + h + j]);
+                const float a = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, __expf(-g))), u);
+                act[h + j] = a;
+                amax = fmaxf(amax, fabsf(a));
+            }
+        }
+        if (!rok) continue;
+        const float scale = __fdiv_rn(fmaxf(amax, 1e-10f), 127.0f);
+        const int tile = (n0 + c0) / GBN;
+        souts[(long)row * tiles_n + tile] = scale;
+        int8_t* dst = qout + (long)row * ldq + (long)tile * HB;
+#pragma unroll
+        for (int v = 0; v < HB; v += 16) {
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                uint32_t word = 0;
+#pragma unroll
+                for (int b = 0; b < 4; ++b) {
+                    const int qi = __float2int_rn(__fdiv_rn(act[v + 4 * k + b], scale));
+                    word |= ((uint32_t)qi & 0xffu) << (8 * b);
+                }
+                w[k] = word;
+            }
+            if (vec_ok) {
+                *(uint4*)(dst + v) = make_uint4(w[0], w[1], w[2], w[3]);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 16; ++k) dst[v + k] = (int8_t)((w[k >> 2] >> (8 * (k & 3))) & 0xff);
+            }
+        }
+    }
+}
+
 // Split-K in the tile kernel: the last CTA to finish a tile (a counter per tile) adds the K slices' int32 partial
 // accumulators ws[slice][128][BN] (exact, so the order is free) and runs the epilogue for rows [r_begin, r_begin + 32)
 // and columns [c_begin, c_end) of the tile.  Lane = column: every load and store is a full row segment.
@@ -426,7 +491,8 @@ __global__ void __launch_bounds__(TileWarps<EPI>::THREADS, 1)
 w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_w,
                  const __grid_constant__ CUtensorMap tm_out, const float* __restrict__ a_s, const float* __restrict__ w_s, void* __restrict__ out, long ldo,
                  const int* __restrict__ n_rows, int M, int N, int K, int word_ok, int split, int kb_per_split,
-                 int32_t* __restrict__ ws, int* __restrict__ counters, const __grid_constant__ RowBlocks rb) {
+                 int32_t* __restrict__ ws, int* __restrict__ counters, const __grid_constant__ RowBlocks rb,
+                 float* __restrict__ souts, int gbn) {
     using C = TileCfg<BN>;
     using W = TileWarps<EPI>;
     extern __shared__ uint8_t smem_raw[];
@@ -480,7 +546,9 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             uint32_t armed_mask = 0;
             int stage = 0;
             uint32_t phase = 0;
-            bool ok = true;
+            // bit 4 of word_ok (failure injection from the host, pb_test_drop_loads): this producer requests nothing, so
+            // the MMA thread's bounded wait for the first stage expires and the CTA leaves through its abort path
+            bool ok = !(word_ok & 16);
             for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
                 const int t = u / split, z = u - t * split;
                 const int m0 = (n_fastest ? t / num_n : t % num_m) * BM, n0 = (n_fastest ? t % num_n : t / num_m) * BN;
@@ -508,7 +576,7 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     }
                 }
             }
-            if (!ok) drain_armed(aux, C::STAGES, armed_parity, armed_mask);
+            if (!ok && armed_mask) drain_armed(aux, C::STAGES, armed_parity, armed_mask);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (one thread)
@@ -646,6 +714,9 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 uint32_t* stg = stage_buf + (warp - 2) * (32 * 32);
                 drain_add((float*)out, ldo, N, live, m0, n0, q, lane, lane_addr, stg, swb, sa, half * (BN / 2),
                           (half + 1) * (BN / 2));
+            } else if (EPI == EPI_SWIGLU) {
+                if (gbn == 128) drain_swiglu<BN, 64>((int8_t*)out, ldo, souts, N, live, m0, n0, q, lane, lane_addr, swb, sa);
+                else drain_swiglu<BN, 32>((int8_t*)out, ldo, souts, N, live, m0, n0, q, lane, lane_addr, swb, sa);
             } else {
                 uint32_t* stg = stage_buf + q * (32 * 33);
                 drain_accumulator<BN, EPI>(out_t, ldo, N, live, m0, n0, q, lane, lane_addr, stg, swb, sa, (word_ok & 1) != 0);
@@ -885,6 +956,7 @@ struct SwapArgs {
     int mode;
     int pdl;                // launched as a programmatic dependent: weights may stream before the wait
     int stages;             // pipeline depth (shared-memory stages per CTA)
+    int gblocks;            // w8a8_groups_kernel: 32-input blocks per scale group (gk / 32)
 };
 
 template <int NB>

@@ -105,10 +105,17 @@ class LinearStack:
             elif group.rank == 0:
                 print(f"prism_b200: peer memory unavailable ({peer.error}); NCCL reduce-scatter instead", flush=True)
 
-    def __call__(self, h_in):
+    def __call__(self, h_in, own_rows=False):
         """One pass: h_in fp32 [M, hidden] is copied into the working residual, which is returned (a view of an
-        internal buffer, overwritten by the next pass)."""
+        internal buffer, overwritten by the next pass).  own_rows (several ranks, row-split pass only): h_in is this
+        rank's block of M / n rows and the rank's block of the result is returned - what a caller that feeds and
+        reads each rank's rows separately needs; the other rows' residual never has to exist on this rank."""
         M, nr, g = self.M, self.n_rows, self.g
+        if own_rows:
+            if not self.by_rows:
+                raise RuntimeError("own_rows needs the row-split pass (several ranks, M / ranks >= 64 rows)")
+            self.h[self.r0:self.r0 + self.Ml].copy_(h_in, non_blocking=True)
+            return self._pass_by_rows(gather=False)
         self.h.copy_(h_in, non_blocking=True)
         if self.by_rows:
             return self._pass_by_rows()
@@ -142,7 +149,7 @@ class LinearStack:
             return tp.out_proj(self.g, a, a_s, w, w_s, self.parts, self.M, self.n_rows)
         return w8a8.gemm(a, a_s, w, w_s, self.h, self.n_rows, a.shape[1], epi=1, slots=self.slots)
 
-    def _pass_by_rows(self):
+    def _pass_by_rows(self, gather=True):
         """Several ranks, many rows.  Between a row-parallel projection and the next column-parallel one every rank
         works on its own M / n rows of the residual stream: int32 partial sums -> reduce-scatter -> fold into the own
         rows -> quantize them -> all-gather the int8 rows and their scales.  Every element sees the operations of the
@@ -177,5 +184,7 @@ class LinearStack:
             tp.quantize_rows(g, quant.swiglu_q8, M, self.amax, self.gu, None, self.dq, self.ds, nr, M)
             pend = out(self.dq, self.ds, lw["down"])
         quant.fold(h_own, None, pend, self.nr_own, Ml)
+        if not gather:
+            return h_own
         g.gather_(self.h, h_own)
         return self.h

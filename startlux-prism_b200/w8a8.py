@@ -42,7 +42,10 @@ class Deferred(NamedTuple):
 
 
 def _workspace(device):
-    """(workspace bytes tensor, zeroed int32 counters) of a device; allocated once, outside any graph capture."""
+    """(workspace bytes tensor, zeroed int32 counters) of a device; allocated once, outside any graph capture.  One
+    array per device, shared by the W8A8, W4A8 and MXFP4 split-K kernels on whatever stream calls them: two products
+    that split K and overlap on the GPU (different streams) race on it - keep split-K products of one device on one
+    stream, or give the second stream its own arrays through the C entry points."""
     key = torch.device(device).index or 0
     if key not in _WORKSPACE:
         if torch.cuda.is_current_stream_capturing():
@@ -50,6 +53,14 @@ def _workspace(device):
         _WORKSPACE[key] = (torch.empty(WS_BYTES, dtype=torch.uint8, device=device),
                            torch.zeros(65536, dtype=torch.int32, device=device))
     return _WORKSPACE[key]
+
+
+def reset_workspace(device=None):
+    """Zero the split-K arrival counters (after a kernel reported PB_DEVICE_TIMEOUT: a CTA that gave up a wait did not
+    count itself in, so its tile's counter is left non-zero)."""
+    for key, (_, counters) in _WORKSPACE.items():
+        if device is None or key == (torch.device(device).index or 0):
+            counters.zero_()
 
 
 GEMV_ROWS = 1        # gk == K: this many rows against few weight rows run on the CUDA cores (PB_W8A8_GEMV_ROWS)
@@ -110,7 +121,7 @@ def gemm(a, a_s, w, w_s, out, n_rows, gk, epi=0, outs=None, cfg=None, slots=None
     M, K = a.shape
     N = w.shape[0]
     if epi == EPI_SWIGLU:
-        raise NotImplementedError("the fused SwiGLU epilogue (epi 2) is not part of this build: use quant.swiglu_q8")
+        return _gemm_swiglu(a, a_s, w, w_s, out, n_rows, gk, outs, cfg)
     if epi not in (EPI_BF16, EPI_ADD, EPI_F32) or (epi == EPI_F32 and (gk != 32 or M > FEW_ROWS)):
         raise ValueError(f"epi {epi}")                 # EPI_F32 (plain fp32 store): the vocabulary head, decode.head_q8
     want = torch.bfloat16 if epi == EPI_BF16 else torch.float32
@@ -118,6 +129,10 @@ def gemm(a, a_s, w, w_s, out, n_rows, gk, epi=0, outs=None, cfg=None, slots=None
         raise RuntimeError(f"w8a8.gemm: out must be {want} [>= {M}, {N}] with unit column stride")
     _scales_ok(a_s, M, K // gk, "a_s")
     _scales_ok(w_s, N, K // gk, "w_s")
+    if gk != K and gk != 32:
+        # any other group size: one kernel shape, groups added in order, no K split
+        _call(a, a_s, w, w_s, out, out.stride(0), n_rows, gk, epi, 1)
+        return None
     if gk != K:
         # Q8_0's own scales: one K slice keeps the reference's group order (bit-exact); cfg = K splits (few rows only)
         # trades that for parallelism: slices added in slice order, within one bf16 step of the unsplit result
@@ -147,6 +162,32 @@ def gemm(a, a_s, w, w_s, out, n_rows, gk, epi=0, outs=None, cfg=None, slots=None
         if split == 1:
             ws = counters = None
     _call(a, a_s, w, w_s, out, out.stride(0), n_rows, gk, epi, split, 0, ws, counters, pdl=pdl)
+    return None
+
+
+def _gemm_swiglu(a, a_s, w, w_s, out, n_rows, gk, outs, cfg):
+    """epi 2 (kernels/w8a8.py:86-98): w is interleave_gate_up(gate, up, bn) (w_s in the same row order); out int8
+    [M, FF] = silu(gate) * up quantized per row and tile of bn / 2 columns, outs fp32 [M, 2 FF / bn] the scales: the
+    input of a down projection with gk = bn / 2.  cfg: bn itself, or the reference's config tuple (bn = cfg[1]);
+    default 128."""
+    M, K = a.shape
+    N = w.shape[0]
+    bn = 128 if cfg is None else int(cfg[1] if isinstance(cfg, (tuple, list)) else cfg)
+    if gk != K:
+        raise RuntimeError("w8a8.gemm epi 2: one scale group over K (gk == K)")
+    if outs is None or outs.dtype != torch.float32 or not outs.is_contiguous() or outs.numel() < M * (N // bn) \
+            or outs.shape[-1] != N // bn:
+        raise RuntimeError(f"w8a8.gemm epi 2: outs must be contiguous fp32 [>= {M}, {N // bn}]")
+    if out.dtype != torch.int8 or out.shape[0] < M or out.shape[1] != N // 2 or out.stride(1) != 1:
+        raise RuntimeError(f"w8a8.gemm epi 2: out must be int8 [>= {M}, {N // 2}]")
+    _lib.need_cuda(a, w, out, outs, n_rows)
+    if a.dtype != torch.int8 or w.dtype != torch.int8 or not a.is_contiguous() or not w.is_contiguous() or w.shape[1] != K:
+        raise RuntimeError("w8a8.gemm: a and w must be contiguous int8 [rows, K]")
+    _scales_ok(a_s, M, 1, "a_s")
+    _scales_ok(w_s, N, 1, "w_s")
+    rc = _lib.lib().pb_w8a8_gemm_swiglu(_lib.ptr(a), _lib.ptr(a_s), _lib.ptr(w), _lib.ptr(w_s), _lib.ptr(out),
+                                        out.stride(0), _lib.ptr(outs), _lib.ptr(n_rows), M, N, K, bn, _lib.stream())
+    _lib.check(rc, f"w8a8 gemm epi 2 M={M} N={N} K={K} bn={bn}")
     return None
 
 

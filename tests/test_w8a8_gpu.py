@@ -256,3 +256,56 @@ def test_q8_0_groups_split_k(dev, M, N, K, split):
     w8a8._workspace(dev)[0].fill_(0xFF)          # a slice read before it was written would give NaN
     run(dev, a, w, sa, sw, res, M, 32, 1, cfg=split)
     assert np.allclose(res.cpu().numpy(), ref1, rtol=1e-5, atol=5e-5)
+
+
+@pytest.mark.parametrize("M,N,K,live,gk", [(16, 512, 1024, 16, 64), (40, 200, 512, 37, 128), (5, 5120, 5120, 5, 256),
+                                           (64, 1000, 2560, 61, 640), (150, 384, 1024, 140, 64), (33, 256, 3072, 33, 96)])
+def test_gemm_any_group_size(dev, M, N, K, live, gk):
+    """Scale groups of any multiple of 32 inputs that divides K (the reference's kernel takes any GK,
+    kernels/w8a8.py:64-76): per group an exact integer sum, the scaled sums added in fp32 in group order."""
+    a, w, sa, sw = rand_w8a8(M, N, K, seed=gk + M, groups=K // gk)
+    ref0 = oracle.w8a8_gemm(a.numpy(), sa.numpy(), w.numpy(), sw.numpy(), gk, 0, live)
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+    run(dev, a, w, sa, sw, out, live, gk, 0)
+    assert same(out, bf16_from_bits(ref0)), first_diff(np_bits(out), ref0)
+    base = torch.randn(M, N, generator=torch.Generator().manual_seed(4))
+    ref1 = oracle.w8a8_gemm(a.numpy(), sa.numpy(), w.numpy(), sw.numpy(), gk, 1, live, out=base.numpy())
+    res = base.to(dev)
+    run(dev, a, w, sa, sw, res, live, gk, 1)
+    assert same(res, ref1), first_diff(res.cpu().numpy(), ref1)
+
+
+@pytest.mark.parametrize("M,FF,K,live,bn", [(70, 256, 512, 66, 128), (20, 192, 256, 20, 64), (300, 640, 1024, 290, 128),
+                                            (16, 17408 // 8, 5120, 16, 128)])
+def test_gemm_swiglu_epilogue(dev, M, FF, K, live, bn):
+    """epi 2: gate|up rows interleaved in tiles of bn, silu(gate) * up quantized per row and tile in the epilogue
+    (kernels/w8a8.py:86-98).  The scales agree with the oracle to 1e-5, the int8 values within one step (the device's
+    exp differs from libm's in the last bits); rows past the live count are untouched.  The output then feeds a down
+    projection with gk = bn / 2, which must equal the oracle's product of the same int8 values bit for bit."""
+    g = torch.Generator().manual_seed(M + FF)
+    gate = torch.randint(-127, 128, (FF, K), generator=g, dtype=torch.int8)
+    up = torch.randint(-127, 128, (FF, K), generator=g, dtype=torch.int8)
+    gs, us = torch.rand(FF, generator=g) * 2e-3, torch.rand(FF, generator=g) * 2e-3
+    a = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8)
+    sa = torch.rand(M, generator=g) * 1e-2
+    w = w8a8.interleave_gate_up(gate, up, bn)
+    ws = w8a8.interleave_gate_up(gs.view(FF, 1), us.view(FF, 1), bn).view(-1)
+    rq, rs = oracle.w8a8_swiglu_epi(a.numpy(), sa.numpy(), w.numpy(), ws.numpy(), bn, live)
+    q = torch.full((M, FF), 77, dtype=torch.int8, device=dev)
+    s = torch.full((M, 2 * FF // bn), -1.0, device=dev)
+    w8a8.gemm(a.to(dev), sa.to(dev), w.to(dev), ws.to(dev), q, n_rows(live, dev), K, epi=2, outs=s, cfg=bn)
+    torch.cuda.synchronize()
+    qn, sn = q.cpu().numpy(), s.cpu().numpy()
+    assert np.allclose(sn[:live], rs[:live], rtol=1e-5, atol=0)
+    d = np.abs(qn[:live].astype(np.int32) - rq[:live].astype(np.int32))
+    assert d.max() <= 1 and (d != 0).mean() < 0.01, (d.max(), (d != 0).mean())
+    assert (qn[live:] == 77).all() and (sn[live:] == -1).all()
+    # the consumer: a down projection whose activation scales are per bn / 2 inputs
+    hb = bn // 2
+    N2 = 256
+    wd_ = torch.randint(-127, 128, (N2, FF), generator=g, dtype=torch.int8)
+    wds = torch.rand(N2, FF // hb, generator=g) * 1e-3
+    ref = oracle.w8a8_gemm(qn, sn, wd_.numpy(), wds.numpy(), hb, 0, live)
+    out = torch.zeros(M, N2, dtype=torch.bfloat16, device=dev)
+    w8a8.gemm(q, s, wd_.to(dev), wds.to(dev), out, n_rows(live, dev), hb)
+    assert same(out, bf16_from_bits(ref)), first_diff(np_bits(out), ref)
