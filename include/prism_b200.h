@@ -24,7 +24,8 @@ extern "C" {
 #define PB_EPI_ADD 1  /* out fp32 [M, N] = add_rn(out, v) */
 #define PB_EPI_SWIGLU 2 /* pb_w8a8_gemm_swiglu only */
 #define PB_EPI_I32 3  /* out int32 = the raw integer sums */
-#define PB_EPI_F32 4  /* out fp32 [M, N] = v (gk == 32, M <= 64: the vocabulary head's logits) */
+#define PB_EPI_F32 4  /* out fp32 [M, N] (gk == 32, M <= 64: the vocabulary head's logits, kernels/decode.py:136-160): per
+                         group acc = fma(float(acc_g) * a_s, w_s, acc), the reference kernel's compiled arithmetic */
 
 #define PB_W8A8_GEMV_ROWS 1 /* pb_w8a8_gemm, gk == K, split == 1, no pdl: this many rows against a matrix of fewer than
                                9,472 rows run on the CUDA cores (the same bits) */

@@ -51,11 +51,12 @@ def bf16_to_f32(bits):
 
 def w8a8_gemm(a, a_s, w, w_s, gk, epi, live=None, out=None):
     """a int8 [M, K], a_s fp32 [M, K/gk], w int8 [N, K], w_s fp32 [N, K/gk].  epi 0 -> bf16 bits uint16 [M, N];
-    epi 1 -> fp32 `out` += (a copy is returned); epi 3 -> int32 [M, N].  Rows >= live keep `out`'s values (zeros)."""
+    epi 1 -> fp32 `out` += (a copy is returned); epi 3 -> int32 [M, N]; epi 4 -> fp32 [M, N] = the groups' sums with the
+    last multiply and the add fused (the vocabulary head).  Rows >= live keep `out`'s values (zeros)."""
     M, K = a.shape
     N = w.shape[0]
     live = M if live is None else live
-    dt = {0: np.uint16, 1: np.float32, 3: np.int32}[epi]
+    dt = {0: np.uint16, 1: np.float32, 3: np.int32, 4: np.float32}[epi]      # 4: the vocabulary head's plain fp32 store
     o = np.zeros((M, N), dt) if out is None else np.array(out, dtype=dt, copy=True, order="C")
     lib().orc_w8a8_gemm(_p(_c(a, np.int8)), _p(_c(a_s, np.float32)), _p(_c(w, np.int8)), _p(_c(w_s, np.float32)),
                         _p(o), ctypes.c_long(N), live, N, K, gk, epi)

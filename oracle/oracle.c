@@ -57,8 +57,18 @@ void orc_w8a8_gemm(const int8_t *a, const float *a_s, const int8_t *w, const flo
             int32_t ai = 0;
             for (int k = g * gk; k < (g + 1) * gk; ++k) ai += (int32_t)ar[k] * (int32_t)wr[k];
             float t = (float)ai * a_s[(long)m * G + g];
+            if (epi == 4) {
+                /* the vocabulary head, kernels/decode.py:136-160 (_head_q8_kernel): `acc += (ai * sa) * sw` written
+                 * without mul_rn / add_rn, which the reference's compiler contracts into one fused multiply-add */
+                acc = fmaf(t, w_s[(long)n * G + g], acc);
+                continue;
+            }
             t = t * w_s[(long)n * G + g];
             acc = acc + t;
+        }
+        if (epi == 4) {
+            ((float *)out)[(long)m * ldo + n] = acc;
+            continue;
         }
         if (epi == 0)
             ((uint16_t *)out)[(long)m * ldo + n] = f32_to_bf16_rne(acc);

@@ -1180,6 +1180,26 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                     // scalar on purpose: the assembler contracts a packed multiply followed by a packed add into one
                     // fused multiply-add (measured: 15 % of results change), which would break the reference's
                     // two-rounding contract.
+                    if (p.epi == EPI_F32) {
+                        // the vocabulary head: the reference's kernel writes `acc += (ai * sa) * sw` without explicit
+                        // roundings (kernels/decode.py:157) and its compiler fuses the second multiply with the add:
+                        // one rounded product, then a fused multiply-add, per group
+#pragma unroll
+                        for (int j = 0; j < 8; j += 2) {
+                            const float4 s0 = sa4[c + j], s1 = sa4[c + j + 1];
+                            float2 a = acc[(c + j) >> 1];
+                            a.x = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[0][j]), s0.x), sw4.x, a.x);
+                            a.y = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[0][j + 1]), s1.x), sw4.x, a.y);
+                            a.x = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[1][j]), s0.y), sw4.y, a.x);
+                            a.y = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[1][j + 1]), s1.y), sw4.y, a.y);
+                            a.x = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[2][j]), s0.z), sw4.z, a.x);
+                            a.y = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[2][j + 1]), s1.z), sw4.z, a.y);
+                            a.x = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[3][j]), s0.w), sw4.w, a.x);
+                            a.y = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[3][j + 1]), s1.w), sw4.w, a.y);
+                            acc[(c + j) >> 1] = a;
+                        }
+                        continue;
+                    }
 #pragma unroll
                     for (int j = 0; j < 8; j += 2) {
                         const float4 s0 = sa4[c + j], s1 = sa4[c + j + 1];

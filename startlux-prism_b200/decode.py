@@ -2,14 +2,14 @@
 (:113-160, :351-364) over the sm_100a library.
 
     head_quant(h, norm, q, s, n, B, eps)       final RMSNorm of the residual rows, int8 per 32 inputs
-    head_q8(a, a_s, w, w_s, out, n, B)         logits fp32 [B, N] = sum over the 32-input groups, in order, of
-                                               (float(a_g . w_g) * a_s[g]) * w_s[g]
+    head_q8(a, a_s, w, w_s, out, n, B)         logits fp32 [B, N]: over the 32-input groups, in order,
+                                               acc = fma(float(a_g . w_g) * a_s[g], w_s[g], acc)
     head_scales(w_s)                           the file's group-major fp16 scales [K/32, N] -> fp32 [N, K/32] (load time)
 
-The GEMM is the per-32-group few-rows W8A8 kernel (w8a8.gemm, gk = 32) with a plain fp32 store.  Its arithmetic is
-fixed: multiply, multiply, add, each rounded to nearest, groups in ascending order.  The reference's Triton expression
-`acc += (ai * sa) * sw` leaves it to its compiler whether the last multiply and the add fuse; where they do, the
-two differ by at most one rounding per group.
+The GEMM is the per-32-group few-rows W8A8 kernel (w8a8.gemm, gk = 32) with a plain fp32 store.  The reference's
+Triton expression `acc += (ai * sa) * sw` carries no explicit roundings and its compiler fuses the second multiply
+with the add; this kernel computes the same - one rounded product, then a fused multiply-add, groups in ascending
+order - and equals the reference kernel's recorded logits bit for bit (tests/golden/gpu_ref.npz).
 """
 from __future__ import annotations
 

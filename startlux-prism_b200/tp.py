@@ -32,18 +32,19 @@ MAX_SPLIT = 4
 
 
 def shard_config(cfg, n):
-    """The config of one rank's shard: its heads and FFN columns; v_heads_full keeps the whole model's value heads."""
-    for what, v in (("attention heads", cfg.n_head), ("kv heads", cfg.n_kv_head),
-                    ("linear-attention key heads", cfg.k_heads), ("FFN width", cfg.ffn)):
-        if v % n:
-            raise ValueError(f"--tp {n} does not divide the model's {v} {what}")
+    """What one of n ranks holds, as a config: 1 / n of the attention heads, kv heads, linear-attention key and value
+    heads and FFN columns.  `v_heads_full` remembers the whole model's value-head count (the gated norm keeps the whole
+    model's head block) and `tp` the group size.  Raises when n does not divide one of them."""
+    split = {"n_head": "attention heads", "n_kv_head": "kv heads", "k_heads": "linear-attention key heads", "ffn": "FFN width"}
+    for field, what in split.items():
+        whole = getattr(cfg, field)
+        if whole % n:
+            raise ValueError(f"--tp {n} does not divide the model's {whole} {what}")
     if cfg.v_heads % cfg.k_heads:
         raise ValueError("value heads must be a multiple of key heads")
-    c = dataclasses.replace(cfg, n_head=cfg.n_head // n, n_kv_head=cfg.n_kv_head // n, k_heads=cfg.k_heads // n,
-                            v_heads=cfg.v_heads // n, ffn=cfg.ffn // n)
-    c.v_heads_full = cfg.v_heads
-    c.tp = n
-    return c
+    shard = dataclasses.replace(cfg, v_heads=cfg.v_heads // n, **{f: getattr(cfg, f) // n for f in split})
+    shard.v_heads_full, shard.tp = cfg.v_heads, n
+    return shard
 
 
 def shard_index(cfg, n, r):

@@ -79,49 +79,61 @@ def repack(kq: GW.KQuant) -> W4:
 
 
 def concat(ws):
-    """Row-concatenation of W4 matrices of one kind (a fused projection)."""
-    kinds = {w.kind for w in ws}
-    if len(kinds) != 1:
-        raise ValueError(f"cannot fuse k-quant kinds {kinds}")
-    cat = lambda f: None if getattr(ws[0], f) is None else torch.cat(      # noqa: E731
-        [getattr(w, f) for w in ws], 0 if f == "q" else 1)
-    return W4(ws[0].kind, cat("q"), cat("sc"), cat("mn"), cat("d"), cat("dm"), sum(w.n for w in ws), ws[0].k)
+    """Stack W4 matrices of ONE kind on top of each other (the rows of a fused projection).  The quants are row-major
+    and grow along dim 0; scales, mins and d are stored super-block-major [k/256, n, ...] and grow along dim 1."""
+    first = ws[0]
+    odd = sorted({w.kind for w in ws} - {first.kind})
+    if odd:
+        raise ValueError(f"one fused segment holds one k-quant kind: {first.kind} cannot take {odd}")
+
+    def joined(field, dim):
+        parts = [getattr(w, field) for w in ws]
+        return None if parts[0] is None else torch.cat(parts, dim)
+    return W4(first.kind, joined("q", 0), joined("sc", 1), joined("mn", 1), joined("d", 1), joined("dm", 1),
+              sum(w.n for w in ws), first.k)
 
 
 def segments(kqs, device):
-    """The KQuant matrices of a fused projection -> [(W4, first output column)]: neighbours of one kind fused (a
-    Q4_K_M file puts a Q6_K v under Q4_K q and k)."""
-    out, off = [], 0
+    """The matrices of a fused projection, top to bottom (e.g. q, k, v of a Q4_K_M file: Q4_K, Q4_K, Q6_K), as
+    [(W4, its first output column)].  Runs of neighbours that share a kind become one W4, so the projection costs one
+    GEMM per kind change, not one per matrix."""
+    runs = []
     for kq in kqs:
         if not isinstance(kq, GW.KQuant):
-            raise ValueError(f"the W4A8 path needs k-quant projections, not {type(kq).__name__}")
+            raise ValueError(f"W4A8 runs on k-quant matrices; a {type(kq).__name__} was given")
         w = repack(kq.to(device))
-        if out and out[-1][0].kind == w.kind:
-            out[-1] = (concat([out[-1][0], w]), out[-1][1])
+        if runs and runs[-1][0].kind == w.kind:
+            runs[-1].append(w)
         else:
-            out.append((w, off))
-        off += w.n
+            runs.append([w])
+    out, column = [], 0
+    for run in runs:
+        w = run[0] if len(run) == 1 else concat(run)
+        out.append((w, column))
+        column += w.n
     return out
 
 
 def seg_rows(segs, r0, r1):
-    """Output columns r0:r1 of a fused projection, as segments with first columns counted from r0."""
-    out = []
-    for w, off in segs:
-        a, b = max(r0, off), min(r1, off + w.n)
-        if a < b:
-            out.append((w.rows(a - off, b - off), a - r0))
-    return out
+    """The part of a fused projection that produces output columns [r0, r1): each segment cut to its overlap with
+    the range, first columns renumbered from r0 (a tensor-parallel rank's slice, or a head's rows)."""
+    picked = []
+    for w, first in segs:
+        lo, hi = max(r0 - first, 0), min(r1 - first, w.n)
+        if hi > lo:
+            picked.append((w.rows(lo, hi), first + lo - r0))
+    return picked
 
 
 def seg_width(segs):
-    return max(off + w.n for w, off in segs)
+    """Output columns of a fused projection."""
+    return max(first + w.n for w, first in segs)
 
 
 def gemm_segs(xq, a, xs, segs, out, n_rows, epi=0, pdl=0):
-    """A fused projection: one GEMM per segment, each into its columns of out."""
-    for w, off in segs:
-        gemm(xq, a, xs, w, out[:, off:off + w.n], n_rows, epi, pdl=pdl)
+    """The fused projection's GEMMs: every segment writes (or adds into) its own column range of `out`."""
+    for w, first in segs:
+        gemm(xq, a, xs, w, out[:, first:first + w.n], n_rows, epi, pdl=pdl)
 
 
 def pick_split(M, N, K, tile=128):

@@ -25,8 +25,28 @@ os.environ["STARTLUX_PRISM_GEMM"] = "triton"            # no dispatch table: the
 
 import numpy as np  # noqa: E402
 import torch  # noqa: E402
+import triton.language as tl  # noqa: E402
+from triton.language import core as _tl_core  # noqa: E402
 
 import gpu_cases as C  # noqa: E402
+
+# The reference pins Triton 3.8, where tl.dot(a, b, acc) takes its result type from the accumulator.  Older Tritons
+# (3.6 is what this image has) assert acc.dtype == out_dtype with out_dtype defaulting to float32, so the reference's
+# int8 dot into an int32 accumulator (kernels/w8a8.py:58,70) fails to compile there.  This shim changes nothing but that
+# default - out_dtype = the accumulator's type when one is given - and leaves the reference's source untouched.
+_dot = tl.dot
+
+
+@_tl_core.builtin
+def _dot_typed_by_acc(input, other, acc=None, input_precision=None, allow_tf32=None, max_num_imprecise_acc=None,
+                      out_dtype=None, _semantic=None):
+    if out_dtype is None:
+        out_dtype = acc.dtype if acc is not None else tl.float32
+    return _dot(input, other, acc, input_precision, allow_tf32, max_num_imprecise_acc, out_dtype, _semantic=_semantic)
+
+
+if tuple(int(x) for x in __import__("triton").__version__.split(".")[:2]) < (3, 8):
+    tl.dot = _tl_core.dot = _dot_typed_by_acc
 from startlux_prism.kernels import decode as RDEC  # noqa: E402
 from startlux_prism.kernels import mxfp4 as RMX  # noqa: E402
 from startlux_prism.kernels import quant as RQ  # noqa: E402

@@ -28,12 +28,13 @@ def test_head_quant(dev, B, HID, live):
 
 @pytest.mark.parametrize("B,N,K,live", [(1, 4000, 1024, 1), (16, 24832, 5120, 13), (64, 1000, 2560, 64)])
 def test_head_q8(dev, B, N, K, live):
-    """logits = sum over groups, in order, of (float(a_g . w_g) * a_s[g]) * w_s[g] with the scales as the file keeps
-    them (fp16, group-major): the oracle's bits; rows >= live untouched."""
+    """logits = the groups' sums in order, acc = fma(float(a_g . w_g) * a_s[g], w_s[g], acc) - what the reference's
+    kernel computes once its compiler has fused `acc += (ai * sa) * sw` (pinned by the recorded reference output,
+    tests/test_reference_kernels.py::test_head) - with the scales as the file keeps them (fp16, group-major): the
+    oracle's bits; rows >= live untouched."""
     a, w, sa, sw = rand_w8a8(B, N, K, seed=N, groups=K // 32)
     sw16 = sw.to(torch.float16)                                     # the file's precision
-    ref = oracle.w8a8_gemm(a.numpy(), sa.numpy(), w.numpy(), sw16.float().numpy(), 32, 1, live,
-                           out=np.zeros((B, N), np.float32))
+    ref = oracle.w8a8_gemm(a.numpy(), sa.numpy(), w.numpy(), sw16.float().numpy(), 32, 4, live)
     ws_file = sw16.t().contiguous()                                 # [K / 32, N]
     out = torch.full((B, N), 7.0, device=dev)
     decode.head_q8(a.to(dev), sa.to(dev), w.to(dev), ws_file.to(dev), out, n_rows(live, dev), B)

@@ -36,6 +36,14 @@ def has(ref, key):
     return ref[key]
 
 
+def ulp_report(what, got, want):
+    """Scales: the reference divides with Triton's `/` (div.full.f32, not correctly rounded); the oracle's contract is the
+    IEEE quotient.  Count the scales that differ and require them to be neighbours."""
+    d = np.abs(got.view(np.uint32).astype(np.int64) - want.view(np.uint32).astype(np.int64))
+    print(f"{what}: {int((d != 0).sum())} of {d.size} scales differ from the reference kernel's, by at most {d.max()} ulp")
+    assert d.max() <= 2, (what, d.max())
+
+
 def step_report(what, got, want):
     """Count of int8 values that differ, all of which must differ by exactly one step."""
     d = np.abs(got.astype(np.int32) - want.astype(np.int32))
@@ -69,7 +77,7 @@ def test_rows_q8(ref, name):
     i = C.rows_inputs(name)
     q, s = oracle.quant_rows(C.bits(i["x"]), None, None if i["inv"] is None else i["inv"].numpy(), i["live"])
     live = i["live"]
-    assert np.array_equal(s.reshape(-1)[:live].view(np.uint32), has(ref, f"rows/{name}/s")[:live].view(np.uint32))
+    ulp_report(f"rows_q8 {name}", s.reshape(-1)[:live], has(ref, f"rows/{name}/s")[:live])
     frac = step_report(f"rows_q8 {name}", q[:live], has(ref, f"rows/{name}/q")[:live])
     assert frac < 1e-3
 
@@ -77,7 +85,7 @@ def test_rows_q8(ref, name):
 def test_quant_rows_groups(ref):
     i = C.groups_inputs()
     q, s = oracle.quant_rows(C.bits(i["x"]), i["gk"])
-    assert np.array_equal(s.view(np.uint32), has(ref, "groups/s").view(np.uint32))
+    ulp_report("quant_rows gk=32", s, has(ref, "groups/s"))
     assert step_report("quant_rows gk=32", q, has(ref, "groups/q")) < 1e-3
 
 
@@ -120,14 +128,11 @@ def test_head(ref):
     q, s = oracle.head_quant(i["h"].numpy(), i["w"].numpy(), C.EPS, live)
     assert np.allclose(s[:live], has(ref, "head/s")[:live], rtol=1e-5, atol=0)
     step_report("head_quant", q[:live], has(ref, "head/q")[:live])
-    # the head GEMM on the reference's own int8 rows: multiply, multiply, add per group (the Triton expression may
-    # contract the last two into one fused multiply-add: compared to fp32 rounding, and the count of equal bits shown)
+    # the head GEMM on the reference's own int8 rows: the reference writes `acc += (ai * sa) * sw` without explicit
+    # roundings and its compiler fuses the second multiply with the add; the oracle's epi 4 states exactly that
     rq, rs = has(ref, "head/q"), has(ref, "head/s")
-    got = oracle.w8a8_gemm(rq[:live], rs[:live], i["wq"].numpy(), i["wd"].float().numpy(), 32, 1, live,
-                           out=np.zeros((live, i["N"]), np.float32))      # 0 + v: the plain fp32 values
-    want = has(ref, "head/logits")[:live]
-    print(f"head_q8: {(got.view(np.uint32) == want.view(np.uint32)).mean():.4f} of the logits bit-equal")
-    assert np.allclose(got, want, rtol=1e-5, atol=1e-5)
+    got = oracle.w8a8_gemm(rq[:live], rs[:live], i["wq"].numpy(), i["wd"].float().numpy(), 32, 4, live)
+    assert np.array_equal(got.view(np.uint32), has(ref, "head/logits")[:live].view(np.uint32))
 
 
 @pytest.mark.parametrize("name", list(C.SWIGLU_EPI_CASES))

@@ -275,7 +275,7 @@ def test_gemm_any_group_size(dev, M, N, K, live, gk):
     assert same(res, ref1), first_diff(res.cpu().numpy(), ref1)
 
 
-@pytest.mark.parametrize("M,FF,K,live,bn", [(70, 256, 512, 66, 128), (20, 192, 256, 20, 64), (300, 640, 1024, 290, 128),
+@pytest.mark.parametrize("M,FF,K,live,bn", [(70, 256, 512, 66, 128), (20, 256, 256, 20, 64), (300, 640, 1024, 290, 128),
                                             (16, 17408 // 8, 5120, 16, 128)])
 def test_gemm_swiglu_epilogue(dev, M, FF, K, live, bn):
     """epi 2: gate|up rows interleaved in tiles of bn, silu(gate) * up quantized per row and tile in the epilogue
