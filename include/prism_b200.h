@@ -117,6 +117,41 @@ int pb_fold(float* h, long ldh, const int32_t* slots, long slot_stride, int S, c
 int pb_quant_rows(const void* x, int x_fp32, long ldx, const float* inv_s, int8_t* q, float* s, const int* n_rows,
                   int T, int K, int gk, int mode, float* amax, void* stream);
 
+/* Exchanges between the GPUs of a tensor-parallel group INSIDE a kernel, for passes of a few rows (decode), where a
+ * collective call per exchange costs more than the work between them.  Replaces the reference's quant.Sync / mode 3 /
+ * _tp_sync / _ll_amax / _fold_parts over symmetric memory (kernels/quant.py:55-141, :190-212; tp.py:358-432); up to 8
+ * ranks (the reference: 4).  Buffers are device memory every rank has mapped (pb_peer_alloc / pb_peer_open):
+ *   epoch   device int64 [1], the pass number: the same on every rank, incremented once per pass before its kernels
+ *   bufs    every rank's 64-bit word buffer as mapped on this GPU, in rank order (bufs[rank] is this rank's own)
+ *   off     row maxima: the first word row of this exchange (a step's rows are (off + t) * world + rank);
+ *           flag handshakes: the step's channel (its flags are off * world + rank)
+ *   others  folds only: the other ranks' int32 slot buffers as mapped here (world - 1 entries), laid out as the own
+ * pb_quant_rows_exchange / pb_swiglu_q8_exchange / pb_gated_norm_q8_exchange: the producers' mode 3 - every row's
+ * maximum over all ranks travels as one word (pass number above the float's bits) per row and rank; fewer than 256
+ * rows per call.  pb_fold_sync / pb_norm_q8_sync: the deferred add over EVERY rank's slots, read over NVLink after a
+ * flag handshake (the grid's first block signals, every block waits) - the int32 all-reduce disappears.
+ * Each wait is bounded (pb_set_wait_limit_ns): a rank that never arrives yields PB_DEVICE_TIMEOUT in the status word,
+ * not a hang.  Peer traffic is plain loads and stores; no TMA and no multicast touches another GPU's memory. */
+typedef struct pb_sync {
+    const long long* epoch;
+    void* bufs[8];
+    const void* others[7];
+    long off;
+    int rank, world;
+} pb_sync;
+int pb_quant_rows_exchange(const void* x, int x_fp32, long ldx, const float* inv_s, int8_t* q, float* s, const int* n_rows,
+                           int T, int K, const pb_sync* sync, void* stream);
+int pb_swiglu_q8_exchange(const void* gu, const float* inv_s, int8_t* q, float* s, const int* n_rows, int T, int FF,
+                          const pb_sync* sync, void* stream);
+int pb_gated_norm_q8_exchange(const float* o, const void* proj, long P, long z_off, const float* w, const float* inv_s,
+                              int8_t* q, float* s, const int* n_rows, int T, int HV, int D, float eps, const pb_sync* sync,
+                              void* stream);
+int pb_fold_sync(float* h, long ldh, const int32_t* slots, long slot_stride, int S, const float* a_s, const float* w_s,
+                 const int* n_rows, int rows, int N, const pb_sync* sync, void* stream);
+int pb_norm_q8_sync(float* h, const float* w, int8_t* q, float* s, const int* n_rows, int T, int HID, float eps,
+                    const int32_t* parts, long part_stride, int n_parts, const float* psa, const float* psw,
+                    const pb_sync* sync, void* stream);
+
 /* RMSNorm + per-token quantization, with a deferred residual add finished first.  Replaces quant.norm_q8 /
  * _norm_q8_kernel (kernels/quant.py:145-171, :418-431): for output row i (input row rows[i] when rows != NULL, else i):
  *   h = add_rn(h, mul_rn(mul_rn(float(sum_p parts[p]), psa[r]), psw[c]))  (n_parts > 0; stored back into h)
@@ -129,7 +164,7 @@ int pb_norm_q8(float* h, const float* w, int8_t* q, float* s, const int* rows, c
 
 /* Gated RMSNorm of the linear-attention output + per-token quantization.  Replaces quant.gated_norm_q8 /
  * _gated_norm_q8_kernel (kernels/quant.py:215-246, :460-470), modes 0 / 1 / 2 (mode 3, the in-kernel cross-rank
- * exchange, is not part of this build).  o fp32 [T, HV * D]; z = bf16 proj[t * P + z_off + ...]; w fp32 [D];
+ * exchange: pb_gated_norm_q8_exchange).  o fp32 [T, HV * D]; z = bf16 proj[t * P + z_off + ...]; w fp32 [D];
  * inv_s fp32 [HV * D]; D in {64, 128, 256}.  y = ((o * rsqrt(mean_D(o^2) + eps)) * w) * silu(z) * inv_s per head,
  * s[t] = max(|y|max, 1e-10) / 127, q = rint(y / s[t]). */
 int pb_gated_norm_q8(const float* o, const void* proj, long P, long z_off, const float* w, const float* inv_s, int8_t* q,

@@ -10,6 +10,15 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 PATH = os.path.join(HERE, "libprism_b200.so")
 
 _vp, _i, _l = ctypes.c_void_p, ctypes.c_int, ctypes.c_long
+
+
+class SyncStruct(ctypes.Structure):
+    """pb_sync of include/prism_b200.h."""
+    _fields_ = [("epoch", ctypes.c_void_p), ("bufs", ctypes.c_void_p * 8), ("others", ctypes.c_void_p * 7),
+                ("off", ctypes.c_long), ("rank", ctypes.c_int), ("world", ctypes.c_int)]
+
+
+_sp = ctypes.POINTER(SyncStruct)
 _SIGS = {
     "pb_version": ([], _i),
     "pb_status_string": ([_i], ctypes.c_char_p),
@@ -26,6 +35,11 @@ _SIGS = {
     "pb_peer_open": ([_vp, _vp], _i),
     "pb_peer_close": ([_vp], _i),
     "pb_peer_free": ([_vp], _i),
+    "pb_quant_rows_exchange": ([_vp, _i, _l, _vp, _vp, _vp, _vp, _i, _i, _sp, _vp], _i),
+    "pb_swiglu_q8_exchange": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _sp, _vp], _i),
+    "pb_gated_norm_q8_exchange": ([_vp, _vp, _l, _l, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, ctypes.c_float, _sp, _vp], _i),
+    "pb_fold_sync": ([_vp, _l, _vp, _l, _i, _vp, _vp, _vp, _i, _i, _sp, _vp], _i),
+    "pb_norm_q8_sync": ([_vp, _vp, _vp, _vp, _vp, _i, _i, ctypes.c_float, _vp, _l, _i, _vp, _vp, _sp, _vp], _i),
     "pb_fold": ([_vp, _l, _vp, _l, _i, _vp, _vp, _vp, _i, _i, _vp], _i),
     "pb_quant_rows": ([_vp, _i, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp], _i),
     "pb_swiglu_q8": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp], _i),

@@ -282,7 +282,20 @@ int launch_swap(const int8_t* a, const float* a_s, const int8_t* w, const float*
     using C = w8a8::SwapCfg<NB, GROUPED>;
     CUtensorMap tw, tx, tsw, tsa;
     int rc;
-    if ((rc = tensor_map(&tw, w, p.K, p.N, p.K, w8a8::BK, w8a8::BM, 0))) return rc;
+    // per-32 groups in one K slice: when the 128-row weight tiles are fewer than about three quarters of the SMs the
+    // CTAs take 64 or 32 weight rows each (the group order, and so every bit, stays the same; PRISM_B200_WROWS overrides)
+    int wrows = w8a8::BM;
+    if (GROUPED && split == 1) {
+        const long mt = (p.M + NB - 1) / NB;
+        const int want = sm_count() * 3 / 4;
+        static const int forced = [] { const char* e = getenv("PRISM_B200_WROWS"); return e ? atoi(e) : 0; }();
+        if (forced == 32 || forced == 64 || forced == 128) wrows = forced;
+        else if (mt * ((p.N + 127) / 128) >= want) wrows = 128;
+        else if (mt * ((p.N + 63) / 64) >= want) wrows = 64;
+        else wrows = 32;
+    }
+    p.wrows = wrows;
+    if ((rc = tensor_map(&tw, w, p.K, p.N, p.K, w8a8::BK, wrows, 0))) return rc;
     if ((rc = tensor_map(&tx, a, p.K, p.M, p.K, w8a8::BK, NB, 0))) return rc;
     if (GROUPED) {
         const uint64_t G = p.K / 32;
@@ -294,7 +307,7 @@ int launch_swap(const int8_t* a, const float* a_s, const int8_t* w, const float*
     }
     auto kern = w8a8::w8a8_swap_kernel<NB, GROUPED>;
     if ((rc = set_smem(kern, C::smem_bytes(C::STAGES_DEEP)))) return rc;
-    dim3 grid((p.N + 127) / 128, split, (p.M + NB - 1) / NB);
+    dim3 grid((p.N + wrows - 1) / wrows, split, (p.M + NB - 1) / NB);
     // a grid no larger than the SM count gets one CTA per SM and the deepest pipeline; a larger one two CTAs per SM
     p.stages = (long)grid.x * grid.y * grid.z <= sm_count() ? C::STAGES_DEEP : C::STAGES;
     const int smem = C::smem_bytes(p.stages);
@@ -602,13 +615,13 @@ bool div_full() {
 
 template <int VPT>
 void launch_rows(bool bf16, bool full, int threads, const void* x, long ldx, const float* inv_s, int8_t* q, float* s,
-                        const int* n_rows, int T, int K, int mode, float* amax, cudaStream_t st) {
+                        const int* n_rows, int T, int K, int mode, float* amax, const tpx::Sync& sy, cudaStream_t st) {
     if (bf16) {
-        if (full) quant::rows_q8_kernel<VPT, true, true><<<T, threads, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax);
-        else quant::rows_q8_kernel<VPT, true, false><<<T, threads, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax);
+        if (full) quant::rows_q8_kernel<VPT, true, true><<<T, threads, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax, sy);
+        else quant::rows_q8_kernel<VPT, true, false><<<T, threads, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax, sy);
     } else {
-        if (full) quant::rows_q8_kernel<VPT, false, true><<<T, threads, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax);
-        else quant::rows_q8_kernel<VPT, false, false><<<T, threads, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax);
+        if (full) quant::rows_q8_kernel<VPT, false, true><<<T, threads, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax, sy);
+        else quant::rows_q8_kernel<VPT, false, false><<<T, threads, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax, sy);
     }
 }
 
@@ -901,11 +914,33 @@ int pb_fold(float* h, long ldh, const int32_t* slots, long slot_stride, int S, c
     return PB_OK;
 }
 
-int pb_quant_rows(const void* x, int x_fp32, long ldx, const float* inv_s, int8_t* q, float* s, const int* n_rows,
-                  int T, int K, int gk, int mode, float* amax, void* stream) {
+// pb_sync (the C struct) -> the kernels' view; world <= 1 when there is none
+static int to_sync(const pb_sync* in, tpx::Sync* out, bool need_others) {
+    memset(out, 0, sizeof(*out));
+    out->world = 1;
+    if (!in) return PB_OK;
+    if (in->world < 2 || in->world > tpx::MAX_RANKS || in->rank < 0 || in->rank >= in->world || !in->epoch) return PB_BAD_ARGUMENT;
+    out->epoch = in->epoch;
+    for (int r = 0; r < in->world; ++r) {
+        if (!in->bufs[r] || ((uintptr_t)in->bufs[r] & 7)) return PB_BAD_ARGUMENT;
+        out->bufs[r] = (unsigned long long*)in->bufs[r];
+    }
+    for (int r = 0; r + 1 < in->world; ++r) {
+        if (need_others && (!in->others[r] || !aligned16(in->others[r]))) return PB_BAD_ARGUMENT;
+        out->others[r] = (const int32_t*)in->others[r];
+    }
+    out->off = in->off;
+    out->rank = in->rank;
+    out->world = in->world;
+    return PB_OK;
+}
+
+static int quant_rows_impl(const void* x, int x_fp32, long ldx, const float* inv_s, int8_t* q, float* s, const int* n_rows,
+                           int T, int K, int gk, int mode, float* amax, const tpx::Sync& sy, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     if (!x || !q || !s || !n_rows || T <= 0 || K <= 0 || gk <= 0 || K % gk) return PB_BAD_ARGUMENT;
-    if (mode < 0 || mode > 2 || (mode != 0 && !amax) || ldx < K) return PB_BAD_ARGUMENT;
+    if (mode < 0 || mode > 3 || ((mode == 1 || mode == 2) && !amax) || ldx < K) return PB_BAD_ARGUMENT;
+    if (mode == 3 && (sy.world < 2 || gk != K)) return PB_BAD_ARGUMENT;
     const bool bf16 = !x_fp32, full = div_full();
     if (gk != K) {
         if (inv_s || mode != 0 || ldx != K) return PB_UNSUPPORTED_SHAPE;
@@ -925,16 +960,16 @@ int pb_quant_rows(const void* x, int x_fp32, long ldx, const float* inv_s, int8_
     const bool fast = K % 8 == 0 && K <= 65536 && aligned16(x) && (ldx * (bf16 ? 2 : 4)) % 16 == 0 && !((uintptr_t)q & 7) && (!inv_s || aligned16(inv_s));
     if (!fast) {
         if (bf16) {
-            if (full) quant::rows_q8_generic_kernel<true, true><<<T, 256, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax);
-            else quant::rows_q8_generic_kernel<true, false><<<T, 256, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax);
+            if (full) quant::rows_q8_generic_kernel<true, true><<<T, 256, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax, sy);
+            else quant::rows_q8_generic_kernel<true, false><<<T, 256, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax, sy);
         } else {
-            if (full) quant::rows_q8_generic_kernel<false, true><<<T, 256, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax);
-            else quant::rows_q8_generic_kernel<false, false><<<T, 256, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax);
+            if (full) quant::rows_q8_generic_kernel<false, true><<<T, 256, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax, sy);
+            else quant::rows_q8_generic_kernel<false, false><<<T, 256, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax, sy);
         }
         PB_CUDA(cudaGetLastError());
         return PB_OK;
     }
-    if (T >= kPipeMinRows && K <= 32768) {
+    if (T >= kPipeMinRows && K <= 32768 && mode != 3) {        // (the in-kernel exchange lives in the one-CTA-per-row kernels)
         quant::PipeArgs pa{x, ldx, inv_s, q, s, n_rows, amax, T, K, mode, K * (bf16 ? 2 : 4), 0};
         const int rc = bf16 ? launch_pipe<quant::PIPE_ROWS, true>(full, pa, st)
                             : launch_pipe<quant::PIPE_ROWS, false>(full, pa, st);
@@ -944,15 +979,32 @@ int pb_quant_rows(const void* x, int x_fp32, long ldx, const float* inv_s, int8_
     const int nvec = K / 8;
     const int vpt = nvec <= 4096 ? 4 : 8;
     const int threads = ((nvec + vpt - 1) / vpt + 31) / 32 * 32;
-    if (vpt == 4) launch_rows<4>(bf16, full, threads, x, ldx, inv_s, q, s, n_rows, T, K, mode, amax, st);
-    else launch_rows<8>(bf16, full, threads, x, ldx, inv_s, q, s, n_rows, T, K, mode, amax, st);
+    if (vpt == 4) launch_rows<4>(bf16, full, threads, x, ldx, inv_s, q, s, n_rows, T, K, mode, amax, sy, st);
+    else launch_rows<8>(bf16, full, threads, x, ldx, inv_s, q, s, n_rows, T, K, mode, amax, sy, st);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }
 
-int pb_norm_q8(float* h, const float* w, int8_t* q, float* s, const int* rows, const int* n_rows, int T, int HID,
-               float eps, const int32_t* parts, long part_stride, int n_parts, const float* psa, const float* psw,
-               void* stream) {
+int pb_quant_rows(const void* x, int x_fp32, long ldx, const float* inv_s, int8_t* q, float* s, const int* n_rows,
+                  int T, int K, int gk, int mode, float* amax, void* stream) {
+    if (mode == 3) return PB_BAD_ARGUMENT;                         // pb_quant_rows_exchange
+    tpx::Sync sy;
+    to_sync(nullptr, &sy, false);
+    return quant_rows_impl(x, x_fp32, ldx, inv_s, q, s, n_rows, T, K, gk, mode, amax, sy, stream);
+}
+
+int pb_quant_rows_exchange(const void* x, int x_fp32, long ldx, const float* inv_s, int8_t* q, float* s, const int* n_rows,
+                           int T, int K, const pb_sync* sync, void* stream) {
+    tpx::Sync sy;
+    int rc = to_sync(sync, &sy, false);
+    if (rc) return rc;
+    if (!sync) return PB_BAD_ARGUMENT;
+    return quant_rows_impl(x, x_fp32, ldx, inv_s, q, s, n_rows, T, K, K, 3, nullptr, sy, stream);
+}
+
+static int norm_q8_impl(float* h, const float* w, int8_t* q, float* s, const int* rows, const int* n_rows, int T, int HID,
+                        float eps, const int32_t* parts, long part_stride, int n_parts, const float* psa, const float* psw,
+                        const tpx::Sync& sy, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     if (!h || !w || !q || !s || !n_rows || T <= 0 || HID <= 0 || n_parts < 0) return PB_BAD_ARGUMENT;
     if (n_parts > 0 && (!parts || !psa || !psw || rows)) return PB_BAD_ARGUMENT;
@@ -964,21 +1016,40 @@ int pb_norm_q8(float* h, const float* w, int8_t* q, float* s, const int* rows, c
     const int vpt = nvec <= 2048 ? 4 : 8;
     const int threads = ((nvec + vpt - 1) / vpt + 31) / 32 * 32;
     if (vpt == 4) {
-        if (full) quant::norm_q8_kernel<4, true><<<T, threads, 0, st>>>(h, w, q, s, rows, n_rows, HID, eps, parts, part_stride, n_parts, psa, psw);
-        else quant::norm_q8_kernel<4, false><<<T, threads, 0, st>>>(h, w, q, s, rows, n_rows, HID, eps, parts, part_stride, n_parts, psa, psw);
+        if (full) quant::norm_q8_kernel<4, true><<<T, threads, 0, st>>>(h, w, q, s, rows, n_rows, HID, eps, parts, part_stride, n_parts, psa, psw, sy);
+        else quant::norm_q8_kernel<4, false><<<T, threads, 0, st>>>(h, w, q, s, rows, n_rows, HID, eps, parts, part_stride, n_parts, psa, psw, sy);
     } else {
-        if (full) quant::norm_q8_kernel<8, true><<<T, threads, 0, st>>>(h, w, q, s, rows, n_rows, HID, eps, parts, part_stride, n_parts, psa, psw);
-        else quant::norm_q8_kernel<8, false><<<T, threads, 0, st>>>(h, w, q, s, rows, n_rows, HID, eps, parts, part_stride, n_parts, psa, psw);
+        if (full) quant::norm_q8_kernel<8, true><<<T, threads, 0, st>>>(h, w, q, s, rows, n_rows, HID, eps, parts, part_stride, n_parts, psa, psw, sy);
+        else quant::norm_q8_kernel<8, false><<<T, threads, 0, st>>>(h, w, q, s, rows, n_rows, HID, eps, parts, part_stride, n_parts, psa, psw, sy);
     }
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }
 
-int pb_gated_norm_q8(const float* o, const void* proj, long P, long z_off, const float* w, const float* inv_s, int8_t* q,
-                     float* s, const int* n_rows, int T, int HV, int D, float eps, int mode, float* amax, void* stream) {
+int pb_norm_q8(float* h, const float* w, int8_t* q, float* s, const int* rows, const int* n_rows, int T, int HID,
+               float eps, const int32_t* parts, long part_stride, int n_parts, const float* psa, const float* psw,
+               void* stream) {
+    tpx::Sync sy;
+    to_sync(nullptr, &sy, false);
+    return norm_q8_impl(h, w, q, s, rows, n_rows, T, HID, eps, parts, part_stride, n_parts, psa, psw, sy, stream);
+}
+
+int pb_norm_q8_sync(float* h, const float* w, int8_t* q, float* s, const int* n_rows, int T, int HID, float eps,
+                    const int32_t* parts, long part_stride, int n_parts, const float* psa, const float* psw,
+                    const pb_sync* sync, void* stream) {
+    tpx::Sync sy;
+    int rc = to_sync(sync, &sy, true);
+    if (rc) return rc;
+    if (!sync || n_parts <= 0) return PB_BAD_ARGUMENT;
+    return norm_q8_impl(h, w, q, s, nullptr, n_rows, T, HID, eps, parts, part_stride, n_parts, psa, psw, sy, stream);
+}
+
+static int gated_norm_q8_impl(const float* o, const void* proj, long P, long z_off, const float* w, const float* inv_s, int8_t* q,
+                              float* s, const int* n_rows, int T, int HV, int D, float eps, int mode, float* amax,
+                              const tpx::Sync& sy, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     if (!o || !proj || !w || !inv_s || !q || !s || !n_rows || T <= 0 || HV <= 0) return PB_BAD_ARGUMENT;
-    if (mode < 0 || mode > 2 || (mode != 0 && !amax)) return PB_BAD_ARGUMENT;
+    if (mode < 0 || mode > 3 || ((mode == 1 || mode == 2) && !amax) || (mode == 3 && sy.world < 2)) return PB_BAD_ARGUMENT;
     if (D != 64 && D != 128 && D != 256) return PB_UNSUPPORTED_SHAPE;
     if (!aligned16(o) || !aligned16(w) || !aligned16(inv_s) || ((uintptr_t)q & 7) || !aligned16(proj) || (P * 2) % 16 ||
         (z_off * 2) % 16)
@@ -990,13 +1061,31 @@ int pb_gated_norm_q8(const float* o, const void* proj, long P, long z_off, const
     const int vpt = nvec <= 1024 ? 1 : nvec <= 2048 ? 2 : 4;
     const int threads = ((nvec + vpt - 1) / vpt + 31) / 32 * 32;
     const __nv_bfloat16* pj = (const __nv_bfloat16*)proj;
-#define PB_GN(V, F) quant::gated_norm_q8_kernel<V, F><<<T, threads, 0, st>>>(o, pj, P, z_off, w, inv_s, q, s, n_rows, HV, D, eps, mode, amax)
+#define PB_GN(V, F) quant::gated_norm_q8_kernel<V, F><<<T, threads, 0, st>>>(o, pj, P, z_off, w, inv_s, q, s, n_rows, HV, D, eps, mode, amax, sy)
     if (vpt == 1) { if (full) PB_GN(1, true); else PB_GN(1, false); }
     else if (vpt == 2) { if (full) PB_GN(2, true); else PB_GN(2, false); }
     else { if (full) PB_GN(4, true); else PB_GN(4, false); }
 #undef PB_GN
     PB_CUDA(cudaGetLastError());
     return PB_OK;
+}
+
+int pb_gated_norm_q8(const float* o, const void* proj, long P, long z_off, const float* w, const float* inv_s, int8_t* q,
+                     float* s, const int* n_rows, int T, int HV, int D, float eps, int mode, float* amax, void* stream) {
+    if (mode == 3) return PB_BAD_ARGUMENT;
+    tpx::Sync sy;
+    to_sync(nullptr, &sy, false);
+    return gated_norm_q8_impl(o, proj, P, z_off, w, inv_s, q, s, n_rows, T, HV, D, eps, mode, amax, sy, stream);
+}
+
+int pb_gated_norm_q8_exchange(const float* o, const void* proj, long P, long z_off, const float* w, const float* inv_s,
+                              int8_t* q, float* s, const int* n_rows, int T, int HV, int D, float eps, const pb_sync* sync,
+                              void* stream) {
+    tpx::Sync sy;
+    int rc = to_sync(sync, &sy, false);
+    if (rc) return rc;
+    if (!sync) return PB_BAD_ARGUMENT;
+    return gated_norm_q8_impl(o, proj, P, z_off, w, inv_s, q, s, n_rows, T, HV, D, eps, 3, nullptr, sy, stream);
 }
 
 int pb_head_quant(const float* h, const float* w, int8_t* q, float* s, const int* n_rows, int B, int HID, float eps,
@@ -1019,14 +1108,14 @@ int pb_head_quant(const float* h, const float* w, int8_t* q, float* s, const int
     return PB_OK;
 }
 
-int pb_swiglu_q8(const void* gu, const float* inv_s, int8_t* q, float* s, const int* n_rows, int T, int FF, int mode,
-                 float* amax, void* stream) {
+static int swiglu_q8_impl(const void* gu, const float* inv_s, int8_t* q, float* s, const int* n_rows, int T, int FF, int mode,
+                          float* amax, const tpx::Sync& sy, void* stream) {
     cudaStream_t st = (cudaStream_t)stream;
     if (!gu || !q || !s || !n_rows || T <= 0 || FF <= 0) return PB_BAD_ARGUMENT;
-    if (mode < 0 || mode > 2 || (mode != 0 && !amax)) return PB_BAD_ARGUMENT;
+    if (mode < 0 || mode > 3 || ((mode == 1 || mode == 2) && !amax) || (mode == 3 && sy.world < 2)) return PB_BAD_ARGUMENT;
     if (FF % 8 || FF > 32768 || !aligned16(gu) || ((uintptr_t)q & 7)) return PB_UNSUPPORTED_SHAPE;
     const bool full = div_full();
-    if (T >= kPipeMinRows) {
+    if (T >= kPipeMinRows && mode != 3) {
         quant::PipeArgs pa{gu, 2l * FF, inv_s, q, s, n_rows, amax, T, FF, mode, 4 * FF, 0};
         const int rc = launch_pipe<quant::PIPE_SWIGLU, true>(full, pa, st);
         if (rc != PB_UNSUPPORTED_SHAPE) return rc;
@@ -1034,8 +1123,39 @@ int pb_swiglu_q8(const void* gu, const float* inv_s, int8_t* q, float* s, const 
     const int nvec = FF / 8;
     const int threads = ((nvec + 3) / 4 + 31) / 32 * 32;          // 4 vectors of 8 outputs per thread
     const __nv_bfloat16* g = (const __nv_bfloat16*)gu;
-    if (full) quant::swiglu_q8_kernel<4, true><<<T, threads, 0, st>>>(g, inv_s, q, s, n_rows, FF, mode, amax);
-    else quant::swiglu_q8_kernel<4, false><<<T, threads, 0, st>>>(g, inv_s, q, s, n_rows, FF, mode, amax);
+    if (full) quant::swiglu_q8_kernel<4, true><<<T, threads, 0, st>>>(g, inv_s, q, s, n_rows, FF, mode, amax, sy);
+    else quant::swiglu_q8_kernel<4, false><<<T, threads, 0, st>>>(g, inv_s, q, s, n_rows, FF, mode, amax, sy);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+int pb_swiglu_q8(const void* gu, const float* inv_s, int8_t* q, float* s, const int* n_rows, int T, int FF, int mode,
+                 float* amax, void* stream) {
+    if (mode == 3) return PB_BAD_ARGUMENT;
+    tpx::Sync sy;
+    to_sync(nullptr, &sy, false);
+    return swiglu_q8_impl(gu, inv_s, q, s, n_rows, T, FF, mode, amax, sy, stream);
+}
+
+int pb_swiglu_q8_exchange(const void* gu, const float* inv_s, int8_t* q, float* s, const int* n_rows, int T, int FF,
+                          const pb_sync* sync, void* stream) {
+    tpx::Sync sy;
+    int rc = to_sync(sync, &sy, false);
+    if (rc) return rc;
+    if (!sync) return PB_BAD_ARGUMENT;
+    return swiglu_q8_impl(gu, inv_s, q, s, n_rows, T, FF, 3, nullptr, sy, stream);
+}
+
+int pb_fold_sync(float* h, long ldh, const int32_t* slots, long slot_stride, int S, const float* a_s, const float* w_s,
+                 const int* n_rows, int rows, int N, const pb_sync* sync, void* stream) {
+    if (!h || !slots || !a_s || !w_s || !n_rows || rows <= 0 || N <= 0 || S < 1 || ldh < N || !sync) return PB_BAD_ARGUMENT;
+    if (N % 4) return PB_UNSUPPORTED_SHAPE;
+    if (!aligned16(h) || !aligned16(slots) || !aligned16(w_s) || (ldh % 4) || (slot_stride % 4)) return PB_BAD_ARGUMENT;
+    tpx::Sync sy;
+    int rc = to_sync(sync, &sy, true);
+    if (rc) return rc;
+    dim3 grid((N / 4 + 255) / 256, rows);
+    quant::fold_sync_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(h, ldh, slots, slot_stride, S, a_s, w_s, n_rows, N, sy);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }

@@ -11,12 +11,14 @@
 // even.  PB_DIV_FULL selects the approximate full-range division (div.full.f32) for both instead.
 #pragma once
 #include "common.cuh"
+#include "tp_sync.cuh"
 
 namespace quant {
 
 constexpr int MODE_PLAIN = 0;      // the row's own maximum
 constexpr int MODE_STORE_AMAX = 1; // also store the row's maximum (tensor parallel, before the max all-reduce)
 constexpr int MODE_USE_AMAX = 2;   // quantize with max(amax[t], own) (after it)
+constexpr int MODE_EXCHANGE = 3;   // the ranks exchange their row maxima inside this launch (tp_sync.cuh; kernels/quant.py:190-212)
 
 template <bool FULL>
 __device__ __forceinline__ float fdiv(float a, float b) {
@@ -108,7 +110,8 @@ __device__ __forceinline__ uint2 quant8(const float (&v)[8], float scale, float 
 template <int VPT, bool BF16, bool FULL>
 __global__ void __launch_bounds__(1024)
 rows_q8_kernel(const void* __restrict__ x, long ldx, const float* __restrict__ inv_s, int8_t* __restrict__ q,
-               float* __restrict__ s, const int* __restrict__ n_rows, int K, int mode, float* __restrict__ amax_io) {
+               float* __restrict__ s, const int* __restrict__ n_rows, int K, int mode, float* __restrict__ amax_io,
+               const tpx::Sync sync) {
     __shared__ float red[32];
     const long t = blockIdx.x;
     if (t >= *n_rows) return;
@@ -134,6 +137,7 @@ rows_q8_kernel(const void* __restrict__ x, long ldx, const float* __restrict__ i
     amax = block_max(amax, red);
     if (mode == MODE_STORE_AMAX && threadIdx.x == 0) amax_io[t] = amax;
     if (mode == MODE_USE_AMAX) amax = fmaxf(amax_io[t], amax);
+    if (mode == MODE_EXCHANGE) amax = tpx::exchange_amax(amax, t, sync);
     const float scale = fdiv<FULL>(fmaxf(amax, 1e-10f), 127.0f);
     const float rcp = __fdiv_rn(1.0f, scale);
 #pragma unroll
@@ -149,7 +153,7 @@ template <bool BF16, bool FULL>
 __global__ void __launch_bounds__(256)
 rows_q8_generic_kernel(const void* __restrict__ x, long ldx, const float* __restrict__ inv_s,
                        int8_t* __restrict__ q, float* __restrict__ s, const int* __restrict__ n_rows, int K, int mode,
-                       float* __restrict__ amax_io) {
+                       float* __restrict__ amax_io, const tpx::Sync sync) {
     __shared__ float red[32];
     const long t = blockIdx.x;
     if (t >= *n_rows) return;
@@ -162,6 +166,7 @@ rows_q8_generic_kernel(const void* __restrict__ x, long ldx, const float* __rest
     amax = block_max(amax, red);
     if (mode == MODE_STORE_AMAX && threadIdx.x == 0) amax_io[t] = amax;
     if (mode == MODE_USE_AMAX) amax = fmaxf(amax_io[t], amax);
+    if (mode == MODE_EXCHANGE) amax = tpx::exchange_amax(amax, t, sync);
     const float scale = fdiv<FULL>(fmaxf(amax, 1e-10f), 127.0f);
     for (int k = threadIdx.x; k < K; k += blockDim.x) q[t * K + k] = (int8_t)__float2int_rn(fdiv<FULL>(val(k), scale));
     if (threadIdx.x == 0) s[t] = scale;
@@ -204,7 +209,8 @@ __device__ __forceinline__ float swiglu(float g, float u) { return __fmul_rn(fdi
 template <int VPT, bool FULL>
 __global__ void __launch_bounds__(1024)
 swiglu_q8_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__ inv_s, int8_t* __restrict__ q,
-                 float* __restrict__ s, const int* __restrict__ n_rows, int FF, int mode, float* __restrict__ amax_io) {
+                 float* __restrict__ s, const int* __restrict__ n_rows, int FF, int mode, float* __restrict__ amax_io,
+                 const tpx::Sync sync) {
     __shared__ float red[32];
     const long t = blockIdx.x;
     if (t >= *n_rows) return;
@@ -231,6 +237,7 @@ swiglu_q8_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__
     amax = block_max(amax, red);
     if (mode == MODE_STORE_AMAX && threadIdx.x == 0) amax_io[t] = amax;
     if (mode == MODE_USE_AMAX) amax = fmaxf(amax_io[t], amax);
+    if (mode == MODE_EXCHANGE) amax = tpx::exchange_amax(amax, t, sync);
     const float scale = fdiv<FULL>(fmaxf(amax, 1e-10f), 127.0f);
     const float rcp = __fdiv_rn(1.0f, scale);
 #pragma unroll
@@ -267,11 +274,13 @@ __global__ void __launch_bounds__(1024)
 norm_q8_kernel(float* __restrict__ h, const float* __restrict__ w, int8_t* __restrict__ q, float* __restrict__ s,
                const int* __restrict__ rows, const int* __restrict__ n_rows, int HID, float eps,
                const int32_t* __restrict__ parts, long part_stride, int n_parts, const float* __restrict__ psa,
-               const float* __restrict__ psw) {
+               const float* __restrict__ psw, const tpx::Sync sync) {
     __shared__ float red[32];
     const long i = blockIdx.x;
     if (i >= *n_rows) return;
     const long r = rows ? (long)rows[i] : i;
+    // tensor parallel, shortest passes: the deferred add's slots are every rank's (read over NVLink after the handshake)
+    if (n_parts > 0) tpx::arrive_and_wait(sync, blockIdx.x == 0);
     const int nvec = HID >> 3;
     float v[VPT][8];
     float ss = 0.0f;
@@ -292,6 +301,13 @@ norm_q8_kernel(float* __restrict__ h, const float* __restrict__ w, int8_t* __res
                     tot[0] += x0.x; tot[1] += x0.y; tot[2] += x0.z; tot[3] += x0.w;
                     tot[4] += x1.x; tot[5] += x1.y; tot[6] += x1.z; tot[7] += x1.w;
                 }
+                for (int o = 0; o + 1 < sync.world; ++o)
+                    for (int pidx = 0; pidx < n_parts; ++pidx) {
+                        const int32_t* pp = sync.others[o] + pidx * part_stride + r * HID + (long)c * 8;
+                        const int4 x0 = tpx::ld_peer4(pp), x1 = tpx::ld_peer4(pp + 4);
+                        tot[0] += x0.x; tot[1] += x0.y; tot[2] += x0.z; tot[3] += x0.w;
+                        tot[4] += x1.x; tot[5] += x1.y; tot[6] += x1.z; tot[7] += x1.w;
+                    }
                 const float4 w0 = __ldg((const float4*)(psw + c * 8)), w1 = __ldg((const float4*)(psw + c * 8 + 4));
                 const float sw[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
@@ -343,7 +359,7 @@ __global__ void __launch_bounds__(1024)
 gated_norm_q8_kernel(const float* __restrict__ o, const __nv_bfloat16* __restrict__ proj, long P, long z_off,
                      const float* __restrict__ w, const float* __restrict__ inv_s, int8_t* __restrict__ q,
                      float* __restrict__ s, const int* __restrict__ n_rows, int HV, int D, float eps, int mode,
-                     float* __restrict__ amax_io) {
+                     float* __restrict__ amax_io, const tpx::Sync sync) {
     __shared__ float red[32];
     const long t = blockIdx.x;
     if (t >= *n_rows) return;
@@ -387,6 +403,7 @@ gated_norm_q8_kernel(const float* __restrict__ o, const __nv_bfloat16* __restric
     amax = block_max(amax, red);
     if (mode == MODE_STORE_AMAX && threadIdx.x == 0) amax_io[t] = amax;
     if (mode == MODE_USE_AMAX) amax = fmaxf(amax_io[t], amax);
+    if (mode == MODE_EXCHANGE) amax = tpx::exchange_amax(amax, t, sync);
     const float scale = fdiv<FULL>(fmaxf(amax, 1e-10f), 127.0f);
     const float rcp = __fdiv_rn(1.0f, scale);
 #pragma unroll
@@ -591,6 +608,38 @@ fold_kernel(float* __restrict__ h, long ldh, const int32_t* __restrict__ slots, 
             h[r * ldh + j] = __fadd_rn(h[r * ldh + j], scale2(tot, sa, w_s[j]));
         }
     }
+}
+
+// The same fold over every rank's slots (the fused all-reduce of the shortest tensor-parallel passes,
+// kernels/quant.py:128-141 with NR > 1): after the handshake the other ranks' slots are read over NVLink, uncached, and
+// added to this rank's - integer sums, exact in any order - before the one scaling.  N % 4 == 0.
+__global__ void __launch_bounds__(256)
+fold_sync_kernel(float* __restrict__ h, long ldh, const int32_t* __restrict__ slots, long slot_stride, int S,
+                 const float* __restrict__ a_s, const float* __restrict__ w_s, const int* __restrict__ n_rows, int N,
+                 const tpx::Sync sync) {
+    const long r = blockIdx.y;
+    if (r >= *n_rows) return;                       // whole block: the live count is the same on every rank
+    tpx::arrive_and_wait(sync, blockIdx.x == 0 && blockIdx.y == 0);
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (c >= N) return;
+    const float sa = a_s[r];
+    int4 tot = __ldcs((const int4*)(slots + r * N + c));
+    for (int p = 1; p < S; ++p) {
+        const int4 v = __ldcs((const int4*)(slots + p * slot_stride + r * N + c));
+        tot.x += v.x; tot.y += v.y; tot.z += v.z; tot.w += v.w;
+    }
+    for (int o = 0; o + 1 < sync.world; ++o)
+        for (int p = 0; p < S; ++p) {
+            const int4 v = tpx::ld_peer4(sync.others[o] + p * slot_stride + r * N + c);
+            tot.x += v.x; tot.y += v.y; tot.z += v.z; tot.w += v.w;
+        }
+    const float4 sw = __ldg((const float4*)(w_s + c));
+    float4 o4 = *(float4*)(h + r * ldh + c);
+    o4.x = __fadd_rn(o4.x, scale2(tot.x, sa, sw.x));
+    o4.y = __fadd_rn(o4.y, scale2(tot.y, sa, sw.y));
+    o4.z = __fadd_rn(o4.z, scale2(tot.z, sa, sw.z));
+    o4.w = __fadd_rn(o4.w, scale2(tot.w, sa, sw.w));
+    *(float4*)(h + r * ldh + c) = o4;
 }
 
 }  // namespace quant

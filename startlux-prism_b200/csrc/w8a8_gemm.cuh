@@ -957,6 +957,9 @@ struct SwapArgs {
     int pdl;                // launched as a programmatic dependent: weights may stream before the wait
     int stages;             // pipeline depth (shared-memory stages per CTA)
     int gblocks;            // w8a8_groups_kernel: 32-input blocks per scale group (gk / 32)
+    int wrows;              // per-32 groups, one K slice: weight rows per CTA (32, 64 or 128; 0 = 128).  Fewer rows =
+                            // more CTAs when N / 128 tiles leave SMs idle; the MMA still spans 128 lanes, the spare
+                            // lanes' sums are never read
 };
 
 template <int NB>
@@ -993,7 +996,8 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 
     int live = *p.n_rows;
     live = live < p.M ? live : p.M;
-    const int n0 = blockIdx.x * BM, m0 = blockIdx.z * NB, z = blockIdx.y;
+    const int WR = (GROUPED && p.wrows > 0) ? p.wrows : BM;     // weight rows this CTA owns
+    const int n0 = blockIdx.x * WR, m0 = blockIdx.z * NB, z = blockIdx.y;
     if (m0 >= live) return;                                    // whole CTA, before any barrier or allocation
     const int KB = (p.K + BK - 1) / BK;
     const int kb0 = z * p.kb_per_split;
@@ -1039,9 +1043,10 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             // activations) still runs.  The weights do not depend on it: the first stages' weight tiles are requested
             // at once, the activation tiles after the wait.
             const int pre = p.pdl ? (nkb < NST ? nkb : NST) : 0;
+            const uint32_t stage_tx = C::STAGE_BYTES_RAW - C::W_BYTES + WR * BK;   // bytes a stage's copies deliver
             for (int i = 0; i < pre; ++i) {
                 const uint32_t bar = smem_u32(&aux->full[i]);
-                mbar_expect_tx(bar, C::STAGE_BYTES_RAW);
+                mbar_expect_tx(bar, stage_tx);
                 uint8_t* st = smem + i * C::STAGE_BYTES;
                 tma_load_2d_hint(smem_u32(st), &tm_w, (kb0 + i) * BK, n0, bar, pol_w);
                 armed_parity[i] = 0;
@@ -1063,7 +1068,7 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                     break;
                 }
                 const uint32_t bar = smem_u32(&aux->full[stage]);
-                mbar_expect_tx(bar, C::STAGE_BYTES_RAW);
+                mbar_expect_tx(bar, stage_tx);
                 uint8_t* st = smem + stage * C::STAGE_BYTES;
                 const int kb = kb0 + i;
                 tma_load_2d_hint(smem_u32(st), &tm_w, kb * BK, n0, bar, pol_w);
@@ -1134,9 +1139,10 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         const int q = warp & 3;
         const int nl = q * 32 + lane;                          // this thread's weight row inside the tile
         if (p.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");   // before any global read or write of this warp
-        const int n = n0 + nl;
+        const int n = nl < WR ? n0 + nl : p.N;                 // lanes past this CTA's rows own no output column
         const uint32_t lane_base = tmem_base + ((uint32_t)(q * 32) << 16);
         if (GROUPED) {
+            const bool active = q * 32 < WR;                   // warp-uniform: does this lane quarter hold weight rows?
             // NH activation rows per warp: all NB with four epilogue warps, half of them with eight (two per lane quarter)
             constexpr int NH = C::EPI_WARPS == 8 ? NB / 2 : NB;
             const int j0 = C::EPI_WARPS == 8 ? ((warp - 2) >> 2) * NH : 0;
@@ -1170,7 +1176,7 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                              w2 = make_float2(sw4.z, sw4.z), w3 = make_float2(sw4.w, sw4.w);
 #pragma unroll
                 for (int c = 0; c < NH; c += 8) {
-                    if (m0 + j0 + c >= live) break;                // these eight rows are not live: nothing to add
+                    if (!active || m0 + j0 + c >= live) break;     // no weight rows here, or these eight rows are not live
                     uint32_t r[4][8];
 #pragma unroll
                     for (int g = 0; g < 4; ++g) tmem_ld8(lane_base + ring * C::BATCH_COLS + g * NB + j0 + c, r[g]);

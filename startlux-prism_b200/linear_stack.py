@@ -104,6 +104,10 @@ class LinearStack:
                 self.token = torch.zeros(1, dtype=torch.int32, device=device)
             elif group.rank == 0:
                 print(f"prism_b200: peer memory unavailable ({peer.error}); NCCL reduce-scatter instead", flush=True)
+        # few rows on several ranks: the exchanges move into the kernels (row maxima as words between the producers, the
+        # int32 sums read by the fold itself); PRISM_B200_TP_FUSED=0 keeps NCCL's all-reduces
+        if (n > 1 and not self.by_rows and group.backend == "nccl" and os.environ.get("PRISM_B200_TP_FUSED", "1") != "0"):
+            group.setup(hidden, words=2 * len(layers))
 
     def __call__(self, h_in, own_rows=False):
         """One pass: h_in fp32 [M, hidden] is copied into the working residual, which is returned (a view of an
@@ -119,6 +123,8 @@ class LinearStack:
         self.h.copy_(h_in, non_blocking=True)
         if self.by_rows:
             return self._pass_by_rows()
+        if g is not None and self.n > 1:
+            g.begin(M)                            # short pass: a new pass number, exchanges inside the kernels
         pend = None
         for lw in self.layers:
             quant.fold(self.h, self.slots, pend, nr, M)

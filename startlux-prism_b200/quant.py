@@ -7,18 +7,68 @@ kernels/quant.py over the sm_100a library.
     fold(h, parts, pending, n, T)                 finish a w8a8.Deferred residual add               (quant.py:448-457)
 
 Tensor-parallel modes (quant.py:14-27): 1 also stores the row's own maximum in `amax`, 2 quantizes with
-max(amax[t], own) after `amax` was max-all-reduced; a maximum is exact in any order, so every rank's int8 values and
-scales are the single-GPU kernel's.  The reference's in-kernel exchange (mode 3) is not built: `sync` must be None.
+max(amax[t], own) after `amax` was max-all-reduced, 3 exchanges the maxima with the other ranks inside the launch (a
+Sync from tp.Group.words(): one 64-bit word per row and rank, pass number above the float's bits, written into every
+other rank's buffer over NVLink); a maximum is exact in any order, so every rank's int8 values and scales are the
+single-GPU kernel's.  fold and norm_q8 take a Deferred whose `sync` (tp.Group.sync()) makes them add every rank's
+int32 slots themselves, read over NVLink after a flag handshake, instead of an all-reduce between two kernels
+(quant.py:29-37).  Every device-side wait is bounded (a rank that never arrives gives PrismError status 4 through
+_lib.device_status, not a hang).
 """
+import ctypes
+from typing import NamedTuple
+
 import torch
 
 from . import _lib
 
 
+class Sync(NamedTuple):
+    """One in-kernel exchange step of a tensor-parallel group (the reference's quant.Sync, kernels/quant.py:55-65):
+    `epoch` int64 [1] on the device, the pass number (the same on every rank); `flags`: every rank's 64-bit word buffer
+    as mapped on this GPU, in rank order (tensors or raw device addresses); `chan`: for a flag handshake the step's
+    channel, for a row-maximum exchange the first word row of the step; `others`: the other ranks' int32 slot buffers
+    as mapped here (folds only); this process's rank and the group's size."""
+    epoch: torch.Tensor
+    flags: tuple
+    chan: int
+    others: tuple
+    rank: int
+    world: int
+
+
+def _addr(t):
+    return int(t) if isinstance(t, int) else t.data_ptr()
+
+
+def _sync_struct(sync):
+    st = _lib.SyncStruct()
+    st.epoch = sync.epoch.data_ptr()
+    if len(sync.flags) != sync.world or sync.world > 8:
+        raise RuntimeError(f"Sync: {len(sync.flags)} buffers for {sync.world} ranks (at most 8)")
+    for r, f in enumerate(sync.flags):
+        st.bufs[r] = _addr(f)
+    for r, o in enumerate(sync.others):
+        st.others[r] = _addr(o)
+    st.off, st.rank, st.world = int(sync.chan), int(sync.rank), int(sync.world)
+    return st
+
+
+def bump(epoch):
+    """A new pass number (int64 [1], device) at the start of a tensor-parallel pass; every rank runs the same passes, so
+    they count alike.  A device-side add on the current stream: graph-capturable (kernels/quant.py:78-87)."""
+    epoch.add_(1)
+
+
 def _mode_args(mode, amax, sync, T):
-    if sync is not None or mode == 3:
-        raise NotImplementedError("in-kernel row-maximum exchange (mode 3 / sync) is not part of this build; "
-                                  "use modes 1 and 2 around a max all-reduce (tp.quantize_rows does)")
+    if mode == 3:
+        if sync is None:
+            raise RuntimeError("mode 3 needs a Sync (tp.Group.words())")
+        if T >= 256:
+            raise RuntimeError("mode 3 (in-kernel row-maximum exchange) serves passes of fewer than 256 rows")
+        return None
+    if sync is not None:
+        raise RuntimeError("a Sync goes with mode 3")
     if mode not in (0, 1, 2):
         raise ValueError(f"mode {mode}")
     if mode and (amax is None or amax.dtype != torch.float32 or amax.numel() < T):
@@ -34,8 +84,13 @@ def rows_q8(x, inv_s, q, s, n, T, mode=0, amax=None, sync=None):
     amax = _mode_args(mode, amax, sync, T)
     if x.dtype not in (torch.bfloat16, torch.float32) or x.shape[1] != K or x.stride(1) != 1 or not q.is_contiguous():
         raise RuntimeError("rows_q8: x must be bf16 / fp32 [T, K] with unit column stride, matching q")
-    rc = _lib.lib().pb_quant_rows(_lib.ptr(x), int(x.dtype == torch.float32), x.stride(0), _lib.ptr(inv_s), _lib.ptr(q),
-                                  _lib.ptr(s), _lib.ptr(n), T, K, K, mode, _lib.ptr(amax), _lib.stream())
+    if mode == 3:
+        rc = _lib.lib().pb_quant_rows_exchange(_lib.ptr(x), int(x.dtype == torch.float32), x.stride(0), _lib.ptr(inv_s),
+                                               _lib.ptr(q), _lib.ptr(s), _lib.ptr(n), T, K,
+                                               ctypes.byref(_sync_struct(sync)), _lib.stream())
+    else:
+        rc = _lib.lib().pb_quant_rows(_lib.ptr(x), int(x.dtype == torch.float32), x.stride(0), _lib.ptr(inv_s),
+                                      _lib.ptr(q), _lib.ptr(s), _lib.ptr(n), T, K, K, mode, _lib.ptr(amax), _lib.stream())
     _lib.check(rc, f"rows_q8 T={T} K={K} mode={mode}")
 
 
@@ -46,8 +101,12 @@ def swiglu_q8(gu, inv_s, q, s, n, T, mode=0, amax=None, sync=None):
     amax = _mode_args(mode, amax, sync, T)
     if gu.dtype != torch.bfloat16 or gu.shape[1] != 2 * FF or not gu.is_contiguous() or not q.is_contiguous():
         raise RuntimeError("swiglu_q8: gu must be contiguous bf16 [T, 2 FF]")
-    rc = _lib.lib().pb_swiglu_q8(_lib.ptr(gu), _lib.ptr(inv_s), _lib.ptr(q), _lib.ptr(s), _lib.ptr(n), T, FF, mode,
-                                 _lib.ptr(amax), _lib.stream())
+    if mode == 3:
+        rc = _lib.lib().pb_swiglu_q8_exchange(_lib.ptr(gu), _lib.ptr(inv_s), _lib.ptr(q), _lib.ptr(s), _lib.ptr(n), T, FF,
+                                              ctypes.byref(_sync_struct(sync)), _lib.stream())
+    else:
+        rc = _lib.lib().pb_swiglu_q8(_lib.ptr(gu), _lib.ptr(inv_s), _lib.ptr(q), _lib.ptr(s), _lib.ptr(n), T, FF, mode,
+                                     _lib.ptr(amax), _lib.stream())
     _lib.check(rc, f"swiglu_q8 T={T} FF={FF} mode={mode}")
 
 
@@ -66,7 +125,11 @@ def norm_q8(h, w_over_s, q, s, n, T, eps, rows=None, parts=None, pending=None):
     if np_ and (parts is None or rows is not None or parts.dtype != torch.int32):
         raise RuntimeError("norm_q8: a pending add needs its int32 slots and no row gather")
     if np_ and getattr(pending, "sync", None) is not None:
-        raise NotImplementedError("norm_q8: in-kernel cross-rank exchanges are not part of this build (use tp.out_proj)")
+        rc = _lib.lib().pb_norm_q8_sync(_lib.ptr(h), _lib.ptr(w_over_s), _lib.ptr(q), _lib.ptr(s), _lib.ptr(n), T, HID,
+                                        float(eps), _lib.ptr(parts), parts.stride(0), np_, _lib.ptr(pending.a_s),
+                                        _lib.ptr(pending.w_s), ctypes.byref(_sync_struct(pending.sync)), _lib.stream())
+        _lib.check(rc, f"norm_q8 T={T} HID={HID} parts={np_} over {pending.sync.world} ranks")
+        return
     rc = _lib.lib().pb_norm_q8(_lib.ptr(h), _lib.ptr(w_over_s), _lib.ptr(q), _lib.ptr(s), _lib.ptr(rows), _lib.ptr(n),
                                T, HID, float(eps), _lib.ptr(parts) if np_ else None, parts.stride(0) if np_ else 0, np_,
                                _lib.ptr(pending.a_s) if np_ else None, _lib.ptr(pending.w_s) if np_ else None,
@@ -85,9 +148,14 @@ def gated_norm_q8(o, proj, z_off, w, inv_s, q, s, n, T, cfg, mode=0, amax=None, 
     if o.dtype != torch.float32 or not o.is_contiguous() or o.shape[1] != HV * D or proj.dtype != torch.bfloat16 \
             or proj.stride(1) != 1 or q.shape[1] != HV * D:
         raise RuntimeError("gated_norm_q8: o fp32 [T, v_heads * gdn_dim] contiguous, proj bf16 with unit column stride")
-    rc = _lib.lib().pb_gated_norm_q8(_lib.ptr(o), _lib.ptr(proj), proj.stride(0), int(z_off), _lib.ptr(w), _lib.ptr(inv_s),
-                                     _lib.ptr(q), _lib.ptr(s), _lib.ptr(n), T, HV, D, float(cfg.eps), mode, _lib.ptr(amax),
-                                     _lib.stream())
+    if mode == 3:
+        rc = _lib.lib().pb_gated_norm_q8_exchange(_lib.ptr(o), _lib.ptr(proj), proj.stride(0), int(z_off), _lib.ptr(w),
+                                                  _lib.ptr(inv_s), _lib.ptr(q), _lib.ptr(s), _lib.ptr(n), T, HV, D,
+                                                  float(cfg.eps), ctypes.byref(_sync_struct(sync)), _lib.stream())
+    else:
+        rc = _lib.lib().pb_gated_norm_q8(_lib.ptr(o), _lib.ptr(proj), proj.stride(0), int(z_off), _lib.ptr(w),
+                                         _lib.ptr(inv_s), _lib.ptr(q), _lib.ptr(s), _lib.ptr(n), T, HV, D, float(cfg.eps),
+                                         mode, _lib.ptr(amax), _lib.stream())
     _lib.check(rc, f"gated_norm_q8 T={T} heads={HV} dim={D} mode={mode}")
 
 
@@ -154,14 +222,19 @@ def fold(h, parts, pending, n, T):
     the unsplit epilogue's roundings.  parts: the int32 slots [S, rows, N] unless the Deferred names its own."""
     if not pending:
         return
-    if pending.sync is not None:
-        raise NotImplementedError("fused cross-rank reads (Deferred.sync) are not part of this build")
     if pending.parts is not None:
         parts = pending.parts
     _lib.need_cuda(h, parts, n)
     N = h.shape[1]
     if h.dtype != torch.float32 or parts.dtype != torch.int32 or parts.shape[2] != N or h.stride(1) != 1:
         raise RuntimeError("fold: h fp32 [T, N], parts int32 [S, rows, N]")
+    if pending.sync is not None:
+        # every rank's slots, read by the kernel itself after a flag handshake (kernels/quant.py:128-141, :434-457)
+        rc = _lib.lib().pb_fold_sync(_lib.ptr(h), h.stride(0), _lib.ptr(parts), parts.stride(0), pending.n,
+                                     _lib.ptr(pending.a_s), _lib.ptr(pending.w_s), _lib.ptr(n), T, N,
+                                     ctypes.byref(_sync_struct(pending.sync)), _lib.stream())
+        _lib.check(rc, f"fold T={T} N={N} S={pending.n} over {pending.sync.world} ranks")
+        return
     rc = _lib.lib().pb_fold(_lib.ptr(h), h.stride(0), _lib.ptr(parts), parts.stride(0), pending.n,
                             _lib.ptr(pending.a_s), _lib.ptr(pending.w_s), _lib.ptr(n), T, N, _lib.stream())
     _lib.check(rc, f"fold T={T} N={N} S={pending.n}")

@@ -3,6 +3,8 @@ projection, one process per GPU over torch.distributed (NCCL over NVLink; gloo o
 
     shard_config(cfg, n), shard_index(cfg, n, r)     which rows / columns a rank holds          (tp.py:83-125)
     Group(rank, world, ...)                          process group: sum_, max_                   (tp.py:333-357, :435-439)
+                                                     setup, symmetric, begin, sync, words: the in-kernel exchanges of
+                                                     short passes (tp.py:358-432)
                                                      scatter_sum_, gather_: the two halves of an all-reduce, for passes
                                                      that keep the residual stream split by rows between them
     PeerBuffer(g, nbytes)                            device memory the other ranks' kernels store into  (tp.py:381-403)
@@ -15,9 +17,14 @@ cannot change a bit) and the residual's next reader scales the total once; a row
 the max over all ranks (exact).  Outputs are therefore bit-identical at every GPU count, 8 included: unlike the
 reference's in-kernel protocols (4 ranks at most) nothing here depends on the group size.
 
-Not built (engine orchestration, outside the linear-layer path): the shared-memory channel to follower processes, the
-mirrored-object RPC, the reference's fused in-kernel exchanges for a few rows (quant.Sync: flag words and peer reads
-inside the fold; this build's fused exchange is the many-rows one, w8a8.gemm_scatter).
+Short passes (a few rows: decode) exchange inside the kernels, as the reference does (tp.py:129-180): up to
+`fast_rows` rows the producers exchange row maxima as 64-bit words (quant mode 3), up to `pull_rows` rows the kernel that
+folds a row-parallel projection reads every rank's int32 slots itself after a flag handshake (quant.Sync) - no
+collective call between the kernels.  The buffers are peer-mapped device memory (PeerBuffer); every device-side wait
+is bounded.  Many-row passes use w8a8.gemm_scatter (linear_stack) or NCCL.
+
+Not built (engine orchestration, outside the linear-layer path): the shared-memory channel to follower processes and
+the mirrored-object RPC.
 """
 from __future__ import annotations
 
@@ -29,6 +36,9 @@ import torch.distributed as dist
 
 SPLIT_ROWS = 512      # output projections split K into several int32 slots only up to this many rows
 MAX_SPLIT = 4
+FAST_ROWS = int(os.environ.get("PRISM_B200_TP_FAST_ROWS", "255"))   # row maxima exchanged inside the producers up to here
+PULL_ROWS = {2: 128, 4: 64, 8: 64}    # int32 sums read by their consumer up to here, per group size (PRISM_B200_TP_PULL_ROWS)
+CHANNELS = 1024                       # flag handshakes per pass at most
 
 
 def shard_config(cfg, n):
@@ -113,7 +123,88 @@ class Group:
             dist.init_process_group(backend, rank=rank, world_size=world,
                                     timeout=datetime.timedelta(seconds=timeout_s), **kw)
         self.pg = dist.group.WORLD
+        # in-kernel exchanges (setup): every rank's buffers as mapped here, and the per-pass bookkeeping
+        self.xs = self.ws = self.fs = None
+        self.fast = self.pull = False
+        self.fast_rows = self.pull_rows = self.parity = self.hidden = self.word_steps = 0
+        self.nsum = self.step = self.mstep = 0
+        self._peers = []
 
+    # ------------------------------------------------------------ in-kernel exchanges (quant.Sync)
+    def setup(self, hidden, words, fast_rows=None, pull_rows=None):
+        """Allocates, on every rank, the peer-mapped buffers of the in-kernel exchanges (the reference's Group.setup,
+        tp.py:358-379): the flag words of the handshakes (CHANNELS x ranks), two parities of int32 slots for the output
+        projections of passes up to pull_rows rows (MAX_SPLIT slots of `hidden` sums each), the row maxima's words
+        (`words` exchanges per pass at most, fast_rows rows, one word per rank) and this rank's pass counter.  A
+        collective: every rank calls it at the same point, once.  Without peer memory (gloo, or CUDA IPC refused) the
+        group keeps exchanging through collectives."""
+        if self.xs is not None:
+            if hidden != self.hidden:
+                raise ValueError("one tensor-parallel group serves one model")
+            return
+        if self.world == 1 or self.backend != "nccl":
+            return
+        fast_rows = FAST_ROWS if fast_rows is None else fast_rows
+        if pull_rows is None:
+            env = os.environ.get("PRISM_B200_TP_PULL_ROWS")
+            pull_rows = int(env) if env else PULL_ROWS.get(self.world, 1)
+        fast_rows = max(0, min(fast_rows, 255))              # the exchange lives in the one-CTA-per-row producers
+        self.hidden, self.fast_rows, self.pull_rows = hidden, fast_rows, max(0, min(pull_rows, fast_rows))
+        self.word_steps = words
+        if fast_rows <= 0:
+            return
+        self.parity = MAX_SPLIT * max(self.pull_rows, 1) * hidden
+        fs = self.symmetric(CHANNELS * self.world, torch.int64)
+        xs = self.symmetric(2 * self.parity, torch.int32)
+        ws = self.symmetric(words * fast_rows * self.world, torch.int64)
+        if fs is None or xs is None or ws is None:
+            self.fast_rows = self.pull_rows = 0
+            return
+        self.fs, self.xs, self.ws = fs, xs, ws
+        self.epoch = torch.zeros(1, dtype=torch.int64, device=self.device)
+
+    def symmetric(self, n, dtype):
+        """n zeroed elements on every rank, each rank's buffer mapped on every other (CUDA IPC over NVLink): returns
+        the ranks' buffers as tensors on this device, in rank order (this rank's own at self.rank), or None when peer
+        memory is unavailable.  The peer tensors are views of another GPU's memory: pass them to this package's
+        kernels only.  A collective."""
+        nbytes = n * torch.empty(0, dtype=dtype).element_size()
+        peer = PeerBuffer(self, nbytes)
+        if not peer.ok:
+            return None
+        self._peers.append(peer)
+        return [torch.as_tensor(_Raw(p, nbytes), device=self.device).view(dtype) for p in peer.ptrs]
+
+    def begin(self, rows):
+        """At the start of a pass, on every rank alike (it is recorded in the pass's graph): up to fast_rows rows the
+        producers exchange the maxima themselves - a new pass number for their words and the flags - and up to
+        pull_rows rows the consumers read the sums (tp.py:405-416)."""
+        from . import quant as KQ
+        assert self.nsum % 2 == 0, "a pass's fused sums must alternate buffers evenly"
+        self.fast = self.xs is not None and 0 < rows <= self.fast_rows
+        self.pull = self.fast and rows <= self.pull_rows
+        self.nsum = self.step = self.mstep = 0
+        if self.fast:
+            KQ.bump(self.epoch)
+
+    def sync(self, buffers):
+        """The next flag handshake's quant.Sync over `buffers` (every rank's slots, as mapped here)."""
+        from . import quant as KQ
+        if self.step >= CHANNELS:
+            raise RuntimeError(f"more than {CHANNELS} fused sums in one pass")
+        self.step += 1
+        return KQ.Sync(self.epoch, tuple(self.fs), self.step - 1,
+                       tuple(b for r, b in enumerate(buffers) if r != self.rank), self.rank, self.world)
+
+    def words(self):
+        """The next row-maximum exchange's quant.Sync (mode 3): every rank's word buffer and the step's first word row."""
+        from . import quant as KQ
+        if self.mstep >= self.word_steps:
+            raise RuntimeError(f"more than {self.word_steps} row-maximum exchanges in one pass")
+        self.mstep += 1
+        return KQ.Sync(self.epoch, tuple(self.ws), (self.mstep - 1) * self.fast_rows, (), self.rank, self.world)
+
+    # ------------------------------------------------------------ collectives (on the current stream; capturable)
     def sum_(self, x):
         if self.world > 1:
             dist.all_reduce(x, op=dist.ReduceOp.SUM, group=self.pg)
@@ -155,6 +246,10 @@ class Group:
             dist.barrier(group=self.pg)
 
     def close(self):
+        for peer in self._peers:
+            peer.close()
+        self._peers = []
+        self.xs = self.ws = self.fs = None
         if dist.is_initialized():
             dist.destroy_process_group()
 
@@ -223,11 +318,15 @@ class PeerBuffer:
 
 
 def quantize_rows(g, fn, rows, amax, *args):
-    """The input of a row-parallel projection, quantized by fn (quant.rows_q8 / swiglu_q8) with the row's maximum over
-    all ranks: this rank's maxima stored (mode 1), max-all-reduced in `amax`, then the rows quantized (mode 2).  One
-    rank: the plain kernel."""
+    """The input of a row-parallel projection, quantized by fn (quant.rows_q8 / swiglu_q8 / gated_norm_q8) with the
+    row's maximum over all ranks.  On a short pass (Group.begin decided: g.fast) in one launch, the maxima exchanged
+    inside the kernel (mode 3); otherwise this rank's maxima stored (mode 1), max-all-reduced in `amax`, then the rows
+    quantized (mode 2).  One rank: the plain kernel."""
     if g is None or g.world == 1:
         fn(*args)
+        return
+    if g.fast:
+        fn(*args, mode=3, sync=g.words())                # one launch: the maxima travel as words between the kernels
         return
     fn(*args, mode=1, amax=amax)
     g.max_(amax[:rows])
@@ -240,6 +339,14 @@ def out_proj(g, a, a_s, w, w_s, flat, rows, n_rows, pdl=0):
     from . import w8a8 as KW
     N = w.shape[0]
     S_max = MAX_SPLIT if rows <= SPLIT_ROWS else 1
+    if g is not None and g.pull:
+        # a short pass: the sums stay in this rank's peer-mapped slots (two parities: the next projection writes the
+        # other one while slow ranks may still read this one) and the fold reads every rank's (tp.py:168-174)
+        lo = (g.nsum % 2) * g.parity
+        g.nsum += 1
+        views = [x[lo:lo + S_max * rows * N].view(S_max, rows, N) for x in g.xs]
+        S = KW.gemm_i32(a, a_s, w, w_s, views[g.rank], n_rows, max_split=S_max, pdl=pdl)
+        return KW.Deferred(S, a_s, w_s, views[g.rank][:S], g.sync([v[:S] for v in views]))
     slots = flat[:S_max * rows * N].view(S_max, rows, N)
     S = KW.gemm_i32(a, a_s, w, w_s, slots, n_rows, max_split=S_max, pdl=pdl)
     if g is not None:

@@ -32,8 +32,9 @@ _WORKSPACE = {}
 
 class Deferred(NamedTuple):
     """A residual add left to the next reader of the residual (quant.fold / quant.norm_q8): `n` int32 slots of partial
-    sums and the projection's scales; `parts` names the slots when they are not the reader's own buffer; `sync` is
-    kept for signature parity with the reference's fused tensor-parallel reads (unused here)."""
+    sums and the projection's scales; `parts` names the slots when they are not the reader's own buffer; `sync` (a
+    quant.Sync from tp.Group.sync()): the slots are this rank's only and the reader adds every rank's itself, over
+    NVLink, after a flag handshake."""
     n: int
     a_s: torch.Tensor
     w_s: torch.Tensor
@@ -79,6 +80,23 @@ def pick_split(M, N, K, limit=MAX_SPLIT):
         return max(1, min(limit, SM_COUNT // tiles, kb // 32))
     tiles = -(-N // 128)
     return max(1, min(limit, RESIDENT_CTAS // tiles, kb // 2))
+
+
+_TABLE = None
+
+
+def _choice(M, N, K, residual):
+    """The measured choice for this projection shape at the nearest measured row count (tune.py's table), or None."""
+    global _TABLE
+    if _TABLE is None:
+        from . import tune
+        _TABLE = tune.load_table()
+    by_m = _TABLE.get((N, K, bool(residual)))
+    if not by_m:
+        return None
+    import math
+    m = min(by_m, key=lambda x: abs(math.log(x) - math.log(max(M, 1))))
+    return by_m[m]
 
 
 def effective_split(K, split):
@@ -146,9 +164,15 @@ def gemm(a, a_s, w, w_s, out, n_rows, gk, epi=0, outs=None, cfg=None, slots=None
         # one row against few weight rows: the library's CUDA-core kernel (no K split: its CTAs already cover the SMs); same bits
         _call(a, a_s, w, w_s, out, out.stride(0), n_rows, gk, epi, 1)
         return None
-    split = int(cfg) if cfg is not None else pick_split(M, N, K)
+    defer_ok = True
+    if cfg is not None:
+        split = int(cfg)
+    else:
+        c = _choice(M, N, K, epi == EPI_ADD) if M <= FEW_ROWS else None
+        split = c["split"] if c else pick_split(M, N, K)
+        defer_ok = c["defer"] if c else True
     split = effective_split(K, split)
-    if split > 1 and M <= FEW_ROWS and epi == EPI_ADD and slots is not None and slots.shape[1] >= M:
+    if split > 1 and M <= FEW_ROWS and epi == EPI_ADD and slots is not None and slots.shape[1] >= M and defer_ok:
         split = effective_split(K, min(split, slots.shape[0]))
         if split > 1:
             _check_slots(slots, M, N)

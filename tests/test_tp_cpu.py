@@ -99,3 +99,56 @@ def test_group_single_rank_is_a_no_op():
     calls = []
     tp.quantize_rows(None, lambda *a, **k: calls.append((a, k)), 4, None, 1, 2)
     assert calls == [((1, 2), {})]
+
+
+def test_exchange_bookkeeping(monkeypatch):
+    """Group.begin / words / sync and out_proj's pull path on stand-in buffers (no process group, no GPU): which
+    passes exchange inside the kernels, the pass counter, the word rows and flag channels handed out, the two slot
+    parities alternating."""
+    sys.path.insert(0, ROOT)
+    from prism_b200 import quant, tp, w8a8
+    hidden, world = 64, 2
+    g = tp.Group.__new__(tp.Group)
+    g.rank, g.world, g.backend, g.device = 1, world, "nccl", torch.device("cpu")
+    g.fast_rows, g.pull_rows, g.word_steps, g.hidden = 255, 128, 4, hidden
+    g.parity = tp.MAX_SPLIT * g.pull_rows * hidden
+    g.fs = [torch.zeros(tp.CHANNELS * world, dtype=torch.int64) for _ in range(world)]
+    g.xs = [torch.zeros(2 * g.parity, dtype=torch.int32) for _ in range(world)]
+    g.ws = [torch.zeros(g.word_steps * g.fast_rows * world, dtype=torch.int64) for _ in range(world)]
+    g.epoch = torch.zeros(1, dtype=torch.int64)
+    g.fast = g.pull = False
+    g.nsum = g.step = g.mstep = 0
+    g.begin(64)
+    assert g.fast and g.pull and int(g.epoch) == 1
+    s0, s1 = g.words(), g.words()
+    assert isinstance(s0, quant.Sync) and (s0.chan, s1.chan) == (0, 255) and s0.rank == 1 and s0.world == 2 and s0.others == ()
+    assert s0.flags[0].data_ptr() == g.ws[0].data_ptr()
+    calls = []
+
+    def gemm_i32(a, a_s, w, w_s, slots, n_rows, max_split=4, pdl=False):
+        calls.append(slots.data_ptr())
+        return 2
+    monkeypatch.setattr(w8a8, "gemm_i32", gemm_i32)
+    a, w = torch.zeros(64, 32, dtype=torch.int8), torch.zeros(hidden, 32, dtype=torch.int8)
+    d0 = tp.out_proj(g, a, None, w, None, None, 64, None)
+    d1 = tp.out_proj(g, a, None, w, None, None, 64, None)
+    assert d0.n == 2 and d0.sync.chan == 0 and d1.sync.chan == 1
+    assert calls[0] == g.xs[1].data_ptr() and calls[1] == g.xs[1].data_ptr() + 4 * g.parity      # own buffer, two parities
+    assert d0.sync.others[0].data_ptr() == g.xs[0].data_ptr() and d1.sync.others[0].data_ptr() == g.xs[0].data_ptr() + 4 * g.parity
+    assert d0.parts.shape == (2, 64, hidden) and d0.sync.flags[1].data_ptr() == g.fs[1].data_ptr()
+    g.begin(200)
+    assert g.fast and not g.pull and int(g.epoch) == 2 and g.step == 0 and g.mstep == 0
+    for _ in range(4):
+        g.words()
+    with pytest.raises(RuntimeError, match="row-maximum exchanges"):
+        g.words()
+    g.begin(300)
+    assert not g.fast and not g.pull and int(g.epoch) == 2          # long pass: collectives, no new pass number
+    seen = []
+    monkeypatch.setattr(g, "max_", lambda x: None, raising=False)
+    tp.quantize_rows(g, lambda *a, **k: seen.append(k), 300, torch.zeros(300), "x")
+    assert [k.get("mode") for k in seen] == [1, 2]
+    g.begin(8)
+    seen.clear()
+    tp.quantize_rows(g, lambda *a, **k: seen.append(k), 8, None, "x")
+    assert len(seen) == 1 and seen[0]["mode"] == 3 and seen[0]["sync"].chan == 0

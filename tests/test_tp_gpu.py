@@ -84,19 +84,26 @@ def _run(cmd, env=None):
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
 
 
-@pytest.mark.parametrize("rows", [1, 64, 700, 2048])
-def test_real_ranks_bit_identical(dev, tmp_path, rows):
+# rows, extra worker arguments, environment: 1 / 64 rows run the in-kernel exchanges (row maxima as words, sums pulled by
+# the fold), eagerly and as a replayed graph, and once more through NCCL's all-reduces; 700 rows NCCL's reduce-scatter;
+# 2048 the scatter fused into the GEMM; the last case is the benchmark's own configuration
+CASES = [(1, [], {}), (64, [], {}), (64, ["graph"], {}), (1, ["graph"], {}), (64, [], {"PRISM_B200_TP_FUSED": "0"}),
+         (200, [], {}), (700, [], {}), (2048, [], {}), (8192, ["full"], {})]
+
+
+@pytest.mark.parametrize("rows,extra,env_extra", CASES)
+def test_real_ranks_bit_identical(dev, tmp_path, rows, extra, env_extra):
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs 2 or more GPUs")
     one = str(tmp_path / "one.pt")
-    _run([sys.executable, os.path.join(HERE, "tp_worker.py"), one, str(rows)])
+    _run([sys.executable, os.path.join(HERE, "tp_worker.py"), one, str(rows)] + [e for e in extra if e == "full"])
     want = torch.load(one)
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **env_extra)
     for world in [w for w in (2, 4, 8) if w <= n]:
         out = str(tmp_path / f"tp{world}.pt")
         _run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
               "--master-addr", "127.0.0.1", "--master-port", str(29500 + world), os.path.join(HERE, "tp_worker.py"),
-              out, str(rows)], env)
+              out, str(rows)] + extra, env)
         got = torch.load(out)
         assert torch.equal(got.view(torch.int32), want.view(torch.int32)), f"{world} ranks differ from one GPU"

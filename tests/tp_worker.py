@@ -2,8 +2,11 @@
 N ranks under torch.distributed.run) and saves rank 0's final residual.  Sizes are reduced (hidden 1024) so the 1-rank
 and N-rank runs take seconds.
 
-    python tests/tp_worker.py OUT.pt ROWS            (1 rank)
-    python -m torch.distributed.run --nproc-per-node N ... tests/tp_worker.py OUT.pt ROWS
+    python tests/tp_worker.py OUT.pt ROWS [graph] [full]            (1 rank)
+    python -m torch.distributed.run --nproc-per-node N ... tests/tp_worker.py OUT.pt ROWS [graph] [full]
+
+graph: the pass is captured once in a CUDA graph and replayed (what a decode loop does: the in-kernel exchanges and
+the pass counter's increment are part of the graph).  full: the benchmark's own sizes (hidden 5120, FFN 17408, 4 layers).
 """
 import os
 import sys
@@ -17,7 +20,10 @@ HID, QC, KVC, FFN, LAYERS = 1024, 1024, 256, 2048, 2
 
 
 def main():
+    global HID, QC, KVC, FFN, LAYERS
     out, rows = sys.argv[1], int(sys.argv[2])
+    if "full" in sys.argv[3:]:
+        HID, QC, KVC, FFN, LAYERS = LS.HIDDEN, LS.Q_COLS, LS.KV_COLS, LS.FFN, 4
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -31,6 +37,17 @@ def main():
     for _ in range(2):                       # twice: the second pass must give the same bits (no state between passes)
         h = stack(h0).clone()
     torch.cuda.synchronize()
+    if "graph" in sys.argv[3:]:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            res = stack(h0)
+        for _ in range(3):
+            res.zero_()
+            graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(res, h), "a replayed pass differs from the eager one"
+        h = res.clone()
+        del graph
     code, where = _lib.device_status()
     assert code == 0, (code, where)
     if rank == 0:
