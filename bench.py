@@ -116,6 +116,23 @@ def reference_gpu_kernels(rows):
             return {"unavailable": "no GPU"}
         sys.path.insert(0, ref)
         os.environ["STARTLUX_PRISM_GEMM"] = "triton"
+        import triton
+        if tuple(int(v) for v in triton.__version__.split(".")[:2]) < (3, 8):
+            # the reference pins Triton 3.8, whose tl.dot takes its result type from the accumulator; older Tritons
+            # default out_dtype to float32 and reject the reference's int32 accumulator (kernels/w8a8.py:58,70).  Only
+            # that default is adapted; the reference's source runs as it is.
+            import triton.language as tl
+            from triton.language import core as tl_core
+            dot = tl.dot
+
+            @tl_core.builtin
+            def dot_typed_by_acc(input, other, acc=None, input_precision=None, allow_tf32=None,
+                                 max_num_imprecise_acc=None, out_dtype=None, _semantic=None):
+                if out_dtype is None:
+                    out_dtype = acc.dtype if acc is not None else tl.float32
+                return dot(input, other, acc, input_precision, allow_tf32, max_num_imprecise_acc, out_dtype,
+                           _semantic=_semantic)
+            tl.dot = tl_core.dot = dot_typed_by_acc
         from startlux_prism.kernels import w8a8 as RW8
         dev = torch.device("cuda", 0)
         gen = torch.Generator(device=dev).manual_seed(3)

@@ -69,6 +69,9 @@ int pb_w8a8_counters(int M, int N);
  *   epi PB_EPI_I32: out = slots int32 [split, rows, N] (ldo = N, slot_stride = rows * N elements): split z's sums.
  *   split > 1 with epi 0 / 1 (gk == K, M <= 64): the splits are added inside the kernel through `workspace`
  *   (pb_w8a8_workspace_bytes) and `counters` (pb_w8a8_counters, zero before the first call; left zero).
+ *   split == 1 with a workspace and counters given (gk == K, M > 64): when the tiles' last wave would fill less than
+ *   60 % of the SMs, that wave's tiles are split along K over the idle SMs (exact, as above; up to 148 x 128 KB of
+ *   workspace and 148 counters are used); without a workspace the last wave runs unsplit.
  *   split > 1 with gk == 32 (M <= 64, epi 0 / 1, same workspace): each K slice adds its groups in order, the slices'
  *   fp32 sums are added in slice order: deterministic, within one bf16 step of the unsplit (reference) order.
  *   pdl != 0 (few rows only; ignored otherwise): launch as a programmatic dependent of the kernel before it on the
@@ -243,6 +246,12 @@ int pb_mxfp4_counters(int M, int N);
 int pb_mxfp4_gemm_split(const void* aq, const void* a_sf, const void* bq, const void* b_sf, void* out, long ldo, int M,
                         int N, int K, int epi, int split, void* workspace, long workspace_bytes, int* counters,
                         int n_counters, void* stream);
+
+/* Weight prefetch into L2: the bytes of up to eight ranges (16-byte aligned starts) are requested from the copy
+ * engine in 4 KB bulk prefetches by ctas x 128 threads, on `stream` (a side stream: the point is to overlap a
+ * latency-bound kernel).  Replaces torch.ops.startlux_prism.l2_prefetch (csrc/l2_prefetch.cu:12-49, kernels/cuda_ext.py:171-173),
+ * which the reference measured as a loss on its GPUs and keeps off by default; off by default here too. */
+int pb_l2_prefetch(const void* const* ptrs, const long* nbytes, int n, int ctas, void* stream);
 
 /* Measurement aid: the int8 tensor-core rate with shared-memory-resident operands and no loads (one CTA per SM, `iters`
  * batches of four 128 x mma_n x 32 MMAs each, mma_n a multiple of 16 up to 256; pattern 0 = zero operands, 1 =

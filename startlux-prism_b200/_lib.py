@@ -40,6 +40,7 @@ _SIGS = {
     "pb_gated_norm_q8_exchange": ([_vp, _vp, _l, _l, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, ctypes.c_float, _sp, _vp], _i),
     "pb_fold_sync": ([_vp, _l, _vp, _l, _i, _vp, _vp, _vp, _i, _i, _sp, _vp], _i),
     "pb_norm_q8_sync": ([_vp, _vp, _vp, _vp, _vp, _i, _i, ctypes.c_float, _vp, _l, _i, _vp, _vp, _sp, _vp], _i),
+    "pb_l2_prefetch": ([_vp, _vp, _i, _i, _vp], _i),
     "pb_fold": ([_vp, _l, _vp, _l, _i, _vp, _vp, _vp, _i, _i, _vp], _i),
     "pb_quant_rows": ([_vp, _i, _l, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp, _vp], _i),
     "pb_swiglu_q8": ([_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _vp], _i),

@@ -305,6 +305,35 @@ __device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t a_desc, u
         : : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// ------------------------------------------------------------------------------------------------- L2 prefetch
+// Up to eight byte ranges pulled into L2 by the copy engine's bulk prefetch (cp.async.bulk.prefetch.L2: one instruction
+// per 4 KB chunk, no register result, no L1 allocation, nothing to wait for).  Run on a side stream while
+// latency-bound kernels leave DRAM idle, so that the projections that follow find their weights in L2 (the role of
+// the reference's csrc/l2_prefetch.cu, which touches every 128-byte line with prefetch.global.L2).
+struct PrefetchRanges {
+    const char* ptr[8];
+    long long bytes[8];          // multiples of 16, 16-byte aligned starts
+    int n;
+};
+__global__ void __launch_bounds__(128) l2_prefetch_kernel(const PrefetchRanges r) {
+    constexpr long long CHUNK = 4096;
+    long long first = 0;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    const long long me = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    for (int i = 0; i < r.n; ++i) {
+        const long long chunks = (r.bytes[i] + CHUNK - 1) / CHUNK;
+        // chunk c of this range is global chunk first + c; threads take global chunks me, me + stride, ...
+        long long c = ((me - first) % stride + stride) % stride;
+        for (; c < chunks; c += stride) {
+            const long long off = c * CHUNK;
+            const long long left = r.bytes[i] - off;
+            const unsigned size = (unsigned)(left < CHUNK ? left : CHUNK);
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(r.ptr[i] + off), "r"(size) : "memory");
+        }
+        first += chunks;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------- numerics
 // The epilogue of every int8 product: (float(acc) * s_a) * s_w with each product rounded to nearest, no fused
 // multiply-add (the reference's explicit mul_rn, kernels/w8a8.py:76, csrc/w8a8_gemm.cu:334-339).

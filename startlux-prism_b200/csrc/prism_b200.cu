@@ -178,10 +178,21 @@ int add_mode() {
     return v;
 }
 
+// PRISM_B200_TAIL=0: never split the last wave of tiles (comparison runs).
+bool tail_split_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("PRISM_B200_TAIL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
 template <int BN, int EPI>
 int launch_tile(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, void* out, long ldo,
                 const int* n_rows, int M, int N, int K, cudaStream_t st, int split = 1, void* workspace = nullptr,
-                int* counters = nullptr, const w8a8::RowBlocks* blocks = nullptr, float* souts = nullptr, int gbn = 0) {
+                int* counters = nullptr, const w8a8::RowBlocks* blocks = nullptr, float* souts = nullptr, int gbn = 0,
+                long workspace_bytes = 0, int n_counters = 0) {
     using C = w8a8::TileCfg<BN>;
     CUtensorMap ta, tw;
     int rc;
@@ -193,25 +204,46 @@ int launch_tile(const int8_t* a, const float* a_s, const int8_t* w, const float*
     if ((rc = set_smem(kern, smem))) return rc;
     // the coalesced epilogue moves 32-bit words: bf16 outputs need an even row stride and a 4-byte aligned base
     int word_ok = EPI == w8a8::EPI_BF16 ? (((uintptr_t)out & 3) == 0 && ldo % 2 == 0) : 1;
+    // K splits.  split > 1 from the caller: every tile is split (few tiles, long K).  split == 1 with a workspace at
+    // hand: the LAST wave of tiles, when it is a partial one, is split over the SMs it would leave idle (exact: the
+    // slices' int32 sums meet in the workspace) - 320 tiles on 148 SMs take 2.2 waves instead of 3.
+    const int KB = (K + 127) / 128;
+    const int tiles = ((M + 127) / 128) * ((N + BN - 1) / BN);
+    const int sms = sm_count();
+    int full_tiles = split > 1 ? 0 : tiles;
+    if (split == 1 && workspace && counters && tail_split_enabled() && tiles > sms) {
+        const int tail = tiles % sms;
+        if (tail > 0 && tail * 5 <= sms * 3) {                     // a last wave less than 60 % full
+            int s = sms / tail;
+            if (s > 8) s = 8;
+            if (s > KB / 8) s = KB / 8;                            // at least eight K blocks per slice
+            if (s > 1 && (long)tail * s * 128 * BN * 4 <= workspace_bytes && tail <= n_counters) {
+                const int per = (KB + s - 1) / s;
+                split = (KB + per - 1) / per;
+                full_tiles = tiles - tail;
+            }
+        }
+    }
     // residual add: 32 x 32 fp32 boxes added into out by the copy engine (bit 1 of word_ok), when out can be a tensor map
     CUtensorMap tout = ta;
-    if (EPI == w8a8::EPI_ADD && split == 1 && add_mode() == 1 && ((uintptr_t)out & 15) == 0 && ldo % 4 == 0) {
+    const bool whole_tiles = full_tiles > 0;
+    if (EPI == w8a8::EPI_ADD && whole_tiles && add_mode() == 1 && ((uintptr_t)out & 15) == 0 && ldo % 4 == 0) {
         if ((rc = tensor_map(&tout, out, N, M, (uint64_t)ldo * 4, 32, 32, 4))) return rc;
         word_ok |= 2;
-    } else if (EPI == w8a8::EPI_ADD && split == 1 && add_mode() == 2) {
+    } else if (EPI == w8a8::EPI_ADD && whole_tiles && add_mode() == 2) {
         word_ok |= 4;
     }
     if (g_drop_loads) word_ok |= 16;                               // failure injection (pb_test_drop_loads)
     // weight tiles fastest when the activations are the larger operand, do not fit in L2 and the weights do
     if ((long)M * K > (long)N * K && (long)M * K > (64l << 20) && (long)N * K <= (100l << 20)) word_ok |= 8;
-    const int KB = (K + 127) / 128;
     const int kbs = (KB + split - 1) / split;
-    const int units = ((M + 127) / 128) * ((N + BN - 1) / BN) * split;
-    const int grid = units < sm_count() ? units : sm_count();
+    const int units = full_tiles + (tiles - full_tiles) * split;
+    const int grid = units < sms ? units : sms;
     w8a8::RowBlocks rb{};
     if (blocks) rb = *blocks;
     kern<<<grid, w8a8::TileWarps<EPI>::THREADS, smem, st>>>(ta, tw, tout, a_s, w_s, out, ldo, n_rows, M, N, K, word_ok,
-                                                           split, kbs, (int32_t*)workspace, counters, rb, souts, gbn);
+                                                           split, kbs, (int32_t*)workspace, counters, rb, souts, gbn,
+                                                           full_tiles);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }
@@ -282,17 +314,14 @@ int launch_swap(const int8_t* a, const float* a_s, const int8_t* w, const float*
     using C = w8a8::SwapCfg<NB, GROUPED>;
     CUtensorMap tw, tx, tsw, tsa;
     int rc;
-    // per-32 groups in one K slice: when the 128-row weight tiles are fewer than about three quarters of the SMs the
-    // CTAs take 64 or 32 weight rows each (the group order, and so every bit, stays the same; PRISM_B200_WROWS overrides)
+    // per-32 groups in one K slice: PRISM_B200_WROWS = 64 / 32 gives every CTA fewer weight rows (more CTAs when the
+    // 128-row tiles are fewer than the SMs; the group order, and so every bit, stays the same).  Measured on B200 at 16
+    // rows: 5120 x 5120 takes 46 us with 32-row tiles against 25.6 us with 128-row ones (the time goes with the number
+    // of K stages a CTA walks through, not with its bytes), so 128 stays the default.
     int wrows = w8a8::BM;
     if (GROUPED && split == 1) {
-        const long mt = (p.M + NB - 1) / NB;
-        const int want = sm_count() * 3 / 4;
         static const int forced = [] { const char* e = getenv("PRISM_B200_WROWS"); return e ? atoi(e) : 0; }();
-        if (forced == 32 || forced == 64 || forced == 128) wrows = forced;
-        else if (mt * ((p.N + 127) / 128) >= want) wrows = 128;
-        else if (mt * ((p.N + 63) / 64) >= want) wrows = 64;
-        else wrows = 32;
+        if (forced == 32 || forced == 64) wrows = forced;
     }
     p.wrows = wrows;
     if ((rc = tensor_map(&tw, w, p.K, p.N, p.K, w8a8::BK, wrows, 0))) return rc;
@@ -802,13 +831,13 @@ int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float
         // 128 x 256 tiles, or 128 x 128 when those would leave more than half of the SMs without a tile
         const bool narrow = N <= 128 || tile_bn(M, N) == 128;
         if (epi == PB_EPI_I32)
-            return narrow ? launch_tile<128, w8a8::EPI_I32>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters)
-                          : launch_tile<256, w8a8::EPI_I32>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters);
+            return narrow ? launch_tile<128, w8a8::EPI_I32>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters, nullptr, nullptr, 0, workspace_bytes, n_counters)
+                          : launch_tile<256, w8a8::EPI_I32>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters, nullptr, nullptr, 0, workspace_bytes, n_counters);
         if (epi == PB_EPI_BF16)
-            return narrow ? launch_tile<128, w8a8::EPI_BF16>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters)
-                          : launch_tile<256, w8a8::EPI_BF16>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters);
-        return narrow ? launch_tile<128, w8a8::EPI_ADD>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters)
-                      : launch_tile<256, w8a8::EPI_ADD>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters);
+            return narrow ? launch_tile<128, w8a8::EPI_BF16>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters, nullptr, nullptr, 0, workspace_bytes, n_counters)
+                          : launch_tile<256, w8a8::EPI_BF16>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters, nullptr, nullptr, 0, workspace_bytes, n_counters);
+        return narrow ? launch_tile<128, w8a8::EPI_ADD>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters, nullptr, nullptr, 0, workspace_bytes, n_counters)
+                      : launch_tile<256, w8a8::EPI_ADD>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters, nullptr, nullptr, 0, workspace_bytes, n_counters);
     }
     // few rows: operands swapped, K split over blockIdx.y
     if (split > KB) split = KB;
@@ -1398,6 +1427,20 @@ int pb_int8_peak_probe(int iters, int pattern, int mma_n, unsigned long long* cy
     int rc = set_smem(w8a8::int8_peak_kernel, smem);
     if (rc) return rc;
     w8a8::int8_peak_kernel<<<sm_count(), 128, smem, (cudaStream_t)stream>>>(iters, pattern, mma_n, cycles);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+int pb_l2_prefetch(const void* const* ptrs, const long* nbytes, int n, int ctas, void* stream) {
+    if (!ptrs || !nbytes || n < 1 || n > 8 || ctas < 1 || ctas > 1024) return PB_BAD_ARGUMENT;
+    PrefetchRanges r{};
+    r.n = n;
+    for (int i = 0; i < n; ++i) {
+        if (!ptrs[i] || nbytes[i] < 0 || !aligned16(ptrs[i])) return PB_BAD_ARGUMENT;
+        r.ptr[i] = (const char*)ptrs[i];
+        r.bytes[i] = nbytes[i] & ~15l;                             // whole 16-byte units (the tail is at most 15 bytes)
+    }
+    l2_prefetch_kernel<<<ctas, 128, 0, (cudaStream_t)stream>>>(r);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }

@@ -478,6 +478,21 @@ struct RowBlocks {
     int rows;
 };
 
+// A work unit of the persistent tile kernel: a whole tile, or one K slice of a tile.  The first `full` tiles are whole
+// (K unsplit); each later tile is `split` units, one per K slice, neighbours in the unit order so that they finish
+// together.  full == 0: every tile is split (few tiles, long K); full == all tiles: nothing is split; in between: only
+// the last, partial wave of tiles is split over the SMs that would otherwise idle through it.
+struct Unit {
+    int t, z, kb0, kb1, split;
+};
+__device__ __forceinline__ Unit unit_of(int u, int full, int split, int kb_per_split, int KB) {
+    if (u < full) return Unit{u, 0, 0, KB, 1};
+    const int v = u - full, t = full + v / split, z = v % split;
+    const int kb0 = z * kb_per_split;
+    const int kb1 = kb0 + kb_per_split < KB ? kb0 + kb_per_split : KB;
+    return Unit{t, z, kb0, kb1, split};
+}
+
 // Epilogue warps: four (one per tensor-memory lane quarter), eight for the residual add (two per quarter, half the
 // columns each: its global round trips are what the main loop must hide).
 template <int EPI>
@@ -492,7 +507,7 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                  const __grid_constant__ CUtensorMap tm_out, const float* __restrict__ a_s, const float* __restrict__ w_s, void* __restrict__ out, long ldo,
                  const int* __restrict__ n_rows, int M, int N, int K, int word_ok, int split, int kb_per_split,
                  int32_t* __restrict__ ws, int* __restrict__ counters, const __grid_constant__ RowBlocks rb,
-                 float* __restrict__ souts, int gbn) {
+                 float* __restrict__ souts, int gbn, int full_tiles) {
     using C = TileCfg<BN>;
     using W = TileWarps<EPI>;
     extern __shared__ uint8_t smem_raw[];
@@ -506,8 +521,9 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
     live = live < M ? live : M;
     const int num_m = (live + BM - 1) / BM, num_n = (N + BN - 1) / BN;
     const int num_tiles = num_m * num_n, KB = (K + BK - 1) / BK;
-    // work units: (tile, K slice), the slices of a tile next to each other so that they finish together
-    const int num_units = num_tiles * split;
+    // work units: whole tiles first, then (tile, K slice) for the rest (unit_of)
+    const int full = full_tiles < num_tiles ? full_tiles : num_tiles;
+    const int num_units = full + (num_tiles - full) * split;
     // Tile order.  Row tiles fastest: a weight panel is read once and the activations come back from L2 for every
     // panel - right while the activations fit in L2.  Weight tiles fastest (bit 3 of word_ok): a group of row tiles
     // is read once and the weights come back from L2 - right when the activations are the larger operand and the
@@ -550,10 +566,10 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             // the MMA thread's bounded wait for the first stage expires and the CTA leaves through its abort path
             bool ok = !(word_ok & 16);
             for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
-                const int t = u / split, z = u - t * split;
+                const Unit un = unit_of(u, full, split, kb_per_split, KB);
+                const int t = un.t;
                 const int m0 = (n_fastest ? t / num_n : t % num_m) * BM, n0 = (n_fastest ? t % num_n : t / num_m) * BN;
-                const int kb_end = (z + 1) * kb_per_split < KB ? (z + 1) * kb_per_split : KB;
-                for (int kb = z * kb_per_split; kb < kb_end; ++kb) {
+                for (int kb = un.kb0; kb < un.kb1; ++kb) {
                     if (!mbar_wait(smem_u32(&aux->empty[stage]), phase ^ 1, abort_flag, 0x100 + stage)) {
                         ok = false;
                         break;
@@ -590,9 +606,8 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             // answer read after them: the thread stays ahead of the tensor core (512 cycles per stage).
             bool ready = mbar_test(smem_u32(&aux->full[0]), 0);
             for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
-                const int z = u % split;
-                const int kb_begin = z * kb_per_split;
-                const int kb_end = kb_begin + kb_per_split < KB ? kb_begin + kb_per_split : KB;
+                const Unit un = unit_of(u, full, split, kb_per_split, KB);
+                const int kb_begin = un.kb0, kb_end = un.kb1;
                 if (!mbar_wait(smem_u32(&aux->tempty[buf]), bphase ^ 1, abort_flag, 0x200 + buf)) break;
                 tc_fence_after();
                 const uint32_t d = tmem_base + buf * BN;
@@ -631,7 +646,8 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
         int buf = 0;
         uint32_t bphase = 0;
         for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
-            const int t = u / split, z = u - t * split;
+            const Unit un = unit_of(u, full, split, kb_per_split, KB);
+            const int t = un.t, z = un.z;
             const int m0 = (n_fastest ? t / num_n : t % num_m) * BM, n0 = (n_fastest ? t % num_n : t / num_m) * BN;
             float* swb = sw_stash + (EPI == EPI_ADD ? 0 : buf * BN);
             void* out_t = out;
@@ -656,7 +672,7 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     const int uu = pass == 0 ? tn : tn + (int)gridDim.x;
                     if (pass == 1 && u != (int)blockIdx.x) break;
                     if (uu >= num_units) break;
-                    const int tt = uu / split;
+                    const int tt = unit_of(uu, full, split, kb_per_split, KB).t;
                     const int pm0 = (n_fastest ? tt / num_n : tt % num_m) * BM, pn0 = (n_fastest ? tt % num_n : tt / num_m) * BN;
                     for (int line = et; line < BM * (BN / 32); line += ET) {
                         const int pr = pm0 + line / (BN / 32), pc = pn0 + (line % (BN / 32)) * 32;
@@ -672,9 +688,9 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
             const bool rok = row < live;
             const float sa = (rok && EPI != EPI_I32) ? a_s[row] : 0.0f;
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * BN;
-            if (split > 1) {
+            if (un.split > 1) {
                 // this slice's int32 accumulator -> workspace (the four warps of the first column half do it all)
-                int32_t* ws_tile = ws + (long)t * split * (BM * BN);
+                int32_t* ws_tile = ws + (long)(t - full) * split * (BM * BN);
                 if (half == 0) {
                     uint32_t* stg = stage_buf + q * (32 * 33);
                     drain_accumulator<BN, EPI_I32>(ws_tile + (long)z * (BM * BN), BN, BN, BM, 0, 0, q, lane, lane_addr,
@@ -687,7 +703,7 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                 __threadfence();
                 asm volatile("bar.sync 1, %0;" ::"n"(ET) : "memory");
                 if (et == 0) {
-                    const int old = atomicAdd(counters + t, 1);
+                    const int old = atomicAdd(counters + (t - full), 1);
                     aux->is_last = (old == split - 1);
                 }
                 asm volatile("bar.sync 1, %0;" ::"n"(ET) : "memory");
@@ -696,7 +712,7 @@ w8a8_tile_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
                     const int cb = EPI == EPI_ADD ? half * (BN / 2) : 0, ce = EPI == EPI_ADD ? (half + 1) * (BN / 2) : BN;
                     reduce_store<BN, EPI>(out_t, ldo, N, live, m0, n0, q, lane, ws_tile, (long)BM * BN, split, swb, sa, cb,
                                           ce);
-                    if (et == 0) counters[t] = 0;
+                    if (et == 0) counters[t - full] = 0;
                 }
                 buf ^= 1;
                 if (buf == 0) bphase ^= 1;

@@ -56,6 +56,15 @@ def _workspace(device):
     return _WORKSPACE[key]
 
 
+def _workspace_if_ready(device):
+    """The device's workspace when it exists or may be allocated now (not during graph capture), else (None, None):
+    for uses that are an optimisation, not a need (the many-rows kernel's split of its last, partial wave of tiles)."""
+    key = torch.device(device).index or 0
+    if key not in _WORKSPACE and torch.cuda.is_current_stream_capturing():
+        return None, None
+    return _workspace(device)
+
+
 def reset_workspace(device=None):
     """Zero the split-K arrival counters (after a kernel reported PB_DEVICE_TIMEOUT: a CTA that gave up a wait did not
     count itself in, so its tile's counter is left non-zero)."""
@@ -185,6 +194,8 @@ def gemm(a, a_s, w, w_s, out, n_rows, gk, epi=0, outs=None, cfg=None, slots=None
             split -= 1
         if split == 1:
             ws = counters = None
+    if split == 1 and M > FEW_ROWS:
+        ws, counters = _workspace_if_ready(a.device)     # lets the kernel split the K range of a partial last wave
     _call(a, a_s, w, w_s, out, out.stride(0), n_rows, gk, epi, split, 0, ws, counters, pdl=pdl)
     return None
 
@@ -237,6 +248,8 @@ def gemm_i32(a, a_s, w, w_s, slots, n_rows, max_split=4, pdl=False, split=None):
             ws, counters = _workspace(a.device)
             if _lib.lib().pb_w8a8_workspace_bytes(M, N, inner) > ws.numel():
                 inner, ws, counters = 1, None, None
+        if inner == 1:
+            ws, counters = _workspace_if_ready(a.device)
         _call(a, a_s, w, w_s, slots, N, n_rows, K, EPI_I32, inner, slots.stride(0), ws, counters, pdl=pdl)
         return 1
     S = effective_split(K, max(1, min(S, max_split, slots.shape[0])))
@@ -300,3 +313,16 @@ def interleave_gate_up(gate, up, bn):
     if FF % h:
         raise ValueError(f"FF {FF} is not a multiple of {h}")
     return torch.stack([gate.view(FF // h, h, K), up.view(FF // h, h, K)], 1).reshape(2 * FF, K).contiguous()
+
+
+def l2_prefetch(tensors, ctas=32):
+    """Request the bytes of up to eight contiguous tensors into L2 on the current stream (the reference's
+    cuda_ext.l2_prefetch, kernels/cuda_ext.py:171-173; four tensors there).  Meant for a side stream while a
+    latency-bound kernel runs; off by default everywhere in this package."""
+    import ctypes
+    tensors = list(tensors)
+    if not 1 <= len(tensors) <= 8 or any(not t.is_cuda or not t.is_contiguous() for t in tensors):
+        raise RuntimeError("l2_prefetch: one to eight contiguous CUDA tensors")
+    ptrs = (ctypes.c_void_p * len(tensors))(*[t.data_ptr() for t in tensors])
+    sizes = (ctypes.c_long * len(tensors))(*[t.numel() * t.element_size() for t in tensors])
+    _lib.check(_lib.lib().pb_l2_prefetch(ptrs, sizes, len(tensors), int(ctas), _lib.stream()), "l2_prefetch")

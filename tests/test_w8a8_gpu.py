@@ -309,3 +309,25 @@ def test_gemm_swiglu_epilogue(dev, M, FF, K, live, bn):
     out = torch.zeros(M, N2, dtype=torch.bfloat16, device=dev)
     w8a8.gemm(q, s, wd_.to(dev), wds.to(dev), out, n_rows(live, dev), hb)
     assert same(out, bf16_from_bits(ref)), first_diff(np_bits(out), ref)
+
+
+def test_l2_prefetch(dev):
+    """The bulk L2 prefetch of weight ranges on a side stream: sizes that are not whole chunks, several tensors, then
+    the GEMM that reads them - the bits do not change (a prefetch only moves cache lines)."""
+    M, N, K = 16, 5120, 5120
+    a, w, sa, sw = rand_w8a8(M, N, K, seed=9)
+    ref0 = oracle.w8a8_gemm(a.numpy(), sa.numpy(), w.numpy(), sw.numpy(), K, 0, M)
+    ad, wd, sad, swd = a.to(dev), w.to(dev), sa.to(dev).view(-1), sw.to(dev).view(-1)
+    odd = torch.zeros(4096 * 3 + 48, dtype=torch.uint8, device=dev)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        w8a8.l2_prefetch([wd, swd, odd], ctas=16)
+        w8a8.l2_prefetch([wd])
+    torch.cuda.current_stream().wait_stream(side)
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
+    w8a8.gemm(ad, sad, wd, swd, out, n_rows(M, dev), K)
+    torch.cuda.synchronize()
+    assert same(out, bf16_from_bits(ref0))
+    with pytest.raises(RuntimeError):
+        w8a8.l2_prefetch([])
