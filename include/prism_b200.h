@@ -132,7 +132,9 @@ int pb_quant_rows(const void* x, int x_fp32, long ldx, const float* inv_s, int8_
  * pb_quant_rows_exchange / pb_swiglu_q8_exchange / pb_gated_norm_q8_exchange: the producers' mode 3 - every row's
  * maximum over all ranks travels as one word (pass number above the float's bits) per row and rank; fewer than 256
  * rows per call.  pb_fold_sync / pb_norm_q8_sync: the deferred add over EVERY rank's slots, read over NVLink after a
- * flag handshake (the grid's first block signals, every block waits) - the int32 all-reduce disappears.
+ * flag handshake (the grid's first block signals, every block waits) - the int32 all-reduce disappears.  pb_fold_sync
+ * with no `others` is the handshake alone: the slots the other ranks' kernels stored into THIS rank's memory
+ * (pb_w8a8_gemm_scatter) are folded once every rank has signalled that its kernel ended - no barrier collective.
  * Each wait is bounded (pb_set_wait_limit_ns): a rank that never arrives yields PB_DEVICE_TIMEOUT in the status word,
  * not a hang.  Peer traffic is plain loads and stores; no TMA and no multicast touches another GPU's memory. */
 typedef struct pb_sync {

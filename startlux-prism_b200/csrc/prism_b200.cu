@@ -178,6 +178,16 @@ int add_mode() {
     return v;
 }
 
+// PRISM_B200_BN192=0: never use 128 x 192 tiles (comparison runs).
+bool wide192_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("PRISM_B200_BN192");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v == 1;
+}
+
 // PRISM_B200_TAIL=0: never split the last wave of tiles (comparison runs).
 bool tail_split_enabled() {
     static int v = -1;
@@ -211,7 +221,9 @@ int launch_tile(const int8_t* a, const float* a_s, const int8_t* w, const float*
     const int tiles = ((M + 127) / 128) * ((N + BN - 1) / BN);
     const int sms = sm_count();
     int full_tiles = split > 1 ? 0 : tiles;
-    if (split == 1 && workspace && counters && tail_split_enabled() && tiles > sms) {
+    // (measured: a gain of 3-8 % for K = 17408, a loss for K = 5120, where a tile's main loop is shorter than the trip of
+    // its slices through the workspace: long K only)
+    if (split == 1 && workspace && counters && tail_split_enabled() && tiles > sms && KB >= 96) {
         const int tail = tiles % sms;
         if (tail > 0 && tail * 5 <= sms * 3) {                     // a last wave less than 60 % full
             int s = sms / tail;
@@ -828,16 +840,21 @@ int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float
             if (workspace_bytes < pb_w8a8_workspace_bytes(M, N, split) || n_counters < pb_w8a8_counters(M, N))
                 return PB_TOO_LARGE;
         }
-        // 128 x 256 tiles, or 128 x 128 when those would leave more than half of the SMs without a tile
-        const bool narrow = N <= 128 || tile_bn(M, N) == 128;
-        if (epi == PB_EPI_I32)
-            return narrow ? launch_tile<128, w8a8::EPI_I32>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters, nullptr, nullptr, 0, workspace_bytes, n_counters)
-                          : launch_tile<256, w8a8::EPI_I32>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters, nullptr, nullptr, 0, workspace_bytes, n_counters);
-        if (epi == PB_EPI_BF16)
-            return narrow ? launch_tile<128, w8a8::EPI_BF16>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters, nullptr, nullptr, 0, workspace_bytes, n_counters)
-                          : launch_tile<256, w8a8::EPI_BF16>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters, nullptr, nullptr, 0, workspace_bytes, n_counters);
-        return narrow ? launch_tile<128, w8a8::EPI_ADD>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters, nullptr, nullptr, 0, workspace_bytes, n_counters)
-                      : launch_tile<256, w8a8::EPI_ADD>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters, nullptr, nullptr, 0, workspace_bytes, n_counters);
+        // tile width: 128 x 256, 128 x 128 when those would leave more than half of the SMs without a tile, or (one K
+        // slice only) 128 x 192 when that needs fewer tile-widths of waves: 5120 columns at 2048 rows are 320 tiles
+        // of 256 = 3 waves x 256, but 432 tiles of 192 = 3 waves x 192
+        int bn = (N <= 128 || tile_bn(M, N) == 128) ? 128 : 256;
+        if (bn == 256 && split == 1 && wide192_enabled()) {
+            const long mt = (M + 127) / 128, sms = sm_count();
+            const long w256 = (mt * ((N + 255) / 256) + sms - 1) / sms * 256 * 100;
+            const long w192 = (mt * ((N + 191) / 192) + sms - 1) / sms * 192 * 107;     // its operand traffic per MMA is higher
+            if (w192 < w256) bn = 192;
+        }
+#define PB_TILE(BN_, EPI_) launch_tile<BN_, w8a8::EPI_>(a, a_s, w, w_s, out, ldo, n_rows, M, N, K, st, split, workspace, counters, nullptr, nullptr, 0, workspace_bytes, n_counters)
+        if (epi == PB_EPI_I32) return bn == 128 ? PB_TILE(128, EPI_I32) : bn == 192 ? PB_TILE(192, EPI_I32) : PB_TILE(256, EPI_I32);
+        if (epi == PB_EPI_BF16) return bn == 128 ? PB_TILE(128, EPI_BF16) : bn == 192 ? PB_TILE(192, EPI_BF16) : PB_TILE(256, EPI_BF16);
+        return bn == 128 ? PB_TILE(128, EPI_ADD) : bn == 192 ? PB_TILE(192, EPI_ADD) : PB_TILE(256, EPI_ADD);
+#undef PB_TILE
     }
     // few rows: operands swapped, K split over blockIdx.y
     if (split > KB) split = KB;
@@ -1181,7 +1198,9 @@ int pb_fold_sync(float* h, long ldh, const int32_t* slots, long slot_stride, int
     if (N % 4) return PB_UNSUPPORTED_SHAPE;
     if (!aligned16(h) || !aligned16(slots) || !aligned16(w_s) || (ldh % 4) || (slot_stride % 4)) return PB_BAD_ARGUMENT;
     tpx::Sync sy;
-    int rc = to_sync(sync, &sy, true);
+    // no `others`: a handshake only - every slot is already in this rank's memory (the other ranks' kernels stored
+    // them there), and the flags say that those kernels have ended
+    int rc = to_sync(sync, &sy, sync->others[0] != nullptr);
     if (rc) return rc;
     dim3 grid((N / 4 + 255) / 256, rows);
     quant::fold_sync_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(h, ldh, slots, slot_stride, S, a_s, w_s, n_rows, N, sy);

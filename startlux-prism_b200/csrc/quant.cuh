@@ -629,7 +629,7 @@ fold_sync_kernel(float* __restrict__ h, long ldh, const int32_t* __restrict__ sl
         tot.x += v.x; tot.y += v.y; tot.z += v.z; tot.w += v.w;
     }
     for (int o = 0; o + 1 < sync.world; ++o)
-        for (int p = 0; p < S; ++p) {
+        for (int p = 0; p < S && sync.others[o]; ++p) {
             const int4 v = tpx::ld_peer4(sync.others[o] + p * slot_stride + r * N + c);
             tot.x += v.x; tot.y += v.y; tot.z += v.z; tot.w += v.w;
         }

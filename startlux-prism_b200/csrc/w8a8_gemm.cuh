@@ -455,7 +455,7 @@ __device__ __forceinline__ void reduce_store(void* __restrict__ out, long ldo, i
 
 template <int BN>
 struct TileCfg {
-    static constexpr int STAGES = (BN == 256) ? 4 : 6;
+    static constexpr int STAGES = (BN >= 192) ? 4 : 6;
     static constexpr int A_BYTES = BM * BK;
     static constexpr int W_BYTES = BN * BK;
     static constexpr int STAGE_BYTES = A_BYTES + W_BYTES;

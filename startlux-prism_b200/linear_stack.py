@@ -106,8 +106,11 @@ class LinearStack:
                 print(f"prism_b200: peer memory unavailable ({peer.error}); NCCL reduce-scatter instead", flush=True)
         # few rows on several ranks: the exchanges move into the kernels (row maxima as words between the producers, the
         # int32 sums read by the fold itself); PRISM_B200_TP_FUSED=0 keeps NCCL's all-reduces
-        if (n > 1 and not self.by_rows and group.backend == "nccl" and os.environ.get("PRISM_B200_TP_FUSED", "1") != "0"):
+        if (n > 1 and group.backend == "nccl" and os.environ.get("PRISM_B200_TP_FUSED", "1") != "0"):
             group.setup(hidden, words=2 * len(layers))
+        # the row-split pass with the scatter fused into the GEMM: flag handshakes inside the folds take the place of
+        # the barrier collectives (PRISM_B200_TP_FLAGS=0 keeps the one-element all-reduce)
+        self.flags = (self.peer is not None and group.fs is not None and os.environ.get("PRISM_B200_TP_FLAGS", "1") != "0")
 
     def __call__(self, h_in, own_rows=False):
         """One pass: h_in fp32 [M, hidden] is copied into the working residual, which is returned (a view of an
@@ -163,6 +166,8 @@ class LinearStack:
         M, nr, g, Ml, r0 = self.M, self.n_rows, self.g, self.Ml, self.r0
         h_own, xq_own, xs_own = self.h[r0:r0 + Ml], self.xq[r0:r0 + Ml], self.xs[r0:r0 + Ml]
         pend = None
+        if self.flags:
+            g.begin_handshakes()
 
         def gathered_input():
             quant.fold(h_own, None, pend, self.nr_own, Ml)
@@ -174,6 +179,9 @@ class LinearStack:
             w, w_s = wt
             if self.peer is not None:
                 w8a8.gemm_scatter(a, w, self.blocks, Ml, self.hidden, nr)
+                if self.flags:
+                    # the fold itself waits until every rank has signalled that its scatter kernel ended
+                    return w8a8.Deferred(self.n, a_s[r0:r0 + Ml], w_s, self.sym, g.handshake())
                 g.sum_(self.token)                 # a barrier: every rank's stores have landed before anyone folds
                 return w8a8.Deferred(self.n, a_s[r0:r0 + Ml], w_s, self.sym)
             w8a8.gemm_i32(a, a_s, w, w_s, self.slots[:1], nr, max_split=1)

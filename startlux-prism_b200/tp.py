@@ -196,6 +196,21 @@ class Group:
         return KQ.Sync(self.epoch, tuple(self.fs), self.step - 1,
                        tuple(b for r, b in enumerate(buffers) if r != self.rank), self.rank, self.world)
 
+    def begin_handshakes(self):
+        """At the start of a many-rows pass whose folds use flag handshakes instead of barrier collectives
+        (linear_stack's row-split pass): a new pass number, the channels counted from zero.  False when the group has
+        no peer-mapped flags (then the caller keeps its collectives)."""
+        from . import quant as KQ
+        if self.fs is None:
+            return False
+        self.step = 0
+        KQ.bump(self.epoch)
+        return True
+
+    def handshake(self):
+        """The next flag handshake alone (no slots to pull): a quant.Sync with no `others`."""
+        return self.sync(())
+
     def words(self):
         """The next row-maximum exchange's quant.Sync (mode 3): every rank's word buffer and the step's first word row."""
         from . import quant as KQ
