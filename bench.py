@@ -214,6 +214,7 @@ def run_gpu(args):
     group = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("NCCL_DEBUG", "WARN")            # NCCL's version banner goes to stdout otherwise
         group = tp.Group(rank, world, backend="nccl", local_rank=local)
     M = args.rows
     layers = []

@@ -1203,7 +1203,20 @@ int pb_fold_sync(float* h, long ldh, const int32_t* slots, long slot_stride, int
     int rc = to_sync(sync, &sy, sync->others[0] != nullptr);
     if (rc) return rc;
     dim3 grid((N / 4 + 255) / 256, rows);
-    quant::fold_sync_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(h, ldh, slots, slot_stride, S, a_s, w_s, n_rows, N, sy);
+    cudaStream_t st = (cudaStream_t)stream;
+    if ((long)grid.x * grid.y > 256) {
+        // many blocks: one small kernel does the handshake (a system-scope wait and fence in each of thousands of blocks
+        // measured slower than NCCL's barrier), the fold after it finds the flags already checked
+        tpx::handshake_kernel<<<1, 32, 0, st>>>(sy);
+        PB_CUDA(cudaGetLastError());
+        if (!sync->others[0]) {
+            quant::fold_kernel<<<grid, 256, 0, st>>>(h, ldh, slots, slot_stride, S, a_s, w_s, n_rows, N);
+            PB_CUDA(cudaGetLastError());
+            return PB_OK;
+        }
+        for (int r = 0; r < tpx::MAX_RANKS; ++r) sy.bufs[r] = nullptr;
+    }
+    quant::fold_sync_kernel<<<grid, 256, 0, st>>>(h, ldh, slots, slot_stride, S, a_s, w_s, n_rows, N, sy);
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }

@@ -88,7 +88,7 @@ __device__ __forceinline__ float exchange_amax(float amax, long t, const Sync& s
 
 // Called by every thread of every block before the first read of another rank's data.
 __device__ __forceinline__ void arrive_and_wait(const Sync& s, bool first_block) {
-    if (s.world <= 1) return;
+    if (s.world <= 1 || !s.bufs[s.rank]) return;              // no flags: the handshake was a kernel of its own
     if (threadIdx.x == 0) {
         const unsigned long long e = (unsigned long long)(*s.epoch);
         const long chan = s.off * s.world;
@@ -102,6 +102,10 @@ __device__ __forceinline__ void arrive_and_wait(const Sync& s, bool first_block)
     }
     __syncthreads();
 }
+
+// The handshake as a kernel of its own (one block): for consumers with thousands of blocks, where a system-scope wait
+// and fence in every block costs more than one extra launch.  Kernels after it on the stream start after it has ended.
+__global__ void __launch_bounds__(32) handshake_kernel(const Sync s) { arrive_and_wait(s, true); }
 
 // Four consecutive int32 sums of another rank's slots, read past this GPU's caches (the data changes between passes).
 __device__ __forceinline__ int4 ld_peer4(const int32_t* p) {

@@ -78,6 +78,9 @@ class LinearStack:
         self.s_max = tp.MAX_SPLIT if M <= tp.SPLIT_ROWS else 1
         self.slots = self.parts[:self.s_max * M * hidden].view(self.s_max, M, hidden)
         self.n_rows = torch.tensor([M], dtype=torch.int32, device=device)
+        # few rows: every GEMM is launched as a programmatic dependent of the quantizer before it (its weights start
+        # streaming while the quantizer still runs).  One row stays on the CUDA-core kernel, which has no such launch.
+        self.pdl = 1 < M <= w8a8.FEW_ROWS and os.environ.get("PRISM_B200_PDL", "1") != "0"
         # several ranks and many rows: the residual stream stays split by rows between the projections (each rank
         # folds, normalises and quantizes M / n rows), a row-parallel projection's int32 sums are reduce-scattered and
         # the int8 rows of the next projection's input all-gathered: 5/8 of an all-reduce's bytes, and 1 / n of the
@@ -132,13 +135,13 @@ class LinearStack:
         for lw in self.layers:
             quant.fold(self.h, self.slots, pend, nr, M)
             quant.rows_q8(self.h, None, self.xq, self.xs, nr, M)
-            w8a8.gemm(self.xq, self.xs, *lw["qkv"], self.qkv, nr, self.hidden)
+            w8a8.gemm(self.xq, self.xs, *lw["qkv"], self.qkv, nr, self.hidden, pdl=self.pdl)
             tp.quantize_rows(g if self.n > 1 else None, quant.rows_q8, M, self.amax, self.qkv[:, :self.ql], None,
                              self.aq, self.as_, nr, M)
             pend = self._out(self.aq, self.as_, lw["o"])
             quant.fold(self.h, self.slots, pend, nr, M)
             quant.rows_q8(self.h, None, self.xq, self.xs, nr, M)
-            w8a8.gemm(self.xq, self.xs, *lw["gate_up"], self.gu, nr, self.hidden)
+            w8a8.gemm(self.xq, self.xs, *lw["gate_up"], self.gu, nr, self.hidden, pdl=self.pdl)
             tp.quantize_rows(g if self.n > 1 else None, quant.swiglu_q8, M, self.amax, self.gu, None, self.dq,
                              self.ds, nr, M)
             pend = self._out(self.dq, self.ds, lw["down"])
@@ -155,8 +158,8 @@ class LinearStack:
         the fold); several ranks all-reduce int32 sums and fold."""
         w, w_s = wt
         if self.n > 1:
-            return tp.out_proj(self.g, a, a_s, w, w_s, self.parts, self.M, self.n_rows)
-        return w8a8.gemm(a, a_s, w, w_s, self.h, self.n_rows, a.shape[1], epi=1, slots=self.slots)
+            return tp.out_proj(self.g, a, a_s, w, w_s, self.parts, self.M, self.n_rows, pdl=self.pdl)
+        return w8a8.gemm(a, a_s, w, w_s, self.h, self.n_rows, a.shape[1], epi=1, slots=self.slots, pdl=self.pdl)
 
     def _pass_by_rows(self, gather=True):
         """Several ranks, many rows.  Between a row-parallel projection and the next column-parallel one every rank
