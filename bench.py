@@ -784,12 +784,14 @@ def run_probe(args):
     if case == "peak":
         return run_peak(dev)
     ri = lambda *s: torch.randint(-127, 128, s, dtype=torch.int8, device=dev, generator=gen)     # noqa: E731
-    if case in ("tile", "tile_add", "decode", "decode32"):
+    if case in ("tile", "tile_add", "decode", "decode32", "config0"):
         M = 2048 if case.startswith("tile") else 16
         N, K = (34816, 5120) if case in ("tile", "decode32") else (5120, 17408)
         if case == "tile_add":
             N, K = 5120, 17408
-        gk = 32 if case == "decode32" else K
+        if case == "config0":                              # BASELINE config 0: Q8_0 groups, 5120 x 5120, 16 rows
+            N, K = 5120, 5120
+        gk = 32 if case in ("decode32", "config0") else K
         a, w = ri(M, K), ri(N, K)
         sa = torch.rand(M, K // gk, device=dev, generator=gen) * 1e-2
         sw = torch.rand(N, K // gk, device=dev, generator=gen) * 1e-3

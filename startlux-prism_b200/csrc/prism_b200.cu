@@ -350,7 +350,8 @@ int launch_swap(const int8_t* a, const float* a_s, const int8_t* w, const float*
     if ((rc = set_smem(kern, C::smem_bytes(C::STAGES_DEEP)))) return rc;
     dim3 grid((p.N + wrows - 1) / wrows, split, (p.M + NB - 1) / NB);
     // a grid no larger than the SM count gets one CTA per SM and the deepest pipeline; a larger one two CTAs per SM
-    p.stages = (long)grid.x * grid.y * grid.z <= sm_count() ? C::STAGES_DEEP : C::STAGES;
+    // (per-32 groups: the accumulator slots fill the SM's tensor memory, so one CTA per SM at any grid size)
+    p.stages = (GROUPED || (long)grid.x * grid.y * grid.z <= sm_count()) ? C::STAGES_DEEP : C::STAGES;
     const int smem = C::smem_bytes(p.stages);
     if (p.pdl) {
         cudaLaunchConfig_t cfg = {};

@@ -946,8 +946,13 @@ struct SwapCfg {
     // SM with all the shared memory (bytes in flight per SM are what hides the DRAM latency)
     static constexpr int STAGES = (108 * 1024 / STAGE_BYTES) > 8 ? 8 : (108 * 1024 / STAGE_BYTES);
     static constexpr int STAGES_DEEP = (212 * 1024 / STAGE_BYTES) > 12 ? 12 : (212 * 1024 / STAGE_BYTES);
-    static constexpr int BATCH_COLS = GROUPED ? 4 * NB : NB;     // accumulator columns written per stage
-    static constexpr int RING = GROUPED ? ((256 / BATCH_COLS) > 4 ? 4 : (256 / BATCH_COLS)) : 1;
+    // per-32 groups: an accumulator slot takes SUPER K stages (4 groups of NB columns each) and the epilogue warps drain
+    // a whole slot per hand-off: one barrier round trip and one tensor-memory load latency per SUPER stages instead of
+    // per stage (that chain of latencies, about 1,000 cycles per stage, was the kernel's whole time).  Two slots: the
+    // MMAs of the next fill while the epilogue drains this one.  512 columns: one CTA per SM.
+    static constexpr int SUPER = GROUPED ? (NB == 16 ? 4 : NB == 32 ? 2 : 1) : 1;
+    static constexpr int BATCH_COLS = GROUPED ? SUPER * 4 * NB : NB;
+    static constexpr int RING = GROUPED ? 2 : 1;
     static constexpr int ACC_COLS = BATCH_COLS * RING;
     static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128
                                    : ACC_COLS <= 256 ? 256 : 512;
@@ -995,6 +1000,57 @@ __device__ __forceinline__ void swap_store(const SwapArgs& p, int n, int m0, int
                 *o = __fadd_rn(*o, v[j]);
             }
         }
+    }
+}
+
+// One K stage's four scale groups of eight activation rows (c .. c + 7 of this warp's rows), added to the rows' fp32 sums
+// in ascending group order.  r[g][j]: the int32 sum of group g and row c + j; sa4[row]: the row's four activation scales
+// of this stage; sw4: this thread's weight row's four scales.
+//   plain: (float(sum) * sa) * sw, each product rounded (two rows per packed multiply), then a scalar add_rn.  The adds
+//          stay scalar on purpose: the assembler contracts a packed multiply followed by a packed add into one fused
+//          multiply-add (measured: 15 % of results change), which would break the reference's two-rounding contract.
+//   fuse:  the vocabulary head - the reference's kernel writes `acc += (ai * sa) * sw` without explicit roundings
+//          (kernels/decode.py:157) and its compiler fuses the second multiply with the add: one rounded product, then
+//          a fused multiply-add, per group.
+__device__ __forceinline__ void add_stage_groups(float2* acc, int c, const uint32_t (&r)[4][8], const float4* sa4,
+                                                 const float4 sw4, bool fuse) {
+    if (fuse) {
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+            const float4 s0 = sa4[c + j], s1 = sa4[c + j + 1];
+            float2 a = acc[(c + j) >> 1];
+            a.x = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[0][j]), s0.x), sw4.x, a.x);
+            a.y = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[0][j + 1]), s1.x), sw4.x, a.y);
+            a.x = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[1][j]), s0.y), sw4.y, a.x);
+            a.y = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[1][j + 1]), s1.y), sw4.y, a.y);
+            a.x = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[2][j]), s0.z), sw4.z, a.x);
+            a.y = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[2][j + 1]), s1.z), sw4.z, a.y);
+            a.x = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[3][j]), s0.w), sw4.w, a.x);
+            a.y = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[3][j + 1]), s1.w), sw4.w, a.y);
+            acc[(c + j) >> 1] = a;
+        }
+        return;
+    }
+    const float2 w0 = make_float2(sw4.x, sw4.x), w1 = make_float2(sw4.y, sw4.y), w2 = make_float2(sw4.z, sw4.z),
+                 w3 = make_float2(sw4.w, sw4.w);
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+        const float4 s0 = sa4[c + j], s1 = sa4[c + j + 1];
+        float2 a = acc[(c + j) >> 1];
+        float2 t;
+        t = __fmul2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[0][j]), __int2float_rn((int)r[0][j + 1])),
+                                  make_float2(s0.x, s1.x)), w0);
+        a.x = __fadd_rn(a.x, t.x); a.y = __fadd_rn(a.y, t.y);
+        t = __fmul2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[1][j]), __int2float_rn((int)r[1][j + 1])),
+                                  make_float2(s0.y, s1.y)), w1);
+        a.x = __fadd_rn(a.x, t.x); a.y = __fadd_rn(a.y, t.y);
+        t = __fmul2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[2][j]), __int2float_rn((int)r[2][j + 1])),
+                                  make_float2(s0.z, s1.z)), w2);
+        a.x = __fadd_rn(a.x, t.x); a.y = __fadd_rn(a.y, t.y);
+        t = __fmul2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[3][j]), __int2float_rn((int)r[3][j + 1])),
+                                  make_float2(s0.w, s1.w)), w3);
+        a.x = __fadd_rn(a.x, t.x); a.y = __fadd_rn(a.y, t.y);
+        acc[(c + j) >> 1] = a;
     }
 }
 
@@ -1108,9 +1164,10 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             // An mbarrier test keeps this thread waiting about 200 cycles for its answer: the tests of the NEXT stage's
             // barriers are issued before the current stage's MMAs, their answers read after them.
             bool ready = nkb > 0 && mbar_test(smem_u32(&aux->full[0]), 0);
-            bool ring_free = true;                                   // a fresh ring slot is free
+            int sub = 0;                                             // per-32 groups: K stage inside the accumulator slot
             for (int i = 0; i < nkb && ok; ++i) {
-                if (GROUPED && !ring_free &&
+                // a new slot must have been drained (a fresh barrier passes at once)
+                if (GROUPED && sub == 0 &&
                     !mbar_wait(smem_u32(&aux->tempty[ring]), rphase ^ 1, abort_flag, 0x600 + ring)) {
                     ok = false;
                     break;
@@ -1121,10 +1178,7 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                 }
                 const int nstage = stage + 1 == NST ? 0 : stage + 1;
                 const uint32_t nphase = nstage == 0 ? phase ^ 1 : phase;
-                const int nring = ring + 1 == C::RING ? 0 : ring + 1;
-                const uint32_t nrphase = nring == 0 ? rphase ^ 1 : rphase;
                 const bool ready_next = mbar_test(smem_u32(&aux->full[nstage]), nphase);
-                const bool ring_free_next = GROUPED ? mbar_test(smem_u32(&aux->tempty[nring]), nrphase ^ 1) : true;
                 tc_fence_after();
                 uint8_t* st = smem + stage * C::STAGE_BYTES;
                 const uint64_t ad = umma_desc_k128(smem_u32(st));
@@ -1132,22 +1186,29 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
 #pragma unroll
                 for (int k = 0; k < BK / 32; ++k) {
                     if (GROUPED)
-                        umma_i8(tmem_base + ring * C::BATCH_COLS + k * NB, umma_desc_advance(ad, k * 32),
+                        umma_i8(tmem_base + ring * C::BATCH_COLS + (sub * 4 + k) * NB, umma_desc_advance(ad, k * 32),
                                 umma_desc_advance(bd, k * 32), idesc, 0u);
                     else
                         umma_i8(tmem_base, umma_desc_advance(ad, k * 32), umma_desc_advance(bd, k * 32), idesc,
                                 (i | k) ? 1u : 0u);
                 }
-                // per-32 groups: the epilogue warps hand the stage back themselves (they read its scales after these
-                // MMAs have completed), so one commit per stage is enough
-                if (GROUPED) tc_commit(smem_u32(&aux->tfull[ring]));
-                else tc_commit(smem_u32(&aux->empty[stage]));
+                if (GROUPED) {
+                    // the epilogue warps hand the stages back themselves (they read the stages' scales after these MMAs
+                    // have completed): one commit per slot
+                    if (++sub == C::SUPER || i + 1 == nkb) {
+                        tc_commit(smem_u32(&aux->tfull[ring]));
+                        sub = 0;
+                        if (++ring == C::RING) {
+                            ring = 0;
+                            rphase ^= 1;
+                        }
+                    }
+                } else {
+                    tc_commit(smem_u32(&aux->empty[stage]));
+                }
                 stage = nstage;
                 phase = nphase;
-                ring = nring;
-                rphase = nrphase;
                 ready = ready_next;
-                ring_free = ring_free_next;
             }
             if (!GROUPED && ok) tc_commit(smem_u32(&aux->tfull[0]));
         }
@@ -1169,91 +1230,79 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             uint32_t phase = 0, rphase = 0;
             bool ok = true;
             // this thread's weight row: four group scales (16 bytes) per stage, read straight from global memory one
-            // stage ahead (a tensor-map box of 128 rows x 16 bytes costs the TMA unit a request per row)
+            // slot ahead (a tensor-map box of 128 rows x 16 bytes costs the TMA unit a request per row)
             const float4* swp = (const float4*)(p.w_s + (long)(n < p.N ? n : 0) * (p.K >> 5)) + kb0;
-            float4 sw_next = nkb > 0 ? __ldg(swp) : make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int i = 0; i < nkb && ok; ++i) {
-                const float4 sw4 = sw_next;
-                if (i + 1 < nkb) sw_next = __ldg(swp + i + 1);
+            float4 sw_ahead[C::SUPER];
+#pragma unroll
+            for (int sidx = 0; sidx < C::SUPER; ++sidx)
+                sw_ahead[sidx] = sidx < nkb ? __ldg(swp + sidx) : make_float4(0.f, 0.f, 0.f, 0.f);
+            const bool fuse = p.epi == EPI_F32;
+            for (int i0 = 0; i0 < nkb && ok; i0 += C::SUPER) {
+                const int ns = nkb - i0 < C::SUPER ? nkb - i0 : C::SUPER;      // K stages in this slot
+                float4 sw4[C::SUPER];
+#pragma unroll
+                for (int sidx = 0; sidx < C::SUPER; ++sidx) {
+                    sw4[sidx] = sw_ahead[sidx];
+                    if (i0 + C::SUPER + sidx < nkb) sw_ahead[sidx] = __ldg(swp + i0 + C::SUPER + sidx);
+                }
                 if (!mbar_wait(smem_u32(&aux->tfull[ring]), rphase, abort_flag, 0x800 + ring)) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-                // the stage's scales landed with its operands: its full barrier has completed (the MMAs ran after
-                // it); testing it here orders this thread's reads after the bulk copies' writes
-                if (!mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, 0x880 + stage)) {
-                    ok = false;
-                    break;
+                // the stages' scales landed with their operands: their full barriers have completed (the MMAs ran after
+                // them); testing them here orders this thread's reads after the bulk copies' writes
+                const float4* sa4[C::SUPER];
+#pragma unroll
+                for (int sidx = 0; sidx < C::SUPER; ++sidx) {
+                    int st = stage + sidx;
+                    uint32_t ph = phase;
+                    if (st >= NST) {
+                        st -= NST;
+                        ph ^= 1;
+                    }
+                    sa4[sidx] = (const float4*)(smem + st * C::STAGE_BYTES + C::W_BYTES + C::X_BYTES) + j0;
+                    if (sidx < ns && ok && !mbar_wait(smem_u32(&aux->full[st]), ph, abort_flag, 0x880 + st)) ok = false;
                 }
-                const uint8_t* st = smem + stage * C::STAGE_BYTES + C::W_BYTES + C::X_BYTES;
-                const float4* sa4 = (const float4*)st + j0;
-                const float2 w0 = make_float2(sw4.x, sw4.x), w1 = make_float2(sw4.y, sw4.y),
-                             w2 = make_float2(sw4.z, sw4.z), w3 = make_float2(sw4.w, sw4.w);
+                if (!ok) break;
 #pragma unroll
                 for (int c = 0; c < NH; c += 8) {
                     if (!active || m0 + j0 + c >= live) break;     // no weight rows here, or these eight rows are not live
-                    uint32_t r[4][8];
+                    // two stages' loads (eight of them) are in flight before each wait
+                    constexpr int LB = C::SUPER >= 2 ? 2 : 1;
 #pragma unroll
-                    for (int g = 0; g < 4; ++g) tmem_ld8(lane_base + ring * C::BATCH_COLS + g * NB + j0 + c, r[g]);
-                    tmem_ld_wait();
-                    // (float(sum_g) * sa[m, g]) * sw[n, g] for two rows per instruction (packed fp32 multiplies, each
-                    // lane rounded to nearest like mul_rn), then scalar add_rn in ascending group order.  The adds stay
-                    // scalar on purpose: the assembler contracts a packed multiply followed by a packed add into one
-                    // fused multiply-add (measured: 15 % of results change), which would break the reference's
-                    // two-rounding contract.
-                    if (p.epi == EPI_F32) {
-                        // the vocabulary head: the reference's kernel writes `acc += (ai * sa) * sw` without explicit
-                        // roundings (kernels/decode.py:157) and its compiler fuses the second multiply with the add:
-                        // one rounded product, then a fused multiply-add, per group
+                    for (int s0 = 0; s0 < C::SUPER; s0 += LB) {
+                        if (s0 >= ns) break;
+                        uint32_t r[LB][4][8];
 #pragma unroll
-                        for (int j = 0; j < 8; j += 2) {
-                            const float4 s0 = sa4[c + j], s1 = sa4[c + j + 1];
-                            float2 a = acc[(c + j) >> 1];
-                            a.x = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[0][j]), s0.x), sw4.x, a.x);
-                            a.y = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[0][j + 1]), s1.x), sw4.x, a.y);
-                            a.x = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[1][j]), s0.y), sw4.y, a.x);
-                            a.y = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[1][j + 1]), s1.y), sw4.y, a.y);
-                            a.x = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[2][j]), s0.z), sw4.z, a.x);
-                            a.y = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[2][j + 1]), s1.z), sw4.z, a.y);
-                            a.x = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[3][j]), s0.w), sw4.w, a.x);
-                            a.y = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[3][j + 1]), s1.w), sw4.w, a.y);
-                            acc[(c + j) >> 1] = a;
-                        }
-                        continue;
-                    }
+                        for (int u = 0; u < LB; ++u)
+                            if (s0 + u < ns) {
 #pragma unroll
-                    for (int j = 0; j < 8; j += 2) {
-                        const float4 s0 = sa4[c + j], s1 = sa4[c + j + 1];
-                        float2 a = acc[(c + j) >> 1];
-                        float2 t;
-                        t = __fmul2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[0][j]), __int2float_rn((int)r[0][j + 1])),
-                                                  make_float2(s0.x, s1.x)), w0);
-                        a.x = __fadd_rn(a.x, t.x); a.y = __fadd_rn(a.y, t.y);
-                        t = __fmul2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[1][j]), __int2float_rn((int)r[1][j + 1])),
-                                                  make_float2(s0.y, s1.y)), w1);
-                        a.x = __fadd_rn(a.x, t.x); a.y = __fadd_rn(a.y, t.y);
-                        t = __fmul2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[2][j]), __int2float_rn((int)r[2][j + 1])),
-                                                  make_float2(s0.z, s1.z)), w2);
-                        a.x = __fadd_rn(a.x, t.x); a.y = __fadd_rn(a.y, t.y);
-                        t = __fmul2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[3][j]), __int2float_rn((int)r[3][j + 1])),
-                                                  make_float2(s0.w, s1.w)), w3);
-                        a.x = __fadd_rn(a.x, t.x); a.y = __fadd_rn(a.y, t.y);
-                        acc[(c + j) >> 1] = a;
+                                for (int g = 0; g < 4; ++g)
+                                    tmem_ld8(lane_base + ring * C::BATCH_COLS + ((s0 + u) * 4 + g) * NB + j0 + c, r[u][g]);
+                            }
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int u = 0; u < LB; ++u)
+                            if (s0 + u < ns) add_stage_groups(acc, c, r[u], sa4[s0 + u], sw4[s0 + u], fuse);
                     }
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) {
                     mbar_arrive(smem_u32(&aux->tempty[ring]));
-                    mbar_arrive(smem_u32(&aux->empty[stage]));
+                    for (int sidx = 0; sidx < ns; ++sidx) {
+                        const int st = stage + sidx >= NST ? stage + sidx - NST : stage + sidx;
+                        mbar_arrive(smem_u32(&aux->empty[st]));
+                    }
                 }
                 if (++ring == C::RING) {
                     ring = 0;
                     rphase ^= 1;
                 }
-                if (++stage == NST) {
-                    stage = 0;
+                stage += ns;
+                if (stage >= NST) {
+                    stage -= NST;
                     phase ^= 1;
                 }
             }

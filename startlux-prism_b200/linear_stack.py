@@ -78,9 +78,10 @@ class LinearStack:
         self.s_max = tp.MAX_SPLIT if M <= tp.SPLIT_ROWS else 1
         self.slots = self.parts[:self.s_max * M * hidden].view(self.s_max, M, hidden)
         self.n_rows = torch.tensor([M], dtype=torch.int32, device=device)
-        # few rows: every GEMM is launched as a programmatic dependent of the quantizer before it (its weights start
-        # streaming while the quantizer still runs).  One row stays on the CUDA-core kernel, which has no such launch.
-        self.pdl = 1 < M <= w8a8.FEW_ROWS and os.environ.get("PRISM_B200_PDL", "1") != "0"
+        # few rows, PRISM_B200_PDL=1: every GEMM is launched as a programmatic dependent of the quantizer before it (its
+        # weights start streaming while the quantizer still runs).  Off by default: inside a replayed graph of the whole
+        # pass it measured level (0.369 against 0.363 ms at 16 rows).  One row stays on the CUDA-core kernel.
+        self.pdl = 1 < M <= w8a8.FEW_ROWS and os.environ.get("PRISM_B200_PDL", "0") == "1"
         # several ranks and many rows: the residual stream stays split by rows between the projections (each rank
         # folds, normalises and quantizes M / n rows), a row-parallel projection's int32 sums are reduce-scattered and
         # the int8 rows of the next projection's input all-gathered: 5/8 of an all-reduce's bytes, and 1 / n of the
