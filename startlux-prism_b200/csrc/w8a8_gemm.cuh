@@ -1014,25 +1014,27 @@ __device__ __forceinline__ void swap_store(const SwapArgs& p, int n, int m0, int
 //          a fused multiply-add, per group.
 __device__ __forceinline__ void add_stage_groups(float2* acc, int c, const uint32_t (&r)[4][8], const float4* sa4,
                                                  const float4 sw4, bool fuse) {
+    const float2 w0 = make_float2(sw4.x, sw4.x), w1 = make_float2(sw4.y, sw4.y), w2 = make_float2(sw4.z, sw4.z),
+                 w3 = make_float2(sw4.w, sw4.w);
     if (fuse) {
+        // two rows per instruction: one packed multiply and one packed fused multiply-add per group (each lane
+        // rounded as the scalar operation: the bits of fma(float(sum) * sa, sw, acc))
 #pragma unroll
         for (int j = 0; j < 8; j += 2) {
             const float4 s0 = sa4[c + j], s1 = sa4[c + j + 1];
             float2 a = acc[(c + j) >> 1];
-            a.x = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[0][j]), s0.x), sw4.x, a.x);
-            a.y = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[0][j + 1]), s1.x), sw4.x, a.y);
-            a.x = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[1][j]), s0.y), sw4.y, a.x);
-            a.y = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[1][j + 1]), s1.y), sw4.y, a.y);
-            a.x = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[2][j]), s0.z), sw4.z, a.x);
-            a.y = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[2][j + 1]), s1.z), sw4.z, a.y);
-            a.x = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[3][j]), s0.w), sw4.w, a.x);
-            a.y = __fmaf_rn(__fmul_rn(__int2float_rn((int)r[3][j + 1]), s1.w), sw4.w, a.y);
+            a = __ffma2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[0][j]), __int2float_rn((int)r[0][j + 1])),
+                                      make_float2(s0.x, s1.x)), w0, a);
+            a = __ffma2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[1][j]), __int2float_rn((int)r[1][j + 1])),
+                                      make_float2(s0.y, s1.y)), w1, a);
+            a = __ffma2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[2][j]), __int2float_rn((int)r[2][j + 1])),
+                                      make_float2(s0.z, s1.z)), w2, a);
+            a = __ffma2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[3][j]), __int2float_rn((int)r[3][j + 1])),
+                                      make_float2(s0.w, s1.w)), w3, a);
             acc[(c + j) >> 1] = a;
         }
         return;
     }
-    const float2 w0 = make_float2(sw4.x, sw4.x), w1 = make_float2(sw4.y, sw4.y), w2 = make_float2(sw4.z, sw4.z),
-                 w3 = make_float2(sw4.w, sw4.w);
 #pragma unroll
     for (int j = 0; j < 8; j += 2) {
         const float4 s0 = sa4[c + j], s1 = sa4[c + j + 1];

@@ -52,6 +52,17 @@ def rel_fro(got, ref):
     return float(np.linalg.norm(got.astype(np.float64) - ref) / np.linalg.norm(ref))
 
 
+def bf16_within_one_step(out, ref64):
+    """A bf16 output against the float64 product rounded to bf16 (round to nearest even): equal, or its neighbour (fp32
+    accumulation in another order can move a value across a rounding boundary).  The output's own rounding alone is
+    1.1e-3 relative Frobenius error, so the bound on the bf16 path is this one, not a Frobenius figure."""
+    want = torch.from_numpy(np.ascontiguousarray(ref64)).to(torch.bfloat16)
+    got = out.detach().cpu()
+    gi, wi = got.view(torch.int16).int(), want.view(torch.int16).int()
+    tiny = (got.float().abs() < 1e-30) & (want.float().abs() < 1e-30)
+    return bool((((gi - wi).abs() <= 1) | tiny).all())
+
+
 @pytest.mark.parametrize("M,N,K", [(32, 512, 256), (257, 1024, 512), (16, 5120, 5120), (300, 1000, 2560),
                                    (1024, 4096, 4096), (1024, 4808, 512), (1000, 4664, 768), (2048, 5120, 1024)])
 def test_gemm(dev, M, N, K):
@@ -63,7 +74,8 @@ def test_gemm(dev, M, N, K):
     out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
     mxfp4.gemm(q, s, wd, out, M, epi=0)
     err0 = rel_fro(out.float().cpu().numpy(), ref)
-    assert err0 < 3e-3, err0                              # bf16 rounding of the output dominates: ~2^-9 / sqrt(3)
+    assert err0 < 2e-3, err0                              # the reference's own bound; the output's bf16 rounding dominates
+    assert bf16_within_one_step(out, ref)                 # ... and every value is the rounded exact product or its neighbour
     h0 = torch.randn(M, N, generator=torch.Generator().manual_seed(1))
     h = h0.to(dev)
     mxfp4.gemm(q, s, wd, h, M, epi=1)
@@ -93,7 +105,7 @@ def test_gemm_k_split(dev, M, N, K):
         assert rel_fro(runs[0].cpu().numpy() - h0.numpy(), ref) < 1e-5, split
         out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
         mxfp4.gemm(q, s, wd, out, M, epi=0, split=split)
-        assert rel_fro(out.float().cpu().numpy(), ref) < 3e-3, split
+        assert rel_fro(out.float().cpu().numpy(), ref) < 2e-3, split
         assert int(counters.abs().sum()) == 0
 
 
@@ -118,15 +130,15 @@ def test_gemv_rows(dev, M, N, K):
     assert np.array_equal(got[M:], h0.numpy()[M:]) and np.array_equal(got[:, N:], h0.numpy()[:, N:])
     out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
     mxfp4.gemv(q, s, wd, out, M, epi=0)
-    assert rel_fro(out.float().cpu().numpy(), ref) < 3e-3
+    assert rel_fro(out.float().cpu().numpy(), ref) < 2e-3 and bf16_within_one_step(out, ref)
     if M == 1:                                            # split="auto" routes one row against few weight rows here
         auto = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
         mxfp4.gemm(q, s, wd, auto, M, epi=0, split="auto")
-        assert rel_fro(auto.float().cpu().numpy(), ref) < 3e-3
+        assert rel_fro(auto.float().cpu().numpy(), ref) < 2e-3
     # and close to the tensor-core kernel's bits: the same exact block products, another order of fp32 additions
     out_tc = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
     mxfp4.gemm(q, s, wd, out_tc, M, epi=0)
-    assert rel_fro(out.float().cpu().numpy(), out_tc.float().cpu().numpy().astype(np.float64)) < 3e-3
+    assert rel_fro(out.float().cpu().numpy(), out_tc.float().cpu().numpy().astype(np.float64)) < 2e-3
 
 
 def test_gemm_fp32_path_tight(dev):
