@@ -107,3 +107,30 @@ def test_real_ranks_bit_identical(dev, tmp_path, rows, extra, env_extra):
               out, str(rows)] + extra, env)
         got = torch.load(out)
         assert torch.equal(got.view(torch.int32), want.view(torch.int32)), f"{world} ranks differ from one GPU"
+
+
+def test_two_devices_in_one_process(dev):
+    """One process driving two GPUs: kernels that need more than 48 KB of shared memory must be opted in on EACH
+    device (the opt-in, the SM count and the occupancy answers are kept per device ordinal), and the static-scratch
+    entry point must look its array up on each device.  Same inputs on cuda:0 and cuda:1: the same bits."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 or more GPUs")
+    from prism_b200 import _lib
+    outs = []
+    for d in (0, 1, 0):
+        device = torch.device("cuda", d)
+        with torch.cuda.device(device):
+            for (M, N, K) in ((300, 1024, 2560), (16, 5120, 5120)):          # tile kernel, few-rows kernel with K split
+                a, w, sa, sw = rand_w8a8(M, N, K, seed=M)
+                out = torch.zeros(M, N, dtype=torch.bfloat16, device=device)
+                w8a8.gemm(a.to(device), sa.to(device).view(-1), w.to(device), sw.to(device).view(-1), out,
+                          n_rows(M, device), K)
+                res = torch.randn(M, N, generator=torch.Generator().manual_seed(1)).to(device)
+                w8a8.gemm(a.to(device), sa.to(device).view(-1), w.to(device), sw.to(device).view(-1), res,
+                          n_rows(M, device), K, epi=1)
+                torch.cuda.synchronize(device)
+                assert _lib.device_status()[0] == 0
+                outs.append((d, M, out.cpu(), res.cpu()))
+    ref = {(M): (o, r) for d, M, o, r in outs if d == 0}
+    for d, M, o, r in outs:
+        assert torch.equal(o.view(torch.int16), ref[M][0].view(torch.int16)) and torch.equal(r, ref[M][1]), (d, M)
