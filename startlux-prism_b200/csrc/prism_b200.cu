@@ -320,10 +320,11 @@ int launch_pair(const int8_t* a, const float* a_s, const int8_t* w, const float*
     return PB_OK;
 }
 
-template <int NB, bool GROUPED>
+template <int NB, bool GROUPED, int RW = 0>
 int launch_swap(const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, w8a8::SwapArgs p, int split,
                 cudaStream_t st) {
     using C = w8a8::SwapCfg<NB, GROUPED>;
+    constexpr int RCTA = RW ? 2 * RW : NB;                         // activation rows per CTA
     CUtensorMap tw, tx, tsw, tsa;
     int rc;
     // per-32 groups in one K slice: PRISM_B200_WROWS = 64 / 32 gives every CTA fewer weight rows (more CTAs when the
@@ -346,9 +347,9 @@ int launch_swap(const int8_t* a, const float* a_s, const int8_t* w, const float*
         tsw = tw;
         tsa = tx;
     }
-    auto kern = w8a8::w8a8_swap_kernel<NB, GROUPED>;
+    auto kern = w8a8::w8a8_swap_kernel<NB, GROUPED, RW>;
     if ((rc = set_smem(kern, C::smem_bytes(C::STAGES_DEEP)))) return rc;
-    dim3 grid((p.N + wrows - 1) / wrows, split, (p.M + NB - 1) / NB);
+    dim3 grid((p.N + wrows - 1) / wrows, split, (p.M + RCTA - 1) / RCTA);
     // a grid no larger than the SM count gets one CTA per SM and the deepest pipeline; a larger one two CTAs per SM
     // (per-32 groups: the accumulator slots fill the SM's tensor memory, so one CTA per SM at any grid size)
     p.stages = (GROUPED || (long)grid.x * grid.y * grid.z <= sm_count()) ? C::STAGES_DEEP : C::STAGES;
@@ -372,9 +373,27 @@ int launch_swap(const int8_t* a, const float* a_s, const int8_t* w, const float*
     return PB_OK;
 }
 
+// Per-32 groups, up to 16 rows, one K slice, fewer weight tiles than SMs: how many activation rows a CTA owns (16, 8 or
+// 4).  Fewer rows per CTA = more CTAs on one weight tile, i.e. the per-group fp32 arithmetic (what bounds this kernel:
+// ncu shows the fp32 pipe saturated on the SMs in use) spread over more SMs; the smallest count whose grid still
+// fits the SMs at once.  PRISM_B200_GROWS forces 16 / 8 / 4.
+int grouped_rows_per_cta(int M, int N) {
+    static const int forced = [] { const char* e = getenv("PRISM_B200_GROWS"); return e ? atoi(e) : 0; }();
+    if (forced == 16 || forced == 8 || forced == 4) return forced;
+    const long tiles = (N + 127) / 128, cap = sm_count() + sm_count() / 10;
+    for (int r : {4, 8})
+        if (M > r && tiles * ((M + r - 1) / r) <= cap) return r;
+    return 16;
+}
+
 template <bool GROUPED>
 int launch_swap_nb(int nb, const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, w8a8::SwapArgs p,
                    int split, cudaStream_t st) {
+    if constexpr (GROUPED) if (nb == 16 && split == 1) {
+        const int r = grouped_rows_per_cta(p.M, p.N);
+        if (r == 4) return launch_swap<16, GROUPED, 2>(a, a_s, w, w_s, p, split, st);
+        if (r == 8) return launch_swap<16, GROUPED, 4>(a, a_s, w, w_s, p, split, st);
+    }
     switch (nb) {
         case 16: return launch_swap<16, GROUPED>(a, a_s, w, w_s, p, split, st);
         case 32: return launch_swap<32, GROUPED>(a, a_s, w, w_s, p, split, st);

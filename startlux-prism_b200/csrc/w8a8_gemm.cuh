@@ -1003,7 +1003,7 @@ __device__ __forceinline__ void swap_store(const SwapArgs& p, int n, int m0, int
     }
 }
 
-// One K stage's four scale groups of eight activation rows (c .. c + 7 of this warp's rows), added to the rows' fp32 sums
+// One K stage's four scale groups of CH (2, 4 or 8) activation rows (c .. c + CH - 1 of this warp's rows), added to the rows' fp32 sums
 // in ascending group order.  r[g][j]: the int32 sum of group g and row c + j; sa4[row]: the row's four activation scales
 // of this stage; sw4: this thread's weight row's four scales.
 //   plain: (float(sum) * sa) * sw, each product rounded (two rows per packed multiply), then a scalar add_rn.  The adds
@@ -1012,7 +1012,8 @@ __device__ __forceinline__ void swap_store(const SwapArgs& p, int n, int m0, int
 //   fuse:  the vocabulary head - the reference's kernel writes `acc += (ai * sa) * sw` without explicit roundings
 //          (kernels/decode.py:157) and its compiler fuses the second multiply with the add: one rounded product, then
 //          a fused multiply-add, per group.
-__device__ __forceinline__ void add_stage_groups(float2* acc, int c, const uint32_t (&r)[4][8], const float4* sa4,
+template <int CH>
+__device__ __forceinline__ void add_stage_groups(float2* acc, int c, const uint32_t (&r)[4][CH], const float4* sa4,
                                                  const float4 sw4, bool fuse) {
     const float2 w0 = make_float2(sw4.x, sw4.x), w1 = make_float2(sw4.y, sw4.y), w2 = make_float2(sw4.z, sw4.z),
                  w3 = make_float2(sw4.w, sw4.w);
@@ -1020,7 +1021,7 @@ __device__ __forceinline__ void add_stage_groups(float2* acc, int c, const uint3
         // two rows per instruction: one packed multiply and one packed fused multiply-add per group (each lane
         // rounded as the scalar operation: the bits of fma(float(sum) * sa, sw, acc))
 #pragma unroll
-        for (int j = 0; j < 8; j += 2) {
+        for (int j = 0; j < CH; j += 2) {
             const float4 s0 = sa4[c + j], s1 = sa4[c + j + 1];
             float2 a = acc[(c + j) >> 1];
             a = __ffma2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[0][j]), __int2float_rn((int)r[0][j + 1])),
@@ -1036,7 +1037,7 @@ __device__ __forceinline__ void add_stage_groups(float2* acc, int c, const uint3
         return;
     }
 #pragma unroll
-    for (int j = 0; j < 8; j += 2) {
+    for (int j = 0; j < CH; j += 2) {
         const float4 s0 = sa4[c + j], s1 = sa4[c + j + 1];
         float2 a = acc[(c + j) >> 1];
         float2 t;
@@ -1056,7 +1057,10 @@ __device__ __forceinline__ void add_stage_groups(float2* acc, int c, const uint3
     }
 }
 
-template <int NB, bool GROUPED>
+// RW > 0 (per-32 groups, NB = 16 only): the CTA owns 2 * RW activation rows (4 or 8) instead of NB - the MMA still spans
+// NB rows (its minimum), the epilogue warps take RW rows each.  More CTAs share one weight tile (re-read from L2), so
+// the per-group fp32 arithmetic of a short batch spreads over more SMs when the weight tiles are fewer than the SMs.
+template <int NB, bool GROUPED, int RW = 0>
 __global__ void __launch_bounds__(SwapCfg<NB, GROUPED>::THREADS, 1)
 w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                  const __grid_constant__ CUtensorMap tm_sw, const __grid_constant__ CUtensorMap tm_sa,
@@ -1071,7 +1075,8 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
     int live = *p.n_rows;
     live = live < p.M ? live : p.M;
     const int WR = (GROUPED && p.wrows > 0) ? p.wrows : BM;     // weight rows this CTA owns
-    const int n0 = blockIdx.x * WR, m0 = blockIdx.z * NB, z = blockIdx.y;
+    constexpr int RCTA = RW ? 2 * RW : NB;                     // activation rows this CTA owns
+    const int n0 = blockIdx.x * WR, m0 = blockIdx.z * RCTA, z = blockIdx.y;
     if (m0 >= live) return;                                    // whole CTA, before any barrier or allocation
     const int KB = (p.K + BK - 1) / BK;
     const int kb0 = z * p.kb_per_split;
@@ -1223,7 +1228,8 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
         if (GROUPED) {
             const bool active = q * 32 < WR;                   // warp-uniform: does this lane quarter hold weight rows?
             // NH activation rows per warp: all NB with four epilogue warps, half of them with eight (two per lane quarter)
-            constexpr int NH = C::EPI_WARPS == 8 ? NB / 2 : NB;
+            constexpr int NH = RW ? RW : (C::EPI_WARPS == 8 ? NB / 2 : NB);
+            constexpr int CH = NH < 8 ? NH : 8;                     // rows per tensor-memory load
             const int j0 = C::EPI_WARPS == 8 ? ((warp - 2) >> 2) * NH : 0;
             float2 acc[NH / 2];                                     // rows (j0 + 2i, j0 + 2i + 1)
 #pragma unroll
@@ -1268,25 +1274,25 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                 }
                 if (!ok) break;
 #pragma unroll
-                for (int c = 0; c < NH; c += 8) {
-                    if (!active || m0 + j0 + c >= live) break;     // no weight rows here, or these eight rows are not live
+                for (int c = 0; c < NH; c += CH) {
+                    if (!active || m0 + j0 + c >= live) break;     // no weight rows here, or these rows are not live
                     // two stages' loads (eight of them) are in flight before each wait
                     constexpr int LB = C::SUPER >= 2 ? 2 : 1;
 #pragma unroll
                     for (int s0 = 0; s0 < C::SUPER; s0 += LB) {
                         if (s0 >= ns) break;
-                        uint32_t r[LB][4][8];
+                        uint32_t r[LB][4][CH];
 #pragma unroll
                         for (int u = 0; u < LB; ++u)
                             if (s0 + u < ns) {
 #pragma unroll
                                 for (int g = 0; g < 4; ++g)
-                                    tmem_ld8(lane_base + ring * C::BATCH_COLS + ((s0 + u) * 4 + g) * NB + j0 + c, r[u][g]);
+                                    tmem_ldn(lane_base + ring * C::BATCH_COLS + ((s0 + u) * 4 + g) * NB + j0 + c, r[u][g]);
                             }
                         tmem_ld_wait();
 #pragma unroll
                         for (int u = 0; u < LB; ++u)
-                            if (s0 + u < ns) add_stage_groups(acc, c, r[u], sa4[s0 + u], sw4[s0 + u], fuse);
+                            if (s0 + u < ns) add_stage_groups<CH>(acc, c, r[u], sa4[s0 + u], sw4[s0 + u], fuse);
                     }
                 }
                 tc_fence_before();
