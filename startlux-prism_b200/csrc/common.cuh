@@ -88,9 +88,10 @@ __device__ __forceinline__ bool mbar_test_sleep(uint32_t bar, uint32_t parity, u
 #define PB_SLEEP_NS 2000u
 #endif
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned where) {
+    if (mbar_test(bar, parity)) return true;             // already complete: the cheapest form of the test
 #pragma unroll 1
     for (int i = 0; i < 4096; ++i)                       // the common case: no clock read, no flag read
-        if (mbar_test_sleep(bar, parity, PB_SLEEP_NS)) return true;
+        if (PB_SLEEP_NS ? mbar_test_sleep(bar, parity, PB_SLEEP_NS) : mbar_test(bar, parity)) return true;
     unsigned long long t0 = global_timer_ns();
     for (unsigned it = 1;; ++it) {
         if (mbar_test(bar, parity)) return true;

@@ -15,6 +15,7 @@
 #include "quant_pipe.cuh"
 #include "w8a8_gemm.cuh"
 #include "w8a8_groups.cuh"
+#include "w8a8_g32.cuh"
 #include "w4a8_gemm.cuh"
 #include "w4a8_few.cuh"
 #include "w4a8_gemv.cuh"
@@ -104,6 +105,39 @@ int tensor_map(CUtensorMap* out, const void* ptr, uint64_t inner, uint64_t outer
                     const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     (kind == 0 || kind == 4) ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        g_last_cuda_error = (int)r;
+        return PB_CUDA_ERROR;
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache.size() > 8192) cache.clear();
+    cache[key] = *out;
+    return PB_OK;
+}
+
+// An int8 matrix [rows, K] (K a multiple of 128) as {128 bytes, rows, K / 128 chunks}: a box of {128, box_rows, 2} is
+// 256 bytes of K for box_rows rows, laid down as two 128-byte-swizzled tiles one after the other.
+int tensor_map_kchunks(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t K, uint32_t box_rows) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapHash> cache;
+    MapKey key{ptr, K, rows, K, 128, box_rows, 100};
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) {
+            *out = it->second;
+            return PB_OK;
+        }
+    }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return PB_CUDA_ERROR;
+    cuuint64_t dims[3] = {128, rows, K / 128};
+    cuuint64_t strides[2] = {K, 128};
+    cuuint32_t box[3] = {128, box_rows, 2};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         g_last_cuda_error = (int)r;
         return PB_CUDA_ERROR;
@@ -380,15 +414,58 @@ int launch_swap(const int8_t* a, const float* a_s, const int8_t* w, const float*
 int grouped_rows_per_cta(int M, int N) {
     static const int forced = [] { const char* e = getenv("PRISM_B200_GROWS"); return e ? atoi(e) : 0; }();
     if (forced == 16 || forced == 8 || forced == 4) return forced;
-    const long tiles = (N + 127) / 128, cap = sm_count() + sm_count() / 10;
+    const long tiles = (N + 127) / 128, cap = sm_count();     // one wave: a CTA takes a whole SM
     for (int r : {4, 8})
         if (M > r && tiles * ((M + r - 1) / r) <= cap) return r;
     return 16;
 }
 
+// Per-32 groups, one K slice (w8a8_g32.cuh): row blocks of 16, 8 or 4 per CTA.
+template <int RW>
+int launch_g32(const int8_t* a, const int8_t* w, w8a8::SwapArgs p, cudaStream_t st) {
+    using C = w8a8::G32;
+    constexpr int RCTA = 2 * RW;
+    CUtensorMap tw, tx;
+    int rc;
+    if ((rc = tensor_map_kchunks(&tw, w, p.N, p.K, w8a8::BM))) return rc;
+    if ((rc = tensor_map_kchunks(&tx, a, p.M, p.K, C::NB))) return rc;
+    p.stages = C::stages_for(p.K, RCTA);
+    const int smem = C::smem_bytes(p.K, RCTA, p.stages);
+    auto kern = w8a8::w8a8_g32_kernel<RW>;
+    if ((rc = set_smem(kern, 232448))) return rc;
+    dim3 grid((p.N + w8a8::BM - 1) / w8a8::BM, 1, (p.M + RCTA - 1) / RCTA);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(C::THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = p.pdl ? 1 : 0;
+    PB_CUDA(cudaLaunchKernelEx(&cfg, kern, tw, tx, p));
+    return PB_OK;
+}
+
+// Can w8a8_g32_kernel take the call?  One K slice, a direct store, and room for at least three stages beside the
+// activation scales (K up to about 80 k).  PRISM_B200_G32=0 keeps the older kernel (for comparisons).
+bool g32_takes(const w8a8::SwapArgs& p, int split) {
+    static const bool on = [] { const char* e = getenv("PRISM_B200_G32"); return !(e && e[0] == '0'); }();
+    return on && split == 1 && p.mode == w8a8::MODE_DIRECT && p.wrows == 0 && p.K % 128 == 0 &&
+           (p.epi == w8a8::EPI_BF16 || p.epi == w8a8::EPI_ADD || p.epi == w8a8::EPI_F32) &&
+           w8a8::G32::stages_for(p.K, 16) >= 3;
+}
+
 template <bool GROUPED>
 int launch_swap_nb(int nb, const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, w8a8::SwapArgs p,
                    int split, cudaStream_t st) {
+    if constexpr (GROUPED) if (g32_takes(p, split)) {
+        const int r = p.M <= 16 ? grouped_rows_per_cta(p.M, p.N) : 16;
+        if (r == 4) return launch_g32<2>(a, w, p, st);
+        if (r == 8) return launch_g32<4>(a, w, p, st);
+        return launch_g32<8>(a, w, p, st);
+    }
     if constexpr (GROUPED) if (nb == 16 && split == 1) {
         const int r = grouped_rows_per_cta(p.M, p.N);
         if (r == 4) return launch_swap<16, GROUPED, 2>(a, a_s, w, w_s, p, split, st);

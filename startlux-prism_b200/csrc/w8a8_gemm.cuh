@@ -1004,17 +1004,25 @@ __device__ __forceinline__ void swap_store(const SwapArgs& p, int n, int m0, int
 }
 
 // One K stage's four scale groups of CH (2, 4 or 8) activation rows (c .. c + CH - 1 of this warp's rows), added to the rows' fp32 sums
-// in ascending group order.  r[g][j]: the int32 sum of group g and row c + j; sa4[row]: the row's four activation scales
-// of this stage; sw4: this thread's weight row's four scales.
+// in ascending group order.  r[g][j]: the int32 sum of group g and row c + j; sa4[row * stride]: the row's four
+// activation scales of this stage; sw4: this thread's weight row's four scales.
 //   plain: (float(sum) * sa) * sw, each product rounded (two rows per packed multiply), then a scalar add_rn.  The adds
 //          stay scalar on purpose: the assembler contracts a packed multiply followed by a packed add into one fused
 //          multiply-add (measured: 15 % of results change), which would break the reference's two-rounding contract.
 //   fuse:  the vocabulary head - the reference's kernel writes `acc += (ai * sa) * sw` without explicit roundings
 //          (kernels/decode.py:157) and its compiler fuses the second multiply with the add: one rounded product, then
 //          a fused multiply-add, per group.
+// Two int32 group sums as floats.  A sum of 32 products of int8 values is below 2^19 in magnitude, so adding it to the
+// bit pattern of 1.5 * 2^23 and subtracting that constant gives exactly float(sum): one integer add each and one packed
+// fp32 add for the pair, instead of two conversions on the slower conversion unit.
+__device__ __forceinline__ float2 float2_of(uint32_t a, uint32_t b) {
+    return __fadd2_rn(make_float2(__uint_as_float(0x4B400000u + a), __uint_as_float(0x4B400000u + b)),
+                      make_float2(-12582912.0f, -12582912.0f));
+}
+
 template <int CH>
 __device__ __forceinline__ void add_stage_groups(float2* acc, int c, const uint32_t (&r)[4][CH], const float4* sa4,
-                                                 const float4 sw4, bool fuse) {
+                                                 int stride, const float4 sw4, bool fuse) {
     const float2 w0 = make_float2(sw4.x, sw4.x), w1 = make_float2(sw4.y, sw4.y), w2 = make_float2(sw4.z, sw4.z),
                  w3 = make_float2(sw4.w, sw4.w);
     if (fuse) {
@@ -1022,15 +1030,15 @@ __device__ __forceinline__ void add_stage_groups(float2* acc, int c, const uint3
         // rounded as the scalar operation: the bits of fma(float(sum) * sa, sw, acc))
 #pragma unroll
         for (int j = 0; j < CH; j += 2) {
-            const float4 s0 = sa4[c + j], s1 = sa4[c + j + 1];
+            const float4 s0 = sa4[(c + j) * stride], s1 = sa4[(c + j + 1) * stride];
             float2 a = acc[(c + j) >> 1];
-            a = __ffma2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[0][j]), __int2float_rn((int)r[0][j + 1])),
+            a = __ffma2_rn(__fmul2_rn(float2_of(r[0][j], r[0][j + 1]),
                                       make_float2(s0.x, s1.x)), w0, a);
-            a = __ffma2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[1][j]), __int2float_rn((int)r[1][j + 1])),
+            a = __ffma2_rn(__fmul2_rn(float2_of(r[1][j], r[1][j + 1]),
                                       make_float2(s0.y, s1.y)), w1, a);
-            a = __ffma2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[2][j]), __int2float_rn((int)r[2][j + 1])),
+            a = __ffma2_rn(__fmul2_rn(float2_of(r[2][j], r[2][j + 1]),
                                       make_float2(s0.z, s1.z)), w2, a);
-            a = __ffma2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[3][j]), __int2float_rn((int)r[3][j + 1])),
+            a = __ffma2_rn(__fmul2_rn(float2_of(r[3][j], r[3][j + 1]),
                                       make_float2(s0.w, s1.w)), w3, a);
             acc[(c + j) >> 1] = a;
         }
@@ -1038,19 +1046,19 @@ __device__ __forceinline__ void add_stage_groups(float2* acc, int c, const uint3
     }
 #pragma unroll
     for (int j = 0; j < CH; j += 2) {
-        const float4 s0 = sa4[c + j], s1 = sa4[c + j + 1];
+        const float4 s0 = sa4[(c + j) * stride], s1 = sa4[(c + j + 1) * stride];
         float2 a = acc[(c + j) >> 1];
         float2 t;
-        t = __fmul2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[0][j]), __int2float_rn((int)r[0][j + 1])),
+        t = __fmul2_rn(__fmul2_rn(float2_of(r[0][j], r[0][j + 1]),
                                   make_float2(s0.x, s1.x)), w0);
         a.x = __fadd_rn(a.x, t.x); a.y = __fadd_rn(a.y, t.y);
-        t = __fmul2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[1][j]), __int2float_rn((int)r[1][j + 1])),
+        t = __fmul2_rn(__fmul2_rn(float2_of(r[1][j], r[1][j + 1]),
                                   make_float2(s0.y, s1.y)), w1);
         a.x = __fadd_rn(a.x, t.x); a.y = __fadd_rn(a.y, t.y);
-        t = __fmul2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[2][j]), __int2float_rn((int)r[2][j + 1])),
+        t = __fmul2_rn(__fmul2_rn(float2_of(r[2][j], r[2][j + 1]),
                                   make_float2(s0.z, s1.z)), w2);
         a.x = __fadd_rn(a.x, t.x); a.y = __fadd_rn(a.y, t.y);
-        t = __fmul2_rn(__fmul2_rn(make_float2(__int2float_rn((int)r[3][j]), __int2float_rn((int)r[3][j + 1])),
+        t = __fmul2_rn(__fmul2_rn(float2_of(r[3][j], r[3][j + 1]),
                                   make_float2(s0.w, s1.w)), w3);
         a.x = __fadd_rn(a.x, t.x); a.y = __fadd_rn(a.y, t.y);
         acc[(c + j) >> 1] = a;
@@ -1237,22 +1245,35 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
             int stage = 0, ring = 0;
             uint32_t phase = 0, rphase = 0;
             bool ok = true;
-            // this thread's weight row: four group scales (16 bytes) per stage, read straight from global memory one
-            // slot ahead (a tensor-map box of 128 rows x 16 bytes costs the TMA unit a request per row)
+            // this thread's weight row: four group scales (16 bytes) per stage, read straight from global memory (a
+            // tensor-map box of 128 rows x 16 bytes costs the TMA unit a request per row)
             const float4* swp = (const float4*)(p.w_s + (long)(n < p.N ? n : 0) * (p.K >> 5)) + kb0;
-            float4 sw_ahead[C::SUPER];
+            // The row's scales of this CTA's whole K range go to L2 now (16 bytes per stage, rows K / 8 bytes apart: a
+            // scattered read whose DRAM latency, met once per slot, was the kernel's whole time), and the loads below run
+            // AHEAD stages in front of their use, so that what they meet is an L2 hit with several slots to land.
+            if (active) {
+                const int part = C::EPI_WARPS == 8 ? (warp - 2) >> 2 : 0, parts = C::EPI_WARPS == 8 ? 2 : 1;
+                const char* row = (const char*)swp;
+                for (int off = part * 128; off < nkb * 16; off += parts * 128)
+                    asm volatile("prefetch.global.L2 [%0];" ::"l"(row + off));
+                if (part == 0 && nkb > 0) asm volatile("prefetch.global.L2 [%0];" ::"l"(row + nkb * 16 - 16));
+            }
+            constexpr int AHEAD = C::SUPER > 4 ? C::SUPER : 4;
+            float4 sw_ahead[AHEAD];
 #pragma unroll
-            for (int sidx = 0; sidx < C::SUPER; ++sidx)
+            for (int sidx = 0; sidx < AHEAD; ++sidx)
                 sw_ahead[sidx] = sidx < nkb ? __ldg(swp + sidx) : make_float4(0.f, 0.f, 0.f, 0.f);
             const bool fuse = p.epi == EPI_F32;
             for (int i0 = 0; i0 < nkb && ok; i0 += C::SUPER) {
                 const int ns = nkb - i0 < C::SUPER ? nkb - i0 : C::SUPER;      // K stages in this slot
                 float4 sw4[C::SUPER];
 #pragma unroll
-                for (int sidx = 0; sidx < C::SUPER; ++sidx) {
-                    sw4[sidx] = sw_ahead[sidx];
-                    if (i0 + C::SUPER + sidx < nkb) sw_ahead[sidx] = __ldg(swp + i0 + C::SUPER + sidx);
-                }
+                for (int sidx = 0; sidx < C::SUPER; ++sidx) sw4[sidx] = sw_ahead[sidx];
+#pragma unroll
+                for (int sidx = 0; sidx + C::SUPER < AHEAD; ++sidx) sw_ahead[sidx] = sw_ahead[sidx + C::SUPER];
+#pragma unroll
+                for (int sidx = 0; sidx < C::SUPER; ++sidx)
+                    if (i0 + AHEAD + sidx < nkb) sw_ahead[AHEAD - C::SUPER + sidx] = __ldg(swp + i0 + AHEAD + sidx);
                 if (!mbar_wait(smem_u32(&aux->tfull[ring]), rphase, abort_flag, 0x800 + ring)) {
                     ok = false;
                     break;
@@ -1292,7 +1313,7 @@ w8a8_swap_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant
                         tmem_ld_wait();
 #pragma unroll
                         for (int u = 0; u < LB; ++u)
-                            if (s0 + u < ns) add_stage_groups<CH>(acc, c, r[u], sa4[s0 + u], sw4[s0 + u], fuse);
+                            if (s0 + u < ns) add_stage_groups<CH>(acc, c, r[u], sa4[s0 + u], 1, sw4[s0 + u], fuse);
                     }
                 }
                 tc_fence_before();

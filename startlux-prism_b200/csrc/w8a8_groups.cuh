@@ -145,6 +145,10 @@ w8a8_groups_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 #pragma unroll
         for (int j = 0; j < NB; ++j) acc[j] = 0.0f;
         const float* swp = p.w_s + (long)(n < p.N ? n : 0) * G;
+        // the row's scales go to L2 now: the loads below, one group ahead of their use, then meet an L2 hit and not a
+        // scattered DRAM read per group
+        for (int off = 0; off < G * 4; off += 128) asm volatile("prefetch.global.L2 [%0];" ::"l"((const char*)swp + off));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"((const char*)swp + G * 4 - 4));
         float sw_next = __ldg(swp);
         int ring = 0;
         uint32_t rphase = 0;
