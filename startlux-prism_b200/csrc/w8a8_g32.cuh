@@ -61,6 +61,75 @@ __device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const CUtensorMap
         : : "r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar), "l"(policy) : "memory");
 }
 
+// Packed fp32 pairs with the rounding written out (an operation with an explicit rounding mode is never contracted
+// into a fused multiply-add): two rows of one output column per instruction.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+    return d;
+}
+__device__ __forceinline__ float2 unpack2(f32x2 v) {
+    float2 d;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(v));
+    return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {          // never directly on a packed product (see add_quad)
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+// Two int32 group sums as a packed pair of floats: |sum| < 2^19, so the sum added to the bit pattern of 1.5 * 2^23
+// minus that constant is exactly float(sum) (two integer adds and one packed add instead of two conversions).
+__device__ __forceinline__ f32x2 pair_of(uint32_t a, uint32_t b) {
+    f32x2 biased;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(biased) : "r"(0x4B400000u + a), "r"(0x4B400000u + b));
+    return add2(biased, pack2(-12582912.0f, -12582912.0f));
+}
+
+// One quad (four groups, 128 bytes of K) of RW activation rows added to the rows' fp32 sums in group order.
+// r[g][j]: int32 sum of group g and row j; sa: the quad's activation scales as row pairs, float2 [RW / 2 pairs at
+// `stride` float4s apart][4 groups] = (row 2i, row 2i + 1) per group; sw4: this thread's weight row's four scales.
+// plain: acc = add_rn(acc, mul_rn(mul_rn(float(sum), sa), sw)); fuse (the vocabulary head, whose reference kernel
+// leaves the roundings to its compiler, kernels/decode.py:157): acc = fma_rn(mul_rn(float(sum), sa), sw, acc).
+template <int RW>
+__device__ __forceinline__ void add_quad(f32x2* acc, const uint32_t (&r)[4][RW], const float4* sa, int stride,
+                                         const float4 sw4, bool fuse) {
+    const f32x2 w[4] = {pack2(sw4.x, sw4.x), pack2(sw4.y, sw4.y), pack2(sw4.z, sw4.z), pack2(sw4.w, sw4.w)};
+#pragma unroll
+    for (int i = 0; i < RW / 2; ++i) {
+        const float4 s01 = sa[i * stride], s23 = sa[i * stride + 1];     // groups 0,1 and 2,3 of rows (2i, 2i + 1)
+        const f32x2 s[4] = {pack2(s01.x, s01.y), pack2(s01.z, s01.w), pack2(s23.x, s23.y), pack2(s23.z, s23.w)};
+        f32x2 a = acc[i];
+        if (fuse) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) a = fma2(mul2(pair_of(r[g][2 * i], r[g][2 * i + 1]), s[g]), w[g], a);
+        } else {
+            // the adds stay scalar: the assembler contracts a packed multiply followed by a packed add into a fused
+            // multiply-add even with the roundings written out (measured: a few results in a thousand change)
+            float2 f = unpack2(a);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+                const float2 t = unpack2(mul2(mul2(pair_of(r[g][2 * i], r[g][2 * i + 1]), s[g]), w[g]));
+                f.x = __fadd_rn(f.x, t.x);
+                f.y = __fadd_rn(f.y, t.y);
+            }
+            a = pack2(f.x, f.y);
+        }
+        acc[i] = a;
+    }
+}
+
 // tm_w: weights [N, K] as {128, N, K / 128} with box {128, 128, 2}; tm_x: activations [M, K] the same way with box
 // {128, 16, 2}.  p: a_s [M, K / 32], w_s [N, K / 32], out, ldo, n_rows, M, N, K (a multiple of 128), epi (bf16, fp32 add
 // or fp32), pdl, stages.  Grid (N / 128 tiles, 1, row blocks of 2 * RW).
@@ -74,7 +143,7 @@ w8a8_g32_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
     const int NST = p.stages;
     const int KC = p.K / BK;                                   // quads = 128-byte chunks of K
     const int QP = C::padded_quads(p.K);
-    float4* sa = (float4*)(smem + NST * C::STAGE_BYTES);       // [RCTA][QP]
+    float4* sa = (float4*)(smem + NST * C::STAGE_BYTES);       // float2 [RCTA / 2 row pairs][QP quads][4 groups]
     Aux* aux = (Aux*)((uint8_t*)sa + C::sa_bytes(p.K, RCTA));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -211,17 +280,23 @@ w8a8_g32_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         // the CTA's activation scales: a_s rows m0 .. m0 + RCTA - 1, one float4 per quad, read once
         {
             const int e = threadIdx.x - 32 * C::FIRST_EPI_WARP;
+            float* saf = (float*)sa;
             for (int idx = e; idx < RCTA * KC; idx += 32 * C::EPI_WARPS) {
                 const int row = idx / KC, qd = idx - row * KC;
                 const int m = m0 + row;
-                sa[row * QP + qd] = m < live ? __ldg((const float4*)(p.a_s + (long)m * G) + qd)
-                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+                const float4 v = m < live ? __ldg((const float4*)(p.a_s + (long)m * G) + qd)
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+                float* dst = saf + (((row >> 1) * QP + qd) * 4) * 2 + (row & 1);
+                dst[0] = v.x;
+                dst[2] = v.y;
+                dst[4] = v.z;
+                dst[6] = v.w;
             }
             asm volatile("bar.sync 1, %0;" ::"n"(32 * C::EPI_WARPS) : "memory");
         }
-        float2 acc[RW / 2];
+        f32x2 acc[RW / 2];                                     // rows (j0 + 2i, j0 + 2i + 1)
 #pragma unroll
-        for (int j = 0; j < RW / 2; ++j) acc[j] = make_float2(0.0f, 0.0f);
+        for (int j = 0; j < RW / 2; ++j) acc[j] = pack2(0.0f, 0.0f);
         const bool fuse = p.epi == EPI_F32;
         const bool mine = m0 + j0 < live;                      // warp-uniform: does this warp hold live rows?
         int ring = 0;
@@ -242,7 +317,7 @@ w8a8_g32_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             }
             tc_fence_after();
             if (mine) {
-                const float4* sa_slot = sa + j0 * QP + slot * C::SLOT_QUADS;
+                const float4* sa_slot = sa + ((j0 >> 1) * QP + slot * C::SLOT_QUADS) * 2;
 #pragma unroll
                 for (int b0 = 0; b0 < C::SLOT_QUADS; b0 += 2) {
                     if (b0 >= nq) break;
@@ -257,7 +332,7 @@ w8a8_g32_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                     tmem_ld_wait();
 #pragma unroll
                     for (int u = 0; u < 2; ++u)
-                        if (b0 + u < nq) add_stage_groups<RW>(acc, 0, r[u], sa_slot + b0 + u, QP, sw4[b0 + u], fuse);
+                        if (b0 + u < nq) add_quad<RW>(acc, r[u], sa_slot + (b0 + u) * 2, QP * 2, sw4[b0 + u], fuse);
                 }
             }
             tc_fence_before();
@@ -272,8 +347,9 @@ w8a8_g32_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             float v[RW];
 #pragma unroll
             for (int j = 0; j < RW / 2; ++j) {
-                v[2 * j] = acc[j].x;
-                v[2 * j + 1] = acc[j].y;
+                const float2 a = unpack2(acc[j]);
+                v[2 * j] = a.x;
+                v[2 * j + 1] = a.y;
             }
             swap_store<RW>(p, n, m0 + j0, live, v);
         }
