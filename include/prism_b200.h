@@ -42,6 +42,14 @@ int pb_last_cuda_error(void);
  * expires.  Synchronizes the device: for tests and error paths, not for the hot path. */
 int pb_device_status(int* code, unsigned* where, int reset);
 
+/* Programmatic dependent launch for the few-row chain.  While on (process-wide), pb_quant_rows with one scale per row,
+ * pb_swiglu_q8, pb_fold and pb_w8a8_gemm at 2 <= M <= 64 launch their kernel as a programmatic dependent of the kernel
+ * before it on the stream: it may begin (set-up, weight reads) before that kernel has ended, and reads the kernel's
+ * output or writes global memory only after it has.  Works inside stream capture (the graph keeps the edges).
+ * Callers' own kernels launched between these calls need no change.  Returns the previous setting.
+ * The reference has no counterpart: its few-row path is a CUDA graph of plain launches (engine/decoder.py). */
+int pb_set_pdl(int on);
+
 /* Every device-side wait (an mbarrier a copy or an MMA completes, a flag or word another GPU writes) is bounded: when
  * the bound runs out the kernel records PB_DEVICE_TIMEOUT with a code for the place, every role of the CTA leaves its
  * loop, copies already requested are given the same bound to land, tensor memory is freed and the kernel returns - no

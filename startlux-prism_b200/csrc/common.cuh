@@ -44,6 +44,13 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// Programmatic dependent launch: both are no-ops in a grid launched without the attribute.  pdl_trigger lets the next
+// kernel of the stream begin (its set-up and whatever it reads that no kernel writes: weights) once every CTA of this
+// grid has called it or exited; pdl_wait returns when the grid before this one has completed and its writes are visible.
+// Rule for every kernel that uses them: no read of another kernel's output and no global write before pdl_wait.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // ------------------------------------------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

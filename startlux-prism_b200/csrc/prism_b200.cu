@@ -6,6 +6,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 #include <unordered_map>
 
@@ -55,6 +56,29 @@ EncodeTiledFn encode_fn() {
             fn = (EncodeTiledFn)p;
     });
     return fn;
+}
+
+// Programmatic dependent launch for the few-row chain (pb_set_pdl): while on, the small producers (rows_q8, swiglu_q8,
+// fold) and the few-row tensor-core GEMMs are launched as programmatic dependents
+// of the kernel before them on the stream; each begins with pdl_trigger and reads another kernel's output, or writes
+// global memory, only after pdl_wait.  Off: plain launches (the two instructions are no-ops then).  The one-row
+// CUDA-core GEMM stays a plain launch: its thousands of short CTAs each paid for the wait (one row measured 0.43 ms
+// per four-layer pass against 0.33).
+std::atomic<int> g_pdl{0};
+
+template <class... KA, class... A>
+cudaError_t launch_dep(void (*kern)(KA...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, A&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl.load(std::memory_order_relaxed) ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, std::forward<A>(args)...);
 }
 
 struct MapKey {
@@ -755,11 +779,11 @@ template <int VPT>
 void launch_rows(bool bf16, bool full, int threads, const void* x, long ldx, const float* inv_s, int8_t* q, float* s,
                         const int* n_rows, int T, int K, int mode, float* amax, const tpx::Sync& sy, cudaStream_t st) {
     if (bf16) {
-        if (full) quant::rows_q8_kernel<VPT, true, true><<<T, threads, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax, sy);
-        else quant::rows_q8_kernel<VPT, true, false><<<T, threads, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax, sy);
+        if (full) (void)(launch_dep(quant::rows_q8_kernel<VPT, true, true>, dim3(T), dim3(threads), 0, st, x, ldx, inv_s, q, s, n_rows, K, mode, amax, sy));
+        else (void)(launch_dep(quant::rows_q8_kernel<VPT, true, false>, dim3(T), dim3(threads), 0, st, x, ldx, inv_s, q, s, n_rows, K, mode, amax, sy));
     } else {
-        if (full) quant::rows_q8_kernel<VPT, false, true><<<T, threads, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax, sy);
-        else quant::rows_q8_kernel<VPT, false, false><<<T, threads, 0, st>>>(x, ldx, inv_s, q, s, n_rows, K, mode, amax, sy);
+        if (full) (void)(launch_dep(quant::rows_q8_kernel<VPT, false, true>, dim3(T), dim3(threads), 0, st, x, ldx, inv_s, q, s, n_rows, K, mode, amax, sy));
+        else (void)(launch_dep(quant::rows_q8_kernel<VPT, false, false>, dim3(T), dim3(threads), 0, st, x, ldx, inv_s, q, s, n_rows, K, mode, amax, sy));
     }
 }
 
@@ -837,6 +861,8 @@ int pb_set_wait_limit_ns(unsigned long long ns) {
     return PB_OK;
 }
 
+int pb_set_pdl(int on) { return g_pdl.exchange(on ? 1 : 0); }
+
 int pb_test_drop_loads(int on) {
     g_drop_loads = on ? 1 : 0;
     return PB_OK;
@@ -874,6 +900,7 @@ int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float
     cudaStream_t st = (cudaStream_t)stream;
     if (!a || !w || !out || !n_rows || M <= 0 || N <= 0 || K <= 0 || split < 1) return PB_BAD_ARGUMENT;
     if (epi != PB_EPI_BF16 && epi != PB_EPI_ADD && epi != PB_EPI_I32 && epi != PB_EPI_F32) return PB_BAD_ARGUMENT;
+    if (g_pdl.load(std::memory_order_relaxed) && M <= 64) pdl = 1;
     if (epi == PB_EPI_F32 && (gk != 32 || M > 64)) return PB_UNSUPPORTED_SHAPE;
     if (epi != PB_EPI_I32 && (!a_s || !w_s)) return PB_BAD_ARGUMENT;
     if (!aligned16(a) || !aligned16(w)) return PB_BAD_ARGUMENT;
@@ -1052,7 +1079,7 @@ int pb_fold(float* h, long ldh, const int32_t* slots, long slot_stride, int S, c
     if ((N % 4 == 0) && (!aligned16(h) || !aligned16(slots) || !aligned16(w_s) || (ldh % 4) || (slot_stride % 4)))
         return PB_BAD_ARGUMENT;
     dim3 grid(((N + 3) / 4 + 255) / 256, rows);
-    quant::fold_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(h, ldh, slots, slot_stride, S, a_s, w_s, n_rows, N);
+    PB_CUDA(launch_dep(quant::fold_kernel, grid, dim3(256), 0, (cudaStream_t)stream, h, ldh, slots, slot_stride, S, a_s, w_s, n_rows, N));
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }
@@ -1266,8 +1293,8 @@ static int swiglu_q8_impl(const void* gu, const float* inv_s, int8_t* q, float* 
     const int nvec = FF / 8;
     const int threads = ((nvec + 3) / 4 + 31) / 32 * 32;          // 4 vectors of 8 outputs per thread
     const __nv_bfloat16* g = (const __nv_bfloat16*)gu;
-    if (full) quant::swiglu_q8_kernel<4, true><<<T, threads, 0, st>>>(g, inv_s, q, s, n_rows, FF, mode, amax, sy);
-    else quant::swiglu_q8_kernel<4, false><<<T, threads, 0, st>>>(g, inv_s, q, s, n_rows, FF, mode, amax, sy);
+    if (full) PB_CUDA(launch_dep(quant::swiglu_q8_kernel<4, true>, dim3(T), dim3(threads), 0, st, g, inv_s, q, s, n_rows, FF, mode, amax, sy));
+    else PB_CUDA(launch_dep(quant::swiglu_q8_kernel<4, false>, dim3(T), dim3(threads), 0, st, g, inv_s, q, s, n_rows, FF, mode, amax, sy));
     PB_CUDA(cudaGetLastError());
     return PB_OK;
 }

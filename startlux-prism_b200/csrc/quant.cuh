@@ -113,6 +113,8 @@ rows_q8_kernel(const void* __restrict__ x, long ldx, const float* __restrict__ i
                float* __restrict__ s, const int* __restrict__ n_rows, int K, int mode, float* __restrict__ amax_io,
                const tpx::Sync sync) {
     __shared__ float red[32];
+    pdl_trigger();
+    pdl_wait();
     const long t = blockIdx.x;
     if (t >= *n_rows) return;
     const int nvec = K >> 3;
@@ -212,6 +214,8 @@ swiglu_q8_kernel(const __nv_bfloat16* __restrict__ gu, const float* __restrict__
                  float* __restrict__ s, const int* __restrict__ n_rows, int FF, int mode, float* __restrict__ amax_io,
                  const tpx::Sync sync) {
     __shared__ float red[32];
+    pdl_trigger();
+    pdl_wait();
     const long t = blockIdx.x;
     if (t >= *n_rows) return;
     const int nvec = FF >> 3;
@@ -583,6 +587,8 @@ gated_norm_g_kernel(const float* __restrict__ o, const __nv_bfloat16* __restrict
 __global__ void __launch_bounds__(256)
 fold_kernel(float* __restrict__ h, long ldh, const int32_t* __restrict__ slots, long slot_stride, int S,
             const float* __restrict__ a_s, const float* __restrict__ w_s, const int* __restrict__ n_rows, int N) {
+    pdl_trigger();
+    pdl_wait();
     const long r = blockIdx.y;
     if (r >= *n_rows) return;
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 4;

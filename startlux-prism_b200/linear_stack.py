@@ -20,7 +20,7 @@ import os
 
 import torch
 
-from . import quant, synth, tp, w8a8
+from . import _lib, quant, synth, tp, w8a8
 
 HIDDEN, Q_COLS, KV_COLS, FFN = 5120, 5120, 1024, 17408
 OPS_PER_ROW_LAYER = 2 * (HIDDEN * (Q_COLS + 2 * KV_COLS) + Q_COLS * HIDDEN + HIDDEN * 2 * FFN + FFN * HIDDEN)
@@ -78,10 +78,12 @@ class LinearStack:
         self.s_max = tp.MAX_SPLIT if M <= tp.SPLIT_ROWS else 1
         self.slots = self.parts[:self.s_max * M * hidden].view(self.s_max, M, hidden)
         self.n_rows = torch.tensor([M], dtype=torch.int32, device=device)
-        # few rows, PRISM_B200_PDL=1: every GEMM is launched as a programmatic dependent of the quantizer before it (its
-        # weights start streaming while the quantizer still runs).  Off by default: inside a replayed graph of the whole
-        # pass it measured level (0.369 against 0.363 ms at 16 rows).  One row stays on the CUDA-core kernel.
-        self.pdl = 1 < M <= w8a8.FEW_ROWS and os.environ.get("PRISM_B200_PDL", "0") == "1"
+        # few rows on one GPU: every kernel of the pass is launched as a programmatic dependent of the one before it
+        # (pb_set_pdl): a GEMM's set-up and first weight reads run while the quantizer before it still works, a
+        # quantizer's launch hides behind the GEMM's tail: 0.364 -> 0.332 ms per four-layer pass at 16 rows, 0.428 ->
+        # 0.402 at 64, as a replayed graph.  One row runs on the CUDA-core GEMM, which stays a plain launch: off there.
+        # PRISM_B200_PDL=0 keeps plain launches.
+        self.pdl = n == 1 and 1 < M <= w8a8.FEW_ROWS and os.environ.get("PRISM_B200_PDL", "1") != "0"
         # several ranks and many rows: the residual stream stays split by rows between the projections (each rank
         # folds, normalises and quantizes M / n rows), a row-parallel projection's int32 sums are reduce-scattered and
         # the int8 rows of the next projection's input all-gathered: 5/8 of an all-reduce's bytes, and 1 / n of the
@@ -132,6 +134,16 @@ class LinearStack:
             return self._pass_by_rows()
         if g is not None and self.n > 1:
             g.begin(M)                            # short pass: a new pass number, exchanges inside the kernels
+        if self.pdl:
+            before = _lib.lib().pb_set_pdl(1)
+            try:
+                return self._pass()
+            finally:
+                _lib.lib().pb_set_pdl(before)
+        return self._pass()
+
+    def _pass(self):
+        M, nr, g = self.M, self.n_rows, self.g
         pend = None
         for lw in self.layers:
             quant.fold(self.h, self.slots, pend, nr, M)
