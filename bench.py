@@ -487,7 +487,8 @@ def quick_detail(dev, pk):
     gen = torch.Generator(device=dev).manual_seed(11)
     hbm = pk["hbm"]
     out = {"hbm_peak_gbs": hbm, "note": "tops at M = 8192 / 2048 (prefill), us and fraction of the measured HBM copy rate "
-           "at M = 16 (decode; weights at GGUF density); o and down include the fp32 residual add"}
+           "at M = 16 (decode; weights at GGUF density); o and down include the fp32 residual add; 'chained': every "
+           "launch a programmatic dependent of the one before it, as the few-row pass runs them"}
     u8 = lambda *sh, lo=0, hi=256: torch.randint(lo, hi, sh, dtype=torch.uint8, device=dev, generator=gen)   # noqa: E731
     i8 = lambda *sh: torch.randint(-127, 128, sh, dtype=torch.int8, device=dev, generator=gen)               # noqa: E731
     f = lambda *sh, m=1e-3: torch.rand(*sh, device=dev, generator=gen) * m                                    # noqa: E731
@@ -523,10 +524,30 @@ def quick_detail(dev, pk):
                     us += graph_time(lambda c: quant.fold(o, slots, pend[0], nr, M), 1, iters=8, reps=3)
                 nbytes = N * K + 4 * N + M * K + 4 * M + (2 if epi == 0 else 8) * M * N
                 row["w8a8_M16_us"], row["w8a8_M16_hbm_frac"] = round(us, 1), round(nbytes / us / 1e3 / hbm, 3)
+
+                # the same product as LinearStack runs it at few rows: every launch a programmatic dependent of the one
+                # before it (set-up and first weight reads overlap the predecessor's tail), the deferred fold in the chain
+                def chained(c):
+                    pd = w8a8.gemm(a, sa1, ws[c], sw1, o, nr, K, epi=epi, slots=slots)
+                    if pd is not None:
+                        quant.fold(o, slots, pd, nr, M)
+                before = _lib.lib().pb_set_pdl(1)
+                try:
+                    us = graph_time(chained, copies, reps=3)
+                finally:
+                    _lib.lib().pb_set_pdl(before)
+                row["w8a8_M16_chained_us"], row["w8a8_M16_chained_hbm_frac"] = round(us, 1), round(nbytes / us / 1e3 / hbm, 3)
                 sa32 = f(M, K // 32, m=1e-2)
                 us = graph_time(lambda c: w8a8.gemm(a, sa32, ws[c], sw32, o, nr, 32, epi=epi), copies, reps=3)
                 nbytes = N * K * 34 / 32 + M * K * 36 / 32 + (2 if epi == 0 else 8) * M * N
                 row["w8a8_q8_0_groups_M16_us"], row["w8a8_q8_0_groups_M16_hbm_frac"] = round(us, 1), round(nbytes / us / 1e3 / hbm, 3)
+                before = _lib.lib().pb_set_pdl(1)
+                try:
+                    us = graph_time(lambda c: w8a8.gemm(a, sa32, ws[c], sw32, o, nr, 32, epi=epi), copies, reps=3)
+                finally:
+                    _lib.lib().pb_set_pdl(before)
+                row["w8a8_q8_0_groups_M16_chained_us"] = round(us, 1)
+                row["w8a8_q8_0_groups_M16_chained_hbm_frac"] = round(nbytes / us / 1e3 / hbm, 3)
             del a, o, slots
         del ws
         torch.cuda.empty_cache()
@@ -578,6 +599,7 @@ def quick_detail(dev, pk):
         torch.cuda.empty_cache()
         out[name] = row
     out["config0_q8_0_5120x5120_M16_us"] = out["o"].get("w8a8_q8_0_groups_M16_us")
+    out["config0_q8_0_5120x5120_M16_chained_us"] = out["o"].get("w8a8_q8_0_groups_M16_chained_us")
     L = _lib.lib()
     if hasattr(L, "pb_mxf4_peak_probe"):
         sms = torch.cuda.get_device_properties(dev).multi_processor_count
