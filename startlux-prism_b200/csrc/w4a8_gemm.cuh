@@ -325,13 +325,16 @@ w4a8_kernel(const __grid_constant__ Maps maps, const Args p) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) y2[j] = make_float2(0.0f, 0.0f);
         bool ok = true;
+        // this row's activation scale of the coming super-block: loaded one super-block ahead (an L2 round trip)
+        float am_next = (NSB > 0 && m0 + ml < p.Ma) ? __ldg(p.a + m0 + ml) : 0.0f;
         for (int b = 0; b < NSB; ++b) {
             const int e = b & 1;
             const uint32_t eph = (b >> 1) & 1;
             const int slot = b & (C::SCL_SLOTS - 1);
             const float2* dv = (const float2*)(smem + C::OFF_SCL + slot * C::SCL_BYTES) + ch * 16;
             const float2* dmv = dv + 32;
-            const float am = (m0 + ml < p.Ma) ? __ldg(p.a + (long)b * p.Ma + m0 + ml) : 0.0f;
+            const float am = am_next;
+            if (b + 1 < NSB && m0 + ml < p.Ma) am_next = __ldg(p.a + (long)(b + 1) * p.Ma + m0 + ml);
             const float2 am2 = make_float2(am, am);
             if (!mbar_wait(smem_u32(&aux->acc_full[e]), eph, abort_flag, 0xD00 + e) ||
                 !mbar_wait(smem_u32(&aux->sfull[slot]), (b / C::SCL_SLOTS) & 1, abort_flag, 0xD20 + slot)) {

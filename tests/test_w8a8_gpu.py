@@ -76,10 +76,16 @@ def test_int32_slots_and_fold(dev, M, N, K, live):
 
 
 @pytest.mark.parametrize("M,N,K,live", [(16, 5120, 5120, 16), (5, 256, 384, 4), (64, 1000, 1024, 61),
-                                        (150, 512, 2560, 140), (3, 35840, 2048, 3)])
+                                        (150, 512, 2560, 140), (3, 35840, 2048, 3),
+                                        # the few-row kernel's corners: one 128-byte chunk of K; an odd number of
+                                        # chunks (the last stage half fill); a last accumulator slot of one stage; row
+                                        # blocks of 16 with one live row in the last; 4 / 8 / 16 rows per CTA; a K long
+                                        # enough that the activation scales leave room for four stages only
+                                        (1, 128, 128, 1), (16, 384, 640, 9), (17, 300, 1152, 17), (40, 5120, 5120, 33),
+                                        (8, 5120, 13824, 8), (12, 640, 896, 12), (4, 256, 32768, 4), (2, 2560, 2560, 2)])
 def test_gemm_q8_0_groups(dev, M, N, K, live):
-    """gk = 32: Q8_0's own block scales, fp32 partial sums added in group order (kernels/w8a8.py:64-76).  The last
-    case has more CTAs than SMs: two CTAs share an SM and its tensor memory."""
+    """gk = 32: Q8_0's own block scales, fp32 partial sums added in group order (kernels/w8a8.py:64-76).  The fifth
+    case has more CTAs than SMs."""
     a, w, sa, sw = rand_w8a8(M, N, K, seed=K + M, groups=K // 32)
     ref0 = oracle.w8a8_gemm(a.numpy(), sa.numpy(), w.numpy(), sw.numpy(), 32, 0, live)
     out = torch.zeros(M, N, dtype=torch.bfloat16, device=dev)
