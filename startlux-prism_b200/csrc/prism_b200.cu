@@ -62,8 +62,8 @@ EncodeTiledFn encode_fn() {
 // fold) and the few-row tensor-core GEMMs are launched as programmatic dependents
 // of the kernel before them on the stream; each begins with pdl_trigger and reads another kernel's output, or writes
 // global memory, only after pdl_wait.  Off: plain launches (the two instructions are no-ops then).  The one-row
-// CUDA-core GEMM stays a plain launch: its thousands of short CTAs each paid for the wait (one row measured 0.43 ms
-// per four-layer pass against 0.33).
+// CUDA-core GEMM stays a plain launch: as a programmatic dependent (first weights requested before the wait) the
+// one-row pass measured 0.42 ms per four layers against 0.33.
 std::atomic<int> g_pdl{0};
 
 template <class... KA, class... A>
@@ -900,6 +900,7 @@ int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float
     cudaStream_t st = (cudaStream_t)stream;
     if (!a || !w || !out || !n_rows || M <= 0 || N <= 0 || K <= 0 || split < 1) return PB_BAD_ARGUMENT;
     if (epi != PB_EPI_BF16 && epi != PB_EPI_ADD && epi != PB_EPI_I32 && epi != PB_EPI_F32) return PB_BAD_ARGUMENT;
+    const int pdl_asked = pdl;                                     // the caller's own request keeps a row off the CUDA-core kernel
     if (g_pdl.load(std::memory_order_relaxed) && M <= 64) pdl = 1;
     if (epi == PB_EPI_F32 && (gk != 32 || M > 64)) return PB_UNSUPPORTED_SHAPE;
     if (epi != PB_EPI_I32 && (!a_s || !w_s)) return PB_BAD_ARGUMENT;
@@ -937,7 +938,7 @@ int pb_w8a8_gemm(const int8_t* a, const float* a_s, const int8_t* w, const float
         if (nb == 32) return launch_groups<32>(a, w, p, st);
         return launch_groups<64>(a, w, p, st);
     }
-    if (M <= PB_W8A8_GEMV_ROWS && (N + 7) / 8 < 8 * sm_count() && split == 1 && !pdl && K % 256 == 0 &&
+    if (M <= PB_W8A8_GEMV_ROWS && (N + 7) / 8 < 8 * sm_count() && split == 1 && !pdl_asked && K % 256 == 0 &&
         (epi == PB_EPI_BF16 || epi == PB_EPI_ADD) && !w8a8_no_gemv()) {
         // one row against a matrix of few rows, no K split asked for: the CUDA-core kernel (the same bits: exact
         // integer sums, the same two multiplies).  Measured at one row: qkv 9.8 / o 7.6 / down 18.4 µs against the

@@ -82,8 +82,9 @@ class LinearStack:
         # (pb_set_pdl): a GEMM's set-up and first weight reads run while the quantizer before it still works, a
         # quantizer's launch hides behind the GEMM's tail: 0.364 -> 0.332 ms per four-layer pass at 16 rows, 0.428 ->
         # 0.402 at 64, as a replayed graph.  One row runs on the CUDA-core GEMM, which stays a plain launch: off there.
-        # PRISM_B200_PDL=0 keeps plain launches.
-        self.pdl = n == 1 and 1 < M <= w8a8.FEW_ROWS and os.environ.get("PRISM_B200_PDL", "1") != "0"
+        # PRISM_B200_PDL=0 keeps plain launches, =all chains the one-row pass too (its GEMMs stay plain launches).
+        mode = os.environ.get("PRISM_B200_PDL", "1")                  # "0": never; "all": at one row too
+        self.pdl = n == 1 and (1 if mode == "all" else 2) <= M <= w8a8.FEW_ROWS and mode != "0"
         # several ranks and many rows: the residual stream stays split by rows between the projections (each rank
         # folds, normalises and quantizes M / n rows), a row-parallel projection's int32 sums are reduce-scattered and
         # the int8 rows of the next projection's input all-gathered: 5/8 of an all-reduce's bytes, and 1 / n of the

@@ -104,7 +104,11 @@ def _choice(M, N, K, residual):
     if not by_m:
         return None
     import math
-    m = min(by_m, key=lambda x: abs(math.log(x) - math.log(max(M, 1))))
+    # the one-row entry was measured on the CUDA-core kernel: it says nothing about the tensor-core kernel at 2+ rows
+    rows = [x for x in by_m if x > GEMV_ROWS] if M > GEMV_ROWS else list(by_m)
+    if not rows:
+        return None
+    m = min(rows, key=lambda x: abs(math.log(x) - math.log(max(M, 1))))
     return by_m[m]
 
 
