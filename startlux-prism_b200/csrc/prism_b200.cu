@@ -444,18 +444,18 @@ int grouped_rows_per_cta(int M, int N) {
     return 16;
 }
 
-// Per-32 groups, one K slice (w8a8_g32.cuh): row blocks of 16, 8 or 4 per CTA.
-template <int RW>
+// Per-32 groups, one K slice (w8a8_g32.cuh): NB = 16 with row blocks of 16, 8 or 4 per CTA, or NB = 32 (more than 16 rows).
+template <int NB, int RW>
 int launch_g32(const int8_t* a, const int8_t* w, w8a8::SwapArgs p, cudaStream_t st) {
-    using C = w8a8::G32;
+    using C = w8a8::G32<NB>;
     constexpr int RCTA = 2 * RW;
     CUtensorMap tw, tx;
     int rc;
     if ((rc = tensor_map_kchunks(&tw, w, p.N, p.K, w8a8::BM))) return rc;
-    if ((rc = tensor_map_kchunks(&tx, a, p.M, p.K, C::NB))) return rc;
+    if ((rc = tensor_map_kchunks(&tx, a, p.M, p.K, NB))) return rc;
     p.stages = C::stages_for(p.K, RCTA);
     const int smem = C::smem_bytes(p.K, RCTA, p.stages);
-    auto kern = w8a8::w8a8_g32_kernel<RW>;
+    auto kern = w8a8::w8a8_g32_kernel<NB, RW>;
     if ((rc = set_smem(kern, 232448))) return rc;
     dim3 grid((p.N + w8a8::BM - 1) / w8a8::BM, 1, (p.M + RCTA - 1) / RCTA);
     cudaLaunchConfig_t cfg = {};
@@ -473,22 +473,29 @@ int launch_g32(const int8_t* a, const int8_t* w, w8a8::SwapArgs p, cudaStream_t 
 }
 
 // Can w8a8_g32_kernel take the call?  One K slice, a direct store, and room for at least three stages beside the
-// activation scales (K up to about 80 k).  PRISM_B200_G32=0 keeps the older kernel (for comparisons).
-bool g32_takes(const w8a8::SwapArgs& p, int split) {
+// activation scales (K up to about 80 k at 16 rows, 40 k at 32).  PRISM_B200_G32=0 keeps the older kernel (comparisons).
+int g32_rows(const w8a8::SwapArgs& p, int split) {
     static const bool on = [] { const char* e = getenv("PRISM_B200_G32"); return !(e && e[0] == '0'); }();
-    return on && split == 1 && p.mode == w8a8::MODE_DIRECT && p.wrows == 0 && p.K % 128 == 0 &&
-           (p.epi == w8a8::EPI_BF16 || p.epi == w8a8::EPI_ADD || p.epi == w8a8::EPI_F32) &&
-           w8a8::G32::stages_for(p.K, 16) >= 3;
+    if (!on || split != 1 || p.mode != w8a8::MODE_DIRECT || p.wrows != 0 || p.K % 128 != 0 ||
+        !(p.epi == w8a8::EPI_BF16 || p.epi == w8a8::EPI_ADD || p.epi == w8a8::EPI_F32))
+        return 0;
+    // more than 16 rows: row blocks of 16 while they all fit one wave (the per-group fp32 chain, which bounds the kernel,
+    // then spreads over more SMs: 20 against 31 us on 5120 x 5120 at 32 rows), blocks of 32 beyond that (half the
+    // re-reads of the weights from L2: 31.6 against 37.8 us at 64 rows)
+    const long blocks16 = (long)((p.N + 127) / 128) * ((p.M + 15) / 16);
+    if (p.M > 16 && blocks16 > sm_count() && w8a8::G32<32>::stages_for(p.K, 32) >= 3) return 32;
+    return w8a8::G32<16>::stages_for(p.K, 16) >= 3 ? 16 : 0;
 }
 
 template <bool GROUPED>
 int launch_swap_nb(int nb, const int8_t* a, const float* a_s, const int8_t* w, const float* w_s, w8a8::SwapArgs p,
                    int split, cudaStream_t st) {
-    if constexpr (GROUPED) if (g32_takes(p, split)) {
+    if constexpr (GROUPED) if (const int rows = g32_rows(p, split)) {
+        if (rows == 32) return launch_g32<32, 16>(a, w, p, st);
         const int r = p.M <= 16 ? grouped_rows_per_cta(p.M, p.N) : 16;
-        if (r == 4) return launch_g32<2>(a, w, p, st);
-        if (r == 8) return launch_g32<4>(a, w, p, st);
-        return launch_g32<8>(a, w, p, st);
+        if (r == 4) return launch_g32<16, 2>(a, w, p, st);
+        if (r == 8) return launch_g32<16, 4>(a, w, p, st);
+        return launch_g32<16, 8>(a, w, p, st);
     }
     if constexpr (GROUPED) if (nb == 16 && split == 1) {
         const int r = grouped_rows_per_cta(p.M, p.N);

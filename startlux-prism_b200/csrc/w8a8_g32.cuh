@@ -15,19 +15,23 @@
 //     memory, and never waits on a pipeline stage: the stages go back to the producer when their MMAs have completed.
 // Roles: warp 0 = TMA producer (one thread), warps 1 and 2 = MMA issuers (one thread each; warp 1 owns the tensor
 // memory), warps 3..10 = epilogue: two warps per lane quarter, each with RW of the CTA's 2 * RW activation rows.
+// Up to 16 rows: NB = 16 and a CTA owns 16, 8 or 4 of them; more rows: NB = 32, row blocks of 32 in grid.z (each block
+// re-reads the weights from L2).
 #pragma once
 #include "w8a8_gemm.cuh"
 
 namespace w8a8 {
 
+template <int NB_>
 struct G32 {
-    static constexpr int NB = 16;                         // MMA N: activation rows (zero-filled past M)
+    static constexpr int NB = NB_;                        // MMA N: activation rows per CTA (zero-filled past M): 16 or 32
     static constexpr int KS = 256;                        // bytes of K per stage
     static constexpr int W_BYTES = BM * KS;               // 32 KB: [2][128 rows][128 bytes], 128-byte swizzle
-    static constexpr int X_BYTES = NB * KS;               // 4 KB: [2][16 rows][128 bytes]
+    static constexpr int X_BYTES = NB * KS;               // [2][NB rows][128 bytes]
     static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
-    static constexpr int SLOT_QUADS = 4;                  // an accumulator slot: 4 quads (a quad = 4 groups = 128 bytes of K)
-    static constexpr int SLOT_COLS = SLOT_QUADS * 4 * NB; // 256 columns
+    static constexpr int SLOT_COLS = 256;                 // an accumulator slot: 16 columns per group and row ...
+    static constexpr int SLOT_QUADS = SLOT_COLS / (4 * NB);   // ... = 4 quads of 16 rows, 2 quads of 32 (a quad = 4 groups = 128 bytes of K)
+    static constexpr int SLOT_STAGES = SLOT_QUADS / 2;    // stages per slot: 2 or 1
     static constexpr int RING = 2;                        // 512 columns: one CTA per SM
     static constexpr int TMEM_COLS = 512;
     static constexpr int EPI_WARPS = 8;
@@ -35,8 +39,8 @@ struct G32 {
     static constexpr int FIRST_EPI_WARP = 1 + MMA_WARPS;
     static constexpr int THREADS = 32 * (FIRST_EPI_WARP + EPI_WARPS);
     static constexpr int MAX_STAGES = 5;
-    // activation scales in shared memory: [rows][quads rounded up to whole slots] float4
-    __host__ __device__ static constexpr int padded_quads(int K) { return (K / 128 + SLOT_QUADS - 1) / SLOT_QUADS * SLOT_QUADS; }
+    // activation scales in shared memory: [rows][quads rounded up to a multiple of four] float4
+    __host__ __device__ static constexpr int padded_quads(int K) { return (K / 128 + 3) / 4 * 4; }
     __host__ __device__ static constexpr int sa_bytes(int K, int rows) { return rows * padded_quads(K) * 16; }
     static constexpr int smem_bytes(int K, int rows, int stages) {
         return 1024 + stages * STAGE_BYTES + sa_bytes(K, rows) + (int)sizeof(Aux);
@@ -131,13 +135,14 @@ __device__ __forceinline__ void add_quad(f32x2* acc, const uint32_t (&r)[4][RW],
 }
 
 // tm_w: weights [N, K] as {128, N, K / 128} with box {128, 128, 2}; tm_x: activations [M, K] the same way with box
-// {128, 16, 2}.  p: a_s [M, K / 32], w_s [N, K / 32], out, ldo, n_rows, M, N, K (a multiple of 128), epi (bf16, fp32 add
+// {128, NB, 2}.  p: a_s [M, K / 32], w_s [N, K / 32], out, ldo, n_rows, M, N, K (a multiple of 128), epi (bf16, fp32 add
 // or fp32), pdl, stages.  Grid (N / 128 tiles, 1, row blocks of 2 * RW).
-template <int RW>
-__global__ void __launch_bounds__(G32::THREADS, 1)
+template <int NB, int RW>
+__global__ void __launch_bounds__(G32<NB>::THREADS, 1)
 w8a8_g32_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const SwapArgs p) {
-    using C = G32;
-    constexpr int RCTA = 2 * RW;
+    using C = G32<NB>;
+    constexpr int RCTA = 2 * RW;                               // activation rows this CTA owns (<= NB)
+    constexpr int RC = RW < 8 ? RW : 8;                        // rows per tensor-memory load
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = align1024(smem_raw);
     const int NST = p.stages;
@@ -160,7 +165,7 @@ w8a8_g32_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             mbar_init(smem_u32(&aux->empty[s]), 1);            // the MMA's commit hands a stage back
         }
         for (int b = 0; b < C::RING; ++b) {
-            mbar_init(smem_u32(&aux->tfull[b]), C::MMA_WARPS);   // one commit per issuing thread
+            mbar_init(smem_u32(&aux->tfull[b]), C::SLOT_STAGES);   // one commit per stage of the slot (= per issuing thread)
             mbar_init(smem_u32(&aux->tempty[b]), C::EPI_WARPS);
         }
         aux->abort_flag = 0;
@@ -227,13 +232,14 @@ w8a8_g32_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
         if (lane == 0) {
             // Stage i belongs to issuing thread i % 2: a thread's loop iteration (two barrier waits, eight MMAs, two
             // commits) takes about 1,500 cycles, twice what the tensor core needs for the stage.  An accumulator slot
-            // is two consecutive stages, one of each thread; each commits its own MMAs to the slot's barrier.
+            // is two consecutive stages, one of each thread (16 rows), or one stage (32 rows); every stage's thread
+            // commits its MMAs to the slot's barrier.
             const int t = warp - 1;
-            const uint32_t idesc = umma_idesc_i8(BM, C::NB);
+            const uint32_t idesc = umma_idesc_i8(BM, NB);
             int stage = t % NST;
             uint32_t phase = (uint32_t)(t / NST) & 1;
             for (int i = t; i < nst; i += C::MMA_WARPS) {
-                const int slot = i >> 1, ring = slot & 1;
+                const int slot = i / C::SLOT_STAGES, ring = slot & 1, sub = i % C::SLOT_STAGES;
                 // the slot must have been drained (a fresh barrier passes at once)
                 if (!mbar_wait(smem_u32(&aux->tempty[ring]), ((uint32_t)(slot >> 1) & 1) ^ 1, abort_flag, 0x2600 + ring)) break;
                 if (!mbar_wait(smem_u32(&aux->full[stage]), phase, abort_flag, 0x2700 + stage)) break;
@@ -243,16 +249,16 @@ w8a8_g32_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
                 for (int c = 0; c < 2; ++c) {
                     if (2 * i + c >= KC) break;                // K / 128 odd: the last stage's second chunk is fill
                     const uint64_t ad = umma_desc_k128(st + c * (BM * BK));
-                    const uint64_t bd = umma_desc_k128(st + C::W_BYTES + c * (C::NB * BK));
+                    const uint64_t bd = umma_desc_k128(st + C::W_BYTES + c * (NB * BK));
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        umma_i8(tmem_base + ring * C::SLOT_COLS + (((i & 1) * 2 + c) * 4 + k) * C::NB,
+                        umma_i8(tmem_base + ring * C::SLOT_COLS + ((sub * 2 + c) * 4 + k) * NB,
                                 umma_desc_advance(ad, k * 32), umma_desc_advance(bd, k * 32), idesc, 0u);
                 }
                 tc_commit(smem_u32(&aux->empty[stage]));       // the stage is free once these MMAs have read it
                 tc_commit(smem_u32(&aux->tfull[ring]));
-                // a last slot of one stage: its barrier still expects the other thread's arrival
-                if ((i & 1) == 0 && i + 1 == nst) tc_commit(smem_u32(&aux->tfull[ring]));
+                // a last slot of one stage where slots have two: its barrier still expects the other thread's arrival
+                if (C::SLOT_STAGES == 2 && sub == 0 && i + 1 == nst) tc_commit(smem_u32(&aux->tfull[ring]));
                 stage += C::MMA_WARPS;
                 if (stage >= NST) {
                     stage -= NST;
@@ -317,22 +323,27 @@ w8a8_g32_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant_
             }
             tc_fence_after();
             if (mine) {
-                const float4* sa_slot = sa + ((j0 >> 1) * QP + slot * C::SLOT_QUADS) * 2;
 #pragma unroll
-                for (int b0 = 0; b0 < C::SLOT_QUADS; b0 += 2) {
-                    if (b0 >= nq) break;
-                    uint32_t r[2][4][RW];                      // two quads' loads in flight before each wait
+                for (int c = 0; c < RW; c += RC) {             // RC rows at a time
+                    if (m0 + j0 + c >= live) break;
+                    const float4* sa_slot = sa + (((j0 + c) >> 1) * QP + slot * C::SLOT_QUADS) * 2;
 #pragma unroll
-                    for (int u = 0; u < 2; ++u)
-                        if (b0 + u < nq) {
+                    for (int b0 = 0; b0 < C::SLOT_QUADS; b0 += 2) {
+                        if (b0 >= nq) break;
+                        uint32_t r[2][4][RC];                  // two quads' loads in flight before each wait
 #pragma unroll
-                            for (int g = 0; g < 4; ++g)
-                                tmem_ldn(lane_base + ring * C::SLOT_COLS + ((b0 + u) * 4 + g) * C::NB + j0, r[u][g]);
-                        }
-                    tmem_ld_wait();
+                        for (int u = 0; u < 2; ++u)
+                            if (b0 + u < nq) {
 #pragma unroll
-                    for (int u = 0; u < 2; ++u)
-                        if (b0 + u < nq) add_quad<RW>(acc, r[u], sa_slot + (b0 + u) * 2, QP * 2, sw4[b0 + u], fuse);
+                                for (int g = 0; g < 4; ++g)
+                                    tmem_ldn(lane_base + ring * C::SLOT_COLS + ((b0 + u) * 4 + g) * NB + j0 + c, r[u][g]);
+                            }
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int u = 0; u < 2; ++u)
+                            if (b0 + u < nq)
+                                add_quad<RC>(acc + c / 2, r[u], sa_slot + (b0 + u) * 2, QP * 2, sw4[b0 + u], fuse);
+                    }
                 }
             }
             tc_fence_before();

@@ -85,6 +85,39 @@ def test_w8a8_at_scale(dev, name, M):
         del out, res, slots
 
 
+@pytest.mark.parametrize("name,M", [("o", 2048), ("qkv", 2048), ("down", 256), ("o", 8192)])
+def test_w8a8_q8_0_groups_at_scale(dev, name, M):
+    """Q8_0's own scale per 32 inputs on both operands (config 1 run with GK = 32) at prefill row counts: the fp32 sum
+    in group order (kernels/w8a8.py:64-76), row blocks of 32 per CTA.  64 sampled rows against the oracle, bf16 store
+    and fp32 residual add, live < M; rows past live keep their poison."""
+    N, K = SHAPES[name]
+    G = K // 32
+    g = torch.Generator().manual_seed(M + N + 1)
+    a = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8)
+    w = torch.randint(-127, 128, (N, K), generator=g, dtype=torch.int8)
+    sa = torch.rand(M, G, generator=g) * 1e-2 + 1e-4
+    sw = torch.rand(N, G, generator=g) * 1e-3 + 1e-5
+    ad, wd, sad, swd = a.to(dev), w.to(dev), sa.to(dev), sw.to(dev)
+    base = torch.randn(M, N, generator=torch.Generator(device=dev).manual_seed(9), device=dev)
+    for live in (M, M - 3):
+        rows = sample_rows(M, live)
+        idx = torch.from_numpy(rows).to(dev)
+        an, san = a[rows].numpy(), sa[rows].numpy()
+        nr = n_rows(live, dev)
+        want0 = oracle.w8a8_gemm(an, san, w.numpy(), sw.numpy(), 32, 0)
+        out = torch.full((M, N), POISON_BF16, dtype=torch.bfloat16, device=dev)
+        w8a8.gemm(ad, sad, wd, swd, out, nr, 32, epi=0)
+        got0 = out[idx].cpu().view(torch.int16).numpy().view(np.uint16)
+        assert np.array_equal(got0, want0), (name, M, live, "bf16", np.argwhere(got0 != want0)[:3])
+        assert bool((out[live:] == POISON_BF16).all())
+        want1 = oracle.w8a8_gemm(an, san, w.numpy(), sw.numpy(), 32, 1, out=base[idx].cpu().numpy())
+        res = base.clone()
+        w8a8.gemm(ad, sad, wd, swd, res, nr, 32, epi=1)
+        assert np.array_equal(res[idx].cpu().numpy().view(np.uint32), want1.view(np.uint32)), (name, M, live, "add")
+        assert torch.equal(res[live:], base[live:])
+        del out, res
+
+
 def random_kquant(kind, n, k, seed):
     """Valid random k-quant blocks (any valid block is a valid input): random quants and 6-bit / int8 sub-block scales,
     fp16 d / dmin of the magnitude N(0, 0.02^2) weights give."""
