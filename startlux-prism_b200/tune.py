@@ -16,7 +16,7 @@ import os
 import sys
 
 DEFAULT_SHAPES = [(7168, 5120), (5120, 5120), (34816, 5120), (5120, 17408)]
-DEFAULT_ROWS = [1, 8, 16, 32, 64]
+DEFAULT_ROWS = [1, 2, 4, 8, 16, 32, 64]
 TABLE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "gemm_table_b200.json")
 L2_BYTES = 126 << 20
 
@@ -42,10 +42,13 @@ def graph_us(fn_of_copy, copies, iters=None, reps=5):
     return best
 
 
-def measure(shapes, rows, log=print):
+def measure(shapes, rows, log=print, chained=True):
+    """chained: rows from 2 up are timed as LinearStack launches them at few rows - every launch a programmatic
+    dependent of the one before it (pb_set_pdl) - so that the choice fits that pass; one row (the CUDA-core kernel,
+    a plain launch) is timed alone."""
     import torch
 
-    from . import quant, w8a8
+    from . import _lib, quant, w8a8
     dev = torch.device("cuda", torch.cuda.current_device())
     gen = torch.Generator(device=dev).manual_seed(4)
     table = {}
@@ -72,9 +75,18 @@ def measure(shapes, rows, log=print):
                         def call(c):
                             pend[0] = w8a8.gemm(a, sa, ws[c], sw, out, nr, K, epi=int(residual), cfg=split,
                                                 slots=slots if defer else None)
-                        us = graph_us(call, copies)
-                        if pend[0] is not None:           # the deferred add is finished by a fold: its time counts
-                            us += graph_us(lambda c: quant.fold(out, slots, pend[0], nr, M), 1, iters=8)
+                            if chained and M > 1 and pend[0] is not None:
+                                quant.fold(out, slots, pend[0], nr, M)        # the fold is part of the chain
+                        if chained and M > 1:
+                            before = _lib.lib().pb_set_pdl(1)
+                            try:
+                                us = graph_us(call, copies)
+                            finally:
+                                _lib.lib().pb_set_pdl(before)
+                        else:
+                            us = graph_us(call, copies)
+                            if pend[0] is not None:       # the deferred add is finished by a fold: its time counts
+                                us += graph_us(lambda c: quant.fold(out, slots, pend[0], nr, M), 1, iters=8)
                         if best is None or us < best["us"]:
                             best = {"split": split, "defer": bool(defer), "us": round(us, 2)}
                 table[key][str(M)] = best
@@ -103,12 +115,14 @@ def main(argv=None):
     ap.add_argument("--out", default=TABLE)
     ap.add_argument("--shapes", default=None)
     ap.add_argument("--rows", default=None)
+    ap.add_argument("--plain", action="store_true", help="time every product alone (no chain of dependent launches)")
     args = ap.parse_args(argv)
     shapes = [tuple(int(v) for v in s.split("x")) for s in args.shapes.split(",")] if args.shapes else DEFAULT_SHAPES
     rows = [int(v) for v in args.rows.split(",")] if args.rows else DEFAULT_ROWS
-    table = measure(shapes, rows)
+    table = measure(shapes, rows, chained=not args.plain)
     doc = {"gpu": torch.cuda.get_device_name(0), "sms": torch.cuda.get_device_properties(0).multi_processor_count,
-           "method": "CUDA graph of calls over rotating weight copies (> 3 x L2), best of 5 replays", "table": table}
+           "method": "CUDA graph of calls over rotating weight copies (> 3 x L2), best of 5 replays"
+           + ("" if args.plain else "; 2 rows and up as a chain of programmatic dependent launches"), "table": table}
     with open(args.out, "w") as f:
         json.dump(doc, f, indent=1)
     print(f"wrote {args.out}")
