@@ -118,6 +118,10 @@ class LinearStack:
         # the row-split pass with the scatter fused into the GEMM: flag handshakes inside the folds take the place of
         # the barrier collectives (PRISM_B200_TP_FLAGS=0 keeps the one-element all-reduce)
         self.flags = (self.peer is not None and group.fs is not None and os.environ.get("PRISM_B200_TP_FLAGS", "1") != "0")
+        # ... and the row maxima of a row-parallel projection's input travel as words between the producers, which then
+        # quantize in one launch instead of two passes around a max-all-reduce (PRISM_B200_TP_WORDS=0 keeps those)
+        self.words = (self.flags and os.environ.get("PRISM_B200_TP_WORDS", "1") != "0"
+                      and group.setup_many(M, 2 * len(layers)))
 
     def __call__(self, h_in, own_rows=False):
         """One pass: h_in fp32 [M, hidden] is copied into the working residual, which is returned (a view of an
@@ -189,8 +193,7 @@ class LinearStack:
         def gathered_input():
             quant.fold(h_own, None, pend, self.nr_own, Ml)
             quant.rows_q8(h_own, None, xq_own, xs_own, self.nr_own, Ml)
-            g.gather_(self.xq, xq_own)
-            g.gather_(self.xs, xs_own)
+            g.gather2_(self.xq, xq_own, self.xs, xs_own)
 
         def out(a, a_s, wt):
             w, w_s = wt
@@ -205,14 +208,20 @@ class LinearStack:
             g.scatter_sum_(self.own[0], self.slots[0])
             return w8a8.Deferred(1, a_s[r0:r0 + Ml], w_s, self.own)
 
+        def quantize(fn, *args):
+            if self.words:
+                fn(*args, mode=3, sync=g.words_many())
+            else:
+                tp.quantize_rows(g, fn, M, self.amax, *args)
+
         for lw in self.layers:
             gathered_input()
             w8a8.gemm(self.xq, self.xs, *lw["qkv"], self.qkv, nr, self.hidden)
-            tp.quantize_rows(g, quant.rows_q8, M, self.amax, self.qkv[:, :self.ql], None, self.aq, self.as_, nr, M)
+            quantize(quant.rows_q8, self.qkv[:, :self.ql], None, self.aq, self.as_, nr, M)
             pend = out(self.aq, self.as_, lw["o"])
             gathered_input()
             w8a8.gemm(self.xq, self.xs, *lw["gate_up"], self.gu, nr, self.hidden)
-            tp.quantize_rows(g, quant.swiglu_q8, M, self.amax, self.gu, None, self.dq, self.ds, nr, M)
+            quantize(quant.swiglu_q8, self.gu, None, self.dq, self.ds, nr, M)
             pend = out(self.dq, self.ds, lw["down"])
         quant.fold(h_own, None, pend, self.nr_own, Ml)
         if not gather:

@@ -64,8 +64,8 @@ def _mode_args(mode, amax, sync, T):
     if mode == 3:
         if sync is None:
             raise RuntimeError("mode 3 needs a Sync (tp.Group.words())")
-        if T >= 256:
-            raise RuntimeError("mode 3 (in-kernel row-maximum exchange) serves passes of fewer than 256 rows")
+        if sync.flags and hasattr(sync.flags[0], "numel") and sync.flags[0].numel() < (sync.chan + T) * sync.world:
+            raise RuntimeError("mode 3: the word buffers are too small for this many rows (tp.Group.setup / setup_many)")
         return None
     if sync is not None:
         raise RuntimeError("a Sync goes with mode 3")

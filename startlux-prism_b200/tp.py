@@ -123,6 +123,7 @@ class Group:
             dist.init_process_group(backend, rank=rank, world_size=world,
                                     timeout=datetime.timedelta(seconds=timeout_s), **kw)
         self.pg = dist.group.WORLD
+        self._coalesce = None                    # gather2_: does this torch build coalesce all-gathers? (None: not tried)
         # in-kernel exchanges (setup): every rank's buffers as mapped here, and the per-pass bookkeeping
         self.xs = self.ws = self.fs = None
         self.fast = self.pull = False
@@ -162,6 +163,28 @@ class Group:
             return
         self.fs, self.xs, self.ws = fs, xs, ws
         self.epoch = torch.zeros(1, dtype=torch.int64, device=self.device)
+
+    def setup_many(self, rows, words):
+        """Word buffers for the row-maximum exchanges of passes with MANY rows (linear_stack's row-split pass): `words`
+        exchanges per pass of `rows` rows, one 64-bit word per row and rank, peer-mapped like setup()'s.  The producers
+        then quantize a row-parallel projection's input in ONE launch (mode 3: the row stays in registers while the
+        other ranks' maxima arrive) instead of a maxima pass, a max-all-reduce and a quantizing pass.  Needs the flag
+        words of setup() (their pass counter tags the words).  A collective; False when peer memory is unavailable."""
+        if self.world == 1 or self.backend != "nccl" or self.fs is None:
+            return False
+        wm = self.symmetric(words * rows * self.world, torch.int64)
+        if wm is None:
+            return False
+        self.wm, self.wm_rows, self.wm_steps = wm, rows, words
+        return True
+
+    def words_many(self):
+        """The next many-rows row-maximum exchange's quant.Sync (begin_handshakes started the pass)."""
+        from . import quant as KQ
+        if self.mstep >= self.wm_steps:
+            raise RuntimeError(f"more than {self.wm_steps} row-maximum exchanges in one pass")
+        self.mstep += 1
+        return KQ.Sync(self.epoch, tuple(self.wm), (self.mstep - 1) * self.wm_rows, (), self.rank, self.world)
 
     def symmetric(self, n, dtype):
         """n zeroed elements on every rank, each rank's buffer mapped on every other (CUDA IPC over NVLink): returns
@@ -203,7 +226,7 @@ class Group:
         from . import quant as KQ
         if self.fs is None:
             return False
-        self.step = 0
+        self.step = self.mstep = 0
         KQ.bump(self.epoch)
         return True
 
@@ -240,6 +263,24 @@ class Group:
             dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.pg)
             rows = x.shape[0] // self.world
             own.copy_(t[self.rank * rows:(self.rank + 1) * rows])
+
+    def gather2_(self, full1, own1, full2, own2):
+        """Two gathers in one NCCL launch (a row block's int8 values and its scales travel together): the group call
+        of the two all-gathers; elsewhere, or where this torch build has no coalescing of all-gathers, two calls."""
+        if self.world > 1 and self.backend == "nccl" and self._coalesce is not False:
+            try:
+                from torch.distributed.distributed_c10d import _coalescing_manager
+                with _coalescing_manager(group=self.pg, device=own1.device, async_ops=False):
+                    dist.all_gather_into_tensor(full1, own1, group=self.pg)
+                    dist.all_gather_into_tensor(full2, own2, group=self.pg)
+                self._coalesce = True
+                return
+            except Exception:                                      # noqa: BLE001
+                if self._coalesce:                                 # it worked before: a real failure
+                    raise
+                self._coalesce = False
+        self.gather_(full1, own1)
+        self.gather_(full2, own2)
 
     def gather_(self, full, own):
         """full [rows, ...] = the ranks' row blocks own [rows / world, ...] in rank order; `own` may be full's own
