@@ -128,6 +128,7 @@ int pb_fold(float* h, long ldh, const int32_t* slots, long slot_stride, int S, c
 int pb_quant_rows(const void* x, int x_fp32, long ldx, const float* inv_s, int8_t* q, float* s, const int* n_rows,
                   int T, int K, int gk, int mode, float* amax, void* stream);
 
+
 /* Exchanges between the GPUs of a tensor-parallel group INSIDE a kernel, for passes of a few rows (decode), where a
  * collective call per exchange costs more than the work between them.  Replaces the reference's quant.Sync / mode 3 /
  * _tp_sync / _ll_amax / _fold_parts over symmetric memory (kernels/quant.py:55-141, :190-212; tp.py:358-432); up to 8
@@ -164,6 +165,15 @@ int pb_fold_sync(float* h, long ldh, const int32_t* slots, long slot_stride, int
 int pb_norm_q8_sync(float* h, const float* w, int8_t* q, float* s, const int* n_rows, int T, int HID, float eps,
                     const int32_t* parts, long part_stride, int n_parts, const float* psa, const float* psw,
                     const pb_sync* sync, void* stream);
+
+/* The send side of an all-gather between the ranks' peer-mapped buffers, and the handshake that tells the receivers:
+ * pb_push stores nbytes (a multiple of 16) from src into each of dsts[0..n) (the same block of the other ranks'
+ * buffers as mapped on this GPU: plain stores over NVLink, no TMA, no multicast); pb_handshake then signals this
+ * rank's flag of the step on every other rank and waits (bounded: PB_DEVICE_TIMEOUT in the status word) until every
+ * other rank has signalled, so that what follows on the stream may read what the others pushed.  The reference
+ * gathers with NCCL (tp.py:435-439). */
+int pb_push(const void* src, void* const* dsts, int n, long nbytes, void* stream);
+int pb_handshake(const pb_sync* sync, void* stream);
 
 /* RMSNorm + per-token quantization, with a deferred residual add finished first.  Replaces quant.norm_q8 /
  * _norm_q8_kernel (kernels/quant.py:145-171, :418-431): for output row i (input row rows[i] when rows != NULL, else i):

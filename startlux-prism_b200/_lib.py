@@ -69,6 +69,8 @@ _OPTIONAL = {
     "pb_int8_peak_probe": ([_i, _i, _i, _vp, _vp], _i),
     "pb_mxf4_peak_probe": ([_i, _i, _vp, _vp], _i),
     "pb_set_pdl": ([_i], _i),
+    "pb_push": ([_vp, _vp, _i, _l, _vp], _i),
+    "pb_handshake": ([_vp, _vp], _i),
     "pb_w8a8_static_scratch_bytes": ([], _l),
     "pb_w8a8_gemm_static": ([_vp, _vp, _vp, _vp, _vp, _l, _vp, _i, _i, _i, _i, _i, _vp], _i),
 }

@@ -1353,6 +1353,36 @@ int pb_fold_sync(float* h, long ldh, const int32_t* slots, long slot_stride, int
     return PB_OK;
 }
 
+int pb_handshake(const pb_sync* sync, void* stream) {
+    if (!sync) return PB_BAD_ARGUMENT;
+    tpx::Sync sy;
+    int rc = to_sync(sync, &sy, false);
+    if (rc) return rc;
+    if (sy.world < 2) return PB_OK;
+    tpx::handshake_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(sy);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
+int pb_push(const void* src, void* const* dsts, int n, long nbytes, void* stream) {
+    if (!src || !dsts || n < 0 || n > tpx::MAX_RANKS - 1 || nbytes < 0 || nbytes % 16 || !aligned16(src)) return PB_BAD_ARGUMENT;
+    if (n == 0 || nbytes == 0) return PB_OK;
+    tpx::PushArgs a{};
+    a.src = (const uint4*)src;
+    a.n16 = nbytes / 16;
+    a.n = n;
+    for (int d = 0; d < n; ++d) {
+        if (!dsts[d] || !aligned16(dsts[d])) return PB_BAD_ARGUMENT;
+        a.dst[d] = (uint4*)dsts[d];
+    }
+    long blocks = (a.n16 + 255) / 256;
+    const long cap = 4l * sm_count();
+    if (blocks > cap) blocks = cap;
+    tpx::push_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(a);
+    PB_CUDA(cudaGetLastError());
+    return PB_OK;
+}
+
 int pb_quant_g(const void* x, int x_fp32, int8_t* q, float* a, int8_t* xs, const int* n_rows, int T, int Ma, int K,
                void* stream) {
     if (!x || !q || !a || !xs || !n_rows || T <= 0 || K <= 0 || Ma < T) return PB_BAD_ARGUMENT;

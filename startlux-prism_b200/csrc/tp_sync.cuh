@@ -107,6 +107,22 @@ __device__ __forceinline__ void arrive_and_wait(const Sync& s, bool first_block)
 // and fence in every block costs more than one extra launch.  Kernels after it on the stream start after it has ended.
 __global__ void __launch_bounds__(32) handshake_kernel(const Sync s) { arrive_and_wait(s, true); }
 
+// One block of this rank's memory stored into the same place of up to seven other ranks' buffers (an all-gather's
+// send side: plain 16-byte loads here, 16-byte stores over NVLink there; the receivers learn of it by a handshake).
+struct PushArgs {
+    const uint4* src;
+    uint4* dst[MAX_RANKS - 1];
+    long n16;                                // 16-byte units
+    int n;                                   // destinations
+};
+__global__ void __launch_bounds__(256) push_kernel(const PushArgs a) {
+    const long stride = (long)gridDim.x * blockDim.x;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < a.n16; i += stride) {
+        const uint4 v = a.src[i];
+        for (int d = 0; d < a.n; ++d) a.dst[d][i] = v;
+    }
+}
+
 // Four consecutive int32 sums of another rank's slots, read past this GPU's caches (the data changes between passes).
 __device__ __forceinline__ int4 ld_peer4(const int32_t* p) {
     int4 v;

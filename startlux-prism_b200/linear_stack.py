@@ -122,6 +122,19 @@ class LinearStack:
         # quantize in one launch instead of two passes around a max-all-reduce (PRISM_B200_TP_WORDS=0 keeps those)
         self.words = (self.flags and os.environ.get("PRISM_B200_TP_WORDS", "1") != "0"
                       and group.setup_many(M, 2 * len(layers)))
+        # ... and the all-gather of a column-parallel projection's int8 input: every rank stores its own rows straight
+        # into the other ranks' input buffers (peer-mapped), a flag handshake tells the readers
+        # (PRISM_B200_TP_PUSH=0 keeps NCCL's all-gather)
+        self.push = False
+        if self.flags and os.environ.get("PRISM_B200_TP_PUSH", "1") != "0":
+            xq_all = group.symmetric(M * hidden, i8)
+            xs_all = group.symmetric(M, f32)
+            if xq_all is not None and xs_all is not None:
+                self.push = True
+                self.xq, self.xs = xq_all[group.rank].view(M, hidden), xs_all[group.rank]
+                lo, hi = self.r0, self.r0 + self.Ml
+                self.xq_peers = [t.view(M, hidden)[lo:hi] for r, t in enumerate(xq_all) if r != group.rank]
+                self.xs_peers = [t[lo:hi] for r, t in enumerate(xs_all) if r != group.rank]
 
     def __call__(self, h_in, own_rows=False):
         """One pass: h_in fp32 [M, hidden] is copied into the working residual, which is returned (a view of an
@@ -193,7 +206,12 @@ class LinearStack:
         def gathered_input():
             quant.fold(h_own, None, pend, self.nr_own, Ml)
             quant.rows_q8(h_own, None, xq_own, xs_own, self.nr_own, Ml)
-            g.gather2_(self.xq, xq_own, self.xs, xs_own)
+            if self.push:
+                quant.push(xq_own, self.xq_peers)
+                quant.push(xs_own, self.xs_peers)
+                quant.handshake(g.handshake())
+            else:
+                g.gather2_(self.xq, xq_own, self.xs, xs_own)
 
         def out(a, a_s, wt):
             w, w_s = wt

@@ -60,6 +60,24 @@ def bump(epoch):
     epoch.add_(1)
 
 
+def push(src, dsts):
+    """src (contiguous, a multiple of 16 bytes) stored into each of dsts: the same block of the other ranks' buffers as
+    mapped on this GPU (tp.Group.symmetric).  The receivers may read it after handshake()."""
+    _lib.need_cuda(src)
+    if not src.is_contiguous() or any(d.numel() * d.element_size() != src.numel() * src.element_size() for d in dsts):
+        raise RuntimeError("push: contiguous blocks of one size")
+    arr = (ctypes.c_void_p * max(len(dsts), 1))(*[d.data_ptr() for d in dsts])
+    rc = _lib.lib().pb_push(_lib.ptr(src), arr, len(dsts), src.numel() * src.element_size(), _lib.stream())
+    _lib.check(rc, f"push {src.numel() * src.element_size()} bytes to {len(dsts)} ranks")
+
+
+def handshake(sync):
+    """The flag handshake of `sync` (tp.Group.handshake()) as a step of its own on the stream: signals every other rank
+    and waits (bounded) for all of them."""
+    rc = _lib.lib().pb_handshake(ctypes.byref(_sync_struct(sync)), _lib.stream())
+    _lib.check(rc, f"handshake over {sync.world} ranks")
+
+
 def _mode_args(mode, amax, sync, T):
     if mode == 3:
         if sync is None:
