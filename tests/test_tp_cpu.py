@@ -152,3 +152,16 @@ def test_exchange_bookkeeping(monkeypatch):
     seen.clear()
     tp.quantize_rows(g, lambda *a, **k: seen.append(k), 8, None, "x")
     assert len(seen) == 1 and seen[0]["mode"] == 3 and seen[0]["sync"].chan == 0
+    # many rows (the row-split pass): a pass number from begin_handshakes, word rows of wm_rows per exchange
+    g.wm = [torch.zeros(3 * 1024 * world, dtype=torch.int64) for _ in range(world)]
+    g.wm_rows, g.wm_steps = 1024, 3
+    assert g.begin_handshakes() and int(g.epoch) == 4 and g.step == 0 and g.mstep == 0
+    m0, m1 = g.words_many(), g.words_many()
+    assert (m0.chan, m1.chan) == (0, 1024) and m0.flags[1].data_ptr() == g.wm[1].data_ptr() and m0.world == 2
+    assert quant._mode_args(3, None, m1, 1024) is None
+    with pytest.raises(RuntimeError, match="too small"):
+        quant._mode_args(3, None, g.words_many(), 1025)           # third exchange, one row more than its buffer holds
+    with pytest.raises(RuntimeError, match="row-maximum exchanges"):
+        g.words_many()
+    h = g.handshake()
+    assert h.chan == 0 and h.others == () and h.flags[0].data_ptr() == g.fs[0].data_ptr()
