@@ -1590,7 +1590,7 @@ int pb_mxfp4_gemm_split(const void* aq, const void* a_sf, const void* bq, const 
             if (rc) return rc;
             by_engine = (epi == 1 || N % 2 == 0) ? 1 : 0;
         }
-        mxfp4::mxfp4_gemm256_kernel<<<grid2, 64 + 32 * mxfp4::EPI2_WARPS, mxfp4::SMEM2, (cudaStream_t)stream>>>(ta, tb2, tout, p, by_engine);
+        mxfp4::mxfp4_gemm256_kernel<<<grid2, mxfp4::THREADS2, mxfp4::SMEM2, (cudaStream_t)stream>>>(ta, tb2, tout, p, by_engine);
         PB_CUDA(cudaGetLastError());
         return PB_OK;
     }
